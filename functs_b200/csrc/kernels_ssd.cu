@@ -1,0 +1,256 @@
+// C3: SSD-style post-process in two launches.
+//
+// Group 1 (ssd_softmax_decode_kernel): softmax over every confidence row with the background column dropped
+// (functs/benchmark/ai_model/ssd/ssd_bbox.py:268) fused with the box decode and its strided in-place clamp
+// (ssd_bbox.py:121-154).  A CTA stages a tile of conf rows in shared memory with one bulk (TMA) copy when the
+// tile is 16-byte aligned, each thread reduces one row (row stride 81 words: conflict-free), and the scores are
+// written class-major so that group 2 reads contiguous runs.
+//
+// Group 2 (ssd_class_nms_kernel): the loop over classes (ssd_bbox.py:163-172 + :212 per class) with every
+// (image, class) iteration mapped onto one CTA: mask > thr, top-k by (score desc, prior asc), gather boxes,
+// greedy NMS, write the kept rows and their count.
+#include "select_nms.cuh"
+
+namespace fb {
+
+constexpr int kSsdTile = 128;     // priors per CTA in group 1
+constexpr int kSsdMaxRow = 96;    // maximum conf columns (C + 1) supported by the register/smem layout
+
+// dynamic smem: [tile rows * ncol floats][8-byte mbarrier]
+__global__ void __launch_bounds__(kSsdTile)
+ssd_softmax_decode_kernel(const float* __restrict__ loc, const float* __restrict__ conf, const float* __restrict__ priors,
+                          int num_priors, int num_classes, float clamp_max, float* __restrict__ boxes,
+                          float* __restrict__ scores_cm, int use_bulk) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int ncol = num_classes + 1;
+    float* tile = reinterpret_cast<float*>(smem_raw);
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw + ((static_cast<size_t>(kSsdTile) * ncol * 4 + 15) / 16) * 16);
+    const int img = blockIdx.y;
+    const int p0 = blockIdx.x * kSsdTile;
+    const int rows = min(kSsdTile, num_priors - p0);
+    const int t = threadIdx.x;
+    const float* gsrc = conf + (static_cast<int64_t>(img) * num_priors + p0) * ncol;
+    const int nfl = rows * ncol;
+    bool staged = false;
+    if (use_bulk) {
+        if (t == 0) {
+            mbar_init(bar, 1);
+            fence_barrier_init();
+        }
+        __syncthreads();
+        if (t == 0) {
+            mbar_arrive_expect_tx(bar, static_cast<uint32_t>(nfl) * 4u);
+            bulk_copy_g2s(tile, gsrc, static_cast<uint32_t>(nfl) * 4u, bar);
+        }
+        staged = mbar_wait_bounded(bar, 0, 200000u);
+        // if the wait ran out (never observed), fall through to the plain loads below after the copy engine
+        // had its chance; staged is uniform enough: every thread polls the same barrier
+        staged = __syncthreads_and(staged ? 1 : 0) != 0;
+    }
+    if (!staged) {
+        for (int i = t; i < nfl; i += kSsdTile) tile[i] = __ldg(gsrc + i);
+        __syncthreads();
+    }
+
+    const int p = p0 + t;
+    if (t < rows) {
+        float* row = tile + t * ncol;
+        float mx = row[0];
+        for (int c = 1; c < ncol; ++c) mx = fmaxf(mx, row[c]);
+        float sum = 0.0f;
+        for (int c = 0; c < ncol; ++c) {
+            float e = expf(__fsub_rn(row[c], mx));
+            row[c] = e;
+            sum = __fadd_rn(sum, e);
+        }
+        const float inv = __fdiv_rn(1.0f, sum);
+        for (int c = 0; c < ncol; ++c) row[c] = __fmul_rn(row[c], inv);
+
+        // decode (centre/size priors, variances 0.1 / 0.2), then clamp x to [0, max], y to [0, max]
+        const float4 pr = __ldg(reinterpret_cast<const float4*>(priors) + p);
+        const float4 d = __ldg(reinterpret_cast<const float4*>(loc) + static_cast<int64_t>(img) * num_priors + p);
+        const float gx = __fadd_rn(pr.x, __fmul_rn(pr.z, __fmul_rn(d.x, 0.1f)));
+        const float gy = __fadd_rn(pr.y, __fmul_rn(pr.w, __fmul_rn(d.y, 0.1f)));
+        const float gw = __fmul_rn(pr.z, expf(__fmul_rn(d.z, 0.2f)));
+        const float gh = __fmul_rn(pr.w, expf(__fmul_rn(d.w, 0.2f)));
+        const float hw = __fmul_rn(gw, 0.5f), hh = __fmul_rn(gh, 0.5f);
+        float4 o;
+        o.x = fminf(fmaxf(__fsub_rn(gx, hw), 0.0f), clamp_max);
+        o.y = fminf(fmaxf(__fsub_rn(gy, hh), 0.0f), clamp_max);
+        o.z = fminf(fmaxf(__fadd_rn(gx, hw), 0.0f), clamp_max);
+        o.w = fminf(fmaxf(__fadd_rn(gy, hh), 0.0f), clamp_max);
+        reinterpret_cast<float4*>(boxes)[static_cast<int64_t>(img) * num_priors + p] = o;
+    }
+    __syncthreads();
+    // class-major store: for a fixed class consecutive threads write consecutive priors
+    if (t < rows) {
+        const float* row = tile + t * ncol;
+        float* dst = scores_cm + static_cast<int64_t>(img) * num_classes * num_priors + p;
+        for (int c = 0; c < num_classes; ++c) dst[static_cast<int64_t>(c) * num_priors] = row[c];
+    }
+}
+
+// ---- group 2 ------------------------------------------------------------------------------------------------
+constexpr int kSsdNmsThreads = 256;
+constexpr int kSsdSelCap = 256;
+constexpr int kSsdWords = kSsdSelCap / 32;
+
+struct SmemScores {
+    const float* s;
+    float thr;
+    __device__ __forceinline__ uint64_t operator()(int i) const {
+        float v = s[i];
+        return (v > thr) ? make_key(v, static_cast<uint32_t>(i)) : 0ull;
+    }
+};
+
+// dynamic smem: [num_priors floats (padded to 16 B)][SelectSmem<256>][NmsBox[256]][mask 256 x 8 words]
+__global__ void __launch_bounds__(kSsdNmsThreads)
+ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ scores_cm, int num_priors, int num_classes,
+                     float score_thr, int topk, float iou_thr, float thr_lo, float thr_hi, float* __restrict__ dets,
+                     int64_t* __restrict__ prior_ids, int32_t* __restrict__ out_counts) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const size_t sc_bytes = (static_cast<size_t>(num_priors) * 4 + 15) / 16 * 16;
+    float* sc = reinterpret_cast<float*>(smem_raw);
+    SelectSmem<kSsdSelCap>& sm = *reinterpret_cast<SelectSmem<kSsdSelCap>*>(smem_raw + sc_bytes);
+    NmsBox* sb = reinterpret_cast<NmsBox*>(smem_raw + sc_bytes + sizeof(SelectSmem<kSsdSelCap>));
+    uint32_t* smask = reinterpret_cast<uint32_t*>(sb + kSsdSelCap);
+    __shared__ uint32_t keep_words[kSsdWords];
+    __shared__ int word_prefix[kSsdWords + 1];
+
+    const int cls = blockIdx.x, img = blockIdx.y;
+    const int t = threadIdx.x;
+    const float* src = scores_cm + (static_cast<int64_t>(img) * num_classes + cls) * num_priors;
+    if ((num_priors & 3) == 0) {
+        const float4* s4 = reinterpret_cast<const float4*>(src);
+        float4* d4 = reinterpret_cast<float4*>(sc);
+        for (int i = t; i < (num_priors >> 2); i += kSsdNmsThreads) d4[i] = __ldg(s4 + i);
+    } else {
+        for (int i = t; i < num_priors; i += kSsdNmsThreads) sc[i] = __ldg(src + i);
+    }
+    __syncthreads();
+
+    SmemScores kf{sc, score_thr};
+    const int n = block_select_topk<kSsdNmsThreads, kSsdSelCap, 4>(kf, num_priors, topk, sm);
+    // (block_select_topk ends with a barrier when n > 1; make the hand-over explicit)
+    __syncthreads();
+
+    const float* bimg = boxes + static_cast<int64_t>(img) * num_priors * 4;
+    float4 mybox = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint64_t mykey = 0ull;
+    if (t < n) {
+        mykey = sm.sel[t];
+        mybox = __ldg(reinterpret_cast<const float4*>(bimg) + key_index(mykey));
+        sb[t] = make_nms_box(mybox.x, mybox.y, mybox.z, mybox.w);
+    }
+    if (t < kSsdWords) keep_words[t] = 0u;
+    __syncthreads();
+
+    // suppression bit matrix: warp r handles rows r, r + 8, ...; lane b tests box 32w + b
+    const int lane = t & 31, warp = t >> 5;
+    const int words = (n + 31) >> 5;
+    for (int i = warp; i < n; i += kSsdNmsThreads / 32) {
+        const NmsBox bi = sb[i];
+        uint32_t bits = 0u;
+        for (int w = i >> 5; w < words; ++w) {
+            const int j = w * 32 + lane;
+            bool pred = false;
+            if (j > i && j < n) pred = iou_exceeds(bi, sb[j], iou_thr, thr_lo, thr_hi);
+            unsigned m = __ballot_sync(kFullMask, pred);
+            if (lane == w) bits = m;
+        }
+        if (lane < kSsdWords) smask[i * kSsdWords + lane] = bits;
+    }
+    __syncthreads();
+    if (warp == 0) warp_nms_scan(smask, kSsdWords, n, words, keep_words);
+    __syncthreads();
+    if (t == 0) {
+        int acc = 0;
+        for (int w = 0; w < kSsdWords; ++w) {
+            word_prefix[w] = acc;
+            acc += __popc(keep_words[w]);
+        }
+        word_prefix[kSsdWords] = acc;
+        out_counts[img * num_classes + cls] = acc;
+    }
+    __syncthreads();
+    const int64_t obase = (static_cast<int64_t>(img) * num_classes + cls) * topk;
+    if (t < n) {
+        const uint32_t kw = keep_words[t >> 5];
+        const int b = t & 31;
+        if ((kw >> b) & 1u) {
+            const int rank = word_prefix[t >> 5] + __popc(kw & ((1u << b) - 1u));
+            float* d = dets + (obase + rank) * 5;
+            d[0] = mybox.x;
+            d[1] = mybox.y;
+            d[2] = mybox.z;
+            d[3] = mybox.w;
+            d[4] = key_score(mykey);
+            prior_ids[obase + rank] = static_cast<int64_t>(key_index(mykey));
+        }
+    }
+    const int kept = word_prefix[kSsdWords];
+    for (int i = kept + t; i < topk; i += kSsdNmsThreads) {
+        float* d = dets + (obase + i) * 5;
+        d[0] = d[1] = d[2] = d[3] = d[4] = 0.0f;
+        prior_ids[obase + i] = -1;
+    }
+}
+
+}  // namespace fb
+
+extern "C" {
+
+int functs_b200_ssd_softmax_decode(const float* loc, const float* conf, const float* priors, int32_t batch,
+                                   int32_t num_priors, int32_t num_classes, float clamp_max, float* boxes,
+                                   float* scores_cm, void* stream) {
+    using namespace fb;
+    FB_REQUIRE(loc && conf && priors && boxes && scores_cm, "ssd_softmax_decode: null pointer");
+    FB_REQUIRE(batch > 0 && batch <= 65535 && num_priors > 0 && num_classes > 0 && num_classes + 1 <= kSsdMaxRow,
+               "ssd_softmax_decode: bad sizes (classes + 1 must be <= %d)", kSsdMaxRow);
+    FB_REQUIRE(((reinterpret_cast<uintptr_t>(loc) | reinterpret_cast<uintptr_t>(priors) | reinterpret_cast<uintptr_t>(boxes)) & 15) == 0,
+               "ssd_softmax_decode: loc, priors and boxes must be 16-byte aligned");
+    const int ncol = num_classes + 1;
+    // the bulk copy needs every tile start and length to be a multiple of 16 bytes
+    const bool aligned = (reinterpret_cast<uintptr_t>(conf) & 15) == 0 && ((static_cast<int64_t>(num_priors) * ncol) % 4 == 0) &&
+                         ((static_cast<int64_t>(kSsdTile) * ncol) % 4 == 0) &&
+                         ((static_cast<int64_t>(num_priors % kSsdTile) * ncol) % 4 == 0);
+    const size_t smem = ((static_cast<size_t>(kSsdTile) * ncol * 4 + 15) / 16) * 16 + 16;
+    FB_TRY(check_cuda(cudaFuncSetAttribute(ssd_softmax_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)),
+                      "ssd_softmax_decode attr"));
+    dim3 grid((num_priors + kSsdTile - 1) / kSsdTile, batch);
+    ssd_softmax_decode_kernel<<<grid, kSsdTile, smem, as_stream(stream)>>>(loc, conf, priors, num_priors, num_classes,
+                                                                           clamp_max, boxes, scores_cm, aligned ? 1 : 0);
+    count_launch();
+    return check_launch("ssd_softmax_decode_kernel");
+}
+
+int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_t batch, int32_t num_priors,
+                              int32_t num_classes, float score_thr, int32_t topk, float iou_thr, float* dets,
+                              int64_t* prior_ids, int32_t* out_counts, void* stream) {
+    using namespace fb;
+    FB_REQUIRE(boxes && scores_cm && dets && prior_ids && out_counts, "ssd_class_nms: null pointer");
+    FB_REQUIRE(batch > 0 && batch <= 65535 && num_priors > 0 && num_classes > 0, "ssd_class_nms: bad sizes");
+    FB_REQUIRE(topk > 0 && topk <= kSsdSelCap, "ssd_class_nms: topk must be in [1, %d]", kSsdSelCap);
+    FB_REQUIRE(score_thr > 0.0f, "ssd_class_nms: score threshold must be positive");
+    FB_REQUIRE(iou_thr > 0.0f && iou_thr < 1.0f, "ssd_class_nms: iou threshold must be in (0, 1)");
+    FB_REQUIRE(((reinterpret_cast<uintptr_t>(boxes) | reinterpret_cast<uintptr_t>(scores_cm)) & 15) == 0,
+               "ssd_class_nms: boxes and scores must be 16-byte aligned");
+    const size_t sc_bytes = (static_cast<size_t>(num_priors) * 4 + 15) / 16 * 16;
+    const size_t smem = sc_bytes + sizeof(SelectSmem<kSsdSelCap>) + sizeof(NmsBox) * kSsdSelCap +
+                        sizeof(uint32_t) * kSsdSelCap * kSsdWords;
+    FB_REQUIRE(smem <= 200 * 1024, "ssd_class_nms: %d priors do not fit in shared memory", num_priors);
+    FB_TRY(check_cuda(cudaFuncSetAttribute(ssd_class_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)),
+                      "ssd_class_nms attr"));
+    const float thr_lo = iou_thr * (1.0f - 1.0e-6f), thr_hi = iou_thr * (1.0f + 1.0e-6f);
+    dim3 grid(num_classes, batch);
+    ssd_class_nms_kernel<<<grid, kSsdNmsThreads, smem, as_stream(stream)>>>(boxes, scores_cm, num_priors, num_classes,
+                                                                            score_thr, topk, iou_thr, thr_lo, thr_hi,
+                                                                            dets, prior_ids, out_counts);
+    count_launch();
+    return check_launch("ssd_class_nms_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,273 @@
+// C2: YOLOv3-style decode group + the post-process pipeline built on the select / NMS kernels.
+//
+// The decode kernel is the fusion group "permute -> reshape -> sigmoid on the xy / objectness / class slices
+// (slice + sigmoid + slice_rev) -> xy grid offset -> exp * anchor -> corner form -> objectness * class score ->
+// score mask" of functs/benchmark/ai_model/yolov3/yolov3_bbox.py:209-220 and :122-127, in one pass over the NCHW
+// logits: threads run along the contiguous spatial axis (coalesced), every thread walks the 85 channels of one
+// box, and the hits of a warp are staged in shared memory and appended to the image's candidate list.
+#include "select_nms.cuh"
+
+namespace fb {
+
+int launch_select_topk(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, int groups, int topk,
+                       uint64_t* out_keys, int32_t* out_counts, cudaStream_t st);
+int64_t nms_scratch_bytes(int groups, int topk);
+int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
+                       const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
+                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* scratch,
+                       cudaStream_t st);
+
+constexpr int kYoloThreads = 128;
+constexpr int kYoloClasses = 80;
+constexpr int kYoloAttrib = 85;
+constexpr int kYoloChunk = 16;     // class logits loaded per thread before any is consumed
+constexpr int kYoloWarpStage = 160;
+
+struct YoloParams {
+    const float* map[3];
+    int size[3];        // S
+    int tiles[3];       // position tiles per (image, anchor) plane
+    int tile_begin[4];  // first CTA of every level, [3] = total
+    int box_begin[3];   // first box index of every level inside an image
+    float stride[3];
+    float anchor_w[3][3];
+    float anchor_h[3][3];
+    int batch;
+    int num_boxes;
+    float thr;
+    float* boxes;
+    float* obj_out;
+    float* cls_out;
+    uint64_t* keys;
+    int32_t* counts;
+    int64_t capacity;
+    int32_t* status;
+};
+
+template <bool DENSE>
+__global__ void __launch_bounds__(kYoloThreads)
+yolo_decode_kernel(const YoloParams P) {
+    __shared__ uint64_t stage_all[kYoloThreads / 32][kYoloWarpStage];
+    const int cta = blockIdx.x;
+    const int lvl = (cta >= P.tile_begin[2]) ? 2 : (cta >= P.tile_begin[1] ? 1 : 0);
+    const int local = cta - P.tile_begin[lvl];
+    const int S = P.size[lvl];
+    const int SS = S * S;
+    const int plane = local / P.tiles[lvl];  // = image * 3 + anchor
+    const int tile = local - plane * P.tiles[lvl];
+    const int img = plane / 3;
+    const int anc = plane - img * 3;
+    const int p = tile * kYoloThreads + threadIdx.x;
+    const bool valid = p < SS;
+    const int pp = valid ? p : (SS - 1);  // clamp so that every lane loads a legal address
+    const float* __restrict__ src = P.map[lvl] + (static_cast<int64_t>(img) * 255 + anc * kYoloAttrib) * SS + pp;
+
+    const float t0 = __ldg(src);
+    const float t1 = __ldg(src + SS);
+    const float t2 = __ldg(src + 2 * SS);
+    const float t3 = __ldg(src + 3 * SS);
+    const float t4 = __ldg(src + 4 * SS);
+
+    const int gy = pp / S, gx = pp - gy * S;
+    const float stride = P.stride[lvl];
+    const float cx = __fmul_rn(__fadd_rn(sigmoid_f32(t0), static_cast<float>(gx)), stride);
+    const float cy = __fmul_rn(__fadd_rn(sigmoid_f32(t1), static_cast<float>(gy)), stride);
+    const float hw = __fmul_rn(__fmul_rn(expf(t2), P.anchor_w[lvl][anc]), 0.5f);
+    const float hh = __fmul_rn(__fmul_rn(expf(t3), P.anchor_h[lvl][anc]), 0.5f);
+    const float so = sigmoid_f32(t4);
+    const int box = P.box_begin[lvl] + pp * 3 + anc;
+    const int64_t gbox = static_cast<int64_t>(img) * P.num_boxes + box;
+    if (valid) {
+        reinterpret_cast<float4*>(P.boxes)[gbox] =
+            make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
+        if (DENSE && P.obj_out != nullptr) P.obj_out[gbox] = so;
+    }
+
+    // A product of two sigmoids (each <= 1) can exceed thr >= 0.5 only if both logits are positive.
+    const bool shortcut = P.thr >= 0.5f;
+    const bool obj_ok = valid && (!shortcut || t4 > 0.0f);
+    uint64_t* stage = stage_all[threadIdx.x >> 5];
+    int fill = 0;
+    uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
+    int32_t* gcount = P.counts + img;
+    const uint32_t flat0 = static_cast<uint32_t>(box) * kYoloClasses;
+    const float* __restrict__ csrc = src + 5 * static_cast<int64_t>(SS);
+
+#pragma unroll 1
+    for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
+        float v[kYoloChunk];
+#pragma unroll
+        for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + static_cast<int64_t>(c0 + u) * SS);
+#pragma unroll
+        for (int u = 0; u < kYoloChunk; ++u) {
+            bool pred = false;
+            float s = 0.0f;
+            if (DENSE) {
+                const float sc = sigmoid_f32(v[u]);
+                if (valid && P.cls_out != nullptr) P.cls_out[gbox * kYoloClasses + c0 + u] = sc;
+                s = __fmul_rn(so, sc);
+                pred = valid && (s > P.thr);
+            } else if (obj_ok && (!shortcut || v[u] > 0.0f)) {
+                s = __fmul_rn(so, sigmoid_f32(v[u]));
+                pred = s > P.thr;
+            }
+            // stage the hits of the warp (fill is warp-uniform)
+            const unsigned m = __ballot_sync(kFullMask, pred);
+            if (pred) {
+                const int off = __popc(m & ((1u << (threadIdx.x & 31)) - 1u));
+                stage[fill + off] = make_key(s, flat0 + static_cast<uint32_t>(c0 + u));
+            }
+            fill += __popc(m);
+            if (fill + 32 > kYoloWarpStage) {
+                __syncwarp();
+                int base = 0;
+                if ((threadIdx.x & 31) == 0) base = atomicAdd(gcount, fill);
+                base = __shfl_sync(kFullMask, base, 0);
+                for (int i = (threadIdx.x & 31); i < fill; i += 32) {
+                    const int64_t pos = static_cast<int64_t>(base) + i;
+                    if (pos < P.capacity) gkeys[pos] = stage[i];
+                    else if (P.status != nullptr) atomicOr(P.status, FB_STATUS_CAND_OVERFLOW);
+                }
+                __syncwarp();
+                fill = 0;
+            }
+        }
+    }
+    __syncwarp();
+    if (fill > 0) {
+        int base = 0;
+        if ((threadIdx.x & 31) == 0) base = atomicAdd(gcount, fill);
+        base = __shfl_sync(kFullMask, base, 0);
+        for (int i = (threadIdx.x & 31); i < fill; i += 32) {
+            const int64_t pos = static_cast<int64_t>(base) + i;
+            if (pos < P.capacity) gkeys[pos] = stage[i];
+            else if (P.status != nullptr) atomicOr(P.status, FB_STATUS_CAND_OVERFLOW);
+        }
+    }
+}
+
+static const float kAnchors[3][3][2] = {{{116, 90}, {156, 198}, {373, 326}},
+                                        {{30, 61}, {62, 45}, {59, 119}},
+                                        {{10, 13}, {16, 30}, {33, 23}}};  // yolov3_bbox.py:191-193
+static const float kStrides[3] = {32.f, 16.f, 8.f};
+
+int launch_yolo_decode(const float* map0, const float* map1, const float* map2, int batch, int s0, int s1, int s2,
+                       float score_thr, float* boxes, float* obj_out, float* cls_out, uint64_t* cand_keys,
+                       int32_t* cand_counts, int64_t capacity, int32_t* status, cudaStream_t st) {
+    FB_REQUIRE(map0 && map1 && map2 && boxes && cand_keys && cand_counts, "yolo_decode: null pointer");
+    FB_REQUIRE(batch > 0 && s0 > 0 && s1 > 0 && s2 > 0 && s0 <= 1024 && s1 <= 1024 && s2 <= 1024 && capacity > 0,
+               "yolo_decode: bad sizes");
+    FB_REQUIRE(score_thr > 0.0f, "yolo_decode: score threshold must be positive (keys require positive scores)");
+    FB_REQUIRE((reinterpret_cast<uintptr_t>(boxes) & 15) == 0, "yolo_decode: boxes must be 16-byte aligned");
+    YoloParams P;
+    P.map[0] = map0;
+    P.map[1] = map1;
+    P.map[2] = map2;
+    const int S[3] = {s0, s1, s2};
+    int64_t tile_acc = 0;
+    int box_acc = 0;
+    for (int l = 0; l < 3; ++l) {
+        P.size[l] = S[l];
+        P.tiles[l] = (S[l] * S[l] + kYoloThreads - 1) / kYoloThreads;
+        P.tile_begin[l] = static_cast<int>(tile_acc);
+        tile_acc += static_cast<int64_t>(P.tiles[l]) * 3 * batch;
+        P.box_begin[l] = box_acc;
+        box_acc += S[l] * S[l] * 3;
+        P.stride[l] = kStrides[l];
+        for (int a = 0; a < 3; ++a) {
+            P.anchor_w[l][a] = kAnchors[l][a][0];
+            P.anchor_h[l][a] = kAnchors[l][a][1];
+        }
+    }
+    FB_REQUIRE(tile_acc < (1ll << 31), "yolo_decode: too many tiles");
+    FB_REQUIRE(static_cast<int64_t>(box_acc) * kYoloClasses < (1ll << 32), "yolo_decode: flat index exceeds 32 bits");
+    P.tile_begin[3] = static_cast<int>(tile_acc);
+    P.batch = batch;
+    P.num_boxes = box_acc;
+    P.thr = score_thr;
+    P.boxes = boxes;
+    P.obj_out = obj_out;
+    P.cls_out = cls_out;
+    P.keys = cand_keys;
+    P.counts = cand_counts;
+    P.capacity = capacity;
+    P.status = status;
+    FB_TRY(check_cuda(cudaMemsetAsync(cand_counts, 0, sizeof(int32_t) * batch, st), "memset cand_counts"));
+    if (obj_out != nullptr || cls_out != nullptr) {
+        yolo_decode_kernel<true><<<static_cast<unsigned>(tile_acc), kYoloThreads, 0, st>>>(P);
+    } else {
+        yolo_decode_kernel<false><<<static_cast<unsigned>(tile_acc), kYoloThreads, 0, st>>>(P);
+    }
+    count_launch();
+    return check_launch("yolo_decode_kernel");
+}
+
+static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct YoloScratch {
+    int64_t keys_off, counts_off, sel_keys_off, sel_counts_off, nms_off, total;
+};
+
+static YoloScratch yolo_scratch_layout(int batch, int64_t capacity, int topk) {
+    YoloScratch L;
+    int64_t off = 0;
+    L.keys_off = off;
+    off = align_up(off + static_cast<int64_t>(batch) * capacity * 8, 256);
+    L.counts_off = off;
+    off = align_up(off + static_cast<int64_t>(batch) * 4, 256);
+    L.sel_keys_off = off;
+    off = align_up(off + static_cast<int64_t>(batch) * topk * 8, 256);
+    L.sel_counts_off = off;
+    off = align_up(off + static_cast<int64_t>(batch) * 4, 256);
+    L.nms_off = off;
+    off = align_up(off + nms_scratch_bytes(batch, topk), 256);
+    L.total = off;
+    return L;
+}
+
+}  // namespace fb
+
+extern "C" {
+
+int functs_b200_yolo_decode(const float* map0, const float* map1, const float* map2, int32_t batch, int32_t s0,
+                            int32_t s1, int32_t s2, float score_thr, float* boxes, float* obj_out, float* cls_out,
+                            uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* status,
+                            void* stream) {
+    return fb::launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, obj_out, cls_out, cand_keys,
+                                  cand_counts, capacity, status, fb::as_stream(stream));
+}
+
+int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
+                                       int32_t topk) {
+    (void)s0;
+    (void)s1;
+    (void)s2;
+    if (batch <= 0 || capacity <= 0 || topk <= 0) return 0;
+    return fb::yolo_scratch_layout(batch, capacity, topk).total;
+}
+
+int functs_b200_yolo_postprocess(const float* map0, const float* map1, const float* map2, int32_t batch, int32_t s0,
+                                 int32_t s1, int32_t s2, float score_thr, int32_t topk, float iou_thr,
+                                 int64_t capacity, float* boxes, float* dets, int64_t* labels, int64_t* flat_ids,
+                                 int32_t* out_counts, int32_t* status, void* scratch, void* stream) {
+    using namespace fb;
+    FB_REQUIRE(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255) == 0,
+               "yolo_postprocess: scratch must be non-null and 256-byte aligned");
+    FB_REQUIRE(batch > 0 && capacity > 0 && topk > 0, "yolo_postprocess: bad sizes");
+    const YoloScratch L = yolo_scratch_layout(batch, capacity, topk);
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    uint64_t* keys = reinterpret_cast<uint64_t*>(base + L.keys_off);
+    int32_t* counts = reinterpret_cast<int32_t*>(base + L.counts_off);
+    uint64_t* sel_keys = reinterpret_cast<uint64_t*>(base + L.sel_keys_off);
+    int32_t* sel_counts = reinterpret_cast<int32_t*>(base + L.sel_counts_off);
+    void* nms_scratch = base + L.nms_off;
+    cudaStream_t st = as_stream(stream);
+    const int num_boxes = 3 * (s0 * s0 + s1 * s1 + s2 * s2);
+    FB_TRY(launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, nullptr, nullptr, keys, counts,
+                              capacity, status, st));
+    FB_TRY(launch_select_topk(keys, counts, capacity, batch, topk, sel_keys, sel_counts, st));
+    return launch_batched_nms(boxes, num_boxes, kYoloClasses, sel_keys, sel_counts, batch, topk, iou_thr, 1, dets,
+                              labels, flat_ids, nullptr, out_counts, nms_scratch, st);
+}
+
+}  // extern "C"

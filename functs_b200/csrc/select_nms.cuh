@@ -1,0 +1,335 @@
+// Block-level building blocks for "mask -> nonzero -> stable descending sort -> top-k -> greedy NMS".
+//
+// All of it is integer / exactly-rounded fp32 work: the selection orders 64-bit keys (score bits, inverted
+// index), and the IoU test reproduces, operation by operation, what a scalar CPU loop over
+//   inter / (area_i + area_j - inter) > thr
+// computes in fp32 (every product, sum and quotient rounded on its own; no fused multiply-add).
+#pragma once
+
+#include "common.cuh"
+
+namespace fb {
+
+constexpr int kHistBits = 11;
+constexpr int kHistBins = 1 << kHistBits;
+constexpr int kBinListCap = 1024;  // keys of the boundary bin that are finished by a local sort
+
+// ---- bitonic sort, descending, on `n` (power of two) 64-bit keys in shared memory -------------------
+template <int NT>
+__device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
+    for (int k = 2; k <= n; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < n; i += NT) {
+                int ixj = i ^ j;
+                if (ixj > i) {
+                    uint64_t a = s[i], b = s[ixj];
+                    bool desc_seg = (i & k) == 0;
+                    if (desc_seg ? (a < b) : (a > b)) {
+                        s[i] = b;
+                        s[ixj] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__device__ __forceinline__ int next_pow2(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+template <int SELCAP>
+struct SelectSmem {
+    uint64_t sel[SELCAP];
+    uint64_t binlist[kBinListCap];
+    int hist[kHistBins];
+    uint64_t red_min[32];
+    uint64_t red_max[32];
+    int red_cnt[32];
+    // broadcast slots
+    uint64_t kmin, kmax;
+    int nvalid;
+    int digit, above, inbin;
+    int sel_cnt, bin_cnt;
+};
+
+// Adds 1 to hist[d] for every lane with valid != 0, one shared-memory atomic per distinct digit per warp.
+__device__ __forceinline__ void warp_hist_add(int* hist, int d, bool valid) {
+    int dd = valid ? d : -1;
+    unsigned peers = __match_any_sync(kFullMask, dd);
+    if (valid) {
+        int leader = __ffs(peers) - 1;
+        if ((threadIdx.x & 31) == leader) atomicAdd(&hist[d], __popc(peers));
+    }
+}
+
+// Selects the `topk` largest non-zero keys among key(0..n-1) and leaves them sorted descending in sm.sel.
+// Returns the number selected (min(#non-zero keys, topk)).  Keys must be distinct; key(i) == 0 means "absent".
+// All NT threads of the block must call it; SELCAP is a power of two >= topk and NT a multiple of 32.
+template <int NT, int SELCAP, int UNROLL, class KeyFn>
+__device__ int block_select_topk(KeyFn key, int n, int topk, SelectSmem<SELCAP>& sm) {
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = NT / 32;
+
+    // pass 0: count, min and max of the present keys
+    uint64_t lmin = ~0ull, lmax = 0ull;
+    int lcnt = 0;
+    for (int base = 0; base < n; base += NT * UNROLL) {
+        uint64_t k[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            int i = base + u * NT + tid;
+            k[u] = (i < n) ? key(i) : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (k[u] != 0ull) {
+                lmin = k[u] < lmin ? k[u] : lmin;
+                lmax = k[u] > lmax ? k[u] : lmax;
+                ++lcnt;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        uint64_t omin = __shfl_xor_sync(kFullMask, lmin, o);
+        uint64_t omax = __shfl_xor_sync(kFullMask, lmax, o);
+        lcnt += __shfl_xor_sync(kFullMask, lcnt, o);
+        lmin = omin < lmin ? omin : lmin;
+        lmax = omax > lmax ? omax : lmax;
+    }
+    if (lane == 0) {
+        sm.red_min[warp] = lmin;
+        sm.red_max[warp] = lmax;
+        sm.red_cnt[warp] = lcnt;
+    }
+    if (tid == 0) {
+        sm.sel_cnt = 0;
+        sm.bin_cnt = 0;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        uint64_t a = lane < NW ? sm.red_min[lane] : ~0ull;
+        uint64_t b = lane < NW ? sm.red_max[lane] : 0ull;
+        int c = lane < NW ? sm.red_cnt[lane] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            uint64_t oa = __shfl_xor_sync(kFullMask, a, o);
+            uint64_t ob = __shfl_xor_sync(kFullMask, b, o);
+            c += __shfl_xor_sync(kFullMask, c, o);
+            a = oa < a ? oa : a;
+            b = ob > b ? ob : b;
+        }
+        if (lane == 0) {
+            sm.kmin = a;
+            sm.kmax = b;
+            sm.nvalid = c;
+        }
+    }
+    __syncthreads();
+    const int nvalid = sm.nvalid;
+    const uint64_t kmin = sm.kmin, kmax = sm.kmax;
+    if (nvalid == 0) return 0;
+
+    int sort_n;
+    int result;
+    if (nvalid <= topk) {
+        // everything is selected
+        for (int base = 0; base < n; base += NT * UNROLL) {
+            uint64_t k[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int i = base + u * NT + tid;
+                k[u] = (i < n) ? key(i) : 0ull;
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (k[u] != 0ull) {
+                    int pos = atomicAdd(&sm.sel_cnt, 1);
+                    if (pos < SELCAP) sm.sel[pos] = k[u];
+                }
+            }
+        }
+        __syncthreads();
+        result = nvalid;
+    } else {
+        // radix descent from the highest bit in which the keys differ
+        uint64_t diff = kmin ^ kmax;  // != 0 because nvalid >= 2 distinct keys
+        int hb = 63 - __clzll(static_cast<long long>(diff));
+        uint64_t mask = (hb >= 63) ? 0ull : ~((1ull << (hb + 1)) - 1ull);
+        uint64_t prefix = kmax & mask;
+        int want = topk;
+        while (true) {
+            int shift = hb - kHistBits + 1;
+            if (shift < 0) shift = 0;
+            const int nb = hb - shift + 1;
+            const int nbins = 1 << nb;
+            for (int i = tid; i < nbins; i += NT) sm.hist[i] = 0;
+            __syncthreads();
+            for (int base = 0; base < n; base += NT * UNROLL) {
+                uint64_t k[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    int i = base + u * NT + tid;
+                    k[u] = (i < n) ? key(i) : 0ull;
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    bool v = (k[u] != 0ull) && ((k[u] & mask) == prefix);
+                    int d = static_cast<int>((k[u] >> shift) & static_cast<uint64_t>(nbins - 1));
+                    warp_hist_add(sm.hist, d, v);
+                }
+            }
+            __syncthreads();
+            // warp 0 finds the largest digit d with (count of digits >= d) >= want
+            if (warp == 0) {
+                const int per = (nbins + 31) / 32;  // bins per lane, lane 31 holds the highest bins
+                int lo = lane * per, hi = lo + per;
+                if (hi > nbins) hi = nbins;
+                int s = 0;
+                for (int i = lo; i < hi; ++i) s += sm.hist[i];
+                // suffix sum over lanes: suf = sum of s over lanes > lane
+                int incl = s;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int t = __shfl_down_sync(kFullMask, incl, o);
+                    if (lane + o < 32) incl += t;
+                }
+                int suf = incl - s;  // strictly higher lanes
+                bool mine = (suf < want) && (incl >= want);
+                if (mine) {
+                    int cum = suf;
+                    int d = hi - 1;
+                    for (; d >= lo; --d) {
+                        int h = sm.hist[d];
+                        if (cum + h >= want) break;
+                        cum += h;
+                    }
+                    sm.digit = d;
+                    sm.above = cum;
+                    sm.inbin = sm.hist[d];
+                }
+            }
+            __syncthreads();
+            const int digit = sm.digit, above = sm.above, inbin = sm.inbin;
+            want -= above;
+            mask |= static_cast<uint64_t>(nbins - 1) << shift;
+            prefix |= static_cast<uint64_t>(digit) << shift;
+            hb = shift - 1;
+            if (inbin == want || shift == 0 || inbin <= kBinListCap) break;
+            __syncthreads();
+        }
+        // collect: strictly above the boundary bin -> sel; inside the bin -> binlist
+        for (int base = 0; base < n; base += NT * UNROLL) {
+            uint64_t k[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                int i = base + u * NT + tid;
+                k[u] = (i < n) ? key(i) : 0ull;
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (k[u] != 0ull) {
+                    uint64_t km = k[u] & mask;
+                    if (km > prefix) {
+                        int pos = atomicAdd(&sm.sel_cnt, 1);
+                        if (pos < SELCAP) sm.sel[pos] = k[u];
+                    } else if (km == prefix) {
+                        int pos = atomicAdd(&sm.bin_cnt, 1);
+                        if (pos < kBinListCap) sm.binlist[pos] = k[u];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        int bc = sm.bin_cnt < kBinListCap ? sm.bin_cnt : kBinListCap;
+        int bn = next_pow2(bc);
+        for (int i = bc + tid; i < bn; i += NT) sm.binlist[i] = 0ull;
+        __syncthreads();
+        bitonic_sort_desc<NT>(sm.binlist, bn);
+        const int have = sm.sel_cnt;  // == topk - want
+        for (int i = tid; i < want && i < bc; i += NT) {
+            if (have + i < SELCAP) sm.sel[have + i] = sm.binlist[i];
+        }
+        __syncthreads();
+        result = topk;
+    }
+    sort_n = next_pow2(result);
+    for (int i = result + tid; i < sort_n; i += NT) sm.sel[i] = 0ull;
+    __syncthreads();
+    bitonic_sort_desc<NT>(sm.sel, sort_n);
+    return result;
+}
+
+// ---- IoU suppression test ------------------------------------------------------------------------
+struct NmsBox {
+    float x1, y1, x2, y2, area;
+};
+
+__device__ __forceinline__ NmsBox make_nms_box(float x1, float y1, float x2, float y2) {
+    NmsBox b;
+    b.x1 = x1;
+    b.y1 = y1;
+    b.x2 = x2;
+    b.y2 = y2;
+    b.area = __fmul_rn(__fsub_rn(x2, x1), __fsub_rn(y2, y1));
+    return b;
+}
+
+// true iff fp32(inter / (area_i + area_j - inter)) > thr.  thr_lo / thr_hi bracket thr by a relative 1e-6:
+// outside the bracket the comparison against thr * union decides without a division, inside it the
+// correctly rounded quotient is formed, so the answer is always that of the division.
+__device__ __forceinline__ bool iou_exceeds(const NmsBox& a, const NmsBox& b, float thr, float thr_lo, float thr_hi) {
+    float xx1 = fmaxf(a.x1, b.x1), yy1 = fmaxf(a.y1, b.y1);
+    float xx2 = fminf(a.x2, b.x2), yy2 = fminf(a.y2, b.y2);
+    float w = fmaxf(0.0f, __fsub_rn(xx2, xx1));
+    float h = fmaxf(0.0f, __fsub_rn(yy2, yy1));
+    float inter = __fmul_rn(w, h);
+    if (!(inter > 0.0f)) return false;  // 0 / u is 0 (or NaN for u == 0): never above a positive threshold
+    float uni = __fsub_rn(__fadd_rn(a.area, b.area), inter);
+    if (uni > 0.0f && uni < 3.0e38f && inter < 3.0e38f) {
+        if (inter > __fmul_rn(uni, thr_hi)) return true;
+        if (inter < __fmul_rn(uni, thr_lo)) return false;
+    }
+    return __fdiv_rn(inter, uni) > thr;
+}
+
+// Serial part of greedy NMS over a precomputed suppression bit matrix, run by ONE warp.
+// mask: row i has `words` 32-bit words (row stride `row_stride` words); bit j of row i set iff j > i and box i
+// suppresses box j.  keep_words[w] receives the keep bits of boxes 32w..32w+31.  words <= 32.
+__device__ __forceinline__ void warp_nms_scan(const uint32_t* mask, int row_stride, int n, int words,
+                                              uint32_t* keep_words) {
+    const int lane = threadIdx.x & 31;
+    uint32_t removed = 0u;  // lane l tracks word l
+    for (int w = 0; w < words; ++w) {
+        uint32_t r = __shfl_sync(kFullMask, removed, w);
+        uint32_t keepw = 0u;
+        const int base = w * 32;
+        // decisions inside the 32x32 diagonal block (every lane computes the same thing from broadcast reads)
+        uint32_t diag[32];
+#pragma unroll
+        for (int b = 0; b < 32; ++b) diag[b] = (base + b < n) ? mask[(base + b) * row_stride + w] : 0u;
+#pragma unroll
+        for (int b = 0; b < 32; ++b) {
+            bool alive = (base + b < n) && !((r >> b) & 1u);
+            if (alive) {
+                keepw |= (1u << b);
+                r |= diag[b];
+            }
+        }
+        // kept rows of this block remove columns in the later words
+        if (lane < words) {
+#pragma unroll 8
+            for (int b = 0; b < 32; ++b) {
+                if ((keepw >> b) & 1u) removed |= mask[(base + b) * row_stride + lane];
+            }
+        }
+        if (lane == 0) keep_words[w] = keepw;
+    }
+}
+
+}  // namespace fb

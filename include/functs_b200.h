@@ -1,0 +1,199 @@
+/*
+ * functs_b200 — C ABI of the B200 (sm_100a) executor for FuncTs fusion groups.
+ *
+ * Every entry point is a thin launcher over precompiled kernels: plain device pointers and
+ * sizes in, an integer status out.  No entry point allocates device memory, synchronises
+ * the device or touches a stream other than the one it is given (``stream`` is a
+ * ``cudaStream_t`` passed as ``void*``; NULL = the legacy default stream).  Work that needs
+ * temporary device memory takes a caller-allocated ``scratch`` pointer whose size the
+ * matching ``*_scratch_bytes`` function reports.
+ *
+ * What each entry point replaces in the reference (paths inside the reference project):
+ * the reference executes a fusion group through ``GraphBuilder::run``
+ * (fait/fuser/graph_builder.cpp:714-927), which marshals IValues, allocates outputs and
+ * calls one NVRTC-compiled kernel per group through ``CudaCodeGenTssa::call``
+ * (fait/tensorexpr/cuda_codegen_tssa.cpp:1167-1290).  Here the group bodies are fixed,
+ * hand-written kernels and the caller (the operator shim) owns allocation.
+ *
+ * Return value: FB_OK (0) or a negative FB_ERR_* code; ``functs_b200_last_error`` gives a
+ * message for the calling thread.  Kernels never trap: data-dependent problems (a candidate
+ * buffer that is too small) are reported through the int32 ``status`` word in device memory.
+ */
+#ifndef FUNCTS_B200_H_
+#define FUNCTS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FB_OK 0
+#define FB_ERR_INVALID_ARGUMENT (-1)
+#define FB_ERR_CUDA (-2)
+#define FB_ERR_UNSUPPORTED (-3)
+#define FB_ERR_NOT_FOUND (-4)
+
+/* bits of the device status word */
+#define FB_STATUS_CAND_OVERFLOW 1 /* a candidate list was longer than its capacity; extra candidates were dropped */
+#define FB_STATUS_WAIT_TIMEOUT 2  /* a bounded device-side wait ran out */
+#define FB_STATUS_INDEX_RANGE 4   /* an index tensor held a row outside the indexed extent */
+
+/* ---- library ------------------------------------------------------------------------- */
+
+/* ABI version of this header (bumped on incompatible change). */
+int functs_b200_abi_version(void);
+/* Message of the last failing call made by this thread ("" if none). */
+const char* functs_b200_last_error(void);
+/* Kernels launched by this library in this process so far (the reference counts launches with
+ * CUPTI, fait/util/profile.cpp:39-41; the "kernels per call" metric is a difference of two reads). */
+uint64_t functs_b200_launch_count(void);
+
+/* ---- C1: loop { select(b,0,i) -> add -> select_rev(b,.,0,i) } on a cloned, carried tensor -- */
+/* Replaces the group printed in the reference README.md:284-299 (examples/get_started.py:10-15):
+ * out = clone(b); out[i,:] = b[i,:] + addend for 0 <= i < n.  b, out: [rows, cols] fp32, contiguous.
+ * One launch; loop iterations map onto CTAs. */
+int functs_b200_rows_select_add_select_rev(const float* b, float* out, int64_t rows, int64_t cols, int64_t n,
+                                           float addend, void* stream);
+
+/* ---- masked index / top-k / NMS building blocks (shared by C2 and C3) ------------------- */
+/* Candidate key = (float bits of the score) << 32 | (0xFFFFFFFF - flat index); descending key order is
+ * "score descending, then index ascending", i.e. nonzero() followed by a stable descending sort
+ * (functs/benchmark/ai_model/ssd/ssd_bbox.py:163-172).  Scores must be > 0. */
+
+/* scores [groups, n] fp32 -> keys of the elements > thr, per group, in unspecified order.
+ * keys [groups, capacity], counts [groups] int32 (must be zeroed by the caller or by zero_counts=1). */
+int functs_b200_threshold_compact(const float* scores, int32_t groups, int64_t n, float thr, uint64_t* keys,
+                                  int32_t* counts, int64_t capacity, int32_t zero_counts, int32_t* status,
+                                  void* stream);
+
+/* Per group: the topk largest keys, sorted descending. in_keys [groups, capacity] with in_counts valid
+ * entries (clamped to capacity); out_keys [groups, topk]; out_counts [groups] = min(count, topk).  topk <= 1024. */
+int functs_b200_select_topk(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, int32_t groups,
+                            int32_t topk, uint64_t* out_keys, int32_t* out_counts, void* stream);
+
+/* Greedy IoU NMS over the selected candidates of every group, as torchvision.ops.nms does on CPU
+ * (call sites yolov3_bbox.py:177, ssd_bbox.py:212), optionally class-wise through the coordinate-offset
+ * trick of yolov3_bbox.py:144-146 (class_offset != 0: offset = label * (max coordinate of the selected boxes + 1)).
+ * boxes [groups, num_boxes, 4]; sel_keys [groups, topk] sorted; flat index = box * num_classes + label.
+ * Outputs (fixed capacity topk per group, first out_counts[g] rows valid, score-descending):
+ *   dets [groups, topk, 5] (x1,y1,x2,y2,score), labels [groups, topk] int64, flat_ids [groups, topk] int64,
+ *   keep [groups, topk] int64 (position in the selected list), out_counts [groups] int32.
+ * scratch: functs_b200_nms_scratch_bytes(groups, topk). */
+int64_t functs_b200_nms_scratch_bytes(int32_t groups, int32_t topk);
+int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_classes, const uint64_t* sel_keys,
+                            const int32_t* sel_counts, int32_t groups, int32_t topk, float iou_thr,
+                            int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids, int64_t* keep,
+                            int32_t* out_counts, void* scratch, void* stream);
+
+/* ---- C2: YOLOv3-style decode + score mask + top-k + class-wise NMS ----------------------- */
+/* Follows functs/benchmark/ai_model/yolov3/yolov3_bbox.py:195-243 at the configured shapes:
+ * three NCHW logit maps [batch, 255, S, S]; box order is level, y, x, anchor. */
+
+/* Decode group (one launch): permute/reshape, sigmoid on the xy / objectness / class slices, xy grid offset and
+ * stride, wh = exp * anchor, corner form, score = obj * cls, mask score > thr, compaction into candidate keys.
+ * boxes [batch, N, 4] with N = 3*(s0^2+s1^2+s2^2); obj_out [batch, N] and cls_out [batch, N, 80] are optional
+ * (NULL = not written; they exist for value-parity checks); cand_keys [batch, capacity]; cand_counts [batch]
+ * is zeroed by the kernel launch sequence. */
+int functs_b200_yolo_decode(const float* map0, const float* map1, const float* map2, int32_t batch, int32_t s0,
+                            int32_t s1, int32_t s2, float score_thr, float* boxes, float* obj_out, float* cls_out,
+                            uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* status,
+                            void* stream);
+
+/* Whole post-process: decode -> select_topk -> batched_nms(class_offset=1).  Outputs as in batched_nms.
+ * scratch: functs_b200_yolo_scratch_bytes(batch, s0, s1, s2, capacity, topk). */
+int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
+                                       int32_t topk);
+int functs_b200_yolo_postprocess(const float* map0, const float* map1, const float* map2, int32_t batch, int32_t s0,
+                                 int32_t s1, int32_t s2, float score_thr, int32_t topk, float iou_thr,
+                                 int64_t capacity, float* boxes, float* dets, int64_t* labels, int64_t* flat_ids,
+                                 int32_t* out_counts, int32_t* status, void* scratch, void* stream);
+
+/* ---- C3: SSD-style post-process ----------------------------------------------------------- */
+/* Follows functs/benchmark/ai_model/ssd/ssd_bbox.py:121-154 (decode with the strided clamp), :268 (softmax, last
+ * column = background dropped) and :163-172 + :212 inside a loop over classes that is mapped onto CTAs. */
+
+/* Group 1 (one launch): softmax over conf rows, box decode (variances 0.1 / 0.2, clamp to [0, clamp_max]).
+ * loc [batch, P, 4]; conf [batch, P, C+1]; priors [P, 4] (cx, cy, w, h); boxes [batch, P, 4];
+ * scores_cm [batch, C, P] (class-major). */
+int functs_b200_ssd_softmax_decode(const float* loc, const float* conf, const float* priors, int32_t batch,
+                                   int32_t num_priors, int32_t num_classes, float clamp_max, float* boxes,
+                                   float* scores_cm, void* stream);
+/* Group 2 (one launch, one CTA per (image, class) loop iteration): mask > thr, top-k, NMS.
+ * dets [batch, C, topk, 5]; prior_ids [batch, C, topk] int64; out_counts [batch, C] int32.  topk <= 256. */
+int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_t batch, int32_t num_priors,
+                              int32_t num_classes, float score_thr, int32_t topk, float iou_thr, float* dets,
+                              int64_t* prior_ids, int32_t* out_counts, void* stream);
+
+/* ---- C4: imperative LSTM with slice-assigned outputs ---------------------------------------- */
+/* Follows functs/benchmark/ai_model/lstm/lstm.py:79-98, 118-133 (one layer; hs[t] = h, cs[t] = c kept).
+ * x [T, B, I]; w_ih [4, I, H]; w_hh [4, H, H]; b_ih, b_hh [4, H]; hs, cs [T, B, H]; gate order i, f, g, o;
+ * h0 = c0 = 0.  scratch: functs_b200_lstm_scratch_bytes(T, B, I, H).
+ * Two launches: the hoisted input projection (tcgen05, 3xTF32) and one persistent recurrent kernel. */
+int64_t functs_b200_lstm_scratch_bytes(int32_t seq_len, int32_t batch, int32_t input, int32_t hidden);
+int functs_b200_lstm_forward(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
+                             const float* b_hh, int32_t seq_len, int32_t batch, int32_t input, int32_t hidden,
+                             float* hs, float* cs, int32_t* status, void* scratch, void* stream);
+/* Same, with the projection path chosen by the caller: mode 0 = default (tensor cores when the shape allows),
+ * mode 1 = fp32 CUDA-core projection (the on-device check of the tensor-core result). */
+int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
+                                  const float* b_hh, int32_t seq_len, int32_t batch, int32_t input, int32_t hidden,
+                                  float* hs, float* cs, int32_t* status, void* scratch, void* stream, int32_t mode);
+
+/* ---- C5: YOLACT-style mask assembly ------------------------------------------------------------ */
+/* Follows functs/benchmark/ai_model/yolact/yolact_mask.py:250-264 and :306-333: per detection
+ * sigmoid(proto @ coef) cropped to the sanitised box by slice assignment, thresholded.
+ * proto [batch, H, W, K] (K = 32); coef [batch, N, K]; boxes [batch, N, 4] (x1, y1, x2, y2 in pixels);
+ * masks [batch, N, H, W] uint8; logits_out optional [batch, N, H, W] fp32 (dense proto @ coef, for value checks).
+ * H*W must be a multiple of 4.  One launch. */
+int functs_b200_yolact_masks(const float* proto, const float* coef, const float* boxes, int32_t batch, int32_t height,
+                             int32_t width, int32_t num_det, float thr, uint8_t* masks, float* logits_out,
+                             void* stream);
+
+/* ---- Access / Assign family as stand-alone launches ------------------------------------------- */
+/* A strided gather description: out[ax] = src[offset + sum_d ((ax_d % mod_d) * stride_d)], rank <= 8.
+ * It expresses immut::select / slice / squeeze / unsqueeze / view / reshape / permute / expand / expand_as /
+ * repeat (index math of functs/csrc/jit/tensorexpr/nnc_ext.cpp:62-401).  elem_size in {1,2,4,8}. */
+typedef struct {
+    int32_t rank;
+    int64_t out_shape[8];
+    int64_t src_stride[8]; /* in elements */
+    int64_t src_mod[8];    /* 0 = no modulo */
+    int64_t src_offset;    /* in elements */
+} functs_b200_access_desc;
+
+int functs_b200_access(const void* src, void* out, const functs_b200_access_desc* desc, int32_t elem_size,
+                       void* stream);
+
+/* The reverse ("assign") forms: out = self everywhere except the region selected along ``dim``, which comes
+ * from src (nnc_ext.cpp:112-164, 187-212).  self/out: contiguous, shape self_shape[rank]; src: contiguous.
+ *   select_rev: region = { ax[dim] == index };  slice_rev: region = { start <= ax[dim] < end, (ax[dim]-start) % step == 0 }.
+ * start/end/index are already normalised by the caller. */
+int functs_b200_select_rev(const void* self, const void* src, void* out, const int64_t* self_shape, int32_t rank,
+                           int32_t dim, int64_t index, int32_t elem_size, void* stream);
+int functs_b200_slice_rev(const void* self, const void* src, void* out, const int64_t* self_shape, int32_t rank,
+                          int32_t dim, int64_t start, int64_t end, int64_t step, int32_t elem_size, void* stream);
+/* immut::index (first index tensor, dim 0, int64 indices): out[i, r] = self[idx[i], r]; index_rev is the row
+ * scatter out = self; out[idx[i], r] = src[i, r] (which of several duplicate indices wins is unspecified,
+ * as for index_put_). */
+int functs_b200_index_rows(const void* self, const int64_t* idx, void* out, int64_t self_rows, int64_t num_idx,
+                           int64_t row_elems, int32_t elem_size, int32_t* status, void* stream);
+int functs_b200_index_rows_rev(const void* self, const void* src, const int64_t* idx, void* out, int64_t self_rows,
+                               int64_t num_idx, int64_t row_elems, int32_t elem_size, int32_t* status, void* stream);
+
+/* ---- group registry: what the tssa::ParallelFunctor operator binds to ------------------------ */
+/* The reference registers one JIT operator whose Operation runs a compiled group
+ * (fait/passes/te_op.cpp:238-249).  Here a group is found by a canonical signature string and launched with
+ * flat argument arrays; the typed entry points above are what the registry dispatches to.
+ * Returns a group id >= 0 or FB_ERR_NOT_FOUND. */
+int functs_b200_group_lookup(const char* signature);
+int functs_b200_group_count(void);
+const char* functs_b200_group_signature(int group_id);
+int functs_b200_group_launch(int group_id, const void* const* in_ptrs, const int64_t* int_args,
+                             const double* float_args, void* const* out_ptrs, void* scratch, int32_t* status,
+                             void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUNCTS_B200_H_ */
