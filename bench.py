@@ -1,0 +1,375 @@
+"""Benchmark of the hot path: YOLOv3-style post-process (decode + score mask + top-k + class-wise NMS), batch 64
+per GPU, synthetic seeded logits.  Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extra]
+
+A step is one pass of the post-process over one batch of 64 images whose logits are already resident in HBM
+(`value`), or, for `e2e`, one call of the public module with HOST (pinned) inputs and a device->host read of the
+detections.  With N > 1 every rank processes its own batch (weak scaling) and the ranks all-gather the padded
+detection records with NCCL at the end of every step.  `--impl reference` times the CPU oracle (the un-functionalized
+TorchScript program the reference's tests use as ground truth) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH = 64
+SIZES = (13, 26, 52)
+NUM_BOXES = 3 * sum(s * s for s in SIZES)           # 10647
+IMG_BYTES = NUM_BOXES * 85 * 4                        # 3 619 980 B of logits per image (algorithmic read)
+OUT_BYTES_PER_IMG = 1000 * (5 * 4 + 8)                # <= 28 000 B of detections per image
+METRIC = "yolov3_postprocess_batches_per_s"
+UNIT = "batches/s (1 batch = 64 images)"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 8 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 8 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 8 for i in range(4) if r[4 + i].lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# CPU oracle timing (reference arm and the cpu_baseline block)
+# ------------------------------------------------------------------------------------------------------------------
+
+
+def cpu_oracle_rate(sample_images: int, steps: int, warmup: int):
+    """TorchScript CPU oracle on `sample_images` images per step; returns (batches/s, ms per step, threads)."""
+    import torch
+    from oracle import workloads as W
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    mod = torch.jit.script(W.YOLOV3Post(sizes=SIZES))
+    maps = W.make_yolo_inputs(sample_images)
+    for _ in range(warmup):
+        mod(maps)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        mod(maps)
+    dt = (time.perf_counter() - t0) / steps
+    return (sample_images / BATCH) / dt, dt * 1e3, threads
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 8
+    rate, ms, threads = cpu_oracle_rate(sample, max(args.steps, 1), max(args.warmup, 1))
+    sample_txt = f"{sample} of the 64 images per step (seeded N(0,1) logits), TorchScript CPU oracle, rate scaled to 64-image batches"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "YOLOv3-style decode + score>0.5 mask + top-1000 + class-wise NMS 0.45, 3 scales 13/26/52, batch 64",
+                   "sample_images_per_step": sample},
+        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_txt},
+        "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------------------
+
+
+def time_events(fn, iters, torch):
+    """Average device time of fn() in ms over iters back-to-back calls (CUDA events on the current stream)."""
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def extra_workloads(torch, fb, W, hbm_peak):
+    """Short device-time measurements of the other four configured workloads (not part of `value`)."""
+    out = {}
+    dev = "cuda"
+    # C1 (0.5 MB: lives in L2; launch-latency bound by construction)
+    a, b, n = W.make_get_started_inputs()
+    bd = b.to(dev)
+    res = torch.empty_like(bd)
+    from functs_b200._lib import check, lib
+    st = torch.cuda.current_stream().cuda_stream
+    f1 = lambda: check(lib.functs_b200_rows_select_add_select_rev(bd.data_ptr(), res.data_ptr(), 64, 1024, n, 1.0, st))
+    for _ in range(20):
+        f1()
+    ms = time_events(f1, 200, torch)
+    out["get_started"] = {"latency_us": ms * 1e3, "kernels_per_call": 1, "hbm_gbs": 524288 / (ms * 1e-3) / 1e9,
+                          "note": "0.5 MB working set (L2-resident); latency-bound"}
+    # C3, batch 64, three input sets rotated (190 MB per set > L2)
+    loc, conf = [t.to(dev) for t in W.make_ssd_inputs(BATCH)]
+    sets = [(loc, conf)] + [(loc.roll(s_, 0).clone(), conf.roll(s_, 0).clone()) for s_ in (1, 2)]
+    ssd = fb.workloads.SSDBBox(W.ssd_priors(), device=dev)
+    it = [0]
+
+    def f3():
+        loc, conf = sets[it[0] % 3]
+        it[0] += 1
+        ssd.forward_padded(loc, conf)
+    for _ in range(5):
+        f3()
+    ms = time_events(f3, 30, torch)
+    by = BATCH * (8732 * 81 * 4 + 8732 * 4 * 4)
+    out["ssd"] = {"batch": BATCH, "latency_us": ms * 1e3, "batches_per_s": 1e3 / ms, "kernels_per_call": 2,
+                  "algorithmic_gbs": by / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / hbm_peak}
+    del sets, ssd
+    # C5, batch 64 (279 MB per call > L2)
+    proto, coef, boxes = [t.to(dev) for t in W.make_yolact_inputs(BATCH)]
+    ym = fb.workloads.YolactBBoxMask(device=dev)
+    f5 = lambda: ym(proto, coef, boxes)
+    for _ in range(5):
+        f5()
+    ms = time_events(f5, 30, torch)
+    by = BATCH * 4356432
+    out["yolact"] = {"batch": BATCH, "latency_us": ms * 1e3, "batches_per_s": 1e3 / ms, "kernels_per_call": 1,
+                     "algorithmic_gbs": by / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / hbm_peak}
+    del proto, ym
+    # C4, T=64 B=64 H=512
+    x, w_ih, w_hh, b_ih, b_hh = W.make_lstm_inputs()
+    lm = fb.workloads.LSTM(w_ih, w_hh, b_ih, b_hh, device=dev)
+    xd = x.to(dev)
+    f4 = lambda: lm.forward_device(xd)
+    for _ in range(3):
+        f4()
+    ms = time_events(f4, 10, torch)
+    fb.ops.raise_on_status(lm._status, "lstm bench")
+    out["lstm"] = {"T": 64, "B": 64, "H": 512, "latency_us": ms * 1e3, "batches_per_s": 1e3 / ms, "kernels_per_call": 2,
+                   "algorithmic_tflops": 17.18e9 / (ms * 1e-3) / 1e12}
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import functs_b200 as fb
+    from functs_b200 import dist as fdist
+    from functs_b200._lib import check, launch_count, lib
+    from oracle import workloads as W  # input generator + cpu_baseline leg only
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: functs_b200 has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hbm_peak, peak_kind = measured_peaks()
+
+    # ---- inputs: this rank's 64 images; three sets rotated so that no step finds its logits in L2 ----
+    n_sets = 3
+    host_maps = W.make_yolo_inputs(BATCH, first=rank * BATCH)
+    sets = [[m.to(dev) for m in host_maps]]
+    for s_ in range(1, n_sets):
+        sets.append([m.roll(s_, 0).clone() for m in sets[0]])  # same images, permuted inside the batch
+    pinned = [m.pin_memory() for m in host_maps]
+    bytes_in = sum(m.numel() * 4 for m in host_maps)
+
+    topk, cap = 1000, NUM_BOXES * 80
+    plan = fb.ops.YoloPostprocessPlan(BATCH, SIZES, topk, cap, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    # stage buffers (the same carve-up the one-call entry point makes inside its scratch)
+    keys = torch.empty(BATCH, cap, dtype=torch.int64, device=dev)
+    counts = torch.empty(BATCH, dtype=torch.int32, device=dev)
+    sel_keys = torch.empty(BATCH, topk, dtype=torch.int64, device=dev)
+    sel_counts = torch.empty(BATCH, dtype=torch.int32, device=dev)
+    nms_scratch = torch.empty(int(lib.functs_b200_nms_scratch_bytes(BATCH, topk)), dtype=torch.uint8, device=dev)
+    rec = torch.empty(BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
+    rec_all = torch.empty(world * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev) if world > 1 else None
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+
+    def step(i, events=None):
+        m = sets[i % n_sets]
+        if events:
+            events[0].record()
+        check(lib.functs_b200_yolo_decode(m[0].data_ptr(), m[1].data_ptr(), m[2].data_ptr(), BATCH, *SIZES, 0.5,
+                                          plan.boxes.data_ptr(), None, None, keys.data_ptr(), counts.data_ptr(), cap,
+                                          plan.status.data_ptr(), st))
+        if events:
+            events[1].record()
+        check(lib.functs_b200_select_topk(keys.data_ptr(), counts.data_ptr(), cap, BATCH, topk, sel_keys.data_ptr(),
+                                          sel_counts.data_ptr(), st))
+        if events:
+            events[2].record()
+        check(lib.functs_b200_batched_nms(plan.boxes.data_ptr(), NUM_BOXES, 80, sel_keys.data_ptr(), sel_counts.data_ptr(),
+                                          BATCH, topk, 0.45, 1, plan.dets.data_ptr(), plan.labels.data_ptr(),
+                                          plan.flat_ids.data_ptr(), None, plan.counts.data_ptr(), nms_scratch.data_ptr(), st))
+        if events:
+            events[3].record()
+        if world > 1:
+            fdist.pack_detections(plan.dets, plan.labels, plan.flat_ids, plan.counts, out=rec)
+            fdist.gather_records(rec, out=rec_all)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = launch_count()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start.record()
+    for i in range(args.steps):
+        step(i, ev[i])
+    t_end.record()
+    barrier()
+    launches = launch_count() - launches0
+    total_ms = t_start.elapsed_time(t_end)
+    fb.ops.raise_on_status(plan.status, "bench")
+    decode_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    select_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    nms_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in ev)
+    kept = int(plan.counts.sum())
+
+    # ---- e2e: public module, pinned host inputs, detections read back ----
+    mod = fb.workloads.YOLOV3BBox(sizes=SIZES, device=dev)
+    e2e_steps = max(2, min(args.steps, 10))
+
+    def e2e_step():
+        dets, labels, flat_ids, cnt = mod.forward_padded(pinned)
+        if world > 1:
+            fdist.pack_detections(dets, labels, flat_ids, cnt, out=rec)
+            r = fdist.gather_records(rec, out=rec_all)
+            return r.cpu()
+        return dets.cpu(), labels.cpu(), cnt.cpu()
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    bytes_out = (rec_all.numel() * 4) if world > 1 else (plan.dets.numel() * 4 + plan.labels.numel() * 8 + plan.counts.numel() * 4)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- max over ranks ----
+    stats = torch.tensor([total_ms, e2e_ms, decode_ms, select_ms, nms_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, decode_ms, select_ms, nms_ms = [float(v) for v in stats.tolist()]
+
+    if rank == 0:
+        ms_per_step = total_ms / args.steps
+        alg_bytes = BATCH * IMG_BYTES                       # bytes the decode kernel must read per launch
+        achieved = alg_bytes / (decode_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": world * 1e3 / ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "YOLOv3-style decode + score>0.5 mask + top-1000 + class-wise NMS 0.45, 3 scales 13/26/52, batch 64 per GPU",
+                       "batch_per_gpu": BATCH, "l2": f"inputs 231.7 MB per step > 126 MB L2, {n_sets} input sets rotated",
+                       "collective": "none" if world == 1 else "NCCL all-gather of padded detection records every step"},
+            "latency_us": ms_per_step * 1e3, "kernels_per_call": launches / args.steps,
+            "images_per_s": world * BATCH * 1e3 / ms_per_step,
+            "stage_us": {"decode_mask_compact": decode_ms * 1e3, "select_topk": select_ms * 1e3, "nms": nms_ms * 1e3},
+            "detections_kept_last_step": kept,
+            "gpu_launches": launches,
+            "e2e": {"value": world * 1e3 / e2e_ms, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
+                    "d2h_bytes_per_step": bytes_out, "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "roofline": {"bound": "hbm", "kernel": "yolo_decode_kernel", "achieved": achieved, "peak": hbm_peak,
+                         "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                         "algorithmic_bytes_per_launch": alg_bytes, "whole_step_frac": (alg_bytes + BATCH * OUT_BYTES_PER_IMG) / (ms_per_step * 1e-3) / 1e9 / hbm_peak},
+            "clocks": clocks,
+        }
+        traffic_file = os.path.join(ROOT, "profiles", "yolo_decode_traffic.json")
+        if os.path.exists(traffic_file):
+            with open(traffic_file) as f:
+                line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch_b64")
+        if not args.no_extra and world == 1:
+            cpu_rate, cpu_ms, threads = cpu_oracle_rate(4, 3, 1)
+            line["cpu_baseline"] = {"value": cpu_rate, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": "4 of the 64 images per step x 3 steps, TorchScript CPU oracle, rate scaled to 64-image batches"}
+            del sets, keys
+            torch.cuda.empty_cache()
+            try:
+                line["workloads"] = extra_workloads(torch, fb, W, hbm_peak)
+            except Exception as exc:  # the headline number must still be printed
+                line["workloads"] = {"error": repr(exc)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the cpu_baseline leg and the other workloads")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
