@@ -226,35 +226,23 @@ def run_ours(args):
 
     topk, cap = 1000, NUM_BOXES * 80
     plan = fb.ops.YoloPostprocessPlan(BATCH, SIZES, topk, cap, device=dev)
-    st = torch.cuda.current_stream().cuda_stream
-    # stage buffers (the same carve-up the one-call entry point makes inside its scratch)
-    keys = torch.empty(BATCH, cap, dtype=torch.int64, device=dev)
-    counts = torch.empty(BATCH, dtype=torch.int32, device=dev)
-    sel_keys = torch.empty(BATCH, topk, dtype=torch.int64, device=dev)
-    sel_counts = torch.empty(BATCH, dtype=torch.int32, device=dev)
-    nms_scratch = torch.empty(int(lib.functs_b200_nms_scratch_bytes(BATCH, topk)), dtype=torch.uint8, device=dev)
     rec = torch.empty(BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
     rec_all = torch.empty(world * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev) if world > 1 else None
+    # per-step stage events, recorded inside the one-call entry point through its profiling hook
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    for row in ev:
+        for e in row:
+            e.record()  # materialises the CUDA event handle
+    torch.cuda.synchronize()
+    import ctypes
+    ev_handles = [(ctypes.c_void_p * 4)(*[e.cuda_event for e in row]) for row in ev]
 
-    def step(i, events=None):
-        m = sets[i % n_sets]
-        if events:
-            events[0].record()
-        check(lib.functs_b200_yolo_decode(m[0].data_ptr(), m[1].data_ptr(), m[2].data_ptr(), BATCH, *SIZES, 0.5,
-                                          plan.boxes.data_ptr(), None, None, keys.data_ptr(), counts.data_ptr(), cap,
-                                          plan.status.data_ptr(), st))
-        if events:
-            events[1].record()
-        check(lib.functs_b200_select_topk(keys.data_ptr(), counts.data_ptr(), cap, BATCH, topk, sel_keys.data_ptr(),
-                                          sel_counts.data_ptr(), st))
-        if events:
-            events[2].record()
-        check(lib.functs_b200_batched_nms(plan.boxes.data_ptr(), NUM_BOXES, 80, sel_keys.data_ptr(), sel_counts.data_ptr(),
-                                          BATCH, topk, 0.45, 1, plan.dets.data_ptr(), plan.labels.data_ptr(),
-                                          plan.flat_ids.data_ptr(), None, plan.counts.data_ptr(), nms_scratch.data_ptr(), st))
-        if events:
-            events[3].record()
+    def step(i, handles=None):
+        if handles is not None:
+            lib.functs_b200_set_stage_events(handles, 4)
+        plan.run(sets[i % n_sets], 0.5, 0.45)   # memset + decode/mask/compact + binned top-k + NMS: 3 kernels
+        if handles is not None:
+            lib.functs_b200_set_stage_events(None, 0)
         if world > 1:
             fdist.pack_detections(plan.dets, plan.labels, plan.flat_ids, plan.counts, out=rec)
             fdist.gather_records(rec, out=rec_all)
@@ -275,7 +263,7 @@ def run_ours(args):
     barrier()
     t_start.record()
     for i in range(args.steps):
-        step(i, ev[i])
+        step(i, ev_handles[i])
     t_end.record()
     barrier()
     launches = launch_count() - launches0
@@ -345,7 +333,7 @@ def run_ours(args):
             cpu_rate, cpu_ms, threads = cpu_oracle_rate(4, 3, 1)
             line["cpu_baseline"] = {"value": cpu_rate, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": "4 of the 64 images per step x 3 steps, TorchScript CPU oracle, rate scaled to 64-image batches"}
-            del sets, keys
+            del sets
             torch.cuda.empty_cache()
             try:
                 line["workloads"] = extra_workloads(torch, fb, W, hbm_peak)

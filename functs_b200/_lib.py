@@ -37,12 +37,16 @@ SIGNATURES = {
     "functs_b200_abi_version": (c_int32, []),
     "functs_b200_last_error": (c_char_p, []),
     "functs_b200_launch_count": (c_uint64, []),
+    "functs_b200_set_stage_events": (None, [POINTER(c_void_p), c_int32]),
     "functs_b200_rows_select_add_select_rev": (c_int32, [P, P, c_int64, c_int64, c_int64, c_float, P]),
-    "functs_b200_threshold_compact": (c_int32, [P, c_int32, c_int64, c_float, P, P, c_int64, c_int32, P, P]),
+    "functs_b200_hist_bins": (c_int32, []),
+    "functs_b200_threshold_compact": (c_int32, [P, c_int32, c_int64, c_float, P, P, c_int64, c_int32, P, P, P]),
+    "functs_b200_select_binned_scratch_bytes": (c_int64, [c_int32]),
+    "functs_b200_select_topk_binned": (c_int32, [P, P, c_int64, P, c_float, c_int32, c_int32, P, P, P, P]),
     "functs_b200_select_topk": (c_int32, [P, P, c_int64, c_int32, c_int32, P, P, P]),
     "functs_b200_nms_scratch_bytes": (c_int64, [c_int32, c_int32]),
     "functs_b200_batched_nms": (c_int32, [P, c_int64, c_int32, P, P, c_int32, c_int32, c_float, c_int32, P, P, P, P, P, P, P]),
-    "functs_b200_yolo_decode": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, P, P, P, P, P, c_int64, P, P]),
+    "functs_b200_yolo_decode": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, P, P, P, P, P, c_int64, P, P, P]),
     "functs_b200_yolo_scratch_bytes": (c_int64, [c_int32, c_int32, c_int32, c_int32, c_int64, c_int32]),
     "functs_b200_yolo_postprocess": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, c_float,
                                                c_int64, P, P, P, P, P, P, P, P]),
@@ -51,6 +55,7 @@ SIGNATURES = {
     "functs_b200_lstm_scratch_bytes": (c_int64, [c_int32, c_int32, c_int32, c_int32]),
     "functs_b200_lstm_forward": (c_int32, [P, P, P, P, P, c_int32, c_int32, c_int32, c_int32, P, P, P, P, P]),
     "functs_b200_lstm_forward_mode": (c_int32, [P, P, P, P, P, c_int32, c_int32, c_int32, c_int32, P, P, P, P, P, c_int32]),
+    "functs_b200_debug_set": (c_int32, [c_char_p, c_int32]),
     "functs_b200_yolact_masks": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, P, P, P]),
     "functs_b200_access": (c_int32, [P, P, POINTER(AccessDesc), c_int32, P]),
     "functs_b200_select_rev": (c_int32, [P, P, P, POINTER(c_int64), c_int32, c_int32, c_int64, c_int32, P]),
@@ -68,7 +73,7 @@ SIGNATURES = {
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m functs_b200.build` (needs nvcc with sm_100a support); "
+            f"{LIB_PATH} is missing: build it with `python functs_b200/build.py` (needs nvcc with sm_100a support); "
             "functs_b200 has no CPU or eager fallback")
     lib = ctypes.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():

@@ -28,6 +28,13 @@ int check_cuda(cudaError_t e, const char* what) {
     return FB_ERR_CUDA;
 }
 
+static thread_local cudaEvent_t g_stage_events[8];
+static thread_local int g_num_stage_events = 0;
+
+void record_stage_event(int index, cudaStream_t st) {
+    if (index >= 0 && index < g_num_stage_events && g_stage_events[index] != nullptr) cudaEventRecord(g_stage_events[index], st);
+}
+
 // ---- group registry -----------------------------------------------------------------------------------
 // A signature names the op sequence of a fusion group the way the group's subgraph prints it, outermost
 // structure first.  Argument conventions are listed per entry; pointers are device pointers.
@@ -51,7 +58,7 @@ static int g_yolo_decode(const void* const* in, const int64_t* ia, const double*
                                    static_cast<const float*>(in[2]), static_cast<int32_t>(ia[0]),
                                    static_cast<int32_t>(ia[1]), static_cast<int32_t>(ia[2]), static_cast<int32_t>(ia[3]),
                                    static_cast<float>(fa[0]), static_cast<float*>(out[0]), nullptr, nullptr,
-                                   static_cast<uint64_t*>(out[1]), static_cast<int32_t*>(out[2]), ia[4], status, stream);
+                                   static_cast<uint64_t*>(out[1]), static_cast<int32_t*>(out[2]), ia[4], nullptr, status, stream);
 }
 
 static int g_select_topk(const void* const* in, const int64_t* ia, const double*, void* const* out, void*, int32_t*,
@@ -136,6 +143,16 @@ extern "C" {
 int functs_b200_abi_version(void) { return 1; }
 const char* functs_b200_last_error(void) { return fb::g_error; }
 uint64_t functs_b200_launch_count(void) { return fb::g_launches.load(std::memory_order_relaxed); }
+
+void functs_b200_set_stage_events(void* const* events, int32_t count) {
+    if (events == nullptr || count <= 0) {
+        fb::g_num_stage_events = 0;
+        return;
+    }
+    if (count > 8) count = 8;
+    for (int i = 0; i < count; ++i) fb::g_stage_events[i] = static_cast<cudaEvent_t>(events[i]);
+    fb::g_num_stage_events = count;
+}
 
 int functs_b200_group_count(void) { return fb::kNumGroups; }
 

@@ -14,6 +14,8 @@ void count_launch(int n = 1);
 // Returns FB_OK, or records the CUDA error text and returns FB_ERR_CUDA.
 int check_cuda(cudaError_t e, const char* what);
 inline int check_launch(const char* what) { return check_cuda(cudaGetLastError(), what); }
+// Profiling hook: records the caller's event number `index` on `st` if functs_b200_set_stage_events armed one.
+void record_stage_event(int index, cudaStream_t st);
 
 #define FB_REQUIRE(cond, ...)                \
     do {                                     \

@@ -9,14 +9,15 @@
 //             applies the gate non-linearities and slice-assigns h and c straight into hs[t] / cs[t] — hs[t] is
 //             at the same time the buffer the other CTAs read h from in step t+1.  Steps are separated by a
 //             device-wide arrive/wait counter whose wait is bounded (status bit FB_STATUS_WAIT_TIMEOUT).
-#include <cooperative_groups.h>
+#include <cstring>
 
 #include "common.cuh"
 
 namespace fb {
 
 int launch_lstm_input_proj_tc(const float* x, const float* w_ih, const float* b_ih, const float* b_hh, int M, int K,
-                              int H, float* pre, void* tc_scratch, cudaStream_t st);  // kernels_lstm_tc.cu
+                              int H, float* pre, void* tc_scratch, int32_t* status, cudaStream_t st);  // kernels_lstm_tc.cu
+void lstm_tc_set_swap(int v);
 int64_t lstm_tc_scratch_bytes(int M, int K, int H);
 bool lstm_tc_supported(int M, int K, int H);
 
@@ -243,7 +244,7 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
     FB_TRY(check_cuda(cudaMemsetAsync(counter, 0, 256, st), "memset step counter"));
 
     if (mode == 0 && lstm_tc_supported(M, input, hidden)) {
-        FB_TRY(launch_lstm_input_proj_tc(x, w_ih, b_ih, b_hh, M, input, hidden, pre, tc_scratch, st));
+        FB_TRY(launch_lstm_input_proj_tc(x, w_ih, b_ih, b_hh, M, input, hidden, pre, tc_scratch, status, st));
     } else {
         dim3 grid(4 * hidden / kGemmBN, (M + kGemmBM - 1) / kGemmBM);
         lstm_input_proj_simt_kernel<<<grid, 256, 0, st>>>(x, w_ih, b_ih, b_hh, M, input, hidden, pre);
@@ -274,6 +275,15 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
     FB_TRY(check_cuda(cudaLaunchCooperativeKernel(kfn, rgrid, dim3(kRecThreads), args, smem, st), "lstm_recurrent launch"));
     count_launch();
     return check_launch("lstm_recurrent_kernel");
+}
+
+int functs_b200_debug_set(const char* name, int32_t value) {
+    if (name != nullptr && std::strcmp(name, "lstm_tc_swap_lbo_sbo") == 0) {
+        fb::lstm_tc_set_swap(value);
+        return FB_OK;
+    }
+    fb::set_error("debug_set: unknown switch");
+    return FB_ERR_NOT_FOUND;
 }
 
 int functs_b200_lstm_forward(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,

@@ -44,7 +44,8 @@ __device__ __forceinline__ void warp_stage_push(uint64_t* stage, int& fill, bool
 
 __global__ void __launch_bounds__(kCompactThreads)
 threshold_compact_kernel(const float* __restrict__ scores, int64_t n, float thr, uint64_t* __restrict__ keys,
-                         int32_t* __restrict__ counts, int64_t capacity, int32_t* status) {
+                         int32_t* __restrict__ counts, int64_t capacity, int32_t* status, int32_t* hist,
+                         uint32_t hist_base, int hist_shift) {
     __shared__ uint64_t stage_all[kCompactThreads / 32][kWarpStage];
     const int g = blockIdx.y;
     const int warp = threadIdx.x >> 5;
@@ -59,7 +60,9 @@ threshold_compact_kernel(const float* __restrict__ scores, int64_t n, float thr,
         int64_t i = start + static_cast<int64_t>(u) * kCompactThreads + threadIdx.x;
         float v = (i < n) ? s[i] : 0.0f;
         bool pred = (i < n) && (v > thr);
-        warp_stage_push(stage, fill, pred, make_key(v, static_cast<uint32_t>(i)));
+        const uint64_t key = make_key(v, static_cast<uint32_t>(i));
+        if (pred && hist != nullptr) atomicAdd(hist + static_cast<int64_t>(g) * kHistBins + hist_digit(key, hist_base, hist_shift), 1);
+        warp_stage_push(stage, fill, pred, key);
         if (fill + 32 > kWarpStage) warp_stage_flush(stage, fill, gkeys, counts + g, capacity, status);
     }
     warp_stage_flush(stage, fill, gkeys, counts + g, capacity, status);
@@ -91,41 +94,182 @@ select_topk_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restri
     if (threadIdx.x == 0) out_counts[g] = m;
 }
 
-// ---- NMS: suppression bit matrix (many CTAs per group) + serial scan (one CTA per group) ---------
-// Both kernels rebuild the same NMS-space boxes from the selected keys: gather the box of every selected
-// candidate, take the maximum coordinate over them, shift each box by label * (max + 1).
+// ---- binned top-k: many CTAs per group collect, the last one to finish sorts --------------------------------
+// Needs the coarse score histogram that the candidate producer filled (hist[g][kHistBins]).  Every CTA finds the
+// boundary bucket d* (the largest d with count(digit >= d) >= topk), scans its share of the candidate list and
+// appends keys above d* to the group's `sel` list and keys inside d* to its `bin` list.  CTAs then take a ticket;
+// the one that draws the last ticket sorts the bin list, tops `sel` up from it and writes the sorted result.
+// No CTA ever waits for another one.
+constexpr int kBinThreads = 256;
+constexpr int kBinSplit = 16;        // CTAs per group
+constexpr int kBinListGlobal = 2048; // capacity of the boundary-bucket list; beyond it the generic selection runs
+
+struct SelectCtr {
+    int32_t sel_cnt, bin_cnt, ticket, pad;
+};
+
+union BinnedSmem {
+    SelectSmem<kSelCap> generic;
+    struct {
+        uint64_t sel[kSelCap];
+        uint64_t bin[kBinListGlobal];
+    } fast;
+};
+
+__global__ void __launch_bounds__(kBinThreads)
+select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restrict__ in_counts, int64_t capacity,
+                     const int32_t* __restrict__ hist, uint32_t hist_base, int hist_shift, int32_t topk,
+                     SelectCtr* ctr, uint64_t* sel_tmp, uint64_t* bin_tmp, uint64_t* __restrict__ out_keys,
+                     int32_t* __restrict__ out_counts) {
+    __shared__ __align__(16) BinnedSmem sm;
+    __shared__ int s_dstar, s_above, s_inbin, s_last;
+    const int g = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int64_t cnt64 = in_counts[g];
+    if (cnt64 > capacity) cnt64 = capacity;
+    if (cnt64 < 0) cnt64 = 0;
+    const int n = static_cast<int>(cnt64);
+    const uint64_t* keys = in_keys + static_cast<int64_t>(g) * capacity;
+    if (tid == 0) {
+        s_dstar = -1;  // n <= topk: everything is "above"
+        s_above = n;
+        s_inbin = 0;
+    }
+    __syncthreads();
+    if (n > topk && warp == 0) {
+        const int32_t* h = hist + static_cast<int64_t>(g) * kHistBins;
+        constexpr int per = kHistBins / 32;
+        const int lo = lane * per, hi = lo + per;
+        int s = 0;
+        for (int i = lo; i < hi; ++i) s += __ldcg(h + i);
+        int incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int t = __shfl_down_sync(kFullMask, incl, o);
+            if (lane + o < 32) incl += t;
+        }
+        const int suf = incl - s;
+        if (suf < topk && incl >= topk) {
+            int cum = suf, d = hi - 1;
+            for (; d >= lo; --d) {
+                int c = __ldcg(h + d);
+                if (cum + c >= topk) break;
+                cum += c;
+            }
+            s_dstar = d;
+            s_above = cum;
+            s_inbin = __ldcg(h + d);
+        }
+    }
+    __syncthreads();
+    const int dstar = s_dstar;
+    SelectCtr* c = ctr + g;
+    uint64_t* gsel = sel_tmp + static_cast<int64_t>(g) * kSelCap;
+    uint64_t* gbin = bin_tmp + static_cast<int64_t>(g) * kBinListGlobal;
+    {
+        const int lo = static_cast<int>(static_cast<int64_t>(n) * blockIdx.x / gridDim.x);
+        const int hi = static_cast<int>(static_cast<int64_t>(n) * (blockIdx.x + 1) / gridDim.x);
+        for (int base = lo; base < hi; base += kBinThreads * 4) {
+            uint64_t k[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * kBinThreads + tid;
+                k[u] = (i < hi) ? __ldg(keys + i) : 0ull;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int d = (k[u] != 0ull) ? hist_digit(k[u], hist_base, hist_shift) : -2;
+                const bool is_sel = d > dstar;
+                const bool is_bin = (d == dstar);
+                const unsigned ms = __ballot_sync(kFullMask, is_sel);
+                const unsigned mb = __ballot_sync(kFullMask, is_bin);
+                if (ms) {
+                    int b0 = 0;
+                    if (lane == 0) b0 = atomicAdd(&c->sel_cnt, __popc(ms));
+                    b0 = __shfl_sync(kFullMask, b0, 0);
+                    if (is_sel) {
+                        const int pos = b0 + __popc(ms & ((1u << lane) - 1u));
+                        if (pos < kSelCap) gsel[pos] = k[u];
+                    }
+                }
+                if (mb) {
+                    int b0 = 0;
+                    if (lane == 0) b0 = atomicAdd(&c->bin_cnt, __popc(mb));
+                    b0 = __shfl_sync(kFullMask, b0, 0);
+                    if (is_bin) {
+                        const int pos = b0 + __popc(mb & ((1u << lane) - 1u));
+                        if (pos < kBinListGlobal) gbin[pos] = k[u];
+                    }
+                }
+            }
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&c->ticket, 1) == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    // ---- the last CTA of the group finishes the selection ----
+    const int sel_cnt = *reinterpret_cast<volatile int32_t*>(&c->sel_cnt);
+    const int bin_cnt = *reinterpret_cast<volatile int32_t*>(&c->bin_cnt);
+    const int result = n < topk ? n : topk;
+    const bool consistent = (n <= topk) ? (sel_cnt == n && sel_cnt <= kSelCap)
+                                        : (sel_cnt == s_above && bin_cnt == s_inbin && sel_cnt < topk &&
+                                           sel_cnt + bin_cnt >= topk && bin_cnt <= kBinListGlobal);
+    if (!consistent) {
+        // the boundary bucket is too crowded (many equal scores) or the histogram does not describe this list:
+        // exact generic selection over the whole list
+        GlobalKeys kf{keys};
+        const int m = block_select_topk<kBinThreads, kSelCap, 4>(kf, n, topk, sm.generic);
+        __syncthreads();
+        for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < m) ? sm.generic.sel[i] : 0ull;
+        if (tid == 0) out_counts[g] = m;
+        return;
+    }
+    for (int i = tid; i < sel_cnt; i += kBinThreads) sm.fast.sel[i] = __ldcg(gsel + i);
+    if (n > topk) {
+        const int bn = next_pow2(bin_cnt);
+        for (int i = tid; i < bn; i += kBinThreads) sm.fast.bin[i] = (i < bin_cnt) ? __ldcg(gbin + i) : 0ull;
+        __syncthreads();
+        bitonic_sort_desc<kBinThreads>(sm.fast.bin, bn);
+        const int want = topk - sel_cnt;
+        for (int i = tid; i < want; i += kBinThreads) sm.fast.sel[sel_cnt + i] = sm.fast.bin[i];
+    }
+    const int sn = next_pow2(result);
+    for (int i = result + tid; i < sn; i += kBinThreads) sm.fast.sel[i] = 0ull;
+    __syncthreads();
+    bitonic_sort_desc<kBinThreads>(sm.fast.sel, sn);
+    for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < result) ? sm.fast.sel[i] : 0ull;
+    if (tid == 0) out_counts[g] = result;
+}
+
+// ---- NMS: suppression bit matrix by several CTAs per group, serial scan by the last one to finish ------------
+// Every CTA rebuilds the NMS-space boxes from the selected keys (gather the box of every selected candidate, take
+// the maximum coordinate over them, shift each box by label * (max + 1)), computes its interleaved share of the
+// rows of the bit matrix into global memory and takes a ticket; the CTA with the last ticket stages the matrix
+// in shared memory, runs the serial keep-scan with one warp and writes the compacted outputs.
 constexpr int kNmsThreads = 1024;
 constexpr int kNmsMaxN = 1024;
 constexpr int kNmsWords = kNmsMaxN / 32;
-
-struct NmsGather {
-    float4 raw;  // un-shifted box
-    float score;
-    int label;
-    uint32_t flat;
-};
+constexpr int kNmsRowsPerCta = 128;
 
 // Every thread t < n gathers candidate t; the block computes the maximum coordinate; returns the shifted box.
 __device__ __forceinline__ NmsBox gather_nms_box(const float* __restrict__ boxes_g, const uint64_t* __restrict__ sel,
-                                                  int n, int num_classes, int class_offset, float* red /*[33]*/,
-                                                  NmsGather& out) {
+                                                  int n, int num_classes, int class_offset, float* red /*[33]*/) {
     const int t = threadIdx.x;
     float4 bx = make_float4(0.f, 0.f, 0.f, 0.f);
-    out.score = 0.f;
-    out.label = 0;
-    out.flat = 0;
+    int label = 0;
     float lmax = -INFINITY;
     if (t < n) {
-        uint64_t k = sel[t];
-        uint32_t flat = key_index(k);
-        uint32_t box = flat / static_cast<uint32_t>(num_classes);
-        out.flat = flat;
-        out.label = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
-        out.score = key_score(k);
+        const uint64_t k = sel[t];
+        const uint32_t flat = key_index(k);
+        const uint32_t box = flat / static_cast<uint32_t>(num_classes);
+        label = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
         bx = reinterpret_cast<const float4*>(boxes_g)[box];
         lmax = fmaxf(fmaxf(bx.x, bx.y), fmaxf(bx.z, bx.w));
     }
-    out.raw = bx;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
     if ((t & 31) == 0) red[t >> 5] = lmax;
@@ -138,68 +282,66 @@ __device__ __forceinline__ NmsBox gather_nms_box(const float* __restrict__ boxes
     }
     __syncthreads();
     float off = 0.0f;
-    if (class_offset) off = __fmul_rn(static_cast<float>(out.label), __fadd_rn(red[32], 1.0f));
+    if (class_offset) off = __fmul_rn(static_cast<float>(label), __fadd_rn(red[32], 1.0f));
     return make_nms_box(__fadd_rn(bx.x, off), __fadd_rn(bx.y, off), __fadd_rn(bx.z, off), __fadd_rn(bx.w, off));
 }
 
-// grid = (row tiles of 32 rows, groups); block = 1024 threads = 32 warps, one row of the bit matrix per warp.
+// grid = (ceil(topk / 128), groups); block = 1024; dynamic smem = 1024 x 32 words (used by the last CTA).
 __global__ void __launch_bounds__(kNmsThreads)
-nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
-                const int32_t* __restrict__ sel_counts, int topk, float thr, float thr_lo, float thr_hi,
-                int class_offset, uint32_t* __restrict__ mask_out) {
+nms_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
+           const int32_t* __restrict__ sel_counts, int topk, float thr, float thr_lo, float thr_hi, int class_offset,
+           uint32_t* mask_g, int32_t* tickets, float* __restrict__ dets, int64_t* __restrict__ labels,
+           int64_t* __restrict__ flat_ids, int64_t* __restrict__ keep, int32_t* __restrict__ out_counts) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint32_t* smask = reinterpret_cast<uint32_t*>(smem_raw);  // [n][32], last CTA only
     __shared__ NmsBox sb[kNmsMaxN];
     __shared__ float red[33];
-    const int g = blockIdx.y;
-    int n = sel_counts[g];
-    if (n > topk) n = topk;
-    const int row0 = blockIdx.x * 32;
-    if (row0 >= n) return;
-    NmsGather gth;
-    NmsBox mine = gather_nms_box(boxes + static_cast<int64_t>(g) * num_boxes * 4, sel_keys + static_cast<int64_t>(g) * topk,
-                                 n, num_classes, class_offset, red, gth);
-    sb[threadIdx.x] = mine;
-    __syncthreads();
-    // warp r owns row row0 + r; lane b tests box 32w + b, so consecutive lanes read consecutive boxes
-    const int r = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int i = row0 + r;
-    const int words = (n + 31) >> 5;
-    uint32_t bits = 0u;
-    if (i < n) {
-        const NmsBox bi = sb[i];
-        for (int w = i >> 5; w < words; ++w) {
-            const int j = w * 32 + lane;
-            bool pred = false;
-            if (j > i && j < n) pred = iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi);
-            unsigned m = __ballot_sync(kFullMask, pred);
-            if (lane == w) bits = m;
-        }
-        mask_out[(static_cast<int64_t>(g) * kNmsMaxN + i) * kNmsWords + lane] = bits;
-    }
-}
-
-// grid = groups; block = 1024.  Stages the group's bit matrix in shared memory, one warp scans, all threads
-// write the compacted outputs.
-__global__ void __launch_bounds__(kNmsThreads)
-nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
-                const int32_t* __restrict__ sel_counts, int topk, const uint32_t* __restrict__ mask_in,
-                float* __restrict__ dets, int64_t* __restrict__ labels, int64_t* __restrict__ flat_ids,
-                int64_t* __restrict__ keep, int32_t* __restrict__ out_counts) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t* smask = reinterpret_cast<uint32_t*>(smem_raw);  // [n][32]
     __shared__ uint32_t keep_words[kNmsWords];
     __shared__ int word_prefix[kNmsWords + 1];
-    const int g = blockIdx.x;
+    __shared__ int s_last;
+    const int g = blockIdx.y;
     const int t = threadIdx.x;
+    const int lane = t & 31, warp = t >> 5;
     int n = sel_counts[g];
     if (n > topk) n = topk;
+    if (n < 0) n = 0;
     const int words = (n + 31) >> 5;
-    // stage rows [0, n) (row stride 32 words), 16 bytes per thread per step
+    const float* boxes_g = boxes + static_cast<int64_t>(g) * num_boxes * 4;
+    const uint64_t* sel = sel_keys + static_cast<int64_t>(g) * topk;
+    uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
+    const int rt = gridDim.x;
+
+    if (static_cast<int>(blockIdx.x) < n) {  // this CTA owns at least one row (rows are interleaved: i = k * rt + blockIdx.x)
+        sb[t] = gather_nms_box(boxes_g, sel, n, num_classes, class_offset, red);
+        __syncthreads();
+        for (int rr = 0; rr < kNmsRowsPerCta / 32; ++rr) {
+            const int i = (warp * (kNmsRowsPerCta / 32) + rr) * rt + blockIdx.x;
+            if (i >= n) continue;  // warp-uniform
+            const NmsBox bi = sb[i];
+            uint32_t bits = 0u;
+            for (int w = i >> 5; w < words; ++w) {
+                const int j = w * 32 + lane;
+                bool pred = false;
+                if (j > i && j < n) pred = iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi);
+                const unsigned m = __ballot_sync(kFullMask, pred);
+                if (lane == w) bits = m;
+            }
+            gmask[i * kNmsWords + lane] = bits;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (t == 0) s_last = (atomicAdd(tickets + g, 1) == rt - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    // ---- last CTA of the group: stage the matrix, scan, write ----
     {
-        const uint4* src = reinterpret_cast<const uint4*>(mask_in + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords);
+        const uint4* src = reinterpret_cast<const uint4*>(gmask);
         uint4* dst = reinterpret_cast<uint4*>(smask);
         const int total = n * (kNmsWords / 4);
-        for (int i = t; i < total; i += kNmsThreads) dst[i] = src[i];
+        for (int i = t; i < total; i += kNmsThreads) dst[i] = __ldcg(src + i);
     }
     if (t < kNmsWords) keep_words[t] = 0u;
     __syncthreads();
@@ -217,14 +359,14 @@ nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
     __syncthreads();
     const int64_t obase = static_cast<int64_t>(g) * topk;
     if (t < n) {
-        uint32_t kw = keep_words[t >> 5];
-        int b = t & 31;
+        const uint32_t kw = keep_words[t >> 5];
+        const int b = t & 31;
         if ((kw >> b) & 1u) {
-            int rank = word_prefix[t >> 5] + __popc(kw & ((1u << b) - 1u));
-            uint64_t k = sel_keys[obase + t];
-            uint32_t flat = key_index(k);
-            uint32_t box = flat / static_cast<uint32_t>(num_classes);
-            float4 bx = reinterpret_cast<const float4*>(boxes + static_cast<int64_t>(g) * num_boxes * 4)[box];
+            const int rank = word_prefix[t >> 5] + __popc(kw & ((1u << b) - 1u));
+            const uint64_t k = sel[t];
+            const uint32_t flat = key_index(k);
+            const uint32_t box = flat / static_cast<uint32_t>(num_classes);
+            const float4 bx = reinterpret_cast<const float4*>(boxes_g)[box];
             float* d = dets + (obase + rank) * 5;
             d[0] = bx.x;
             d[1] = bx.y;
@@ -249,13 +391,20 @@ nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
 
 // ---- host launchers (internal C++ API, used by the C ABI and by the YOLO pipeline) ----------------
 int launch_threshold_compact(const float* scores, int groups, int64_t n, float thr, uint64_t* keys, int32_t* counts,
-                             int64_t capacity, int zero_counts, int32_t* status, cudaStream_t st) {
+                             int64_t capacity, int zero_counts, int32_t* hist, int32_t* status, cudaStream_t st) {
     FB_REQUIRE(scores && keys && counts, "threshold_compact: null pointer");
     FB_REQUIRE(groups > 0 && groups <= 65535 && n > 0 && n < (1ll << 32) && capacity > 0, "threshold_compact: bad sizes");
-    if (zero_counts) FB_TRY(check_cuda(cudaMemsetAsync(counts, 0, sizeof(int32_t) * groups, st), "memset counts"));
+    FB_REQUIRE(thr > 0.0f, "threshold_compact: the threshold must be positive (keys need positive scores)");
+    if (zero_counts) {
+        FB_TRY(check_cuda(cudaMemsetAsync(counts, 0, sizeof(int32_t) * groups, st), "memset counts"));
+        if (hist != nullptr)
+            FB_TRY(check_cuda(cudaMemsetAsync(hist, 0, sizeof(int32_t) * groups * kHistBins, st), "memset hist"));
+    }
+    const HistParams hp = hist_params_for(thr);
     const int64_t chunk = static_cast<int64_t>(kCompactThreads) * kCompactPerThread;
     dim3 grid(static_cast<unsigned>((n + chunk - 1) / chunk), groups);
-    threshold_compact_kernel<<<grid, kCompactThreads, 0, st>>>(scores, n, thr, keys, counts, capacity, status);
+    threshold_compact_kernel<<<grid, kCompactThreads, 0, st>>>(scores, n, thr, keys, counts, capacity, status, hist, hp.base,
+                                                               hp.shift);
     count_launch();
     return check_launch("threshold_compact_kernel");
 }
@@ -274,37 +423,61 @@ int launch_select_topk(const uint64_t* in_keys, const int32_t* in_counts, int64_
     return check_launch("select_topk_kernel");
 }
 
-int64_t nms_scratch_bytes(int groups, int topk) {
-    (void)topk;
-    return static_cast<int64_t>(groups) * kNmsMaxN * kNmsWords * sizeof(uint32_t);
+// Work area of the binned selection: [SelectCtr x groups (padded to 256 B)][sel lists][bin lists].
+int64_t select_binned_ctr_bytes(int groups) { return (static_cast<int64_t>(groups) * sizeof(SelectCtr) + 255) / 256 * 256; }
+int64_t select_binned_lists_bytes(int groups) {
+    return static_cast<int64_t>(groups) * (kSelCap + kBinListGlobal) * sizeof(uint64_t);
 }
 
+// ctr must be zero when the kernel starts (zero_ctr != 0 makes this call clear it).
+int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, const int32_t* hist,
+                         float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
+                         void* lists, int zero_ctr, cudaStream_t st) {
+    FB_REQUIRE(in_keys && in_counts && hist && out_keys && out_counts && ctr && lists, "select_topk_binned: null pointer");
+    FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kSelCap && capacity > 0 && capacity < (1ll << 31),
+               "select_topk_binned: bad sizes (topk must be in [1, %d])", kSelCap);
+    FB_REQUIRE(thr > 0.0f, "select_topk_binned: the threshold must be positive");
+    if (zero_ctr) FB_TRY(check_cuda(cudaMemsetAsync(ctr, 0, select_binned_ctr_bytes(groups), st), "memset select counters"));
+    const HistParams hp = hist_params_for(thr);
+    uint64_t* sel_tmp = static_cast<uint64_t*>(lists);
+    uint64_t* bin_tmp = sel_tmp + static_cast<int64_t>(groups) * kSelCap;
+    dim3 grid(kBinSplit, groups);
+    select_binned_kernel<<<grid, kBinThreads, 0, st>>>(in_keys, in_counts, capacity, hist, hp.base, hp.shift, topk,
+                                                       static_cast<SelectCtr*>(ctr), sel_tmp, bin_tmp, out_keys, out_counts);
+    count_launch();
+    return check_launch("select_binned_kernel");
+}
+
+int64_t nms_mask_bytes(int groups) { return static_cast<int64_t>(groups) * kNmsMaxN * kNmsWords * sizeof(uint32_t); }
+int64_t nms_ticket_bytes(int groups) { return (static_cast<int64_t>(groups) * sizeof(int32_t) + 255) / 256 * 256; }
+int64_t nms_scratch_bytes(int groups, int topk) {
+    (void)topk;
+    return nms_mask_bytes(groups) + nms_ticket_bytes(groups);
+}
+
+// tickets must be zero when the kernel starts (zero_tickets != 0 makes this call clear them).
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
-                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* scratch,
-                       cudaStream_t st) {
-    FB_REQUIRE(boxes && sel_keys && sel_counts && dets && labels && flat_ids && out_counts && scratch,
+                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask,
+                       void* tickets, int zero_tickets, cudaStream_t st) {
+    FB_REQUIRE(boxes && sel_keys && sel_counts && dets && labels && flat_ids && out_counts && mask && tickets,
                "batched_nms: null pointer");
     FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kNmsMaxN && num_classes > 0 && num_boxes > 0,
                "batched_nms: bad sizes (topk must be in [1, %d])", kNmsMaxN);
     FB_REQUIRE(iou_thr > 0.0f && iou_thr < 1.0f, "batched_nms: iou threshold must be in (0, 1)");
-    FB_REQUIRE((reinterpret_cast<uintptr_t>(boxes) & 15) == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0,
+    FB_REQUIRE((reinterpret_cast<uintptr_t>(boxes) & 15) == 0 && (reinterpret_cast<uintptr_t>(mask) & 15) == 0,
                "batched_nms: boxes and scratch must be 16-byte aligned");
+    if (zero_tickets) FB_TRY(check_cuda(cudaMemsetAsync(tickets, 0, nms_ticket_bytes(groups), st), "memset nms tickets"));
     const float thr_lo = iou_thr * (1.0f - 1.0e-6f), thr_hi = iou_thr * (1.0f + 1.0e-6f);
-    uint32_t* mask = static_cast<uint32_t*>(scratch);
-    dim3 grid((topk + 31) / 32, groups);
-    nms_mask_kernel<<<grid, kNmsThreads, 0, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk, iou_thr,
-                                                  thr_lo, thr_hi, class_offset, mask);
-    count_launch();
-    FB_TRY(check_launch("nms_mask_kernel"));
     const size_t smem = static_cast<size_t>(kNmsMaxN) * kNmsWords * sizeof(uint32_t);
-    FB_TRY(check_cuda(cudaFuncSetAttribute(nms_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem)),
-                      "nms_scan attr"));
-    nms_scan_kernel<<<groups, kNmsThreads, smem, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk, mask,
-                                                       dets, labels, flat_ids, keep, out_counts);
+    FB_TRY(check_cuda(cudaFuncSetAttribute(nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                      "nms attr"));
+    dim3 grid((topk + kNmsRowsPerCta - 1) / kNmsRowsPerCta, groups);
+    nms_kernel<<<grid, kNmsThreads, smem, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk, iou_thr, thr_lo,
+                                                thr_hi, class_offset, static_cast<uint32_t*>(mask),
+                                                static_cast<int32_t*>(tickets), dets, labels, flat_ids, keep, out_counts);
     count_launch();
-    return check_launch("nms_scan_kernel");
+    return check_launch("nms_kernel");
 }
 
 }  // namespace fb
@@ -313,9 +486,9 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
 extern "C" {
 
 int functs_b200_threshold_compact(const float* scores, int32_t groups, int64_t n, float thr, uint64_t* keys,
-                                  int32_t* counts, int64_t capacity, int32_t zero_counts, int32_t* status,
-                                  void* stream) {
-    return fb::launch_threshold_compact(scores, groups, n, thr, keys, counts, capacity, zero_counts, status,
+                                  int32_t* counts, int64_t capacity, int32_t zero_counts, int32_t* hist,
+                                  int32_t* status, void* stream) {
+    return fb::launch_threshold_compact(scores, groups, n, thr, keys, counts, capacity, zero_counts, hist, status,
                                         fb::as_stream(stream));
 }
 
@@ -325,15 +498,42 @@ int functs_b200_select_topk(const uint64_t* in_keys, const int32_t* in_counts, i
                                   fb::as_stream(stream));
 }
 
-int64_t functs_b200_nms_scratch_bytes(int32_t groups, int32_t topk) { return fb::nms_scratch_bytes(groups, topk); }
+int32_t functs_b200_hist_bins(void) { return fb::kHistBins; }
+
+int64_t functs_b200_select_binned_scratch_bytes(int32_t groups) {
+    if (groups <= 0) return 0;
+    return fb::select_binned_ctr_bytes(groups) + fb::select_binned_lists_bytes(groups);
+}
+
+int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity,
+                                   const int32_t* hist, float thr, int32_t groups, int32_t topk, uint64_t* out_keys,
+                                   int32_t* out_counts, void* scratch, void* stream) {
+    if (scratch == nullptr || (reinterpret_cast<uintptr_t>(scratch) & 255) != 0) {
+        fb::set_error("select_topk_binned: scratch must be non-null and 256-byte aligned");
+        return FB_ERR_INVALID_ARGUMENT;
+    }
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    return fb::launch_select_binned(in_keys, in_counts, capacity, hist, thr, groups, topk, out_keys, out_counts, base,
+                                    base + fb::select_binned_ctr_bytes(groups > 0 ? groups : 1), 1, fb::as_stream(stream));
+}
+
+int64_t functs_b200_nms_scratch_bytes(int32_t groups, int32_t topk) {
+    if (groups <= 0) return 0;
+    return fb::nms_scratch_bytes(groups, topk);
+}
 
 int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_classes, const uint64_t* sel_keys,
                             const int32_t* sel_counts, int32_t groups, int32_t topk, float iou_thr,
                             int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids, int64_t* keep,
                             int32_t* out_counts, void* scratch, void* stream) {
+    if (scratch == nullptr || groups <= 0) {
+        fb::set_error("batched_nms: null scratch or bad group count");
+        return FB_ERR_INVALID_ARGUMENT;
+    }
+    unsigned char* base = static_cast<unsigned char*>(scratch);
     return fb::launch_batched_nms(boxes, num_boxes, num_classes, sel_keys, sel_counts, groups, topk, iou_thr,
-                                  class_offset, dets, labels, flat_ids, keep, out_counts, scratch,
-                                  fb::as_stream(stream));
+                                  class_offset, dets, labels, flat_ids, keep, out_counts, base,
+                                  base + fb::nms_mask_bytes(groups), 1, fb::as_stream(stream));
 }
 
 }  // extern "C"

@@ -107,8 +107,9 @@ struct SmemScores {
 // dynamic smem: [num_priors floats (padded to 16 B)][SelectSmem<256>][NmsBox[256]][mask 256 x 8 words]
 __global__ void __launch_bounds__(kSsdNmsThreads)
 ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ scores_cm, int num_priors, int num_classes,
-                     float score_thr, int topk, float iou_thr, float thr_lo, float thr_hi, float* __restrict__ dets,
-                     int64_t* __restrict__ prior_ids, int32_t* __restrict__ out_counts) {
+                     float score_thr, uint32_t hist_base, int hist_shift, int topk, float iou_thr, float thr_lo,
+                     float thr_hi, float* __restrict__ dets, int64_t* __restrict__ prior_ids,
+                     int32_t* __restrict__ out_counts) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const size_t sc_bytes = (static_cast<size_t>(num_priors) * 4 + 15) / 16 * 16;
     float* sc = reinterpret_cast<float*>(smem_raw);
@@ -131,7 +132,7 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     __syncthreads();
 
     SmemScores kf{sc, score_thr};
-    const int n = block_select_topk<kSsdNmsThreads, kSsdSelCap, 4>(kf, num_priors, topk, sm);
+    const int n = block_select_topk_binned<kSsdNmsThreads, kSsdSelCap, 4>(kf, num_priors, topk, hist_base, hist_shift, sm);
     // (block_select_topk ends with a barrier when n > 1; make the hand-over explicit)
     __syncthreads();
 
@@ -246,9 +247,10 @@ int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_
                       "ssd_class_nms attr"));
     const float thr_lo = iou_thr * (1.0f - 1.0e-6f), thr_hi = iou_thr * (1.0f + 1.0e-6f);
     dim3 grid(num_classes, batch);
+    const HistParams hp = hist_params_for(score_thr);
     ssd_class_nms_kernel<<<grid, kSsdNmsThreads, smem, as_stream(stream)>>>(boxes, scores_cm, num_priors, num_classes,
-                                                                            score_thr, topk, iou_thr, thr_lo, thr_hi,
-                                                                            dets, prior_ids, out_counts);
+                                                                            score_thr, hp.base, hp.shift, topk, iou_thr,
+                                                                            thr_lo, thr_hi, dets, prior_ids, out_counts);
     count_launch();
     return check_launch("ssd_class_nms_kernel");
 }

@@ -9,19 +9,25 @@
 
 namespace fb {
 
-int launch_select_topk(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, int groups, int topk,
-                       uint64_t* out_keys, int32_t* out_counts, cudaStream_t st);
-int64_t nms_scratch_bytes(int groups, int topk);
+int64_t select_binned_ctr_bytes(int groups);
+int64_t select_binned_lists_bytes(int groups);
+int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, const int32_t* hist,
+                         float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
+                         void* lists, int zero_ctr, cudaStream_t st);
+int64_t nms_mask_bytes(int groups);
+int64_t nms_ticket_bytes(int groups);
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
-                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* scratch,
-                       cudaStream_t st);
+                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask,
+                       void* tickets, int zero_tickets, cudaStream_t st);
 
 constexpr int kYoloThreads = 128;
 constexpr int kYoloClasses = 80;
 constexpr int kYoloAttrib = 85;
-constexpr int kYoloChunk = 16;     // class logits loaded per thread before any is consumed
-constexpr int kYoloWarpStage = 160;
+constexpr int kYoloChunk = 16;      // class logits loaded per thread before any is consumed
+constexpr int kYoloSub = 8;         // classes whose hits are queued at once (bounds the queue)
+constexpr int kYoloWarpStage = 160; // staged candidate keys per warp
+constexpr int kYoloQueue = 32 + 32 * kYoloSub;  // pending (logit, lane, class) entries per warp
 
 struct YoloParams {
     const float* map[3];
@@ -42,12 +48,63 @@ struct YoloParams {
     int32_t* counts;
     int64_t capacity;
     int32_t* status;
+    int32_t* hist;       // optional [batch][kHistBins] histogram of candidate scores (for the binned top-k), or null
+    uint32_t hist_base;  // float bits of the score threshold
+    int hist_shift;
 };
+
+struct YoloWarpSmem {
+    uint64_t stage[kYoloWarpStage];
+    float qv[kYoloQueue];
+    uint32_t qmeta[kYoloQueue];  // lane << 8 | class
+};
+
+// Appends the staged keys of a warp to the image's candidate list (one atomic per flush).
+__device__ __forceinline__ void yolo_flush(YoloWarpSmem& ws, int& fill, uint64_t* gkeys, int32_t* gcount, int64_t capacity,
+                                           int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();
+    int base = 0;
+    if (lane == 0) base = atomicAdd(gcount, fill);
+    base = __shfl_sync(kFullMask, base, 0);
+    for (int i = lane; i < fill; i += 32) {
+        const int64_t pos = static_cast<int64_t>(base) + i;
+        if (pos < capacity) gkeys[pos] = ws.stage[i];
+        else if (status != nullptr) atomicOr(status, FB_STATUS_CAND_OVERFLOW);
+    }
+    __syncwarp();
+    fill = 0;
+}
+
+// One dense batch: lane i evaluates queue entry i (nb <= 32 entries), hits go to the staging buffer.
+__device__ __forceinline__ void yolo_eval_batch(YoloWarpSmem& ws, int head, int nb, float so, uint32_t flat0,
+                                                const YoloParams& P, int img, int& fill, uint64_t* gkeys,
+                                                int32_t* gcount) {
+    const int lane = threadIdx.x & 31;
+    const bool act = lane < nb;
+    const float v = act ? ws.qv[head + lane] : 0.0f;
+    const uint32_t meta = act ? ws.qmeta[head + lane] : 0u;
+    const float so_src = __shfl_sync(kFullMask, so, static_cast<int>(meta >> 8));
+    const uint32_t flat_src = __shfl_sync(kFullMask, flat0, static_cast<int>(meta >> 8));
+    const float s = __fmul_rn(so_src, sigmoid_f32(v));
+    const bool pred = act && (s > P.thr);
+    const unsigned m = __ballot_sync(kFullMask, pred);
+    if (pred) {
+        const int off = __popc(m & ((1u << lane) - 1u));
+        ws.stage[fill + off] = make_key(s, flat_src + (meta & 255u));
+        if (P.hist != nullptr) {
+            const int d = hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift);
+            atomicAdd(P.hist + static_cast<int64_t>(img) * kHistBins + d, 1);
+        }
+    }
+    fill += __popc(m);
+    if (fill + 32 > kYoloWarpStage) yolo_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+}
 
 template <bool DENSE>
 __global__ void __launch_bounds__(kYoloThreads)
 yolo_decode_kernel(const YoloParams P) {
-    __shared__ uint64_t stage_all[kYoloThreads / 32][kYoloWarpStage];
+    __shared__ YoloWarpSmem smem_all[kYoloThreads / 32];
     const int cta = blockIdx.x;
     const int lvl = (cta >= P.tile_begin[2]) ? 2 : (cta >= P.tile_begin[1] ? 1 : 0);
     const int local = cta - P.tile_begin[lvl];
@@ -60,6 +117,7 @@ yolo_decode_kernel(const YoloParams P) {
     const int p = tile * kYoloThreads + threadIdx.x;
     const bool valid = p < SS;
     const int pp = valid ? p : (SS - 1);  // clamp so that every lane loads a legal address
+    const int lane = threadIdx.x & 31;
     const float* __restrict__ src = P.map[lvl] + (static_cast<int64_t>(img) * 255 + anc * kYoloAttrib) * SS + pp;
 
     const float t0 = __ldg(src);
@@ -67,6 +125,10 @@ yolo_decode_kernel(const YoloParams P) {
     const float t2 = __ldg(src + 2 * SS);
     const float t3 = __ldg(src + 3 * SS);
     const float t4 = __ldg(src + 4 * SS);
+    const float* __restrict__ csrc = src + 5 * static_cast<int64_t>(SS);
+    float v[kYoloChunk];
+#pragma unroll
+    for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + static_cast<int64_t>(u) * SS);
 
     const int gy = pp / S, gx = pp - gy * S;
     const float stride = P.stride[lvl];
@@ -83,67 +145,88 @@ yolo_decode_kernel(const YoloParams P) {
         if (DENSE && P.obj_out != nullptr) P.obj_out[gbox] = so;
     }
 
-    // A product of two sigmoids (each <= 1) can exceed thr >= 0.5 only if both logits are positive.
-    const bool shortcut = P.thr >= 0.5f;
-    const bool obj_ok = valid && (!shortcut || t4 > 0.0f);
-    uint64_t* stage = stage_all[threadIdx.x >> 5];
-    int fill = 0;
+    // Logit cut: score = so * sigmoid(v) can exceed thr only if sigmoid(v) > thr / so.  The cut is placed a
+    // relative 1e-5 below that (hundreds of fp32 ulps, covering the rounding of sigmoid and of the product) and
+    // another 0.02 lower in the logit domain (covering the rounding of the logit itself), so it never loses a
+    // candidate; everything above the cut is evaluated exactly.
+    float v_cut = INFINITY;
+    if (valid && so > P.thr) {
+        const float q = (P.thr / so) * (1.0f - 1.0e-5f);
+        v_cut = logf(q / (1.0f - q)) - 0.02f;
+    }
+
+    YoloWarpSmem& ws = smem_all[threadIdx.x >> 5];
+    int fill = 0;   // staged keys (warp-uniform)
+    int qfill = 0;  // queued entries (warp-uniform)
     uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
     int32_t* gcount = P.counts + img;
     const uint32_t flat0 = static_cast<uint32_t>(box) * kYoloClasses;
-    const float* __restrict__ csrc = src + 5 * static_cast<int64_t>(SS);
 
 #pragma unroll 1
     for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
-        float v[kYoloChunk];
+        if (c0 > 0) {
 #pragma unroll
-        for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + static_cast<int64_t>(c0 + u) * SS);
+            for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + static_cast<int64_t>(c0 + u) * SS);
+        }
+        if (DENSE) {
+            if (valid && P.cls_out != nullptr) {
 #pragma unroll
-        for (int u = 0; u < kYoloChunk; ++u) {
-            bool pred = false;
-            float s = 0.0f;
-            if (DENSE) {
-                const float sc = sigmoid_f32(v[u]);
-                if (valid && P.cls_out != nullptr) P.cls_out[gbox * kYoloClasses + c0 + u] = sc;
-                s = __fmul_rn(so, sc);
-                pred = valid && (s > P.thr);
-            } else if (obj_ok && (!shortcut || v[u] > 0.0f)) {
-                s = __fmul_rn(so, sigmoid_f32(v[u]));
-                pred = s > P.thr;
+                for (int u = 0; u < kYoloChunk; ++u) P.cls_out[gbox * kYoloClasses + c0 + u] = sigmoid_f32(v[u]);
             }
-            // stage the hits of the warp (fill is warp-uniform)
-            const unsigned m = __ballot_sync(kFullMask, pred);
-            if (pred) {
-                const int off = __popc(m & ((1u << (threadIdx.x & 31)) - 1u));
-                stage[fill + off] = make_key(s, flat0 + static_cast<uint32_t>(c0 + u));
+        }
+#pragma unroll
+        for (int h = 0; h < kYoloChunk / kYoloSub; ++h) {
+            uint32_t hits = 0u;
+#pragma unroll
+            for (int u = 0; u < kYoloSub; ++u) hits |= (v[h * kYoloSub + u] > v_cut ? 1u : 0u) << u;
+            // exclusive prefix of the per-lane hit counts
+            const int cnt = __popc(hits);
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(kFullMask, incl, o);
+                if (lane >= o) incl += t;
             }
-            fill += __popc(m);
-            if (fill + 32 > kYoloWarpStage) {
-                __syncwarp();
-                int base = 0;
-                if ((threadIdx.x & 31) == 0) base = atomicAdd(gcount, fill);
-                base = __shfl_sync(kFullMask, base, 0);
-                for (int i = (threadIdx.x & 31); i < fill; i += 32) {
-                    const int64_t pos = static_cast<int64_t>(base) + i;
-                    if (pos < P.capacity) gkeys[pos] = stage[i];
-                    else if (P.status != nullptr) atomicOr(P.status, FB_STATUS_CAND_OVERFLOW);
+            const int total = __shfl_sync(kFullMask, incl, 31);
+            if (total > 0) {  // warp-uniform
+                int pos = qfill + incl - cnt;
+#pragma unroll
+                for (int u = 0; u < kYoloSub; ++u) {
+                    if ((hits >> u) & 1u) {
+                        ws.qv[pos] = v[h * kYoloSub + u];
+                        ws.qmeta[pos] = (static_cast<uint32_t>(lane) << 8) | static_cast<uint32_t>(c0 + h * kYoloSub + u);
+                        ++pos;
+                    }
                 }
+                qfill += total;
                 __syncwarp();
-                fill = 0;
+                // evaluate full batches from the front, then move the remainder (< 32 entries) to the front
+                int head = 0;
+                while (qfill - head >= 32) {
+                    yolo_eval_batch(ws, head, 32, so, flat0, P, img, fill, gkeys, gcount);
+                    head += 32;
+                }
+                const int rest = qfill - head;
+                if (head > 0) {
+                    float rv = 0.0f;
+                    uint32_t rm = 0u;
+                    if (lane < rest) {
+                        rv = ws.qv[head + lane];
+                        rm = ws.qmeta[head + lane];
+                    }
+                    __syncwarp();
+                    if (lane < rest) {
+                        ws.qv[lane] = rv;
+                        ws.qmeta[lane] = rm;
+                    }
+                    __syncwarp();
+                }
+                qfill = rest;
             }
         }
     }
-    __syncwarp();
-    if (fill > 0) {
-        int base = 0;
-        if ((threadIdx.x & 31) == 0) base = atomicAdd(gcount, fill);
-        base = __shfl_sync(kFullMask, base, 0);
-        for (int i = (threadIdx.x & 31); i < fill; i += 32) {
-            const int64_t pos = static_cast<int64_t>(base) + i;
-            if (pos < P.capacity) gkeys[pos] = stage[i];
-            else if (P.status != nullptr) atomicOr(P.status, FB_STATUS_CAND_OVERFLOW);
-        }
-    }
+    if (qfill > 0) yolo_eval_batch(ws, 0, qfill, so, flat0, P, img, fill, gkeys, gcount);
+    if (fill > 0) yolo_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
 }
 
 static const float kAnchors[3][3][2] = {{{116, 90}, {156, 198}, {373, 326}},
@@ -153,7 +236,8 @@ static const float kStrides[3] = {32.f, 16.f, 8.f};
 
 int launch_yolo_decode(const float* map0, const float* map1, const float* map2, int batch, int s0, int s1, int s2,
                        float score_thr, float* boxes, float* obj_out, float* cls_out, uint64_t* cand_keys,
-                       int32_t* cand_counts, int64_t capacity, int32_t* status, cudaStream_t st) {
+                       int32_t* cand_counts, int64_t capacity, int32_t* hist, int zero_first, int32_t* status,
+                       cudaStream_t st) {
     FB_REQUIRE(map0 && map1 && map2 && boxes && cand_keys && cand_counts, "yolo_decode: null pointer");
     FB_REQUIRE(batch > 0 && s0 > 0 && s1 > 0 && s2 > 0 && s0 <= 1024 && s1 <= 1024 && s2 <= 1024 && capacity > 0,
                "yolo_decode: bad sizes");
@@ -192,7 +276,15 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     P.counts = cand_counts;
     P.capacity = capacity;
     P.status = status;
-    FB_TRY(check_cuda(cudaMemsetAsync(cand_counts, 0, sizeof(int32_t) * batch, st), "memset cand_counts"));
+    P.hist = hist;
+    const HistParams hp = hist_params_for(score_thr);
+    P.hist_base = hp.base;
+    P.hist_shift = hp.shift;
+    if (zero_first) {
+        FB_TRY(check_cuda(cudaMemsetAsync(cand_counts, 0, sizeof(int32_t) * batch, st), "memset cand_counts"));
+        if (hist != nullptr)
+            FB_TRY(check_cuda(cudaMemsetAsync(hist, 0, sizeof(int32_t) * batch * kHistBins, st), "memset hist"));
+    }
     if (obj_out != nullptr || cls_out != nullptr) {
         yolo_decode_kernel<true><<<static_cast<unsigned>(tile_acc), kYoloThreads, 0, st>>>(P);
     } else {
@@ -204,23 +296,35 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
 
 static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
+// Scratch of the one-call post-process.  The first `zero_bytes` bytes hold everything that must be zero when a
+// call starts (candidate counts, score histogram, selection counters, NMS tickets) and are cleared by ONE memset.
 struct YoloScratch {
-    int64_t keys_off, counts_off, sel_keys_off, sel_counts_off, nms_off, total;
+    int64_t counts_off, hist_off, ctr_off, tickets_off, zero_bytes;
+    int64_t keys_off, sel_keys_off, sel_counts_off, lists_off, mask_off, total;
 };
 
 static YoloScratch yolo_scratch_layout(int batch, int64_t capacity, int topk) {
     YoloScratch L;
     int64_t off = 0;
-    L.keys_off = off;
-    off = align_up(off + static_cast<int64_t>(batch) * capacity * 8, 256);
     L.counts_off = off;
     off = align_up(off + static_cast<int64_t>(batch) * 4, 256);
+    L.hist_off = off;
+    off = align_up(off + static_cast<int64_t>(batch) * kHistBins * 4, 256);
+    L.ctr_off = off;
+    off = align_up(off + select_binned_ctr_bytes(batch), 256);
+    L.tickets_off = off;
+    off = align_up(off + nms_ticket_bytes(batch), 256);
+    L.zero_bytes = off;
+    L.keys_off = off;
+    off = align_up(off + static_cast<int64_t>(batch) * capacity * 8, 256);
     L.sel_keys_off = off;
     off = align_up(off + static_cast<int64_t>(batch) * topk * 8, 256);
     L.sel_counts_off = off;
     off = align_up(off + static_cast<int64_t>(batch) * 4, 256);
-    L.nms_off = off;
-    off = align_up(off + nms_scratch_bytes(batch, topk), 256);
+    L.lists_off = off;
+    off = align_up(off + select_binned_lists_bytes(batch), 256);
+    L.mask_off = off;
+    off = align_up(off + nms_mask_bytes(batch), 256);
     L.total = off;
     return L;
 }
@@ -231,10 +335,10 @@ extern "C" {
 
 int functs_b200_yolo_decode(const float* map0, const float* map1, const float* map2, int32_t batch, int32_t s0,
                             int32_t s1, int32_t s2, float score_thr, float* boxes, float* obj_out, float* cls_out,
-                            uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* status,
-                            void* stream) {
+                            uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
+                            int32_t* status, void* stream) {
     return fb::launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, obj_out, cls_out, cand_keys,
-                                  cand_counts, capacity, status, fb::as_stream(stream));
+                                  cand_counts, capacity, hist, 1, status, fb::as_stream(stream));
 }
 
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
@@ -256,18 +360,25 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
     FB_REQUIRE(batch > 0 && capacity > 0 && topk > 0, "yolo_postprocess: bad sizes");
     const YoloScratch L = yolo_scratch_layout(batch, capacity, topk);
     unsigned char* base = static_cast<unsigned char*>(scratch);
-    uint64_t* keys = reinterpret_cast<uint64_t*>(base + L.keys_off);
     int32_t* counts = reinterpret_cast<int32_t*>(base + L.counts_off);
+    int32_t* hist = reinterpret_cast<int32_t*>(base + L.hist_off);
+    uint64_t* keys = reinterpret_cast<uint64_t*>(base + L.keys_off);
     uint64_t* sel_keys = reinterpret_cast<uint64_t*>(base + L.sel_keys_off);
     int32_t* sel_counts = reinterpret_cast<int32_t*>(base + L.sel_counts_off);
-    void* nms_scratch = base + L.nms_off;
     cudaStream_t st = as_stream(stream);
     const int num_boxes = 3 * (s0 * s0 + s1 * s1 + s2 * s2);
+    FB_TRY(check_cuda(cudaMemsetAsync(base, 0, static_cast<size_t>(L.zero_bytes), st), "memset yolo counters"));
+    record_stage_event(0, st);
     FB_TRY(launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, nullptr, nullptr, keys, counts,
-                              capacity, status, st));
-    FB_TRY(launch_select_topk(keys, counts, capacity, batch, topk, sel_keys, sel_counts, st));
-    return launch_batched_nms(boxes, num_boxes, kYoloClasses, sel_keys, sel_counts, batch, topk, iou_thr, 1, dets,
-                              labels, flat_ids, nullptr, out_counts, nms_scratch, st);
+                              capacity, hist, 0, status, st));
+    record_stage_event(1, st);
+    FB_TRY(launch_select_binned(keys, counts, capacity, hist, score_thr, batch, topk, sel_keys, sel_counts,
+                                base + L.ctr_off, base + L.lists_off, 0, st));
+    record_stage_event(2, st);
+    const int rc = launch_batched_nms(boxes, num_boxes, kYoloClasses, sel_keys, sel_counts, batch, topk, iou_thr, 1, dets,
+                                      labels, flat_ids, nullptr, out_counts, base + L.mask_off, base + L.tickets_off, 0, st);
+    record_stage_event(3, st);
+    return rc;
 }
 
 }  // extern "C"

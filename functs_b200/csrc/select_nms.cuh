@@ -14,6 +14,36 @@ constexpr int kHistBits = 11;
 constexpr int kHistBins = 1 << kHistBits;
 constexpr int kBinListCap = 1024;  // keys of the boundary bin that are finished by a local sort
 
+// ---- coarse score histogram shared by a candidate producer and the binned top-k ----------------------------
+// Positive fp32 bit patterns are ordered like their values, so (bits - bits(thr)) >> shift is a monotone bucketing
+// of the scores above thr; everything at or above the last bucket is clamped into it.
+struct HistParams {
+    uint32_t base;
+    int shift;
+};
+
+inline HistParams hist_params_for(float thr) {
+    HistParams h;
+    uint32_t one_bits = 0x3F800000u;  // scores are products of probabilities: <= 1.0
+    float t = thr > 0.0f ? thr : 0.0f;
+    uint32_t b;
+    static_assert(sizeof(float) == 4, "fp32");
+    __builtin_memcpy(&b, &t, 4);
+    h.base = b;
+    uint32_t diff = one_bits > b ? one_bits - b : 1u;
+    h.shift = 0;
+    while (((diff - 1u) >> h.shift) > static_cast<uint32_t>(kHistBins - 1)) ++h.shift;
+    return h;
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ int hist_digit(uint64_t key, uint32_t base, int shift) {
+    uint32_t bits = static_cast<uint32_t>(key >> 32);
+    uint32_t d = bits > base ? (bits - base) >> shift : 0u;
+    return d > static_cast<uint32_t>(kHistBins - 1) ? kHistBins - 1 : static_cast<int>(d);
+}
+#endif
+
 // ---- bitonic sort, descending, on `n` (power of two) 64-bit keys in shared memory -------------------
 template <int NT>
 __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
@@ -259,6 +289,114 @@ __device__ int block_select_topk(KeyFn key, int n, int topk, SelectSmem<SELCAP>&
         result = topk;
     }
     sort_n = next_pow2(result);
+    for (int i = result + tid; i < sort_n; i += NT) sm.sel[i] = 0ull;
+    __syncthreads();
+    bitonic_sort_desc<NT>(sm.sel, sort_n);
+    return result;
+}
+
+// Same result as block_select_topk, but in two passes for keys whose scores lie above a known threshold: one pass
+// fills the coarse score histogram (hist_digit), the second collects the keys above / inside the boundary bucket,
+// and only the boundary bucket is sorted.  Falls back to block_select_topk when that bucket exceeds kBinListCap.
+template <int NT, int SELCAP, int UNROLL, class KeyFn>
+__device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t hist_base, int hist_shift,
+                                        SelectSmem<SELCAP>& sm) {
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < kHistBins; i += NT) sm.hist[i] = 0;
+    if (tid == 0) {
+        sm.sel_cnt = 0;
+        sm.bin_cnt = 0;
+        sm.digit = -1;
+        sm.above = 0;
+        sm.inbin = 0;
+        sm.nvalid = 0;
+    }
+    __syncthreads();
+    for (int base = 0; base < n; base += NT * UNROLL) {
+        uint64_t k[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int i = base + u * NT + tid;
+            k[u] = (i < n) ? key(i) : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (k[u] != 0ull) atomicAdd(&sm.hist[hist_digit(k[u], hist_base, hist_shift)], 1);
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        constexpr int per = kHistBins / 32;
+        const int lo = lane * per, hi = lo + per;
+        int s = 0;
+        for (int i = lo; i < hi; ++i) s += sm.hist[i];
+        int incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_down_sync(kFullMask, incl, o);
+            if (lane + o < 32) incl += t;
+        }
+        const int total = __shfl_sync(kFullMask, incl, 0);
+        if (lane == 0) sm.nvalid = total;
+        const int suf = incl - s;
+        if (total > topk && suf < topk && incl >= topk) {
+            int cum = suf, d = hi - 1;
+            for (; d >= lo; --d) {
+                const int h = sm.hist[d];
+                if (cum + h >= topk) break;
+                cum += h;
+            }
+            sm.digit = d;
+            sm.above = cum;
+            sm.inbin = sm.hist[d];
+        }
+    }
+    __syncthreads();
+    const int nvalid = sm.nvalid;
+    if (nvalid == 0) return 0;
+    const int dstar = sm.digit;  // -1: everything is selected
+    if (sm.inbin > kBinListCap) {
+        __syncthreads();
+        return block_select_topk<NT, SELCAP, UNROLL>(key, n, topk, sm);
+    }
+    for (int base = 0; base < n; base += NT * UNROLL) {
+        uint64_t k[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int i = base + u * NT + tid;
+            k[u] = (i < n) ? key(i) : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (k[u] != 0ull) {
+                const int d = hist_digit(k[u], hist_base, hist_shift);
+                if (d > dstar) {
+                    const int pos = atomicAdd(&sm.sel_cnt, 1);
+                    if (pos < SELCAP) sm.sel[pos] = k[u];
+                } else if (d == dstar) {
+                    const int pos = atomicAdd(&sm.bin_cnt, 1);
+                    if (pos < kBinListCap) sm.binlist[pos] = k[u];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const int result = nvalid < topk ? nvalid : topk;
+    if (dstar >= 0) {
+        const int bc = sm.bin_cnt;
+        const int bn = next_pow2(bc);
+        for (int i = bc + tid; i < bn; i += NT) sm.binlist[i] = 0ull;
+        __syncthreads();
+        bitonic_sort_desc<NT>(sm.binlist, bn);
+        const int have = sm.sel_cnt;
+        const int want = topk - have;
+        for (int i = tid; i < want && i < bc; i += NT) {
+            if (have + i < SELCAP) sm.sel[have + i] = sm.binlist[i];
+        }
+        __syncthreads();
+    }
+    const int sort_n = next_pow2(result);
     for (int i = result + tid; i < sort_n; i += NT) sm.sel[i] = 0ull;
     __syncthreads();
     bitonic_sort_desc<NT>(sm.sel, sort_n);

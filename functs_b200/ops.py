@@ -63,16 +63,32 @@ def rows_select_add_select_rev(b: torch.Tensor, n: int, addend: float = 1.0) -> 
 
 
 def threshold_compact(scores: torch.Tensor, thr: float, capacity: Optional[int] = None,
-                      status: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """scores [G, n] -> (keys uint64-as-int64 [G, capacity], counts int32 [G])."""
+                      status: Optional[torch.Tensor] = None, with_hist: bool = False):
+    """scores [G, n] -> (keys uint64-as-int64 [G, capacity], counts int32 [G][, hist int32 [G, bins]])."""
     scores = _req(scores, torch.float32, "scores")
     g, n = scores.shape
     capacity = int(capacity or n)
     keys = torch.empty(g, capacity, dtype=torch.int64, device=scores.device)
     counts = torch.empty(g, dtype=torch.int32, device=scores.device)
+    hist = torch.empty(g, int(lib.functs_b200_hist_bins()), dtype=torch.int32, device=scores.device) if with_hist else None
     check(lib.functs_b200_threshold_compact(_ptr(scores), g, n, float(thr), _ptr(keys), _ptr(counts), capacity, 1,
-                                            _ptr(status), _stream()), "threshold_compact")
-    return keys, counts
+                                            _ptr(hist), _ptr(status), _stream()), "threshold_compact")
+    return (keys, counts, hist) if with_hist else (keys, counts)
+
+
+def select_topk_binned(keys: torch.Tensor, counts: torch.Tensor, hist: torch.Tensor, thr: float, topk: int):
+    """Wide variant of select_topk driven by the producer's score histogram (same thr as the producer)."""
+    keys = _req(keys, torch.int64, "keys")
+    counts = _req(counts, torch.int32, "counts")
+    hist = _req(hist, torch.int32, "hist")
+    g, capacity = keys.shape
+    out_keys = torch.empty(g, topk, dtype=torch.int64, device=keys.device)
+    out_counts = torch.empty(g, dtype=torch.int32, device=keys.device)
+    scratch = torch.empty(int(lib.functs_b200_select_binned_scratch_bytes(g)), dtype=torch.uint8, device=keys.device)
+    check(lib.functs_b200_select_topk_binned(_ptr(keys), _ptr(counts), capacity, _ptr(hist), float(thr), g, int(topk),
+                                             _ptr(out_keys), _ptr(out_counts), _ptr(scratch), _stream()),
+          "select_topk_binned")
+    return out_keys, out_counts
 
 
 def select_topk(keys: torch.Tensor, counts: torch.Tensor, topk: int) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -110,8 +126,8 @@ def batched_nms(boxes: torch.Tensor, num_classes: int, sel_keys: torch.Tensor, s
 
 
 def yolo_decode(maps: List[torch.Tensor], score_thr: float, capacity: Optional[int] = None, dense: bool = False,
-                status: Optional[torch.Tensor] = None):
-    """-> (boxes [B,N,4], obj [B,N] | None, cls [B,N,80] | None, cand_keys [B,cap], cand_counts [B])."""
+                status: Optional[torch.Tensor] = None, with_hist: bool = False):
+    """-> (boxes [B,N,4], obj [B,N] | None, cls [B,N,80] | None, cand_keys [B,cap], cand_counts [B][, hist])."""
     maps = [_req(m, torch.float32, "pred map") for m in maps]
     if len(maps) != 3 or any(m.dim() != 4 or m.size(1) != 255 or m.size(2) != m.size(3) for m in maps):
         raise ValueError("expected three [B, 255, S, S] maps")
@@ -125,9 +141,12 @@ def yolo_decode(maps: List[torch.Tensor], score_thr: float, capacity: Optional[i
     cls = torch.empty(b, n, 80, dtype=torch.float32, device=dev) if dense else None
     keys = torch.empty(b, capacity, dtype=torch.int64, device=dev)
     counts = torch.empty(b, dtype=torch.int32, device=dev)
+    hist = torch.empty(b, int(lib.functs_b200_hist_bins()), dtype=torch.int32, device=dev) if with_hist else None
     check(lib.functs_b200_yolo_decode(_ptr(maps[0]), _ptr(maps[1]), _ptr(maps[2]), b, s[0], s[1], s[2], float(score_thr),
-                                      _ptr(boxes), _ptr(obj), _ptr(cls), _ptr(keys), _ptr(counts), capacity,
+                                      _ptr(boxes), _ptr(obj), _ptr(cls), _ptr(keys), _ptr(counts), capacity, _ptr(hist),
                                       _ptr(status), _stream()), "yolo_decode")
+    if with_hist:
+        return boxes, obj, cls, keys, counts, hist
     return boxes, obj, cls, keys, counts
 
 

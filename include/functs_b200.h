@@ -49,6 +49,11 @@ const char* functs_b200_last_error(void);
  * CUPTI, fait/util/profile.cpp:39-41; the "kernels per call" metric is a difference of two reads). */
 uint64_t functs_b200_launch_count(void);
 
+/* Profiling hook (the reference brackets regions with prof::Begin/End ops, fait/util/profile.cpp:123-149): arms up to
+ * 8 caller-owned cudaEvent_t handles for the calling thread; multi-stage entry points record event k on their stream
+ * before stage k and the next one after the last stage.  count = 0 disarms. */
+void functs_b200_set_stage_events(void* const* events, int32_t count);
+
 /* ---- C1: loop { select(b,0,i) -> add -> select_rev(b,.,0,i) } on a cloned, carried tensor -- */
 /* Replaces the group printed in the reference README.md:284-299 (examples/get_started.py:10-15):
  * out = clone(b); out[i,:] = b[i,:] + addend for 0 <= i < n.  b, out: [rows, cols] fp32, contiguous.
@@ -62,15 +67,27 @@ int functs_b200_rows_select_add_select_rev(const float* b, float* out, int64_t r
  * (functs/benchmark/ai_model/ssd/ssd_bbox.py:163-172).  Scores must be > 0. */
 
 /* scores [groups, n] fp32 -> keys of the elements > thr, per group, in unspecified order.
- * keys [groups, capacity], counts [groups] int32 (must be zeroed by the caller or by zero_counts=1). */
+ * keys [groups, capacity], counts [groups] int32 (must be zeroed by the caller or by zero_counts=1).
+ * hist (optional, [groups, functs_b200_hist_bins()] int32, zeroed like counts): coarse histogram of the candidate
+ * scores, the input of functs_b200_select_topk_binned. */
+int32_t functs_b200_hist_bins(void);
 int functs_b200_threshold_compact(const float* scores, int32_t groups, int64_t n, float thr, uint64_t* keys,
-                                  int32_t* counts, int64_t capacity, int32_t zero_counts, int32_t* status,
-                                  void* stream);
+                                  int32_t* counts, int64_t capacity, int32_t zero_counts, int32_t* hist,
+                                  int32_t* status, void* stream);
 
 /* Per group: the topk largest keys, sorted descending. in_keys [groups, capacity] with in_counts valid
  * entries (clamped to capacity); out_keys [groups, topk]; out_counts [groups] = min(count, topk).  topk <= 1024. */
 int functs_b200_select_topk(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, int32_t groups,
                             int32_t topk, uint64_t* out_keys, int32_t* out_counts, void* stream);
+
+/* The same selection for long candidate lists: 16 CTAs per group collect the keys above / inside the boundary
+ * bucket of the score histogram `hist` (filled by the candidate producer with the same thr), the CTA that finishes
+ * last sorts.  Falls back to the exact generic selection when the boundary bucket holds more than 2048 keys.
+ * scratch: functs_b200_select_binned_scratch_bytes(groups), 256-byte aligned. */
+int64_t functs_b200_select_binned_scratch_bytes(int32_t groups);
+int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity,
+                                   const int32_t* hist, float thr, int32_t groups, int32_t topk, uint64_t* out_keys,
+                                   int32_t* out_counts, void* scratch, void* stream);
 
 /* Greedy IoU NMS over the selected candidates of every group, as torchvision.ops.nms does on CPU
  * (call sites yolov3_bbox.py:177, ssd_bbox.py:212), optionally class-wise through the coordinate-offset
@@ -93,14 +110,15 @@ int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_c
 /* Decode group (one launch): permute/reshape, sigmoid on the xy / objectness / class slices, xy grid offset and
  * stride, wh = exp * anchor, corner form, score = obj * cls, mask score > thr, compaction into candidate keys.
  * boxes [batch, N, 4] with N = 3*(s0^2+s1^2+s2^2); obj_out [batch, N] and cls_out [batch, N, 80] are optional
- * (NULL = not written; they exist for value-parity checks); cand_keys [batch, capacity]; cand_counts [batch]
- * is zeroed by the kernel launch sequence. */
+ * (NULL = not written; they exist for value-parity checks); cand_keys [batch, capacity]; cand_counts [batch] and
+ * the optional score histogram hist [batch, functs_b200_hist_bins()] are zeroed by the launch sequence. */
 int functs_b200_yolo_decode(const float* map0, const float* map1, const float* map2, int32_t batch, int32_t s0,
                             int32_t s1, int32_t s2, float score_thr, float* boxes, float* obj_out, float* cls_out,
-                            uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* status,
-                            void* stream);
+                            uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
+                            int32_t* status, void* stream);
 
-/* Whole post-process: decode -> select_topk -> batched_nms(class_offset=1).  Outputs as in batched_nms.
+/* Whole post-process: one memset + decode -> select_topk_binned -> batched_nms(class_offset=1): 3 launches.
+ * Outputs as in batched_nms.
  * scratch: functs_b200_yolo_scratch_bytes(batch, s0, s1, s2, capacity, topk). */
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
                                        int32_t topk);
@@ -129,7 +147,8 @@ int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_
 /* Follows functs/benchmark/ai_model/lstm/lstm.py:79-98, 118-133 (one layer; hs[t] = h, cs[t] = c kept).
  * x [T, B, I]; w_ih [4, I, H]; w_hh [4, H, H]; b_ih, b_hh [4, H]; hs, cs [T, B, H]; gate order i, f, g, o;
  * h0 = c0 = 0.  scratch: functs_b200_lstm_scratch_bytes(T, B, I, H).
- * Two launches: the hoisted input projection (tcgen05, 3xTF32) and one persistent recurrent kernel. */
+ * Three launches: operand split + pre-tiling, the hoisted input projection (tcgen05, 3xTF32), and one persistent
+ * recurrent kernel. */
 int64_t functs_b200_lstm_scratch_bytes(int32_t seq_len, int32_t batch, int32_t input, int32_t hidden);
 int functs_b200_lstm_forward(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
                              const float* b_hh, int32_t seq_len, int32_t batch, int32_t input, int32_t hidden,
@@ -139,6 +158,10 @@ int functs_b200_lstm_forward(const float* x, const float* w_ih, const float* w_h
 int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
                                   const float* b_hh, int32_t seq_len, int32_t batch, int32_t input, int32_t hidden,
                                   float* hs, float* cs, int32_t* status, void* scratch, void* stream, int32_t mode);
+
+/* Debugging switches (name -> value); returns FB_ERR_NOT_FOUND for an unknown name.
+ *   "lstm_tc_swap_lbo_sbo": exchange the two stride fields of the tensor-core shared-memory descriptors. */
+int functs_b200_debug_set(const char* name, int32_t value);
 
 /* ---- C5: YOLACT-style mask assembly ------------------------------------------------------------ */
 /* Follows functs/benchmark/ai_model/yolact/yolact_mask.py:250-264 and :306-333: per detection

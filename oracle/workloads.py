@@ -248,7 +248,7 @@ class SSDPost(torch.nn.Module):
         dets_l = []
         labels_l = []
         ids_l = []
-        for c in range(self.num_classes):
+        for c in range(scores.size(1)):
             dets, ids = self.class_single(bboxes, scores[:, c])
             dets_l.append(dets)
             ids_l.append(ids)

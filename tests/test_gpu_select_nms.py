@@ -86,25 +86,40 @@ def test_select_topk_matches_stable_sort(fb, cuda_device, n, k, quant):
     thr = 0.5
     if n == 0:
         s = torch.zeros(groups, 1)
-    keys, counts = fb.ops.threshold_compact(s.cuda(), thr)
-    sel, m = fb.ops.select_topk(keys, counts, k)
-    sel, m = sel.cpu(), m.cpu()
-    for gi in range(groups):
-        want = oracle_topk(s[gi], thr, k)
-        assert int(m[gi]) == want.numel()
-        assert torch.equal(sel[gi, :want.numel()], want), f"group {gi}"
-        assert bool((sel[gi, want.numel():] == 0).all())
+    keys, counts, hist = fb.ops.threshold_compact(s.cuda(), thr, with_hist=True)
+    assert torch.equal(hist.sum(dim=1), counts)
+    for name, (sel, m) in {"generic": fb.ops.select_topk(keys, counts, k),
+                           "binned": fb.ops.select_topk_binned(keys, counts, hist, thr, k)}.items():
+        sel, m = sel.cpu(), m.cpu()
+        for gi in range(groups):
+            want = oracle_topk(s[gi], thr, k)
+            assert int(m[gi]) == want.numel(), name
+            assert torch.equal(sel[gi, :want.numel()], want), f"{name}: group {gi}"
+            assert bool((sel[gi, want.numel():] == 0).all()), name
 
 
 def test_select_topk_varied_exponents(fb, cuda_device):
     # scores across many binades (as softmax outputs are), shuffled candidate order
     g = gen(77)
     s = torch.exp(torch.randn(2, 8732, generator=g) * 2 - 4).clamp(max=0.99)
-    keys, counts = fb.ops.threshold_compact(s.cuda(), 0.01)
+    keys, counts, hist = fb.ops.threshold_compact(s.cuda(), 0.01, with_hist=True)
     sel, m = fb.ops.select_topk(keys, counts, 200)
+    sel_b, m_b = fb.ops.select_topk_binned(keys, counts, hist, 0.01, 200)
     for gi in range(2):
         want = oracle_topk(s[gi], 0.01, 200)
         assert torch.equal(sel[gi].cpu()[:want.numel()], want)
+        assert torch.equal(sel_b[gi].cpu()[:want.numel()], want)
+
+
+def test_select_binned_with_wrong_histogram_falls_back(fb, cuda_device):
+    """A histogram that does not describe the list (all zero) must not change the answer: the generic path runs."""
+    g = gen(123)
+    s = torch.rand(2, 20000, generator=g) * 0.45 + 0.52
+    keys, counts, hist = fb.ops.threshold_compact(s.cuda(), 0.5, with_hist=True)
+    sel, m = fb.ops.select_topk_binned(keys, counts, torch.zeros_like(hist), 0.5, 1000)
+    for gi in range(2):
+        want = oracle_topk(s[gi], 0.5, 1000)
+        assert torch.equal(sel[gi].cpu(), want)
 
 
 # ---- NMS -------------------------------------------------------------------------------------------------

@@ -47,8 +47,9 @@ def check_batch(fb, oracle_mod, maps, sizes, thr=0.5, topk=1000, iou=0.45):
     scale = torch.cat([centre + extent, centre + extent], dim=-1)
     close(boxes_c, obb, rtol=1e-5, scale=scale, what="decoded boxes")
     # candidates == nonzero(score > thr) of the GPU's own scores, and the non-dense kernel gives the same list
-    boxes2, _, _, keys2, counts2 = fb.ops.yolo_decode(cmaps, thr, dense=False)
+    boxes2, _, _, keys2, counts2, hist2 = fb.ops.yolo_decode(cmaps, thr, dense=False, with_hist=True)
     assert torch.equal(boxes2, boxes)
+    assert torch.equal(hist2.sum(dim=1).cpu(), counts.cpu())
     keys_c, counts_c = keys.cpu(), counts.cpu()
     for b in range(batch):
         sc = obj_c[b][:, None] * cls_c[b]
@@ -63,7 +64,7 @@ def check_batch(fb, oracle_mod, maps, sizes, thr=0.5, topk=1000, iou=0.45):
     # full pipeline
     mod = fb.workloads.YOLOV3BBox(sizes=sizes, score_thr=thr, topk=topk, iou_thr=iou)
     dets, labels, flat_ids, cnt = mod.forward_padded(cmaps)
-    assert mod.kernels_last_call == 4
+    assert mod.kernels_last_call == 3
     fb.ops.raise_on_status(mod._plan.status, "yolo")
     dets, labels, flat_ids, cnt = dets.cpu(), labels.cpu(), flat_ids.cpu(), cnt.cpu()
     o_eager = W.YOLOV3Post(sizes=sizes, score_thr=thr, topk=topk, iou_thr=iou)
