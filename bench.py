@@ -168,7 +168,17 @@ def extra_workloads(torch, fb, W, hbm_peak):
         f3()
     ms = time_events(f3, 30, torch)
     by = BATCH * (8732 * 81 * 4 + 8732 * 4 * 4)
+    e0, e1, e2 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    loc, conf = sets[0]
+    _, bx_, sc_, dets_, ids_, cnt_ = ssd._bufs
+    e0.record()
+    fb.ops.ssd_softmax_decode(loc, conf, ssd.priors, 300.0, out=(bx_, sc_))
+    e1.record()
+    fb.ops.ssd_class_nms(bx_, sc_, 0.01, 200, 0.45, out=(dets_, ids_, cnt_))
+    e2.record()
+    torch.cuda.synchronize()
     out["ssd"] = {"batch": BATCH, "latency_us": ms * 1e3, "batches_per_s": 1e3 / ms, "kernels_per_call": 2,
+                  "stage_us": {"softmax_decode": e0.elapsed_time(e1) * 1e3, "class_topk_nms": e1.elapsed_time(e2) * 1e3},
                   "algorithmic_gbs": by / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / hbm_peak}
     del sets, ssd
     # C5, batch 64 (279 MB per call > L2)
@@ -191,7 +201,19 @@ def extra_workloads(torch, fb, W, hbm_peak):
         f4()
     ms = time_events(f4, 10, torch)
     fb.ops.raise_on_status(lm._status, "lstm bench")
-    out["lstm"] = {"T": 64, "B": 64, "H": 512, "latency_us": ms * 1e3, "batches_per_s": 1e3 / ms, "kernels_per_call": 2,
+    import ctypes
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for e in evs:
+        e.record()
+    torch.cuda.synchronize()
+    lib.functs_b200_set_stage_events((ctypes.c_void_p * 3)(*[e.cuda_event for e in evs]), 3)
+    f4()
+    lib.functs_b200_set_stage_events(None, 0)
+    torch.cuda.synchronize()
+    out["lstm"] = {"T": 64, "B": 64, "H": 512, "latency_us": ms * 1e3, "batches_per_s": 1e3 / ms,
+                   "kernels_per_call": lm.kernels_last_call,
+                   "stage_us": {"input_projection_tcgen05": evs[0].elapsed_time(evs[1]) * 1e3,
+                                "recurrence": evs[1].elapsed_time(evs[2]) * 1e3},
                    "algorithmic_tflops": 17.18e9 / (ms * 1e-3) / 1e12}
     return out
 

@@ -243,6 +243,7 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
     void* tc_scratch = base + 256 + align_up(static_cast<int64_t>(M) * 4 * hidden * 4, 256);
     FB_TRY(check_cuda(cudaMemsetAsync(counter, 0, 256, st), "memset step counter"));
 
+    record_stage_event(0, st);
     if (mode == 0 && lstm_tc_supported(M, input, hidden)) {
         FB_TRY(launch_lstm_input_proj_tc(x, w_ih, b_ih, b_hh, M, input, hidden, pre, tc_scratch, status, st));
     } else {
@@ -252,6 +253,7 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
         FB_TRY(check_launch("lstm_input_proj_simt_kernel"));
     }
 
+    record_stage_event(1, st);
     const int btiles = (batch + kRecB - 1) / kRecB;
     dim3 rgrid(hidden / kRecJ, btiles);
     const int hrow = hidden + 64;
@@ -274,6 +276,7 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
     void* args[] = {(void*)&pre_c, (void*)&w_hh, (void*)&T, (void*)&B, (void*)&hs, (void*)&cs, (void*)&counter, (void*)&status};
     FB_TRY(check_cuda(cudaLaunchCooperativeKernel(kfn, rgrid, dim3(kRecThreads), args, smem, st), "lstm_recurrent launch"));
     count_launch();
+    record_stage_event(2, st);
     return check_launch("lstm_recurrent_kernel");
 }
 

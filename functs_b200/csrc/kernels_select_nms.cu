@@ -136,29 +136,35 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
         s_inbin = 0;
     }
     __syncthreads();
-    if (n > topk && warp == 0) {
+    if (n > topk) {
+        // stage the group's histogram (coalesced), then one warp finds the boundary bucket
+        int* sh = sm.generic.hist;
         const int32_t* h = hist + static_cast<int64_t>(g) * kHistBins;
-        constexpr int per = kHistBins / 32;
-        const int lo = lane * per, hi = lo + per;
-        int s = 0;
-        for (int i = lo; i < hi; ++i) s += __ldcg(h + i);
-        int incl = s;
+        for (int i = tid; i < kHistBins; i += kBinThreads) sh[i] = __ldcg(h + i);
+        __syncthreads();
+        if (warp == 0) {
+            constexpr int per = kHistBins / 32;
+            const int lo = lane * per, hi = lo + per;
+            int s = 0;
+            for (int i = lo; i < hi; ++i) s += sh[i];
+            int incl = s;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            int t = __shfl_down_sync(kFullMask, incl, o);
-            if (lane + o < 32) incl += t;
-        }
-        const int suf = incl - s;
-        if (suf < topk && incl >= topk) {
-            int cum = suf, d = hi - 1;
-            for (; d >= lo; --d) {
-                int c = __ldcg(h + d);
-                if (cum + c >= topk) break;
-                cum += c;
+            for (int o = 1; o < 32; o <<= 1) {
+                int t = __shfl_down_sync(kFullMask, incl, o);
+                if (lane + o < 32) incl += t;
             }
-            s_dstar = d;
-            s_above = cum;
-            s_inbin = __ldcg(h + d);
+            const int suf = incl - s;
+            if (suf < topk && incl >= topk) {
+                int cum = suf, d = hi - 1;
+                for (; d >= lo; --d) {
+                    const int c = sh[d];
+                    if (cum + c >= topk) break;
+                    cum += c;
+                }
+                s_dstar = d;
+                s_above = cum;
+                s_inbin = sh[d];
+            }
         }
     }
     __syncthreads();
@@ -245,103 +251,125 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     if (tid == 0) out_counts[g] = result;
 }
 
-// ---- NMS: suppression bit matrix by several CTAs per group, serial scan by the last one to finish ------------
-// Every CTA rebuilds the NMS-space boxes from the selected keys (gather the box of every selected candidate, take
-// the maximum coordinate over them, shift each box by label * (max + 1)), computes its interleaved share of the
-// rows of the bit matrix into global memory and takes a ticket; the CTA with the last ticket stages the matrix
-// in shared memory, runs the serial keep-scan with one warp and writes the compacted outputs.
-constexpr int kNmsThreads = 1024;
+// ---- NMS: suppression bit matrix (many small CTAs per group) + serial keep-scan (one CTA per group) ------------
+// Both kernels work on the NMS-space boxes rebuilt from the selected keys: gather the box of every selected
+// candidate, take the maximum coordinate over them, shift each box by label * (max + 1).
 constexpr int kNmsMaxN = 1024;
 constexpr int kNmsWords = kNmsMaxN / 32;
-constexpr int kNmsRowsPerCta = 128;
+constexpr int kMaskThreads = 256;
+constexpr int kMaskRowsPerCta = 64;   // 8 rows per warp, interleaved over the CTAs of a group
+constexpr int kScanThreads = 1024;
 
-// Every thread t < n gathers candidate t; the block computes the maximum coordinate; returns the shifted box.
-__device__ __forceinline__ NmsBox gather_nms_box(const float* __restrict__ boxes_g, const uint64_t* __restrict__ sel,
-                                                  int n, int num_classes, int class_offset, float* red /*[33]*/) {
-    const int t = threadIdx.x;
-    float4 bx = make_float4(0.f, 0.f, 0.f, 0.f);
-    int label = 0;
-    float lmax = -INFINITY;
-    if (t < n) {
-        const uint64_t k = sel[t];
-        const uint32_t flat = key_index(k);
-        const uint32_t box = flat / static_cast<uint32_t>(num_classes);
-        label = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
-        bx = reinterpret_cast<const float4*>(boxes_g)[box];
-        lmax = fmaxf(fmaxf(bx.x, bx.y), fmaxf(bx.z, bx.w));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
-    if ((t & 31) == 0) red[t >> 5] = lmax;
-    __syncthreads();
-    if (t < 32) {
-        float v = (t < (blockDim.x >> 5)) ? red[t] : -INFINITY;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
-        if (t == 0) red[32] = v;
-    }
-    __syncthreads();
-    float off = 0.0f;
-    if (class_offset) off = __fmul_rn(static_cast<float>(label), __fadd_rn(red[32], 1.0f));
-    return make_nms_box(__fadd_rn(bx.x, off), __fadd_rn(bx.y, off), __fadd_rn(bx.z, off), __fadd_rn(bx.w, off));
-}
-
-// grid = (ceil(topk / 128), groups); block = 1024; dynamic smem = 1024 x 32 words (used by the last CTA).
-__global__ void __launch_bounds__(kNmsThreads)
-nms_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
-           const int32_t* __restrict__ sel_counts, int topk, float thr, float thr_lo, float thr_hi, int class_offset,
-           uint32_t* mask_g, int32_t* tickets, float* __restrict__ dets, int64_t* __restrict__ labels,
-           int64_t* __restrict__ flat_ids, int64_t* __restrict__ keep, int32_t* __restrict__ out_counts) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t* smask = reinterpret_cast<uint32_t*>(smem_raw);  // [n][32], last CTA only
+// grid = (ceil(topk / 64), groups); block = 256.
+__global__ void __launch_bounds__(kMaskThreads)
+nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
+                const int32_t* __restrict__ sel_counts, int topk, float thr, float thr_lo, float thr_hi, int class_offset,
+                uint32_t* __restrict__ mask_g) {
     __shared__ NmsBox sb[kNmsMaxN];
-    __shared__ float red[33];
-    __shared__ uint32_t keep_words[kNmsWords];
-    __shared__ int word_prefix[kNmsWords + 1];
-    __shared__ int s_last;
+    __shared__ float red[kMaskThreads / 32 + 1];
     const int g = blockIdx.y;
     const int t = threadIdx.x;
     const int lane = t & 31, warp = t >> 5;
+    int n = sel_counts[g];
+    if (n > topk) n = topk;
+    const int rt = gridDim.x;
+    if (static_cast<int>(blockIdx.x) >= n) return;  // rows are interleaved: i = k * rt + blockIdx.x
+    const float* boxes_g = boxes + static_cast<int64_t>(g) * num_boxes * 4;
+    const uint64_t* sel = sel_keys + static_cast<int64_t>(g) * topk;
+    uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
+
+    // gather: thread t owns candidates t, t + 256, ...
+    constexpr int kPer = kNmsMaxN / kMaskThreads;
+    float4 bx[kPer];
+    int label[kPer];
+    float lmax = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+        const int c = t + q * kMaskThreads;
+        bx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        label[q] = 0;
+        if (c < n) {
+            const uint32_t flat = key_index(sel[c]);
+            const uint32_t box = flat / static_cast<uint32_t>(num_classes);
+            label[q] = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
+            bx[q] = reinterpret_cast<const float4*>(boxes_g)[box];
+            lmax = fmaxf(lmax, fmaxf(fmaxf(bx[q].x, bx[q].y), fmaxf(bx[q].z, bx[q].w)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
+    if (lane == 0) red[warp] = lmax;
+    __syncthreads();
+    if (t < 32) {
+        float v = (t < kMaskThreads / 32) ? red[t] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
+        if (t == 0) red[kMaskThreads / 32] = v;
+    }
+    __syncthreads();
+    const float scale = __fadd_rn(red[kMaskThreads / 32], 1.0f);
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+        const int c = t + q * kMaskThreads;
+        if (c < n) {
+            const float off = class_offset ? __fmul_rn(static_cast<float>(label[q]), scale) : 0.0f;
+            sb[c] = make_nms_box(__fadd_rn(bx[q].x, off), __fadd_rn(bx[q].y, off), __fadd_rn(bx[q].z, off),
+                                 __fadd_rn(bx[q].w, off));
+        }
+    }
+    __syncthreads();
+
+    const int words = (n + 31) >> 5;
+    for (int rr = 0; rr < kMaskRowsPerCta / (kMaskThreads / 32); ++rr) {
+        const int i = (warp * (kMaskRowsPerCta / (kMaskThreads / 32)) + rr) * rt + blockIdx.x;
+        if (i >= n) continue;  // warp-uniform
+        const NmsBox bi = sb[i];
+        uint32_t bits = 0u;
+        for (int w = i >> 5; w < words; ++w) {
+            const int j = w * 32 + lane;
+            bool pred = false;
+            if (j > i && j < n) pred = iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi);
+            const unsigned m = __ballot_sync(kFullMask, pred);
+            if (lane == w) bits = m;
+        }
+        gmask[i * kNmsWords + lane] = bits;
+    }
+}
+
+// grid = groups; block = 1024; dynamic smem = 1024 x 32 words.  Stages the group's bit matrix in shared memory, one
+// warp scans, all threads write the compacted outputs.
+__global__ void __launch_bounds__(kScanThreads)
+nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
+                const int32_t* __restrict__ sel_counts, int topk, const uint32_t* __restrict__ mask_g,
+                float* __restrict__ dets, int64_t* __restrict__ labels, int64_t* __restrict__ flat_ids,
+                int64_t* __restrict__ keep, int32_t* __restrict__ out_counts) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint32_t* smask = reinterpret_cast<uint32_t*>(smem_raw);  // [n][32]
+    __shared__ uint32_t keep_words[kNmsWords];
+    __shared__ int word_prefix[kNmsWords + 1];
+    const int g = blockIdx.x;
+    const int t = threadIdx.x;
     int n = sel_counts[g];
     if (n > topk) n = topk;
     if (n < 0) n = 0;
     const int words = (n + 31) >> 5;
     const float* boxes_g = boxes + static_cast<int64_t>(g) * num_boxes * 4;
     const uint64_t* sel = sel_keys + static_cast<int64_t>(g) * topk;
-    uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
-    const int rt = gridDim.x;
-
-    if (static_cast<int>(blockIdx.x) < n) {  // this CTA owns at least one row (rows are interleaved: i = k * rt + blockIdx.x)
-        sb[t] = gather_nms_box(boxes_g, sel, n, num_classes, class_offset, red);
-        __syncthreads();
-        for (int rr = 0; rr < kNmsRowsPerCta / 32; ++rr) {
-            const int i = (warp * (kNmsRowsPerCta / 32) + rr) * rt + blockIdx.x;
-            if (i >= n) continue;  // warp-uniform
-            const NmsBox bi = sb[i];
-            uint32_t bits = 0u;
-            for (int w = i >> 5; w < words; ++w) {
-                const int j = w * 32 + lane;
-                bool pred = false;
-                if (j > i && j < n) pred = iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi);
-                const unsigned m = __ballot_sync(kFullMask, pred);
-                if (lane == w) bits = m;
-            }
-            gmask[i * kNmsWords + lane] = bits;
-        }
-    }
-    __threadfence();
-    __syncthreads();
-    if (t == 0) s_last = (atomicAdd(tickets + g, 1) == rt - 1) ? 1 : 0;
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-
-    // ---- last CTA of the group: stage the matrix, scan, write ----
     {
-        const uint4* src = reinterpret_cast<const uint4*>(gmask);
+        const uint4* src = reinterpret_cast<const uint4*>(mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords);
         uint4* dst = reinterpret_cast<uint4*>(smask);
         const int total = n * (kNmsWords / 4);
-        for (int i = t; i < total; i += kNmsThreads) dst[i] = __ldcg(src + i);
+        for (int i = t; i < total; i += kScanThreads) dst[i] = __ldg(src + i);
+    }
+    // the gathers for the output rows do not depend on the scan: issue them before it
+    uint64_t k = 0ull;
+    float4 bx = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint32_t flat = 0u, box = 0u;
+    if (t < n) {
+        k = sel[t];
+        flat = key_index(k);
+        box = flat / static_cast<uint32_t>(num_classes);
+        bx = reinterpret_cast<const float4*>(boxes_g)[box];
     }
     if (t < kNmsWords) keep_words[t] = 0u;
     __syncthreads();
@@ -363,10 +391,6 @@ nms_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, 
         const int b = t & 31;
         if ((kw >> b) & 1u) {
             const int rank = word_prefix[t >> 5] + __popc(kw & ((1u << b) - 1u));
-            const uint64_t k = sel[t];
-            const uint32_t flat = key_index(k);
-            const uint32_t box = flat / static_cast<uint32_t>(num_classes);
-            const float4 bx = reinterpret_cast<const float4*>(boxes_g)[box];
             float* d = dets + (obase + rank) * 5;
             d[0] = bx.x;
             d[1] = bx.y;
@@ -380,7 +404,7 @@ nms_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, 
     }
     // zero the tail so that the padded outputs are deterministic
     const int total_kept = word_prefix[kNmsWords];
-    for (int i = total_kept + t; i < topk; i += kNmsThreads) {
+    for (int i = total_kept + t; i < topk; i += kScanThreads) {
         float* d = dets + (obase + i) * 5;
         d[0] = d[1] = d[2] = d[3] = d[4] = 0.0f;
         labels[obase + i] = -1;
@@ -449,35 +473,37 @@ int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int6
 }
 
 int64_t nms_mask_bytes(int groups) { return static_cast<int64_t>(groups) * kNmsMaxN * kNmsWords * sizeof(uint32_t); }
-int64_t nms_ticket_bytes(int groups) { return (static_cast<int64_t>(groups) * sizeof(int32_t) + 255) / 256 * 256; }
 int64_t nms_scratch_bytes(int groups, int topk) {
     (void)topk;
-    return nms_mask_bytes(groups) + nms_ticket_bytes(groups);
+    return nms_mask_bytes(groups);
 }
 
-// tickets must be zero when the kernel starts (zero_tickets != 0 makes this call clear them).
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
                        int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask,
-                       void* tickets, int zero_tickets, cudaStream_t st) {
-    FB_REQUIRE(boxes && sel_keys && sel_counts && dets && labels && flat_ids && out_counts && mask && tickets,
+                       cudaStream_t st) {
+    FB_REQUIRE(boxes && sel_keys && sel_counts && dets && labels && flat_ids && out_counts && mask,
                "batched_nms: null pointer");
     FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kNmsMaxN && num_classes > 0 && num_boxes > 0,
                "batched_nms: bad sizes (topk must be in [1, %d])", kNmsMaxN);
     FB_REQUIRE(iou_thr > 0.0f && iou_thr < 1.0f, "batched_nms: iou threshold must be in (0, 1)");
     FB_REQUIRE((reinterpret_cast<uintptr_t>(boxes) & 15) == 0 && (reinterpret_cast<uintptr_t>(mask) & 15) == 0,
                "batched_nms: boxes and scratch must be 16-byte aligned");
-    if (zero_tickets) FB_TRY(check_cuda(cudaMemsetAsync(tickets, 0, nms_ticket_bytes(groups), st), "memset nms tickets"));
     const float thr_lo = iou_thr * (1.0f - 1.0e-6f), thr_hi = iou_thr * (1.0f + 1.0e-6f);
-    const size_t smem = static_cast<size_t>(kNmsMaxN) * kNmsWords * sizeof(uint32_t);
-    FB_TRY(check_cuda(cudaFuncSetAttribute(nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
-                      "nms attr"));
-    dim3 grid((topk + kNmsRowsPerCta - 1) / kNmsRowsPerCta, groups);
-    nms_kernel<<<grid, kNmsThreads, smem, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk, iou_thr, thr_lo,
-                                                thr_hi, class_offset, static_cast<uint32_t*>(mask),
-                                                static_cast<int32_t*>(tickets), dets, labels, flat_ids, keep, out_counts);
+    dim3 grid((topk + kMaskRowsPerCta - 1) / kMaskRowsPerCta, groups);
+    nms_mask_kernel<<<grid, kMaskThreads, 0, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk, iou_thr,
+                                                   thr_lo, thr_hi, class_offset, static_cast<uint32_t*>(mask));
     count_launch();
-    return check_launch("nms_kernel");
+    FB_TRY(check_launch("nms_mask_kernel"));
+    const size_t smem = static_cast<size_t>(kNmsMaxN) * kNmsWords * sizeof(uint32_t);
+    FB_TRY(check_cuda(cudaFuncSetAttribute(nms_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)),
+                      "nms_scan attr"));
+    nms_scan_kernel<<<groups, kScanThreads, smem, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk,
+                                                        static_cast<const uint32_t*>(mask), dets, labels, flat_ids, keep,
+                                                        out_counts);
+    count_launch();
+    return check_launch("nms_scan_kernel");
 }
 
 }  // namespace fb
@@ -530,10 +556,9 @@ int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_c
         fb::set_error("batched_nms: null scratch or bad group count");
         return FB_ERR_INVALID_ARGUMENT;
     }
-    unsigned char* base = static_cast<unsigned char*>(scratch);
     return fb::launch_batched_nms(boxes, num_boxes, num_classes, sel_keys, sel_counts, groups, topk, iou_thr,
-                                  class_offset, dets, labels, flat_ids, keep, out_counts, base,
-                                  base + fb::nms_mask_bytes(groups), 1, fb::as_stream(stream));
+                                  class_offset, dets, labels, flat_ids, keep, out_counts, scratch,
+                                  fb::as_stream(stream));
 }
 
 }  // extern "C"

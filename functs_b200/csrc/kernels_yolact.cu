@@ -3,19 +3,21 @@
 // Reference structure (functs/benchmark/ai_model/yolact/yolact_mask.py:250-264, 306-333): per image
 // mask = sigmoid(proto @ coef.T), cropped to each detection's sanitised box, here by slice assignment inside a
 // loop over detections, then thresholded.  The loop iterations only differ in the detection index, so the loop
-// is folded into the kernel: a thread keeps the 32 prototype channels of 4 consecutive pixels in registers,
-// walks the detections, evaluates the 32-term dot product (fixed k order, fp32 FMA) only where the pixel lies
-// inside the crop, and stores 4 mask bytes at once.  Coefficients and crop bounds live in shared memory and are
-// read as warp broadcasts.
+// is folded into the kernel.  A warp owns a 16 x 8 pixel tile; a thread keeps the 32 prototype channels of a 2 x 2
+// pixel block in registers and walks the detections.  Per 32 detections the warp ballots which crops touch its
+// tile at all; for the others it only stores zeros, for those it evaluates the 32-term dot products (fixed k order,
+// fp32 FMA) and the sigmoid-threshold test.  Coefficients and crop bounds live in shared memory and are read as
+// warp broadcasts.
+#include <cmath>
+
 #include "common.cuh"
 
 namespace fb {
 
 constexpr int kYolactThreads = 128;
-constexpr int kYolactPix = 4;                            // pixels per thread (consecutive in the flat H*W order)
-constexpr int kYolactTile = kYolactThreads * kYolactPix;  // pixels per CTA
 constexpr int kYolactK = 32;
 constexpr int kYolactMaxDet = 256;
+constexpr int kYolactTileW = 16, kYolactTileH = 8;  // pixels per warp tile
 
 // sanitize_coordinates (yolact_mask.py:327-333) followed by "col >= x1 and col < x2" as integer bounds.
 __device__ __forceinline__ void crop_range(float a, float b, int size, int& lo, int& hi) {
@@ -27,11 +29,20 @@ __device__ __forceinline__ void crop_range(float a, float b, int size, int& lo, 
     hi = static_cast<int>(ceilf(x2));
 }
 
+// sigmoid(v) > thr.  Outside [v_lo, v_hi] (a band around logit(thr) that is far wider than the rounding of the fp32
+// sigmoid) the answer is known from v alone; inside it the fp32 sigmoid is formed and compared, so the result is
+// always that of the comparison on the fp32 sigmoid.
+__device__ __forceinline__ bool sigmoid_exceeds(float v, float thr, float v_lo, float v_hi) {
+    if (v > v_hi) return true;
+    if (v < v_lo) return false;
+    return sigmoid_f32(v) > thr;
+}
+
 template <bool LOGITS>
 __global__ void __launch_bounds__(kYolactThreads, 3)
 yolact_masks_kernel(const float* __restrict__ proto, const float* __restrict__ coef, const float* __restrict__ boxes,
-                    int height, int width, int num_det, float thr, uint8_t* __restrict__ masks,
-                    float* __restrict__ logits) {
+                    int height, int width, int num_det, float thr, float v_lo, float v_hi, int tiles_x, int num_tiles,
+                    uint8_t* __restrict__ masks, float* __restrict__ logits) {
     __shared__ __align__(16) float s_coef[kYolactMaxDet * kYolactK];
     __shared__ int4 s_bounds[kYolactMaxDet];
     const int img = blockIdx.y;
@@ -51,68 +62,82 @@ yolact_masks_kernel(const float* __restrict__ proto, const float* __restrict__ c
     }
     __syncthreads();
 
-    const int p0 = blockIdx.x * kYolactTile + t * kYolactPix;
-    if (p0 >= hw) return;  // hw is a multiple of 4, so a thread's 4 pixels are all in or all out
+    const int lane = t & 31;
+    const int wt = blockIdx.x * (kYolactThreads / 32) + (t >> 5);  // warp tile
+    if (wt >= num_tiles) return;
+    const int ty = wt / tiles_x, tx = wt - ty * tiles_x;
+    const int x0 = tx * kYolactTileW, y0 = ty * kYolactTileH;
+    const int x = x0 + 2 * (lane & 7);   // this thread: pixels (y, x), (y, x+1), (y+1, x), (y+1, x+1); width is even
+    const int y = y0 + 2 * (lane >> 3);
+    const bool vx = x < width;
+    const bool vrow0 = vx && (y < height), vrow1 = vx && (y + 1 < height);
 
-    // prototype channels of the 4 pixels -> registers (each thread reads 512 contiguous bytes)
-    float pr[kYolactPix][kYolactK];
+    float pr[4][kYolactK];
     {
-        const float4* psrc = reinterpret_cast<const float4*>(proto + (static_cast<int64_t>(img) * hw + p0) * kYolactK);
+        const float* pimg = proto + static_cast<int64_t>(img) * hw * kYolactK;
 #pragma unroll
-        for (int u = 0; u < kYolactPix; ++u) {
+        for (int r = 0; r < 2; ++r) {
+            const bool ok = r == 0 ? vrow0 : vrow1;
+            const float4* psrc = reinterpret_cast<const float4*>(pimg + (static_cast<int64_t>(y + r) * width + x) * kYolactK);
 #pragma unroll
-            for (int q = 0; q < kYolactK / 4; ++q) {
-                const float4 v = __ldg(psrc + u * (kYolactK / 4) + q);
-                pr[u][4 * q + 0] = v.x;
-                pr[u][4 * q + 1] = v.y;
-                pr[u][4 * q + 2] = v.z;
-                pr[u][4 * q + 3] = v.w;
+            for (int q = 0; q < 2 * (kYolactK / 4); ++q) {
+                const float4 v = ok ? __ldg(psrc + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const int u = 2 * r + q / (kYolactK / 4), k4 = (q % (kYolactK / 4)) * 4;
+                pr[u][k4 + 0] = v.x;
+                pr[u][k4 + 1] = v.y;
+                pr[u][k4 + 2] = v.z;
+                pr[u][k4 + 3] = v.w;
             }
         }
     }
-    int px[kYolactPix], py[kYolactPix];
-#pragma unroll
-    for (int u = 0; u < kYolactPix; ++u) {
-        py[u] = (p0 + u) / width;
-        px[u] = (p0 + u) - py[u] * width;
-    }
 
-    uint8_t* mdst = masks + static_cast<int64_t>(img) * num_det * hw + p0;
-    float* ldst = LOGITS ? logits + static_cast<int64_t>(img) * num_det * hw + p0 : nullptr;
+    uint8_t* mrow0 = masks + static_cast<int64_t>(img) * num_det * hw + static_cast<int64_t>(y) * width + x;
+    float* lrow0 = LOGITS ? logits + static_cast<int64_t>(img) * num_det * hw + static_cast<int64_t>(y) * width + x : nullptr;
 #pragma unroll 1
-    for (int d = 0; d < num_det; ++d) {
-        const int4 bd = s_bounds[d];
-        bool in[kYolactPix];
-        bool any = false;
-#pragma unroll
-        for (int u = 0; u < kYolactPix; ++u) {
-            in[u] = px[u] >= bd.x && px[u] < bd.y && py[u] >= bd.z && py[u] < bd.w;
-            any = any || in[u];
+    for (int c0 = 0; c0 < num_det; c0 += 32) {
+        // which of the detections c0 .. c0+31 have a crop that touches this warp's tile?
+        bool touch = false;
+        if (c0 + lane < num_det) {
+            const int4 bd = s_bounds[c0 + lane];
+            touch = bd.x < x0 + kYolactTileW && bd.y > x0 && bd.z < y0 + kYolactTileH && bd.w > y0;
         }
-        uint32_t packed = 0u;
-        if (any || LOGITS) {
-            float acc[kYolactPix] = {0.f, 0.f, 0.f, 0.f};
-            const float4* c4 = reinterpret_cast<const float4*>(s_coef + d * kYolactK);
+        const unsigned word = LOGITS ? kFullMask : __ballot_sync(kFullMask, touch);
+        const int dend = min(32, num_det - c0);
+#pragma unroll 1
+        for (int b = 0; b < dend; ++b) {
+            const int d = c0 + b;
+            uint32_t out0 = 0u, out1 = 0u;
+            if ((word >> b) & 1u) {  // warp-uniform
+                const int4 bd = s_bounds[d];
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const float4* c4 = reinterpret_cast<const float4*>(s_coef + d * kYolactK);
 #pragma unroll
-            for (int q = 0; q < kYolactK / 4; ++q) {
-                const float4 c = c4[q];
+                for (int q = 0; q < kYolactK / 4; ++q) {
+                    const float4 c = c4[q];
 #pragma unroll
-                for (int u = 0; u < kYolactPix; ++u) {
-                    acc[u] = fmaf(pr[u][4 * q + 0], c.x, acc[u]);
-                    acc[u] = fmaf(pr[u][4 * q + 1], c.y, acc[u]);
-                    acc[u] = fmaf(pr[u][4 * q + 2], c.z, acc[u]);
-                    acc[u] = fmaf(pr[u][4 * q + 3], c.w, acc[u]);
+                    for (int u = 0; u < 4; ++u) {
+                        acc[u] = fmaf(pr[u][4 * q + 0], c.x, acc[u]);
+                        acc[u] = fmaf(pr[u][4 * q + 1], c.y, acc[u]);
+                        acc[u] = fmaf(pr[u][4 * q + 2], c.z, acc[u]);
+                        acc[u] = fmaf(pr[u][4 * q + 3], c.w, acc[u]);
+                    }
+                }
+                const bool inx0 = x >= bd.x && x < bd.y, inx1 = x + 1 >= bd.x && x + 1 < bd.y;
+                const bool iny0 = y >= bd.z && y < bd.w, iny1 = y + 1 >= bd.z && y + 1 < bd.w;
+                if (inx0 && iny0 && sigmoid_exceeds(acc[0], thr, v_lo, v_hi)) out0 |= 1u;
+                if (inx1 && iny0 && sigmoid_exceeds(acc[1], thr, v_lo, v_hi)) out0 |= 0x100u;
+                if (inx0 && iny1 && sigmoid_exceeds(acc[2], thr, v_lo, v_hi)) out1 |= 1u;
+                if (inx1 && iny1 && sigmoid_exceeds(acc[3], thr, v_lo, v_hi)) out1 |= 0x100u;
+                if (LOGITS) {
+                    float* l = lrow0 + static_cast<int64_t>(d) * hw;
+                    if (vrow0) *reinterpret_cast<float2*>(l) = make_float2(acc[0], acc[1]);
+                    if (vrow1) *reinterpret_cast<float2*>(l + width) = make_float2(acc[2], acc[3]);
                 }
             }
-#pragma unroll
-            for (int u = 0; u < kYolactPix; ++u) {
-                if (in[u] && sigmoid_f32(acc[u]) > thr) packed |= (1u << (8 * u));
-            }
-            if (LOGITS) {
-                *reinterpret_cast<float4*>(ldst + static_cast<int64_t>(d) * hw) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            }
+            uint8_t* m = mrow0 + static_cast<int64_t>(d) * hw;
+            if (vrow0) *reinterpret_cast<uint16_t*>(m) = static_cast<uint16_t>(out0);
+            if (vrow1) *reinterpret_cast<uint16_t*>(m + width) = static_cast<uint16_t>(out1);
         }
-        *reinterpret_cast<uint32_t*>(mdst + static_cast<int64_t>(d) * hw) = packed;
     }
 }
 
@@ -128,19 +153,37 @@ int functs_b200_yolact_masks(const float* proto, const float* coef, const float*
     FB_REQUIRE(batch > 0 && batch <= 65535 && height > 0 && width > 0, "yolact_masks: bad sizes");
     FB_REQUIRE(num_det > 0 && num_det <= kYolactMaxDet, "yolact_masks: detections per image must be in [1, %d]",
                kYolactMaxDet);
+    FB_REQUIRE(width % 2 == 0, "yolact_masks: the mask width must be even (pixels are stored in pairs)");
+    FB_REQUIRE(thr > 0.0f && thr < 1.0f, "yolact_masks: the threshold must be in (0, 1)");
     const int64_t hw = static_cast<int64_t>(height) * width;
-    FB_REQUIRE(hw % 4 == 0 && hw < (1ll << 30), "yolact_masks: height * width must be a multiple of 4");
+    FB_REQUIRE(hw < (1ll << 30), "yolact_masks: mask too large");
     FB_REQUIRE(((reinterpret_cast<uintptr_t>(proto) | reinterpret_cast<uintptr_t>(coef) | reinterpret_cast<uintptr_t>(boxes)) & 15) == 0 &&
-                   (reinterpret_cast<uintptr_t>(masks) & 3) == 0 &&
-                   (logits_out == nullptr || (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0),
+                   (reinterpret_cast<uintptr_t>(masks) & 1) == 0 &&
+                   (logits_out == nullptr || (reinterpret_cast<uintptr_t>(logits_out) & 7) == 0),
                "yolact_masks: misaligned pointer");
-    dim3 grid(static_cast<unsigned>((hw + kYolactTile - 1) / kYolactTile), batch);
+    // band around logit(thr) inside which the fp32 sigmoid decides; far outside the sigmoid's rounding error
+    float v_lo = 1.0f, v_hi = -1.0f;  // empty band position = "always evaluate"
+    if (thr <= 0.999f && thr >= 0.001f) {
+        const double l = std::log(static_cast<double>(thr) / (1.0 - static_cast<double>(thr)));
+        v_lo = static_cast<float>(l - 1.0e-3);
+        v_hi = static_cast<float>(l + 1.0e-3);
+    } else {
+        v_lo = -INFINITY;
+        v_hi = INFINITY;
+    }
+    const int tiles_x = (width + kYolactTileW - 1) / kYolactTileW;
+    const int tiles_y = (height + kYolactTileH - 1) / kYolactTileH;
+    const int num_tiles = tiles_x * tiles_y;
+    const int warps = kYolactThreads / 32;
+    dim3 grid(static_cast<unsigned>((num_tiles + warps - 1) / warps), batch);
     if (logits_out != nullptr) {
         yolact_masks_kernel<true><<<grid, kYolactThreads, 0, as_stream(stream)>>>(proto, coef, boxes, height, width, num_det,
-                                                                                  thr, masks, logits_out);
+                                                                                  thr, v_lo, v_hi, tiles_x, num_tiles, masks,
+                                                                                  logits_out);
     } else {
         yolact_masks_kernel<false><<<grid, kYolactThreads, 0, as_stream(stream)>>>(proto, coef, boxes, height, width, num_det,
-                                                                                   thr, masks, nullptr);
+                                                                                   thr, v_lo, v_hi, tiles_x, num_tiles, masks,
+                                                                                   nullptr);
     }
     count_launch();
     return check_launch("yolact_masks_kernel");

@@ -15,19 +15,17 @@ int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int6
                          float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
                          void* lists, int zero_ctr, cudaStream_t st);
 int64_t nms_mask_bytes(int groups);
-int64_t nms_ticket_bytes(int groups);
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
                        int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask,
-                       void* tickets, int zero_tickets, cudaStream_t st);
+                       cudaStream_t st);
 
 constexpr int kYoloThreads = 128;
 constexpr int kYoloClasses = 80;
 constexpr int kYoloAttrib = 85;
-constexpr int kYoloChunk = 16;      // class logits loaded per thread before any is consumed
-constexpr int kYoloSub = 8;         // classes whose hits are queued at once (bounds the queue)
-constexpr int kYoloWarpStage = 160; // staged candidate keys per warp
-constexpr int kYoloQueue = 32 + 32 * kYoloSub;  // pending (logit, lane, class) entries per warp
+constexpr int kYoloChunk = 16;       // class logits loaded per thread before any is consumed
+constexpr int kYoloWarpStage = 160;  // staged candidate keys per warp
+constexpr int kYoloQueue = 1024;     // circular queue of pending (lane, class) hits per warp (a chunk adds <= 512)
 
 struct YoloParams {
     const float* map[3];
@@ -55,8 +53,8 @@ struct YoloParams {
 
 struct YoloWarpSmem {
     uint64_t stage[kYoloWarpStage];
-    float qv[kYoloQueue];
-    uint32_t qmeta[kYoloQueue];  // lane << 8 | class
+    uint32_t queue[kYoloQueue];  // lane << 8 | class
+    int qtail;                   // total entries ever pushed (the warp keeps the matching head in a register)
 };
 
 // Appends the staged keys of a warp to the image's candidate list (one atomic per flush).
@@ -76,22 +74,26 @@ __device__ __forceinline__ void yolo_flush(YoloWarpSmem& ws, int& fill, uint64_t
     fill = 0;
 }
 
-// One dense batch: lane i evaluates queue entry i (nb <= 32 entries), hits go to the staging buffer.
-__device__ __forceinline__ void yolo_eval_batch(YoloWarpSmem& ws, int head, int nb, float so, uint32_t flat0,
-                                                const YoloParams& P, int img, int& fill, uint64_t* gkeys,
-                                                int32_t* gcount) {
+// One dense batch: lane i evaluates queue entry head + i (nb <= 32 entries).  The logit is read again (it was
+// loaded by this warp a moment ago), objectness comes from the owning lane by shuffle; hits go to the staging buffer.
+__device__ __forceinline__ void yolo_eval_batch(YoloWarpSmem& ws, int head, int nb, float so, const float* __restrict__ cls0,
+                                                int SS, uint32_t flat0, const YoloParams& P, int img, int& fill,
+                                                uint64_t* gkeys, int32_t* gcount) {
     const int lane = threadIdx.x & 31;
     const bool act = lane < nb;
-    const float v = act ? ws.qv[head + lane] : 0.0f;
-    const uint32_t meta = act ? ws.qmeta[head + lane] : 0u;
-    const float so_src = __shfl_sync(kFullMask, so, static_cast<int>(meta >> 8));
-    const uint32_t flat_src = __shfl_sync(kFullMask, flat0, static_cast<int>(meta >> 8));
+    const uint32_t meta = act ? ws.queue[(head + lane) & (kYoloQueue - 1)] : (static_cast<uint32_t>(lane) << 8);
+    const int src = static_cast<int>(meta >> 8);
+    const int cls = static_cast<int>(meta & 255u);
+    const float so_src = __shfl_sync(kFullMask, so, src);
+    // cls0 points at class 0 of THIS lane's position; the owning lane sits (src - lane) positions away
+    const float v = __ldg(cls0 + static_cast<int64_t>(cls) * SS + (src - lane));
     const float s = __fmul_rn(so_src, sigmoid_f32(v));
     const bool pred = act && (s > P.thr);
     const unsigned m = __ballot_sync(kFullMask, pred);
     if (pred) {
         const int off = __popc(m & ((1u << lane) - 1u));
-        ws.stage[fill + off] = make_key(s, flat_src + (meta & 255u));
+        const uint32_t flat_src = flat0 + static_cast<uint32_t>((src - lane) * 3 * kYoloClasses);
+        ws.stage[fill + off] = make_key(s, flat_src + static_cast<uint32_t>(cls));
         if (P.hist != nullptr) {
             const int d = hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift);
             atomicAdd(P.hist + static_cast<int64_t>(img) * kHistBins + d, 1);
@@ -101,23 +103,21 @@ __device__ __forceinline__ void yolo_eval_batch(YoloWarpSmem& ws, int head, int 
     if (fill + 32 > kYoloWarpStage) yolo_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
 }
 
-template <bool DENSE>
-__global__ void __launch_bounds__(kYoloThreads)
-yolo_decode_kernel(const YoloParams P) {
-    __shared__ YoloWarpSmem smem_all[kYoloThreads / 32];
-    const int cta = blockIdx.x;
-    const int lvl = (cta >= P.tile_begin[2]) ? 2 : (cta >= P.tile_begin[1] ? 1 : 0);
-    const int local = cta - P.tile_begin[lvl];
-    const int S = P.size[lvl];
+// Body for one pyramid level.  S_T > 0 fixes the map size at compile time (channel strides become immediates).
+template <int S_T, bool DENSE>
+__device__ __forceinline__ void yolo_decode_level(const YoloParams& P, const int lvl, const int local, YoloWarpSmem& ws) {
+    const int S = S_T > 0 ? S_T : P.size[lvl];
     const int SS = S * S;
     const int plane = local / P.tiles[lvl];  // = image * 3 + anchor
     const int tile = local - plane * P.tiles[lvl];
     const int img = plane / 3;
     const int anc = plane - img * 3;
     const int p = tile * kYoloThreads + threadIdx.x;
-    const bool valid = p < SS;
-    const int pp = valid ? p : (SS - 1);  // clamp so that every lane loads a legal address
     const int lane = threadIdx.x & 31;
+    // Lanes past the end of the plane are clamped so that every lane loads a legal address.  A warp is then either
+    // fully valid, or its tail lanes all alias position SS - 1; aliased lanes never produce candidates.
+    const bool valid = p < SS;
+    const int pp = valid ? p : (SS - 1);
     const float* __restrict__ src = P.map[lvl] + (static_cast<int64_t>(img) * 255 + anc * kYoloAttrib) * SS + pp;
 
     const float t0 = __ldg(src);
@@ -125,10 +125,10 @@ yolo_decode_kernel(const YoloParams P) {
     const float t2 = __ldg(src + 2 * SS);
     const float t3 = __ldg(src + 3 * SS);
     const float t4 = __ldg(src + 4 * SS);
-    const float* __restrict__ csrc = src + 5 * static_cast<int64_t>(SS);
+    const float* __restrict__ csrc = src + 5 * SS;
     float v[kYoloChunk];
 #pragma unroll
-    for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + static_cast<int64_t>(u) * SS);
+    for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + u * SS);
 
     const int gy = pp / S, gx = pp - gy * S;
     const float stride = P.stride[lvl];
@@ -155,18 +155,24 @@ yolo_decode_kernel(const YoloParams P) {
         v_cut = logf(q / (1.0f - q)) - 0.02f;
     }
 
-    YoloWarpSmem& ws = smem_all[threadIdx.x >> 5];
-    int fill = 0;   // staged keys (warp-uniform)
-    int qfill = 0;  // queued entries (warp-uniform)
+    int fill = 0;    // staged keys (warp-uniform)
+    int head = 0;    // queue entries consumed so far (warp-uniform)
+    int pushed = 0;  // queue entries pushed so far (warp-uniform copy of ws.qtail)
+    if (lane == 0) ws.qtail = 0;
+    __syncwarp();
     uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
     int32_t* gcount = P.counts + img;
-    const uint32_t flat0 = static_cast<uint32_t>(box) * kYoloClasses;
+    // flat index of class 0 of this lane's UNCLAMPED position (dense batches offset it to the owning lane)
+    const uint32_t flat0 = static_cast<uint32_t>(P.box_begin[lvl] + p * 3 + anc) * kYoloClasses;
+    // the dense batches address other lanes' positions relative to this lane's pointer; clamped lanes must not be
+    // used as a base, so every lane uses the pointer of its UNCLAMPED position (only ever dereferenced for valid hits)
+    const float* __restrict__ cls0 = P.map[lvl] + (static_cast<int64_t>(img) * 255 + anc * kYoloAttrib + 5) * SS + p;
 
 #pragma unroll 1
     for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
         if (c0 > 0) {
 #pragma unroll
-            for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + static_cast<int64_t>(c0 + u) * SS);
+            for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + (c0 + u) * SS);
         }
         if (DENSE) {
             if (valid && P.cls_out != nullptr) {
@@ -174,59 +180,48 @@ yolo_decode_kernel(const YoloParams P) {
                 for (int u = 0; u < kYoloChunk; ++u) P.cls_out[gbox * kYoloClasses + c0 + u] = sigmoid_f32(v[u]);
             }
         }
+        uint32_t hits = 0u;
 #pragma unroll
-        for (int h = 0; h < kYoloChunk / kYoloSub; ++h) {
-            uint32_t hits = 0u;
-#pragma unroll
-            for (int u = 0; u < kYoloSub; ++u) hits |= (v[h * kYoloSub + u] > v_cut ? 1u : 0u) << u;
-            // exclusive prefix of the per-lane hit counts
-            const int cnt = __popc(hits);
-            int incl = cnt;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(kFullMask, incl, o);
-                if (lane >= o) incl += t;
+        for (int u = 0; u < kYoloChunk; ++u) hits |= (v[u] > v_cut ? 1u : 0u) << u;
+        const int cnt = __popc(hits);
+        const int total = __reduce_add_sync(kFullMask, cnt);
+        if (total > 0) {  // warp-uniform
+            if (cnt > 0) {
+                int pos = atomicAdd(&ws.qtail, cnt);
+                const uint32_t meta0 = (static_cast<uint32_t>(lane) << 8) | static_cast<uint32_t>(c0);
+                while (hits) {
+                    const int u = __ffs(hits) - 1;
+                    hits &= hits - 1u;
+                    ws.queue[pos & (kYoloQueue - 1)] = meta0 + static_cast<uint32_t>(u);
+                    ++pos;
+                }
             }
-            const int total = __shfl_sync(kFullMask, incl, 31);
-            if (total > 0) {  // warp-uniform
-                int pos = qfill + incl - cnt;
-#pragma unroll
-                for (int u = 0; u < kYoloSub; ++u) {
-                    if ((hits >> u) & 1u) {
-                        ws.qv[pos] = v[h * kYoloSub + u];
-                        ws.qmeta[pos] = (static_cast<uint32_t>(lane) << 8) | static_cast<uint32_t>(c0 + h * kYoloSub + u);
-                        ++pos;
-                    }
-                }
-                qfill += total;
-                __syncwarp();
-                // evaluate full batches from the front, then move the remainder (< 32 entries) to the front
-                int head = 0;
-                while (qfill - head >= 32) {
-                    yolo_eval_batch(ws, head, 32, so, flat0, P, img, fill, gkeys, gcount);
-                    head += 32;
-                }
-                const int rest = qfill - head;
-                if (head > 0) {
-                    float rv = 0.0f;
-                    uint32_t rm = 0u;
-                    if (lane < rest) {
-                        rv = ws.qv[head + lane];
-                        rm = ws.qmeta[head + lane];
-                    }
-                    __syncwarp();
-                    if (lane < rest) {
-                        ws.qv[lane] = rv;
-                        ws.qmeta[lane] = rm;
-                    }
-                    __syncwarp();
-                }
-                qfill = rest;
+            __syncwarp();
+            pushed += total;  // == ws.qtail
+            while (pushed - head >= 32) {
+                yolo_eval_batch(ws, head, 32, so, cls0, SS, flat0, P, img, fill, gkeys, gcount);
+                head += 32;
             }
         }
     }
-    if (qfill > 0) yolo_eval_batch(ws, 0, qfill, so, flat0, P, img, fill, gkeys, gcount);
+    const int rest = pushed - head;
+    if (rest > 0) yolo_eval_batch(ws, head, rest, so, cls0, SS, flat0, P, img, fill, gkeys, gcount);
     if (fill > 0) yolo_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+}
+
+template <int S0, int S1, int S2, bool DENSE>
+__global__ void __launch_bounds__(kYoloThreads)
+yolo_decode_kernel(const YoloParams P) {
+    __shared__ YoloWarpSmem smem_all[kYoloThreads / 32];
+    YoloWarpSmem& ws = smem_all[threadIdx.x >> 5];
+    const int cta = blockIdx.x;
+    if (cta >= P.tile_begin[2]) {
+        yolo_decode_level<S2, DENSE>(P, 2, cta - P.tile_begin[2], ws);
+    } else if (cta >= P.tile_begin[1]) {
+        yolo_decode_level<S1, DENSE>(P, 1, cta - P.tile_begin[1], ws);
+    } else {
+        yolo_decode_level<S0, DENSE>(P, 0, cta, ws);
+    }
 }
 
 static const float kAnchors[3][3][2] = {{{116, 90}, {156, 198}, {373, 326}},
@@ -285,10 +280,15 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
         if (hist != nullptr)
             FB_TRY(check_cuda(cudaMemsetAsync(hist, 0, sizeof(int32_t) * batch * kHistBins, st), "memset hist"));
     }
-    if (obj_out != nullptr || cls_out != nullptr) {
-        yolo_decode_kernel<true><<<static_cast<unsigned>(tile_acc), kYoloThreads, 0, st>>>(P);
+    const unsigned nblk = static_cast<unsigned>(tile_acc);
+    const bool dense = obj_out != nullptr || cls_out != nullptr;
+    const bool std_sizes = s0 == 13 && s1 == 26 && s2 == 52;  // the configured pyramid: strides compiled in
+    if (dense) {
+        if (std_sizes) yolo_decode_kernel<13, 26, 52, true><<<nblk, kYoloThreads, 0, st>>>(P);
+        else yolo_decode_kernel<0, 0, 0, true><<<nblk, kYoloThreads, 0, st>>>(P);
     } else {
-        yolo_decode_kernel<false><<<static_cast<unsigned>(tile_acc), kYoloThreads, 0, st>>>(P);
+        if (std_sizes) yolo_decode_kernel<13, 26, 52, false><<<nblk, kYoloThreads, 0, st>>>(P);
+        else yolo_decode_kernel<0, 0, 0, false><<<nblk, kYoloThreads, 0, st>>>(P);
     }
     count_launch();
     return check_launch("yolo_decode_kernel");
@@ -297,9 +297,9 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
 static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 // Scratch of the one-call post-process.  The first `zero_bytes` bytes hold everything that must be zero when a
-// call starts (candidate counts, score histogram, selection counters, NMS tickets) and are cleared by ONE memset.
+// call starts (candidate counts, score histogram, selection counters) and are cleared by ONE memset.
 struct YoloScratch {
-    int64_t counts_off, hist_off, ctr_off, tickets_off, zero_bytes;
+    int64_t counts_off, hist_off, ctr_off, zero_bytes;
     int64_t keys_off, sel_keys_off, sel_counts_off, lists_off, mask_off, total;
 };
 
@@ -312,8 +312,6 @@ static YoloScratch yolo_scratch_layout(int batch, int64_t capacity, int topk) {
     off = align_up(off + static_cast<int64_t>(batch) * kHistBins * 4, 256);
     L.ctr_off = off;
     off = align_up(off + select_binned_ctr_bytes(batch), 256);
-    L.tickets_off = off;
-    off = align_up(off + nms_ticket_bytes(batch), 256);
     L.zero_bytes = off;
     L.keys_off = off;
     off = align_up(off + static_cast<int64_t>(batch) * capacity * 8, 256);
@@ -376,7 +374,7 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
                                 base + L.ctr_off, base + L.lists_off, 0, st));
     record_stage_event(2, st);
     const int rc = launch_batched_nms(boxes, num_boxes, kYoloClasses, sel_keys, sel_counts, batch, topk, iou_thr, 1, dets,
-                                      labels, flat_ids, nullptr, out_counts, base + L.mask_off, base + L.tickets_off, 0, st);
+                                      labels, flat_ids, nullptr, out_counts, base + L.mask_off, st);
     record_stage_event(3, st);
     return rc;
 }

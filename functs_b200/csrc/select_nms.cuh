@@ -422,12 +422,12 @@ __device__ __forceinline__ NmsBox make_nms_box(float x1, float y1, float x2, flo
 // outside the bracket the comparison against thr * union decides without a division, inside it the
 // correctly rounded quotient is formed, so the answer is always that of the division.
 __device__ __forceinline__ bool iou_exceeds(const NmsBox& a, const NmsBox& b, float thr, float thr_lo, float thr_hi) {
-    float xx1 = fmaxf(a.x1, b.x1), yy1 = fmaxf(a.y1, b.y1);
-    float xx2 = fminf(a.x2, b.x2), yy2 = fminf(a.y2, b.y2);
-    float w = fmaxf(0.0f, __fsub_rn(xx2, xx1));
-    float h = fmaxf(0.0f, __fsub_rn(yy2, yy1));
+    // x extent first: boxes of different classes sit in disjoint coordinate ranges, so most pairs end here
+    float w = fmaxf(0.0f, __fsub_rn(fminf(a.x2, b.x2), fmaxf(a.x1, b.x1)));
+    if (!(w > 0.0f)) return false;  // inter = w * h = 0: the quotient is 0 (or NaN): never above a positive threshold
+    float h = fmaxf(0.0f, __fsub_rn(fminf(a.y2, b.y2), fmaxf(a.y1, b.y1)));
     float inter = __fmul_rn(w, h);
-    if (!(inter > 0.0f)) return false;  // 0 / u is 0 (or NaN for u == 0): never above a positive threshold
+    if (!(inter > 0.0f)) return false;
     float uni = __fsub_rn(__fadd_rn(a.area, b.area), inter);
     if (uni > 0.0f && uni < 3.0e38f && inter < 3.0e38f) {
         if (inter > __fmul_rn(uni, thr_hi)) return true;

@@ -117,7 +117,7 @@ int functs_b200_yolo_decode(const float* map0, const float* map1, const float* m
                             uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
                             int32_t* status, void* stream);
 
-/* Whole post-process: one memset + decode -> select_topk_binned -> batched_nms(class_offset=1): 3 launches.
+/* Whole post-process: one memset + decode -> select_topk_binned -> batched_nms(class_offset=1): 4 launches.
  * Outputs as in batched_nms.
  * scratch: functs_b200_yolo_scratch_bytes(batch, s0, s1, s2, capacity, topk). */
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
@@ -168,7 +168,7 @@ int functs_b200_debug_set(const char* name, int32_t value);
  * sigmoid(proto @ coef) cropped to the sanitised box by slice assignment, thresholded.
  * proto [batch, H, W, K] (K = 32); coef [batch, N, K]; boxes [batch, N, 4] (x1, y1, x2, y2 in pixels);
  * masks [batch, N, H, W] uint8; logits_out optional [batch, N, H, W] fp32 (dense proto @ coef, for value checks).
- * H*W must be a multiple of 4.  One launch. */
+ * W must be even.  One launch. */
 int functs_b200_yolact_masks(const float* proto, const float* coef, const float* boxes, int32_t batch, int32_t height,
                              int32_t width, int32_t num_det, float thr, uint8_t* masks, float* logits_out,
                              void* stream);
