@@ -338,7 +338,7 @@ def run_ours(args):
             "latency_us": ms_per_step * 1e3, "kernels_per_call": launches / args.steps,
             "images_per_s": world * BATCH * 1e3 / ms_per_step,
             "stage_us": {"decode_mask_compact": decode_ms * 1e3, "select_topk": select_ms * 1e3, "nms": nms_ms * 1e3},
-            "detections_kept_last_step": kept,
+            "detections_kept_last_step": kept, "select_fallbacks_last_step": plan.select_fallbacks(),
             "gpu_launches": launches,
             "e2e": {"value": world * 1e3 / e2e_ms, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
                     "d2h_bytes_per_step": bytes_out, "ms_per_step": e2e_ms, "steps": e2e_steps},

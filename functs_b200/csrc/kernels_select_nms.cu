@@ -105,7 +105,8 @@ constexpr int kBinSplit = 16;        // CTAs per group
 constexpr int kBinListGlobal = 2048; // capacity of the boundary-bucket list; beyond it the generic selection runs
 
 struct SelectCtr {
-    int32_t sel_cnt, bin_cnt, ticket, pad;
+    int32_t sel_cnt, bin_cnt, ticket;
+    int32_t fallback;  // set to 1 when the group was finished by the generic selection (observability only)
 };
 
 union BinnedSmem {
@@ -228,6 +229,7 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
         // the boundary bucket is too crowded (many equal scores) or the histogram does not describe this list:
         // exact generic selection over the whole list
         GlobalKeys kf{keys};
+        if (tid == 0) c->fallback = 1;
         const int m = block_select_topk<kBinThreads, kSelCap, 4>(kf, n, topk, sm.generic);
         __syncthreads();
         for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < m) ? sm.generic.sel[i] : 0ull;
@@ -327,9 +329,7 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
         uint32_t bits = 0u;
         for (int w = i >> 5; w < words; ++w) {
             const int j = w * 32 + lane;
-            bool pred = false;
-            if (j > i && j < n) pred = iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi);
-            const unsigned m = __ballot_sync(kFullMask, pred);
+            const unsigned m = nms_row_word(bi, sb, j, j > i && j < n, thr, thr_lo, thr_hi);
             if (lane == w) bits = m;
         }
         gmask[i * kNmsWords + lane] = bits;

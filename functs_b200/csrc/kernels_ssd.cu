@@ -91,7 +91,7 @@ ssd_softmax_decode_kernel(const float* __restrict__ loc, const float* __restrict
 }
 
 // ---- group 2 ------------------------------------------------------------------------------------------------
-constexpr int kSsdNmsThreads = 256;
+constexpr int kSsdNmsThreads = 512;
 constexpr int kSsdSelCap = 256;
 constexpr int kSsdWords = kSsdSelCap / 32;
 
@@ -155,9 +155,7 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
         uint32_t bits = 0u;
         for (int w = i >> 5; w < words; ++w) {
             const int j = w * 32 + lane;
-            bool pred = false;
-            if (j > i && j < n) pred = iou_exceeds(bi, sb[j], iou_thr, thr_lo, thr_hi);
-            unsigned m = __ballot_sync(kFullMask, pred);
+            const unsigned m = nms_row_word(bi, sb, j, j > i && j < n, iou_thr, thr_lo, thr_hi);
             if (lane == w) bits = m;
         }
         if (lane < kSsdWords) smask[i * kSsdWords + lane] = bits;

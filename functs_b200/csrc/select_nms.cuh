@@ -436,6 +436,19 @@ __device__ __forceinline__ bool iou_exceeds(const NmsBox& a, const NmsBox& b, fl
     return __fdiv_rn(inter, uni) > thr;
 }
 
+// One word of a row of the suppression matrix: lane b tests box j = 32w + b against box i (valid = j > i && j < n).
+// The x extents are compared first for the whole warp; only if some lane overlaps in x is the full test run.
+// Must be called by all 32 lanes.
+__device__ __forceinline__ uint32_t nms_row_word(const NmsBox& bi, const NmsBox* sb, int j, bool valid, float thr,
+                                                 float thr_lo, float thr_hi) {
+    bool cand = false;
+    if (valid) cand = fminf(bi.x2, sb[j].x2) > fmaxf(bi.x1, sb[j].x1);  // positive overlap in x
+    if (__ballot_sync(kFullMask, cand) == 0u) return 0u;
+    bool pred = false;
+    if (cand) pred = iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi);
+    return __ballot_sync(kFullMask, pred);
+}
+
 // Serial part of greedy NMS over a precomputed suppression bit matrix, run by ONE warp.
 // mask: row i has `words` 32-bit words (row stride `row_stride` words); bit j of row i set iff j > i and box i
 // suppresses box j.  keep_words[w] receives the keep bits of boxes 32w..32w+31.  words <= 32.

@@ -76,8 +76,10 @@ def threshold_compact(scores: torch.Tensor, thr: float, capacity: Optional[int] 
     return (keys, counts, hist) if with_hist else (keys, counts)
 
 
-def select_topk_binned(keys: torch.Tensor, counts: torch.Tensor, hist: torch.Tensor, thr: float, topk: int):
-    """Wide variant of select_topk driven by the producer's score histogram (same thr as the producer)."""
+def select_topk_binned(keys: torch.Tensor, counts: torch.Tensor, hist: torch.Tensor, thr: float, topk: int,
+                       return_fallbacks: bool = False):
+    """Wide variant of select_topk driven by the producer's score histogram (same thr as the producer).
+    return_fallbacks adds an int32 [G] tensor: 1 where the group was finished by the generic selection."""
     keys = _req(keys, torch.int64, "keys")
     counts = _req(counts, torch.int32, "counts")
     hist = _req(hist, torch.int32, "hist")
@@ -88,6 +90,8 @@ def select_topk_binned(keys: torch.Tensor, counts: torch.Tensor, hist: torch.Ten
     check(lib.functs_b200_select_topk_binned(_ptr(keys), _ptr(counts), capacity, _ptr(hist), float(thr), g, int(topk),
                                              _ptr(out_keys), _ptr(out_counts), _ptr(scratch), _stream()),
           "select_topk_binned")
+    if return_fallbacks:
+        return out_keys, out_counts, scratch[: g * 16].view(torch.int32).reshape(g, 4)[:, 3].clone()
     return out_keys, out_counts
 
 
@@ -167,6 +171,13 @@ class YoloPostprocessPlan:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         nbytes = int(lib.functs_b200_yolo_scratch_bytes(batch, *self.sizes, self.capacity, topk))
         self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+
+    def select_fallbacks(self) -> int:
+        """Number of images of the last call whose top-k was finished by the generic (slow, exact) selection."""
+        counts_bytes = (self.batch * 4 + 255) // 256 * 256
+        hist_bytes = (self.batch * int(lib.functs_b200_hist_bins()) * 4 + 255) // 256 * 256
+        ctr = self.scratch[counts_bytes + hist_bytes: counts_bytes + hist_bytes + self.batch * 16].view(torch.int32)
+        return int(ctr.reshape(self.batch, 4)[:, 3].sum())
 
     def run(self, maps: List[torch.Tensor], score_thr: float = 0.5, iou_thr: float = 0.45) -> None:
         s = self.sizes

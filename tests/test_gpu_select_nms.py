@@ -116,7 +116,10 @@ def test_select_binned_with_wrong_histogram_falls_back(fb, cuda_device):
     g = gen(123)
     s = torch.rand(2, 20000, generator=g) * 0.45 + 0.52
     keys, counts, hist = fb.ops.threshold_compact(s.cuda(), 0.5, with_hist=True)
-    sel, m = fb.ops.select_topk_binned(keys, counts, torch.zeros_like(hist), 0.5, 1000)
+    sel, m, fell = fb.ops.select_topk_binned(keys, counts, torch.zeros_like(hist), 0.5, 1000, return_fallbacks=True)
+    assert fell.tolist() == [1, 1]
+    _, _, fell = fb.ops.select_topk_binned(keys, counts, hist, 0.5, 1000, return_fallbacks=True)
+    assert fell.tolist() == [0, 0], "well-spread scores must be finished by the binned path"
     for gi in range(2):
         want = oracle_topk(s[gi], 0.5, 1000)
         assert torch.equal(sel[gi].cpu(), want)

@@ -138,6 +138,7 @@ def test_yolo_full_batch_properties(fb):
     mod = fb.workloads.YOLOV3BBox(sizes=sizes)
     dets, labels, flat_ids, cnt = [t.clone() for t in mod.forward_padded(maps)]
     fb.ops.raise_on_status(mod._plan.status, "yolo")
+    assert mod._plan.select_fallbacks() == 0, "the binned top-k must finish these images itself"
     mod8 = fb.workloads.YOLOV3BBox(sizes=sizes)
     for start in (0, 56):
         d8, l8, f8, c8 = mod8.forward_padded([m[start:start + 8].contiguous() for m in maps])
