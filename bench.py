@@ -367,6 +367,39 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_single_workload(args):
+    """Runs a few steps of ONE of the other workloads and exits (no JSON line): the command ncu captures wrap."""
+    import torch
+    import functs_b200 as fb
+    from oracle import workloads as W  # seeded input generator only
+    dev = "cuda"
+    b = args.batch
+    if args.only == "ssd":
+        loc, conf = [t.to(dev) for t in W.make_ssd_inputs(b)]
+        mod = fb.workloads.SSDBBox(W.ssd_priors(), device=dev)
+        fn = lambda: mod.forward_padded(loc, conf)
+    elif args.only == "yolact":
+        proto, coef, boxes = [t.to(dev) for t in W.make_yolact_inputs(b)]
+        mod = fb.workloads.YolactBBoxMask(device=dev)
+        fn = lambda: mod(proto, coef, boxes)
+    elif args.only == "lstm":
+        x, w_ih, w_hh, b_ih, b_hh = W.make_lstm_inputs(64, b, 512)
+        mod = fb.workloads.LSTM(w_ih, w_hh, b_ih, b_hh, device=dev)
+        xd = x.to(dev)
+        fn = lambda: mod.forward_device(xd)
+    elif args.only == "get_started":
+        a, bb, n = W.make_get_started_inputs()
+        fn = lambda: fb.workloads.get_started(a, bb.to(dev), n)
+    else:
+        maps = [m.to(dev) for m in W.make_yolo_inputs(b)]
+        mod = fb.workloads.YOLOV3BBox(device=dev)
+        fn = lambda: mod.forward_padded(maps)
+    for _ in range(args.warmup + args.steps):
+        fn()
+    torch.cuda.synchronize()
+    print(f"ran {args.only} batch {b}: {args.warmup + args.steps} calls")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -374,7 +407,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the cpu_baseline leg and the other workloads")
+    ap.add_argument("--only", default=None, choices=["yolo", "ssd", "yolact", "lstm", "get_started"],
+                    help="run a few calls of one workload and exit (for profiler captures)")
+    ap.add_argument("--batch", type=int, default=8, help="batch size for --only")
     args = ap.parse_args()
+    if args.only is not None:
+        run_single_workload(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -123,6 +123,13 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
     float c_state = 0.0f;
     if (tid == 0) s_abort = 0;
     __syncthreads();
+    // the input projection of step t does not depend on h: it is fetched one step ahead, before the inter-step wait
+    float pre_g[4] = {0.f, 0.f, 0.f, 0.f};
+    if (b0 + eb < B) {
+        const float* prow = pre + (static_cast<int64_t>(0) * B + b0 + eb) * (4 * H) + j0 + ej;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) pre_g[g] = __ldg(prow + g * H);
+    }
 
     for (int t = 0; t < T; ++t) {
         // ---- wait until every CTA has published hs[t-1] ----
@@ -139,7 +146,6 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
                         if (status != nullptr) atomicOr(status, FB_STATUS_WAIT_TIMEOUT);
                         break;
                     }
-                    __nanosleep(32);
                 }
             }
             __syncthreads();
@@ -184,13 +190,17 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
             const int gb = b0 + eb;
             if (gb < B) {
                 float gate[4];
-                const float* prow = pre + (static_cast<int64_t>(t) * B + gb) * (4 * H) + j0 + ej;
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     float s = 0.0f;
 #pragma unroll
                     for (int s16 = 0; s16 < kRecKS; ++s16) s = __fadd_rn(s, part[(s16 * kRecB + eb) * kPartStride + g * 8 + ej]);
-                    gate[g] = __fadd_rn(__ldg(prow + g * H), s);
+                    gate[g] = __fadd_rn(pre_g[g], s);
+                }
+                if (t + 1 < T) {
+                    const float* prow = pre + (static_cast<int64_t>(t + 1) * B + gb) * (4 * H) + j0 + ej;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) pre_g[g] = __ldg(prow + g * H);
                 }
                 const float ig = sigmoid_f32(gate[0]);
                 const float fg = sigmoid_f32(gate[1]);
