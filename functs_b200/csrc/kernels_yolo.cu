@@ -23,15 +23,14 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
 constexpr int kYoloThreads = 128;
 constexpr int kYoloClasses = 80;
 constexpr int kYoloAttrib = 85;
-constexpr int kYoloChunk = 8;        // class planes loaded per thread before any is consumed (x VEC positions each)
+constexpr int kYoloChunk = 16;       // class logits loaded per thread before any is consumed
+constexpr int kYoloSub = 8;          // logits whose hits are queued at once: <= 32 lanes * 8 = 256 new entries
 constexpr int kYoloWarpStage = 96;   // staged candidate keys per warp (flushed when fewer than 32 slots remain)
-constexpr int kYoloSub = 4;           // class planes whose hits are queued at once: <= 32 lanes * 4 planes * 4 positions = 512
-constexpr int kYoloQueue = 1024;     // circular queue of pending hits per warp (512 new + < 32 left over)
+constexpr int kYoloQueue = 512;      // circular queue of pending hits per warp (256 new + < 32 left over)
 
 struct YoloParams {
     const float* map[3];
     int size[3];        // S
-    int vec[3];         // positions per thread: 4 when S*S % 4 == 0 (128-bit loads), else 1
     int tiles[3];       // position tiles per (image, anchor) plane
     int tile_begin[4];  // first CTA of every level, [3] = total
     int box_begin[3];   // first box index of every level inside an image
@@ -55,13 +54,14 @@ struct YoloParams {
 
 struct __align__(8) YoloHit {
     float v;        // class logit
-    uint32_t meta;  // position inside the CTA tile << 8 | class
+    uint32_t meta;  // owning lane << 8 | class
 };
 
 struct YoloWarpSmem {
     uint64_t stage[kYoloWarpStage];
     YoloHit queue[kYoloQueue];
-    int qtail;  // entries ever pushed (the warp keeps the matching head in a register)
+    float vals[kYoloSub][32];  // the logits of the current sub-chunk, so that a hit can be fetched by a runtime index
+    int qtail;                 // total entries ever pushed (the warp keeps the matching head in a register)
 };
 
 // Appends the staged keys of a warp to the image's candidate list (one atomic per flush).
@@ -81,24 +81,27 @@ __device__ __forceinline__ void yolo_flush(YoloWarpSmem& ws, int& fill, uint64_t
     fill = 0;
 }
 
-// One dense batch: lane i evaluates queue entry head + i (nb <= 32 entries): score = objectness * sigmoid(logit),
-// compared with the threshold exactly; hits go to the staging buffer and to the score histogram.
-__device__ __forceinline__ void yolo_eval_batch(YoloWarpSmem& ws, int head, int nb, const float* so_s, uint32_t flat_tile,
+// One dense batch: lane i evaluates queue entry head + i (nb <= 32 entries).  Objectness comes from the owning
+// lane by shuffle; hits go to the staging buffer and to the score histogram.
+__device__ __forceinline__ void yolo_eval_batch(YoloWarpSmem& ws, int head, int nb, float so, uint32_t flat0,
                                                 const YoloParams& P, int img, int& fill, uint64_t* gkeys,
                                                 int32_t* gcount) {
     const int lane = threadIdx.x & 31;
     const bool act = lane < nb;
     YoloHit e;
     e.v = 0.0f;
-    e.meta = 0u;
+    e.meta = static_cast<uint32_t>(lane) << 8;
     if (act) e = ws.queue[(head + lane) & (kYoloQueue - 1)];
-    const uint32_t pos = e.meta >> 8, cls = e.meta & 255u;
-    const float s = __fmul_rn(so_s[pos], sigmoid_f32(e.v));
+    const int src = static_cast<int>(e.meta >> 8);
+    const int cls = static_cast<int>(e.meta & 255u);
+    const float so_src = __shfl_sync(kFullMask, so, src);
+    const float s = __fmul_rn(so_src, sigmoid_f32(e.v));
     const bool pred = act && (s > P.thr);
     const unsigned m = __ballot_sync(kFullMask, pred);
     if (pred) {
         const int off = __popc(m & ((1u << lane) - 1u));
-        ws.stage[fill + off] = make_key(s, flat_tile + pos * (3u * kYoloClasses) + cls);
+        const uint32_t flat_src = flat0 + static_cast<uint32_t>((src - lane) * 3 * kYoloClasses);
+        ws.stage[fill + off] = make_key(s, flat_src + static_cast<uint32_t>(cls));
         if (P.hist != nullptr) {
             const int d = hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift);
             atomicAdd(P.hist + static_cast<int64_t>(img) * kHistBins + d, 1);
@@ -108,75 +111,56 @@ __device__ __forceinline__ void yolo_eval_batch(YoloWarpSmem& ws, int head, int 
     if (fill + 32 > kYoloWarpStage) yolo_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
 }
 
-template <int VEC> struct YoloVec;
-template <> struct YoloVec<4> {
-    using T = float4;
-    static __device__ __forceinline__ void unpack(const float4& q, float* o) { o[0] = q.x; o[1] = q.y; o[2] = q.z; o[3] = q.w; }
-};
-template <> struct YoloVec<1> {
-    using T = float;
-    static __device__ __forceinline__ void unpack(const float& q, float* o) { o[0] = q; }
-};
-
-// Body for one pyramid level.  A CTA owns 128 * VEC consecutive positions of one (image, anchor) plane; a thread owns
-// VEC of them (one 128-bit load per channel plane when VEC = 4).
-//   pass A: the five box channels -> decoded box, objectness (kept in shared memory), per-position logit cut
-//   pass B: the 80 class planes, 8 at a time: compare against the cut, queue the few hits, evaluate them densely
-template <int VEC, bool DENSE>
-__device__ __forceinline__ void yolo_decode_level(const YoloParams& P, const int lvl, const int local, YoloWarpSmem& ws,
-                                                  float* so_cta) {
-    using V = typename YoloVec<VEC>::T;
-    const int S = P.size[lvl];
+// Body for one pyramid level.  S_T > 0 fixes the map size at compile time (channel strides become immediates).
+template <int S_T, bool DENSE>
+__device__ __forceinline__ void yolo_decode_level(const YoloParams& P, const int lvl, const int local, YoloWarpSmem& ws) {
+    const int S = S_T > 0 ? S_T : P.size[lvl];
     const int SS = S * S;
     const int plane = local / P.tiles[lvl];  // = image * 3 + anchor
     const int tile = local - plane * P.tiles[lvl];
     const int img = plane / 3;
     const int anc = plane - img * 3;
+    const int p = tile * kYoloThreads + threadIdx.x;
     const int lane = threadIdx.x & 31;
-    const int tile_p0 = tile * (kYoloThreads * VEC);
-    const int lp = threadIdx.x * VEC;         // first position of this thread inside the tile
-    const int p = tile_p0 + lp;
-    const bool valid = p < SS;                // SS % VEC == 0: a thread's positions are all valid or all invalid
-    const int pp = valid ? p : 0;             // invalid threads load position 0 (legal address, results unused)
+    // Lanes past the end of the plane are clamped so that every lane loads a legal address.  A warp is then either
+    // fully valid, or its tail lanes all alias position SS - 1; aliased lanes never produce candidates.
+    const bool valid = p < SS;
+    const int pp = valid ? p : (SS - 1);
     const float* __restrict__ src = P.map[lvl] + (static_cast<int64_t>(img) * 255 + anc * kYoloAttrib) * SS + pp;
 
-    float t[5][VEC];
-#pragma unroll
-    for (int c = 0; c < 5; ++c) YoloVec<VEC>::unpack(__ldg(reinterpret_cast<const V*>(src + c * SS)), t[c]);
+    const float t0 = __ldg(src);
+    const float t1 = __ldg(src + SS);
+    const float t2 = __ldg(src + 2 * SS);
+    const float t3 = __ldg(src + 3 * SS);
+    const float t4 = __ldg(src + 4 * SS);
     const float* __restrict__ csrc = src + 5 * SS;
-    V vraw[kYoloChunk];
+    float v[kYoloChunk];
 #pragma unroll
-    for (int u = 0; u < kYoloChunk; ++u) vraw[u] = __ldg(reinterpret_cast<const V*>(csrc + u * SS));
+    for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + u * SS);
 
-    float* so_s = so_cta + (threadIdx.x >> 5) * (32 * VEC);  // this warp's objectness values
-    float v_cut[VEC];
+    const int gy = pp / S, gx = pp - gy * S;
     const float stride = P.stride[lvl];
-    const float aw = P.anchor_w[lvl][anc], ah = P.anchor_h[lvl][anc];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-        const int q = pp + j;
-        const int gy = q / S, gx = q - gy * S;
-        const float cx = __fmul_rn(__fadd_rn(sigmoid_f32(t[0][j]), static_cast<float>(gx)), stride);
-        const float cy = __fmul_rn(__fadd_rn(sigmoid_f32(t[1][j]), static_cast<float>(gy)), stride);
-        const float hw = __fmul_rn(__fmul_rn(expf(t[2][j]), aw), 0.5f);
-        const float hh = __fmul_rn(__fmul_rn(expf(t[3][j]), ah), 0.5f);
-        const float so = sigmoid_f32(t[4][j]);
-        so_s[lane * VEC + j] = so;
-        // Logit cut: score = so * sigmoid(v) can exceed thr only if sigmoid(v) > thr / so.  The cut is placed a
-        // relative 1e-5 below that (hundreds of fp32 ulps, covering the rounding of sigmoid and of the product) and
-        // another 0.02 lower in the logit domain (covering the rounding of the logit itself), so it never loses a
-        // candidate; everything above the cut is evaluated exactly.
-        v_cut[j] = INFINITY;
-        if (valid && so > P.thr) {
-            const float r = (P.thr / so) * (1.0f - 1.0e-5f);
-            v_cut[j] = logf(r / (1.0f - r)) - 0.02f;
-        }
-        if (valid) {
-            const int64_t gbox = static_cast<int64_t>(img) * P.num_boxes + P.box_begin[lvl] + q * 3 + anc;
-            reinterpret_cast<float4*>(P.boxes)[gbox] =
-                make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
-            if (DENSE && P.obj_out != nullptr) P.obj_out[gbox] = so;
-        }
+    const float cx = __fmul_rn(__fadd_rn(sigmoid_f32(t0), static_cast<float>(gx)), stride);
+    const float cy = __fmul_rn(__fadd_rn(sigmoid_f32(t1), static_cast<float>(gy)), stride);
+    const float hw = __fmul_rn(__fmul_rn(expf(t2), P.anchor_w[lvl][anc]), 0.5f);
+    const float hh = __fmul_rn(__fmul_rn(expf(t3), P.anchor_h[lvl][anc]), 0.5f);
+    const float so = sigmoid_f32(t4);
+    const int box = P.box_begin[lvl] + pp * 3 + anc;
+    const int64_t gbox = static_cast<int64_t>(img) * P.num_boxes + box;
+    if (valid) {
+        reinterpret_cast<float4*>(P.boxes)[gbox] =
+            make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
+        if (DENSE && P.obj_out != nullptr) P.obj_out[gbox] = so;
+    }
+
+    // Logit cut: score = so * sigmoid(v) can exceed thr only if sigmoid(v) > thr / so.  The cut is placed a
+    // relative 1e-5 below that (hundreds of fp32 ulps, covering the rounding of sigmoid and of the product) and
+    // another 0.02 lower in the logit domain (covering the rounding of the logit itself), so it never loses a
+    // candidate; everything above the cut is evaluated exactly.
+    float v_cut = INFINITY;
+    if (valid && so > P.thr) {
+        const float q = (P.thr / so) * (1.0f - 1.0e-5f);
+        v_cut = logf(q / (1.0f - q)) - 0.02f;
     }
 
     int fill = 0;    // staged keys (warp-uniform)
@@ -186,81 +170,72 @@ __device__ __forceinline__ void yolo_decode_level(const YoloParams& P, const int
     __syncwarp();
     uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
     int32_t* gcount = P.counts + img;
-    // flat index of (first position of this WARP's slice, class 0); queue entries hold positions relative to it
-    const int warp_p0 = tile_p0 + (threadIdx.x >> 5) * (32 * VEC);
-    const uint32_t flat_tile = static_cast<uint32_t>(P.box_begin[lvl] + warp_p0 * 3 + anc) * kYoloClasses;
-    const uint32_t meta_lane = static_cast<uint32_t>(lane * VEC) << 8;
+    // flat index of class 0 of this lane's UNCLAMPED position (dense batches offset it to the owning lane)
+    const uint32_t flat0 = static_cast<uint32_t>(P.box_begin[lvl] + p * 3 + anc) * kYoloClasses;
 
 #pragma unroll 1
     for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
-        float v[kYoloChunk][VEC];
+        if (c0 > 0) {
 #pragma unroll
-        for (int u = 0; u < kYoloChunk; ++u) YoloVec<VEC>::unpack(vraw[u], v[u]);
-        if (c0 + kYoloChunk < kYoloClasses) {  // next chunk's loads are in flight while this one is consumed
-#pragma unroll
-            for (int u = 0; u < kYoloChunk; ++u)
-                vraw[u] = __ldg(reinterpret_cast<const V*>(csrc + (c0 + kYoloChunk + u) * SS));
+            for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + (c0 + u) * SS);
         }
         if (DENSE) {
             if (valid && P.cls_out != nullptr) {
 #pragma unroll
-                for (int u = 0; u < kYoloChunk; ++u)
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) {
-                        const int64_t gbox = static_cast<int64_t>(img) * P.num_boxes + P.box_begin[lvl] + (pp + j) * 3 + anc;
-                        P.cls_out[gbox * kYoloClasses + c0 + u] = sigmoid_f32(v[u][j]);
-                    }
+                for (int u = 0; u < kYoloChunk; ++u) P.cls_out[gbox * kYoloClasses + c0 + u] = sigmoid_f32(v[u]);
             }
         }
 #pragma unroll
         for (int h = 0; h < kYoloChunk; h += kYoloSub) {
-            int cnt = 0;
+            uint32_t hits = 0u;
 #pragma unroll
-            for (int u = h; u < h + kYoloSub; ++u)
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) cnt += (v[u][j] > v_cut[j]) ? 1 : 0;
+            for (int u = 0; u < kYoloSub; ++u) hits |= (v[h + u] > v_cut ? 1u : 0u) << u;
+            const int cnt = __popc(hits);
             const int total = __reduce_add_sync(kFullMask, cnt);
             if (total > 0) {  // warp-uniform
+                __syncwarp();
+#pragma unroll
+                for (int u = 0; u < kYoloSub; ++u) ws.vals[u][lane] = v[h + u];
                 if (cnt > 0) {
                     int pos = atomicAdd(&ws.qtail, cnt);
-#pragma unroll
-                    for (int u = h; u < h + kYoloSub; ++u)
-#pragma unroll
-                        for (int j = 0; j < VEC; ++j) {
-                            if (v[u][j] > v_cut[j]) {
-                                YoloHit e;
-                                e.v = v[u][j];
-                                e.meta = meta_lane + (static_cast<uint32_t>(j) << 8) + static_cast<uint32_t>(c0 + u);
-                                ws.queue[pos & (kYoloQueue - 1)] = e;
-                                ++pos;
-                            }
-                        }
+                    const uint32_t meta0 = (static_cast<uint32_t>(lane) << 8) | static_cast<uint32_t>(c0 + h);
+                    while (hits) {
+                        const int u = __ffs(hits) - 1;
+                        hits &= hits - 1u;
+                        YoloHit e;
+                        e.v = ws.vals[u][lane];
+                        e.meta = meta0 + static_cast<uint32_t>(u);
+                        ws.queue[pos & (kYoloQueue - 1)] = e;
+                        ++pos;
+                    }
                 }
                 __syncwarp();
                 pushed += total;  // == ws.qtail
                 while (pushed - head >= 32) {
-                    yolo_eval_batch(ws, head, 32, so_s, flat_tile, P, img, fill, gkeys, gcount);
+                    yolo_eval_batch(ws, head, 32, so, flat0, P, img, fill, gkeys, gcount);
                     head += 32;
                 }
             }
         }
     }
     const int rest = pushed - head;
-    if (rest > 0) yolo_eval_batch(ws, head, rest, so_s, flat_tile, P, img, fill, gkeys, gcount);
+    if (rest > 0) yolo_eval_batch(ws, head, rest, so, flat0, P, img, fill, gkeys, gcount);
     if (fill > 0) yolo_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
 }
 
-template <bool DENSE>
+template <int S0, int S1, int S2, bool DENSE>
 __global__ void __launch_bounds__(kYoloThreads)
 yolo_decode_kernel(const YoloParams P) {
     __shared__ YoloWarpSmem smem_all[kYoloThreads / 32];
-    __shared__ __align__(16) float so_cta[kYoloThreads * 4];
     YoloWarpSmem& ws = smem_all[threadIdx.x >> 5];
     const int cta = blockIdx.x;
-    const int lvl = (cta >= P.tile_begin[2]) ? 2 : (cta >= P.tile_begin[1] ? 1 : 0);
-    const int local = cta - P.tile_begin[lvl];
-    if (P.vec[lvl] == 4) yolo_decode_level<4, DENSE>(P, lvl, local, ws, so_cta);
-    else yolo_decode_level<1, DENSE>(P, lvl, local, ws, so_cta);
+    if (cta >= P.tile_begin[2]) {
+        yolo_decode_level<S2, DENSE>(P, 2, cta - P.tile_begin[2], ws);
+    } else if (cta >= P.tile_begin[1]) {
+        yolo_decode_level<S1, DENSE>(P, 1, cta - P.tile_begin[1], ws);
+    } else {
+        yolo_decode_level<S0, DENSE>(P, 0, cta, ws);
+    }
 }
 
 static const float kAnchors[3][3][2] = {{{116, 90}, {156, 198}, {373, 326}},
@@ -286,9 +261,7 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     int box_acc = 0;
     for (int l = 0; l < 3; ++l) {
         P.size[l] = S[l];
-        // 128-bit loads need every channel plane of the level to start on a 16-byte boundary
-        P.vec[l] = ((S[l] * S[l]) % 4 == 0 && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 4 : 1;
-        P.tiles[l] = (S[l] * S[l] + kYoloThreads * P.vec[l] - 1) / (kYoloThreads * P.vec[l]);
+        P.tiles[l] = (S[l] * S[l] + kYoloThreads - 1) / kYoloThreads;
         P.tile_begin[l] = static_cast<int>(tile_acc);
         tile_acc += static_cast<int64_t>(P.tiles[l]) * 3 * batch;
         P.box_begin[l] = box_acc;
@@ -322,8 +295,15 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
             FB_TRY(check_cuda(cudaMemsetAsync(hist, 0, sizeof(int32_t) * batch * kHistBins, st), "memset hist"));
     }
     const unsigned nblk = static_cast<unsigned>(tile_acc);
-    if (obj_out != nullptr || cls_out != nullptr) yolo_decode_kernel<true><<<nblk, kYoloThreads, 0, st>>>(P);
-    else yolo_decode_kernel<false><<<nblk, kYoloThreads, 0, st>>>(P);
+    const bool dense = obj_out != nullptr || cls_out != nullptr;
+    const bool std_sizes = s0 == 13 && s1 == 26 && s2 == 52;  // the configured pyramid: strides compiled in
+    if (dense) {
+        if (std_sizes) yolo_decode_kernel<13, 26, 52, true><<<nblk, kYoloThreads, 0, st>>>(P);
+        else yolo_decode_kernel<0, 0, 0, true><<<nblk, kYoloThreads, 0, st>>>(P);
+    } else {
+        if (std_sizes) yolo_decode_kernel<13, 26, 52, false><<<nblk, kYoloThreads, 0, st>>>(P);
+        else yolo_decode_kernel<0, 0, 0, false><<<nblk, kYoloThreads, 0, st>>>(P);
+    }
     count_launch();
     return check_launch("yolo_decode_kernel");
 }
