@@ -166,7 +166,7 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
         // ---- partial dot products over this thread's k-slice ----
         {
             const float* hrow = h_s + ks * KSL + ks * 4;
-#pragma unroll 2
+#pragma unroll 4
             for (int b = 0; b < kRecB; ++b) {
                 float a0 = 0.0f, a1 = 0.0f;
 #pragma unroll

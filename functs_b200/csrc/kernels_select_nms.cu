@@ -100,8 +100,8 @@ select_topk_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restri
 // appends keys above d* to the group's `sel` list and keys inside d* to its `bin` list.  CTAs then take a ticket;
 // the one that draws the last ticket sorts the bin list, tops `sel` up from it and writes the sorted result.
 // No CTA ever waits for another one.
-constexpr int kBinThreads = 256;
-constexpr int kBinSplit = 16;        // CTAs per group
+constexpr int kBinThreads = 1024;
+constexpr int kBinSplit = 4;         // CTAs per group
 constexpr int kBinListGlobal = 2048; // capacity of the boundary-bucket list; beyond it the generic selection runs
 
 struct SelectCtr {
@@ -259,16 +259,27 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
 constexpr int kNmsMaxN = 1024;
 constexpr int kNmsWords = kNmsMaxN / 32;
 constexpr int kMaskThreads = 256;
-constexpr int kMaskRowsPerCta = 64;   // 8 rows per warp, interleaved over the CTAs of a group
+constexpr int kMaskRowsPerCta = 128;  // 16 rows per warp, interleaved over the CTAs of a group
+constexpr int kMaskMaxBuckets = 1024; // class buckets used for pruning (more classes than this: one bucket)
 constexpr int kScanThreads = 1024;
 
-// grid = (ceil(topk / 64), groups); block = 256.
+// grid = (ceil(topk / 128), groups); block = 256.
+// Class pruning.  With class offsets, class c occupies the coordinate range [c*M + lo, c*M + hi] (M = hi + 1, lo / hi the
+// extreme coordinates of the selected boxes), so boxes whose labels differ by more than K = floor((hi - lo) / M) + 1
+// cannot intersect.  The candidates are bucketed by label (counting sort in shared memory) and a row only tests the
+// members of the buckets within K of its own label; every pair that can intersect is still tested with the exact
+// IoU expression, so the matrix is the same as the one an all-pairs loop produces.
 __global__ void __launch_bounds__(kMaskThreads)
 nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
                 const int32_t* __restrict__ sel_counts, int topk, float thr, float thr_lo, float thr_hi, int class_offset,
                 uint32_t* __restrict__ mask_g) {
     __shared__ NmsBox sb[kNmsMaxN];
-    __shared__ float red[kMaskThreads / 32 + 1];
+    __shared__ uint16_t slabel[kNmsMaxN];   // bucket of every candidate
+    __shared__ uint16_t order[kNmsMaxN];    // candidates grouped by bucket
+    __shared__ int bstart[kMaskMaxBuckets + 1];
+    __shared__ int bcursor[kMaskMaxBuckets];
+    __shared__ uint32_t rowbuf[kMaskThreads / 32][kNmsWords];
+    __shared__ float red_hi[kMaskThreads / 32 + 1], red_lo[kMaskThreads / 32 + 1];
     const int g = blockIdx.y;
     const int t = threadIdx.x;
     const int lane = t & 31, warp = t >> 5;
@@ -279,12 +290,14 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
     const float* boxes_g = boxes + static_cast<int64_t>(g) * num_boxes * 4;
     const uint64_t* sel = sel_keys + static_cast<int64_t>(g) * topk;
     uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
+    const int nb = (class_offset && num_classes <= kMaskMaxBuckets) ? num_classes : 1;
 
     // gather: thread t owns candidates t, t + 256, ...
     constexpr int kPer = kNmsMaxN / kMaskThreads;
     float4 bx[kPer];
     int label[kPer];
-    float lmax = -INFINITY;
+    float lmax = -INFINITY, lmin = INFINITY;
+    for (int i = t; i < nb; i += kMaskThreads) bcursor[i] = 0;
 #pragma unroll
     for (int q = 0; q < kPer; ++q) {
         const int c = t + q * kMaskThreads;
@@ -296,20 +309,41 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
             label[q] = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
             bx[q] = reinterpret_cast<const float4*>(boxes_g)[box];
             lmax = fmaxf(lmax, fmaxf(fmaxf(bx[q].x, bx[q].y), fmaxf(bx[q].z, bx[q].w)));
+            lmin = fminf(lmin, fminf(fminf(bx[q].x, bx[q].y), fminf(bx[q].z, bx[q].w)));
         }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
-    if (lane == 0) red[warp] = lmax;
-    __syncthreads();
-    if (t < 32) {
-        float v = (t < kMaskThreads / 32) ? red[t] : -INFINITY;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
-        if (t == 0) red[kMaskThreads / 32] = v;
+    for (int o = 16; o > 0; o >>= 1) {
+        lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
+        lmin = fminf(lmin, __shfl_xor_sync(kFullMask, lmin, o));
+    }
+    if (lane == 0) {
+        red_hi[warp] = lmax;
+        red_lo[warp] = lmin;
     }
     __syncthreads();
-    const float scale = __fadd_rn(red[kMaskThreads / 32], 1.0f);
+    if (t < 32) {
+        float v = (t < kMaskThreads / 32) ? red_hi[t] : -INFINITY;
+        float u = (t < kMaskThreads / 32) ? red_lo[t] : INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
+            u = fminf(u, __shfl_xor_sync(kFullMask, u, o));
+        }
+        if (t == 0) {
+            red_hi[kMaskThreads / 32] = v;
+            red_lo[kMaskThreads / 32] = u;
+        }
+    }
+    __syncthreads();
+    const float hi = red_hi[kMaskThreads / 32], lo = red_lo[kMaskThreads / 32];
+    const float scale = __fadd_rn(hi, 1.0f);
+    // label distance beyond which two boxes cannot intersect (one extra bucket covers the fp32 rounding of the shifts)
+    int reach = nb;
+    if (nb > 1 && scale > 0.0f) {
+        const float r = floorf((hi - lo) / scale) + 1.0f;
+        if (r < static_cast<float>(nb)) reach = static_cast<int>(r);
+    }
 #pragma unroll
     for (int q = 0; q < kPer; ++q) {
         const int c = t + q * kMaskThreads;
@@ -317,22 +351,60 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
             const float off = class_offset ? __fmul_rn(static_cast<float>(label[q]), scale) : 0.0f;
             sb[c] = make_nms_box(__fadd_rn(bx[q].x, off), __fadd_rn(bx[q].y, off), __fadd_rn(bx[q].z, off),
                                  __fadd_rn(bx[q].w, off));
+            const int bucket = nb > 1 ? label[q] : 0;
+            slabel[c] = static_cast<uint16_t>(bucket);
+            atomicAdd(&bcursor[bucket], 1);
         }
     }
     __syncthreads();
+    // exclusive prefix of the bucket counts (one warp, contiguous chunk per lane), then the scatter
+    if (warp == 0) {
+        const int per = (nb + 31) / 32;
+        const int b0 = lane * per, b1 = min(nb, b0 + per);
+        int s = 0;
+        for (int i = b0; i < b1; ++i) s += bcursor[i];
+        int incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += v;
+        }
+        int run = incl - s;
+        for (int i = b0; i < b1; ++i) {
+            const int c = bcursor[i];
+            bstart[i] = run;
+            bcursor[i] = run;
+            run += c;
+        }
+        if (lane == 31) bstart[nb] = incl;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+        const int c = t + q * kMaskThreads;
+        if (c < n) order[atomicAdd(&bcursor[slabel[c]], 1)] = static_cast<uint16_t>(c);
+    }
+    __syncthreads();
 
-    const int words = (n + 31) >> 5;
+    uint32_t* myrow = rowbuf[warp];
     for (int rr = 0; rr < kMaskRowsPerCta / (kMaskThreads / 32); ++rr) {
         const int i = (warp * (kMaskRowsPerCta / (kMaskThreads / 32)) + rr) * rt + blockIdx.x;
         if (i >= n) continue;  // warp-uniform
         const NmsBox bi = sb[i];
-        uint32_t bits = 0u;
-        for (int w = i >> 5; w < words; ++w) {
-            const int j = w * 32 + lane;
-            const unsigned m = nms_row_word(bi, sb, j, j > i && j < n, thr, thr_lo, thr_hi);
-            if (lane == w) bits = m;
+        const int li = slabel[i];
+        const int p0 = bstart[max(li - reach, 0)], p1 = bstart[min(li + reach + 1, nb)];
+        myrow[lane] = 0u;
+        __syncwarp();
+        for (int base = p0; base < p1; base += 32) {
+            const int p = base + lane;
+            if (p < p1) {
+                const int j = order[p];
+                if (j > i && iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi)) atomicOr(&myrow[j >> 5], 1u << (j & 31));
+            }
         }
-        gmask[i * kNmsWords + lane] = bits;
+        __syncwarp();
+        gmask[i * kNmsWords + lane] = myrow[lane];
+        __syncwarp();
     }
 }
 

@@ -458,27 +458,28 @@ __device__ __forceinline__ void warp_nms_scan(const uint32_t* mask, int row_stri
     uint32_t removed = 0u;  // lane l tracks word l
     for (int w = 0; w < words; ++w) {
         uint32_t r = __shfl_sync(kFullMask, removed, w);
-        uint32_t keepw = 0u;
         const int base = w * 32;
-        // decisions inside the 32x32 diagonal block (every lane computes the same thing from broadcast reads)
-        uint32_t diag[32];
-#pragma unroll
-        for (int b = 0; b < 32; ++b) diag[b] = (base + b < n) ? mask[(base + b) * row_stride + w] : 0u;
+        const int rows = min(32, n - base);
+        // loads first (none depends on a decision): the diagonal 32x32 block (broadcast reads, identical on every
+        // lane) and this lane's column word of the 32 rows
+        uint32_t diag[32], col[32];
 #pragma unroll
         for (int b = 0; b < 32; ++b) {
-            bool alive = (base + b < n) && !((r >> b) & 1u);
-            if (alive) {
-                keepw |= (1u << b);
-                r |= diag[b];
-            }
+            const bool in = b < rows;
+            diag[b] = in ? mask[(base + b) * row_stride + w] : 0u;
+            col[b] = (in && lane < words) ? mask[(base + b) * row_stride + lane] : 0u;
+        }
+        // 32 serial decisions, branch-free: box b is kept iff its bit of r is still clear
+        uint32_t keepw = 0u;
+#pragma unroll
+        for (int b = 0; b < 32; ++b) {
+            const uint32_t alive = (b < rows && !(r & (1u << b))) ? 0xffffffffu : 0u;
+            keepw |= alive & (1u << b);
+            r |= diag[b] & alive;
         }
         // kept rows of this block remove columns in the later words
-        if (lane < words) {
-#pragma unroll 8
-            for (int b = 0; b < 32; ++b) {
-                if ((keepw >> b) & 1u) removed |= mask[(base + b) * row_stride + lane];
-            }
-        }
+#pragma unroll
+        for (int b = 0; b < 32; ++b) removed |= (keepw & (1u << b)) ? col[b] : 0u;
         if (lane == 0) keep_words[w] = keepw;
     }
 }
