@@ -85,8 +85,3 @@ def test_script_front_door(fjit):
     f = fjit.script(get_started)
     a, b = rnd(8, 16), rnd(8, 16, seed=1)
     assert torch.equal(f(a.cuda(), b.cuda(), 5).cpu(), get_started(a, b, 5))
-
-
-def test_immut_ops_have_no_cpu_kernel(fjit):
-    with pytest.raises((RuntimeError, NotImplementedError)):
-        torch.ops.immut.select(rnd(3, 4), 0, 1)
