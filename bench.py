@@ -342,7 +342,7 @@ def run_ours(args):
             "gpu_launches": launches,
             "e2e": {"value": world * 1e3 / e2e_ms, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
                     "d2h_bytes_per_step": bytes_out, "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "roofline": {"bound": "hbm", "kernel": "yolo_decode_kernel", "achieved": achieved, "peak": hbm_peak,
+            "roofline": {"bound": "hbm", "kernel": "yolo_decode_staged_kernel", "achieved": achieved, "peak": hbm_peak,
                          "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_bytes_per_launch": alg_bytes, "whole_step_frac": (alg_bytes + BATCH * OUT_BYTES_PER_IMG) / (ms_per_step * 1e-3) / 1e9 / hbm_peak},
             "clocks": clocks,

@@ -8,7 +8,8 @@ import os
 from ctypes import POINTER, c_char_p, c_double, c_float, c_int32, c_int64, c_uint64, c_void_p
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libfuncts_b200.so")
+# FUNCTS_B200_LIBRARY names another build of the same library (for example one compiled with profiling marks).
+LIB_PATH = os.environ.get("FUNCTS_B200_LIBRARY") or os.path.join(_PKG, "libfuncts_b200.so")
 
 FB_OK = 0
 FB_STATUS_CAND_OVERFLOW = 1

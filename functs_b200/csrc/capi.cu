@@ -35,6 +35,26 @@ void record_stage_event(int index, cudaStream_t st) {
     if (index >= 0 && index < g_num_stage_events && g_stage_events[index] != nullptr) cudaEventRecord(g_stage_events[index], st);
 }
 
+#ifdef FB_PHASE_PROBE
+static struct { const char* file; void (*fn)(unsigned long long*, int); } g_phase_readers[32];
+static int g_num_phase_readers = 0;
+void register_phase_reader(const char* file, void (*fn)(unsigned long long*, int)) {
+    if (g_num_phase_readers < 32) g_phase_readers[g_num_phase_readers++] = {file, fn};
+}
+}  // namespace fb
+extern "C" int functs_b200_phase_read(const char* file_part, unsigned long long* out32, int reset) {
+    for (int i = 0; i < fb::g_num_phase_readers; ++i) {
+        if (strstr(fb::g_phase_readers[i].file, file_part) != nullptr) {
+            cudaDeviceSynchronize();
+            fb::g_phase_readers[i].fn(out32, reset);
+            return 0;
+        }
+    }
+    return 1;
+}
+namespace fb {
+#endif
+
 // ---- group registry -----------------------------------------------------------------------------------
 // A signature names the op sequence of a fusion group the way the group's subgraph prints it, outermost
 // structure first.  Argument conventions are listed per entry; pointers are device pointers.

@@ -98,6 +98,49 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gm
                  : "memory");
 }
 
+// ---- phase clocks (development builds only) ---------------------------------------------------------------
+// Compiled with -DFB_PHASE_PROBE a kernel adds, at every FB_PHASE(k), the cycles its CTA spent since the previous
+// mark to g_phase_cycles[k] (thread 0's clock, after a barrier); functs_b200_phase_read(file name part, out[32], reset)
+// copies the sums of one translation unit to the host.  In the library build the marks expand to nothing.
+#ifdef FB_PHASE_PROBE
+static __device__ unsigned long long g_phase_cycles[32];  // one copy per translation unit
+void register_phase_reader(const char* file, void (*fn)(unsigned long long*, int));
+namespace {
+struct PhaseReader {
+    explicit PhaseReader(const char* file) {
+        register_phase_reader(file, [](unsigned long long* out, int reset) {
+            cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(g_phase_cycles));
+            if (reset) {
+                unsigned long long zero[32] = {0};
+                cudaMemcpyToSymbol(g_phase_cycles, zero, sizeof(zero));
+            }
+        });
+    }
+};
+static PhaseReader g_phase_reader{__BASE_FILE__};
+}  // namespace
+__device__ __forceinline__ long long& phase_prev() {
+    __shared__ long long v;
+    return v;
+}
+#define FB_PHASE_BEGIN()                               \
+    do {                                               \
+        if (threadIdx.x == 0) fb::phase_prev() = clock64(); \
+    } while (0)
+#define FB_PHASE(k)                                                                     \
+    do {                                                                                \
+        __syncthreads();                                                                \
+        if (threadIdx.x == 0) {                                                         \
+            const long long now_ = clock64();                                           \
+            atomicAdd(&fb::g_phase_cycles[k], static_cast<unsigned long long>(now_ - fb::phase_prev())); \
+            fb::phase_prev() = now_;                                                    \
+        }                                                                               \
+    } while (0)
+#else
+#define FB_PHASE_BEGIN() do { } while (0)
+#define FB_PHASE(k) do { } while (0)
+#endif
+
 #endif  // __CUDACC__
 
 }  // namespace fb

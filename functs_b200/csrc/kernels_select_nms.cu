@@ -100,8 +100,8 @@ select_topk_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restri
 // appends keys above d* to the group's `sel` list and keys inside d* to its `bin` list.  CTAs then take a ticket;
 // the one that draws the last ticket sorts the bin list, tops `sel` up from it and writes the sorted result.
 // No CTA ever waits for another one.
-constexpr int kBinThreads = 1024;
-constexpr int kBinSplit = 4;         // CTAs per group
+constexpr int kBinThreads = 512;
+constexpr int kBinSplit = 8;         // CTAs per group
 constexpr int kBinListGlobal = 2048; // capacity of the boundary-bucket list; beyond it the generic selection runs
 
 struct SelectCtr {
@@ -109,15 +109,13 @@ struct SelectCtr {
     int32_t fallback;  // set to 1 when the group was finished by the generic selection (observability only)
 };
 
-union BinnedSmem {
-    SelectSmem<kSelCap> generic;
-    struct {
-        uint64_t sel[kSelCap];
-        uint64_t bin[kBinListGlobal];
-    } fast;
+struct BinnedSmem {
+    uint64_t sel[kSelCap];
+    uint64_t bin[kBinListGlobal];
+    int hist[kHistBins];
 };
 
-__global__ void __launch_bounds__(kBinThreads)
+__global__ void __launch_bounds__(kBinThreads, 2)
 select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restrict__ in_counts, int64_t capacity,
                      const int32_t* __restrict__ hist, uint32_t hist_base, int hist_shift, int32_t topk,
                      SelectCtr* ctr, uint64_t* sel_tmp, uint64_t* bin_tmp, uint64_t* __restrict__ out_keys,
@@ -126,6 +124,7 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     __shared__ int s_dstar, s_above, s_inbin, s_last;
     const int g = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    FB_PHASE_BEGIN();
     int64_t cnt64 = in_counts[g];
     if (cnt64 > capacity) cnt64 = capacity;
     if (cnt64 < 0) cnt64 = 0;
@@ -139,7 +138,7 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     __syncthreads();
     if (n > topk) {
         // stage the group's histogram (coalesced), then one warp finds the boundary bucket
-        int* sh = sm.generic.hist;
+        int* sh = sm.hist;
         const int32_t* h = hist + static_cast<int64_t>(g) * kHistBins;
         for (int i = tid; i < kHistBins; i += kBinThreads) sh[i] = __ldcg(h + i);
         __syncthreads();
@@ -169,10 +168,19 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
         }
     }
     __syncthreads();
+    FB_PHASE(10);
     const int dstar = s_dstar;
     SelectCtr* c = ctr + g;
     uint64_t* gsel = sel_tmp + static_cast<int64_t>(g) * kSelCap;
     uint64_t* gbin = bin_tmp + static_cast<int64_t>(g) * kBinListGlobal;
+    // collect this CTA's share into shared-memory lists first (shared atomics), then reserve space in the group's
+    // global lists with ONE atomic per list and copy
+    __shared__ int s_nsel, s_nbin, s_bsel, s_bbin;
+    if (tid == 0) {
+        s_nsel = 0;
+        s_nbin = 0;
+    }
+    __syncthreads();
     {
         const int lo = static_cast<int>(static_cast<int64_t>(n) * blockIdx.x / gridDim.x);
         const int hi = static_cast<int>(static_cast<int64_t>(n) * (blockIdx.x + 1) / gridDim.x);
@@ -185,36 +193,34 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int d = (k[u] != 0ull) ? hist_digit(k[u], hist_base, hist_shift) : -2;
-                const bool is_sel = d > dstar;
-                const bool is_bin = (d == dstar);
-                const unsigned ms = __ballot_sync(kFullMask, is_sel);
-                const unsigned mb = __ballot_sync(kFullMask, is_bin);
-                if (ms) {
-                    int b0 = 0;
-                    if (lane == 0) b0 = atomicAdd(&c->sel_cnt, __popc(ms));
-                    b0 = __shfl_sync(kFullMask, b0, 0);
-                    if (is_sel) {
-                        const int pos = b0 + __popc(ms & ((1u << lane) - 1u));
-                        if (pos < kSelCap) gsel[pos] = k[u];
-                    }
-                }
-                if (mb) {
-                    int b0 = 0;
-                    if (lane == 0) b0 = atomicAdd(&c->bin_cnt, __popc(mb));
-                    b0 = __shfl_sync(kFullMask, b0, 0);
-                    if (is_bin) {
-                        const int pos = b0 + __popc(mb & ((1u << lane) - 1u));
-                        if (pos < kBinListGlobal) gbin[pos] = k[u];
-                    }
+                if (k[u] == 0ull) continue;
+                const int d = hist_digit(k[u], hist_base, hist_shift);
+                if (d > dstar) {
+                    const int pos = atomicAdd(&s_nsel, 1);
+                    if (pos < kSelCap) sm.sel[pos] = k[u];
+                } else if (d == dstar) {
+                    const int pos = atomicAdd(&s_nbin, 1);
+                    if (pos < kBinListGlobal) sm.bin[pos] = k[u];
                 }
             }
         }
     }
+    __syncthreads();
+    FB_PHASE(11);
+    if (tid == 0) {
+        s_bsel = s_nsel > 0 ? atomicAdd(&c->sel_cnt, s_nsel) : 0;
+        s_bbin = s_nbin > 0 ? atomicAdd(&c->bin_cnt, s_nbin) : 0;
+    }
+    __syncthreads();
+    for (int i = tid; i < min(s_nsel, kSelCap); i += kBinThreads)
+        if (s_bsel + i < kSelCap) gsel[s_bsel + i] = sm.sel[i];
+    for (int i = tid; i < min(s_nbin, kBinListGlobal); i += kBinThreads)
+        if (s_bbin + i < kBinListGlobal) gbin[s_bbin + i] = sm.bin[i];
     __threadfence();
     __syncthreads();
     if (tid == 0) s_last = (atomicAdd(&c->ticket, 1) == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
     __syncthreads();
+    FB_PHASE(12);
     if (!s_last) return;
     __threadfence();
 
@@ -227,30 +233,48 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
                                            sel_cnt + bin_cnt >= topk && bin_cnt <= kBinListGlobal);
     if (!consistent) {
         // the boundary bucket is too crowded (many equal scores) or the histogram does not describe this list:
-        // exact generic selection over the whole list
-        GlobalKeys kf{keys};
+        // leave the group to the exact generic selection (select_fixup_kernel, launched right after this kernel)
         if (tid == 0) c->fallback = 1;
-        const int m = block_select_topk<kBinThreads, kSelCap, 4>(kf, n, topk, sm.generic);
-        __syncthreads();
-        for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < m) ? sm.generic.sel[i] : 0ull;
-        if (tid == 0) out_counts[g] = m;
         return;
     }
-    for (int i = tid; i < sel_cnt; i += kBinThreads) sm.fast.sel[i] = __ldcg(gsel + i);
+    for (int i = tid; i < sel_cnt; i += kBinThreads) sm.sel[i] = __ldcg(gsel + i);
     if (n > topk) {
         const int bn = next_pow2(bin_cnt);
-        for (int i = tid; i < bn; i += kBinThreads) sm.fast.bin[i] = (i < bin_cnt) ? __ldcg(gbin + i) : 0ull;
+        for (int i = tid; i < bn; i += kBinThreads) sm.bin[i] = (i < bin_cnt) ? __ldcg(gbin + i) : 0ull;
         __syncthreads();
-        bitonic_sort_desc<kBinThreads>(sm.fast.bin, bn);
+        bitonic_sort_desc<kBinThreads>(sm.bin, bn);
         const int want = topk - sel_cnt;
-        for (int i = tid; i < want; i += kBinThreads) sm.fast.sel[sel_cnt + i] = sm.fast.bin[i];
+        for (int i = tid; i < want; i += kBinThreads) sm.sel[sel_cnt + i] = sm.bin[i];
     }
+    FB_PHASE(13);
     const int sn = next_pow2(result);
-    for (int i = result + tid; i < sn; i += kBinThreads) sm.fast.sel[i] = 0ull;
+    for (int i = result + tid; i < sn; i += kBinThreads) sm.sel[i] = 0ull;
     __syncthreads();
-    bitonic_sort_desc<kBinThreads>(sm.fast.sel, sn);
-    for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < result) ? sm.fast.sel[i] : 0ull;
+    bitonic_sort_desc<kBinThreads>(sm.sel, sn);
+    FB_PHASE(14);
+    for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < result) ? sm.sel[i] : 0ull;
     if (tid == 0) out_counts[g] = result;
+    FB_PHASE(15);
+}
+
+// Groups that the binned kernel handed back (SelectCtr::fallback) are selected by the generic block-wide routine;
+// for every other group the CTA exits at once.
+__global__ void __launch_bounds__(kSelectThreads)
+select_fixup_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restrict__ in_counts, int64_t capacity,
+                    int32_t topk, const SelectCtr* __restrict__ ctr, uint64_t* __restrict__ out_keys,
+                    int32_t* __restrict__ out_counts) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int g = blockIdx.x;
+    if (ctr[g].fallback == 0) return;
+    SelectSmem<kSelCap>& sm = *reinterpret_cast<SelectSmem<kSelCap>*>(smem_raw);
+    int64_t cnt = in_counts[g];
+    if (cnt > capacity) cnt = capacity;
+    if (cnt < 0) cnt = 0;
+    GlobalKeys kf{in_keys + static_cast<int64_t>(g) * capacity};
+    const int m = block_select_topk<kSelectThreads, kSelCap, 4>(kf, static_cast<int>(cnt), topk, sm);
+    __syncthreads();
+    for (int i = threadIdx.x; i < topk; i += kSelectThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < m) ? sm.sel[i] : 0ull;
+    if (threadIdx.x == 0) out_counts[g] = m;
 }
 
 // ---- NMS: suppression bit matrix (many small CTAs per group) + serial keep-scan (one CTA per group) ------------
@@ -287,6 +311,7 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
     if (n > topk) n = topk;
     const int rt = gridDim.x;
     if (static_cast<int>(blockIdx.x) >= n) return;  // rows are interleaved: i = k * rt + blockIdx.x
+    FB_PHASE_BEGIN();
     const float* boxes_g = boxes + static_cast<int64_t>(g) * num_boxes * 4;
     const uint64_t* sel = sel_keys + static_cast<int64_t>(g) * topk;
     uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
@@ -336,6 +361,7 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
         }
     }
     __syncthreads();
+    FB_PHASE(25);
     const float hi = red_hi[kMaskThreads / 32], lo = red_lo[kMaskThreads / 32];
     const float scale = __fadd_rn(hi, 1.0f);
     // label distance beyond which two boxes cannot intersect (one extra bucket covers the fp32 rounding of the shifts)
@@ -385,6 +411,7 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
         if (c < n) order[atomicAdd(&bcursor[slabel[c]], 1)] = static_cast<uint16_t>(c);
     }
     __syncthreads();
+    FB_PHASE(26);
 
     uint32_t* myrow = rowbuf[warp];
     for (int rr = 0; rr < kMaskRowsPerCta / (kMaskThreads / 32); ++rr) {
@@ -406,6 +433,7 @@ nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
         gmask[i * kNmsWords + lane] = myrow[lane];
         __syncwarp();
     }
+    FB_PHASE(27);
 }
 
 // grid = groups; block = 1024; dynamic smem = 1024 x 32 words.  Stages the group's bit matrix in shared memory, one
@@ -421,6 +449,7 @@ nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
     __shared__ int word_prefix[kNmsWords + 1];
     const int g = blockIdx.x;
     const int t = threadIdx.x;
+    FB_PHASE_BEGIN();
     int n = sel_counts[g];
     if (n > topk) n = topk;
     if (n < 0) n = 0;
@@ -445,8 +474,10 @@ nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
     }
     if (t < kNmsWords) keep_words[t] = 0u;
     __syncthreads();
+    FB_PHASE(20);
     if (t < 32) warp_nms_scan(smask, kNmsWords, n, words, keep_words);
     __syncthreads();
+    FB_PHASE(21);
     if (t == 0) {
         int acc = 0;
         for (int w = 0; w < kNmsWords; ++w) {
@@ -483,6 +514,7 @@ nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
         flat_ids[obase + i] = -1;
         if (keep != nullptr) keep[obase + i] = -1;
     }
+    FB_PHASE(22);
 }
 
 // ---- host launchers (internal C++ API, used by the C ABI and by the YOLO pipeline) ----------------
@@ -541,7 +573,12 @@ int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int6
     select_binned_kernel<<<grid, kBinThreads, 0, st>>>(in_keys, in_counts, capacity, hist, hp.base, hp.shift, topk,
                                                        static_cast<SelectCtr*>(ctr), sel_tmp, bin_tmp, out_keys, out_counts);
     count_launch();
-    return check_launch("select_binned_kernel");
+    FB_TRY(check_launch("select_binned_kernel"));
+    const size_t smem = sizeof(SelectSmem<kSelCap>);
+    select_fixup_kernel<<<groups, kSelectThreads, smem, st>>>(in_keys, in_counts, capacity, topk,
+                                                               static_cast<const SelectCtr*>(ctr), out_keys, out_counts);
+    count_launch();
+    return check_launch("select_fixup_kernel");
 }
 
 int64_t nms_mask_bytes(int groups) { return static_cast<int64_t>(groups) * kNmsMaxN * kNmsWords * sizeof(uint32_t); }

@@ -121,6 +121,7 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
 
     const int cls = blockIdx.x, img = blockIdx.y;
     const int t = threadIdx.x;
+    FB_PHASE_BEGIN();
     const float* src = scores_cm + (static_cast<int64_t>(img) * num_classes + cls) * num_priors;
     if ((num_priors & 3) == 0) {
         const float4* s4 = reinterpret_cast<const float4*>(src);
@@ -130,6 +131,7 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
         for (int i = t; i < num_priors; i += kSsdNmsThreads) sc[i] = __ldg(src + i);
     }
     __syncthreads();
+    FB_PHASE(0);
 
     SmemScores kf{sc, score_thr};
     const int n = block_select_topk_binned<kSsdNmsThreads, kSsdSelCap, 4>(kf, num_priors, topk, hist_base, hist_shift, sm);
@@ -146,6 +148,7 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     }
     if (t < kSsdWords) keep_words[t] = 0u;
     __syncthreads();
+    FB_PHASE(6);
 
     // suppression bit matrix: warp r handles rows r, r + 8, ...; lane b tests box 32w + b
     const int lane = t & 31, warp = t >> 5;
@@ -161,8 +164,10 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
         if (lane < kSsdWords) smask[i * kSsdWords + lane] = bits;
     }
     __syncthreads();
+    FB_PHASE(7);
     if (warp == 0) warp_nms_scan(smask, kSsdWords, n, words, keep_words);
     __syncthreads();
+    FB_PHASE(8);
     if (t == 0) {
         int acc = 0;
         for (int w = 0; w < kSsdWords; ++w) {
@@ -194,6 +199,7 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
         d[0] = d[1] = d[2] = d[3] = d[4] = 0.0f;
         prior_ids[obase + i] = -1;
     }
+    FB_PHASE(9);
 }
 
 }  // namespace fb

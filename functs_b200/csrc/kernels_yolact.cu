@@ -3,8 +3,8 @@
 // Reference structure (functs/benchmark/ai_model/yolact/yolact_mask.py:250-264, 306-333): per image
 // mask = sigmoid(proto @ coef.T), cropped to each detection's sanitised box, here by slice assignment inside a
 // loop over detections, then thresholded.  The loop iterations only differ in the detection index, so the loop
-// is folded into the kernel.  A warp owns a 16 x 8 pixel tile; a thread keeps the 32 prototype channels of a 2 x 2
-// pixel block in registers and walks the detections.  Per 32 detections the warp ballots which crops touch its
+// is folded into the kernel.  A warp owns a 16 x 4 pixel tile; a thread keeps the 32 prototype channels of two
+// horizontally adjacent pixels in registers and walks the detections.  Per 32 detections the warp ballots which crops touch its
 // tile at all; for the others it only stores zeros, for those it evaluates the 32-term dot products (fixed k order,
 // fp32 FMA) and the sigmoid-threshold test.  Coefficients and crop bounds live in shared memory and are read as
 // warp broadcasts.
@@ -17,7 +17,7 @@ namespace fb {
 constexpr int kYolactThreads = 128;
 constexpr int kYolactK = 32;
 constexpr int kYolactMaxDet = 256;
-constexpr int kYolactTileW = 16, kYolactTileH = 8;  // pixels per warp tile
+constexpr int kYolactTileW = 16, kYolactTileH = 4;  // pixels per warp tile: 8 lanes x 2 pixels wide, 4 rows
 
 // sanitize_coordinates (yolact_mask.py:327-333) followed by "col >= x1 and col < x2" as integer bounds.
 __device__ __forceinline__ void crop_range(float a, float b, int size, int& lo, int& hi) {
@@ -39,7 +39,7 @@ __device__ __forceinline__ bool sigmoid_exceeds(float v, float thr, float v_lo, 
 }
 
 template <bool LOGITS>
-__global__ void __launch_bounds__(kYolactThreads, 3)
+__global__ void __launch_bounds__(kYolactThreads, 5)
 yolact_masks_kernel(const float* __restrict__ proto, const float* __restrict__ coef, const float* __restrict__ boxes,
                     int height, int width, int num_det, float thr, float v_lo, float v_hi, int tiles_x, int num_tiles,
                     uint8_t* __restrict__ masks, float* __restrict__ logits) {
@@ -67,32 +67,26 @@ yolact_masks_kernel(const float* __restrict__ proto, const float* __restrict__ c
     if (wt >= num_tiles) return;
     const int ty = wt / tiles_x, tx = wt - ty * tiles_x;
     const int x0 = tx * kYolactTileW, y0 = ty * kYolactTileH;
-    const int x = x0 + 2 * (lane & 7);   // this thread: pixels (y, x), (y, x+1), (y+1, x), (y+1, x+1); width is even
-    const int y = y0 + 2 * (lane >> 3);
-    const bool vx = x < width;
-    const bool vrow0 = vx && (y < height), vrow1 = vx && (y + 1 < height);
+    const int x = x0 + 2 * (lane & 7);   // this thread: pixels (y, x) and (y, x + 1); the width is even
+    const int y = y0 + (lane >> 3);
+    const bool vpix = x < width && y < height;
 
-    float pr[4][kYolactK];
+    float pr[2][kYolactK];
     {
-        const float* pimg = proto + static_cast<int64_t>(img) * hw * kYolactK;
+        const float4* psrc = reinterpret_cast<const float4*>(proto + (static_cast<int64_t>(img) * hw + static_cast<int64_t>(y) * width + x) * kYolactK);
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const bool ok = r == 0 ? vrow0 : vrow1;
-            const float4* psrc = reinterpret_cast<const float4*>(pimg + (static_cast<int64_t>(y + r) * width + x) * kYolactK);
-#pragma unroll
-            for (int q = 0; q < 2 * (kYolactK / 4); ++q) {
-                const float4 v = ok ? __ldg(psrc + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-                const int u = 2 * r + q / (kYolactK / 4), k4 = (q % (kYolactK / 4)) * 4;
-                pr[u][k4 + 0] = v.x;
-                pr[u][k4 + 1] = v.y;
-                pr[u][k4 + 2] = v.z;
-                pr[u][k4 + 3] = v.w;
-            }
+        for (int q = 0; q < 2 * (kYolactK / 4); ++q) {
+            const float4 v = vpix ? __ldg(psrc + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const int u = q / (kYolactK / 4), k4 = (q % (kYolactK / 4)) * 4;
+            pr[u][k4 + 0] = v.x;
+            pr[u][k4 + 1] = v.y;
+            pr[u][k4 + 2] = v.z;
+            pr[u][k4 + 3] = v.w;
         }
     }
 
-    uint8_t* mrow0 = masks + static_cast<int64_t>(img) * num_det * hw + static_cast<int64_t>(y) * width + x;
-    float* lrow0 = LOGITS ? logits + static_cast<int64_t>(img) * num_det * hw + static_cast<int64_t>(y) * width + x : nullptr;
+    uint8_t* mrow = masks + static_cast<int64_t>(img) * num_det * hw + static_cast<int64_t>(y) * width + x;
+    float* lrow = LOGITS ? logits + static_cast<int64_t>(img) * num_det * hw + static_cast<int64_t>(y) * width + x : nullptr;
 #pragma unroll 1
     for (int c0 = 0; c0 < num_det; c0 += 32) {
         // which of the detections c0 .. c0+31 have a crop that touches this warp's tile?
@@ -106,37 +100,29 @@ yolact_masks_kernel(const float* __restrict__ proto, const float* __restrict__ c
 #pragma unroll 1
         for (int b = 0; b < dend; ++b) {
             const int d = c0 + b;
-            uint32_t out0 = 0u, out1 = 0u;
+            uint32_t out = 0u;
             if ((word >> b) & 1u) {  // warp-uniform
                 const int4 bd = s_bounds[d];
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                float acc0 = 0.f, acc1 = 0.f;
                 const float4* c4 = reinterpret_cast<const float4*>(s_coef + d * kYolactK);
 #pragma unroll
                 for (int q = 0; q < kYolactK / 4; ++q) {
                     const float4 c = c4[q];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        acc[u] = fmaf(pr[u][4 * q + 0], c.x, acc[u]);
-                        acc[u] = fmaf(pr[u][4 * q + 1], c.y, acc[u]);
-                        acc[u] = fmaf(pr[u][4 * q + 2], c.z, acc[u]);
-                        acc[u] = fmaf(pr[u][4 * q + 3], c.w, acc[u]);
-                    }
+                    acc0 = fmaf(pr[0][4 * q + 0], c.x, acc0);
+                    acc1 = fmaf(pr[1][4 * q + 0], c.x, acc1);
+                    acc0 = fmaf(pr[0][4 * q + 1], c.y, acc0);
+                    acc1 = fmaf(pr[1][4 * q + 1], c.y, acc1);
+                    acc0 = fmaf(pr[0][4 * q + 2], c.z, acc0);
+                    acc1 = fmaf(pr[1][4 * q + 2], c.z, acc1);
+                    acc0 = fmaf(pr[0][4 * q + 3], c.w, acc0);
+                    acc1 = fmaf(pr[1][4 * q + 3], c.w, acc1);
                 }
-                const bool inx0 = x >= bd.x && x < bd.y, inx1 = x + 1 >= bd.x && x + 1 < bd.y;
-                const bool iny0 = y >= bd.z && y < bd.w, iny1 = y + 1 >= bd.z && y + 1 < bd.w;
-                if (inx0 && iny0 && sigmoid_exceeds(acc[0], thr, v_lo, v_hi)) out0 |= 1u;
-                if (inx1 && iny0 && sigmoid_exceeds(acc[1], thr, v_lo, v_hi)) out0 |= 0x100u;
-                if (inx0 && iny1 && sigmoid_exceeds(acc[2], thr, v_lo, v_hi)) out1 |= 1u;
-                if (inx1 && iny1 && sigmoid_exceeds(acc[3], thr, v_lo, v_hi)) out1 |= 0x100u;
-                if (LOGITS) {
-                    float* l = lrow0 + static_cast<int64_t>(d) * hw;
-                    if (vrow0) *reinterpret_cast<float2*>(l) = make_float2(acc[0], acc[1]);
-                    if (vrow1) *reinterpret_cast<float2*>(l + width) = make_float2(acc[2], acc[3]);
-                }
+                const bool iny = y >= bd.z && y < bd.w;
+                if (iny && x >= bd.x && x < bd.y && sigmoid_exceeds(acc0, thr, v_lo, v_hi)) out |= 1u;
+                if (iny && x + 1 >= bd.x && x + 1 < bd.y && sigmoid_exceeds(acc1, thr, v_lo, v_hi)) out |= 0x100u;
+                if (LOGITS && vpix) *reinterpret_cast<float2*>(lrow + static_cast<int64_t>(d) * hw) = make_float2(acc0, acc1);
             }
-            uint8_t* m = mrow0 + static_cast<int64_t>(d) * hw;
-            if (vrow0) *reinterpret_cast<uint16_t*>(m) = static_cast<uint16_t>(out0);
-            if (vrow1) *reinterpret_cast<uint16_t*>(m + width) = static_cast<uint16_t>(out1);
+            if (vpix) *reinterpret_cast<uint16_t*>(mrow + static_cast<int64_t>(d) * hw) = static_cast<uint16_t>(out);
         }
     }
 }

@@ -23,7 +23,7 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
 constexpr int kYoloThreads = 128;
 constexpr int kYoloClasses = 80;
 constexpr int kYoloAttrib = 85;
-constexpr int kYoloChunk = 16;       // class logits loaded per thread before any is consumed
+constexpr int kYoloChunk = 8;        // class logits per thread and step; the next step's loads are issued before this step is consumed
 constexpr int kYoloSub = 8;          // logits whose hits are queued at once: <= 32 lanes * 8 = 256 new entries
 constexpr int kYoloWarpStage = 96;   // staged candidate keys per warp (flushed when fewer than 32 slots remain)
 constexpr int kYoloQueue = 512;      // circular queue of pending hits per warp (256 new + < 32 left over)
@@ -33,6 +33,8 @@ struct YoloParams {
     int size[3];        // S
     int tiles[3];       // position tiles per (image, anchor) plane
     int tile_begin[4];  // first CTA of every level, [3] = total
+    int live_begin[4];  // the same for the candidate-only kernel (tiles of (anchor, position) slots per image)
+    int staged[3];      // level goes through the bulk-copy staged path (16-byte aligned planes)
     int box_begin[3];   // first box index of every level inside an image
     float stride[3];
     float anchor_w[3][3];
@@ -175,9 +177,14 @@ __device__ __forceinline__ void yolo_decode_level(const YoloParams& P, const int
 
 #pragma unroll 1
     for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
-        if (c0 > 0) {
+        // software pipeline: the loads of the next step are in flight while this step's logits are consumed
+        float vn[kYoloChunk];
+        if (c0 + kYoloChunk < kYoloClasses) {
 #pragma unroll
-            for (int u = 0; u < kYoloChunk; ++u) v[u] = __ldg(csrc + (c0 + u) * SS);
+            for (int u = 0; u < kYoloChunk; ++u) vn[u] = __ldg(csrc + (c0 + kYoloChunk + u) * SS);
+        } else {
+#pragma unroll
+            for (int u = 0; u < kYoloChunk; ++u) vn[u] = 0.0f;
         }
         if (DENSE) {
             if (valid && P.cls_out != nullptr) {
@@ -217,6 +224,8 @@ __device__ __forceinline__ void yolo_decode_level(const YoloParams& P, const int
                 }
             }
         }
+#pragma unroll
+        for (int u = 0; u < kYoloChunk; ++u) v[u] = vn[u];
     }
     const int rest = pushed - head;
     if (rest > 0) yolo_eval_batch(ws, head, rest, so, flat0, P, img, fill, gkeys, gcount);
@@ -235,6 +244,494 @@ yolo_decode_kernel(const YoloParams P) {
         yolo_decode_level<S1, DENSE>(P, 1, cta - P.tile_begin[1], ws);
     } else {
         yolo_decode_level<S0, DENSE>(P, 0, cta, ws);
+    }
+}
+
+// ---- candidate-only decode ("live box" form) ------------------------------------------------------------------
+// Used when no dense objectness / class-score output is requested (the fused post-process).  A box whose objectness
+// does not exceed the threshold cannot yield a candidate, so the class logits are only walked for the boxes that
+// survive that test: a CTA decodes a tile of kLiveTile (anchor, position) slots of one image and level (two slots per
+// thread), compacts the surviving slots into a shared list, and then lets thread k walk the 80 class logits of the
+// k-th survivor.  Hits are packed with a ballot into the warp's queue and evaluated 32 at a time.
+constexpr int kLiveThreads = 256;
+constexpr int kLiveSlots = 2;  // slots per thread in the first phase
+constexpr int kLiveTile = kLiveThreads * kLiveSlots;
+constexpr int kLiveSub = 4;     // class steps between two looks at the queue: <= 128 new entries
+constexpr int kLiveQueue = 256;  // > 128 new + 31 left over
+constexpr int kLiveStage = 96;
+
+struct __align__(16) YoloLive {
+    float so;        // objectness score
+    float v_cut;     // class logits at or below this cannot reach the threshold
+    uint32_t chan;   // offset of the slot's class-0 logit inside the image's level map
+    uint32_t flat0;  // flat (box, class 0) index inside the image
+};
+
+struct YoloLiveWarp {
+    uint64_t stage[kLiveStage];
+    YoloHit queue[kLiveQueue];  // meta = live index << 8 | class
+};
+
+struct YoloLiveSmem {
+    YoloLive live[kLiveTile];
+    YoloLiveWarp w[kLiveThreads / 32];
+    int warp_cnt[kLiveThreads / 32];
+};
+
+__device__ __forceinline__ void live_flush(YoloLiveWarp& ws, int& fill, uint64_t* gkeys, int32_t* gcount, int64_t capacity,
+                                           int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();
+    int base = 0;
+    if (lane == 0) base = atomicAdd(gcount, fill);
+    base = __shfl_sync(kFullMask, base, 0);
+    for (int i = lane; i < fill; i += 32) {
+        const int64_t pos = static_cast<int64_t>(base) + i;
+        if (pos < capacity) gkeys[pos] = ws.stage[i];
+        else if (status != nullptr) atomicOr(status, FB_STATUS_CAND_OVERFLOW);
+    }
+    __syncwarp();
+    fill = 0;
+}
+
+// lane i evaluates queue entry head + i (nb <= 32 entries): exact score, threshold, key, histogram.
+__device__ __forceinline__ void live_eval_batch(const YoloLiveSmem& sm, YoloLiveWarp& ws, int head, int nb,
+                                                const YoloParams& P, int32_t* ghist, int& fill, uint64_t* gkeys,
+                                                int32_t* gcount) {
+    const int lane = threadIdx.x & 31;
+    const bool act = lane < nb;
+    bool pred = false;
+    float s = 0.0f;
+    uint32_t flat = 0u;
+    if (act) {
+        const YoloHit e = ws.queue[(head + lane) & (kLiveQueue - 1)];
+        const YoloLive o = sm.live[e.meta >> 8];
+        s = __fmul_rn(o.so, sigmoid_f32(e.v));
+        flat = o.flat0 + (e.meta & 255u);
+        pred = s > P.thr;
+    }
+    const unsigned m = __ballot_sync(kFullMask, pred);
+    if (pred) {
+        ws.stage[fill + __popc(m & ((1u << lane) - 1u))] = make_key(s, flat);
+        if (ghist != nullptr) atomicAdd(ghist + hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift), 1);
+    }
+    fill += __popc(m);
+    if (fill + 32 > kLiveStage) live_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+}
+
+template <int S_T>
+__device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int lvl, const int local, YoloLiveSmem& sm) {
+    const int S = S_T > 0 ? S_T : P.size[lvl];
+    const int SS = S * S;
+    const int nslots = 3 * SS;
+    const int tiles = (nslots + kLiveTile - 1) / kLiveTile;
+    const int img = local / tiles;
+    const int tile = local - img * tiles;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const float* __restrict__ base = P.map[lvl] + static_cast<int64_t>(img) * 255 * SS;
+    const float stride = P.stride[lvl];
+
+    // ---- phase 1: box decode + objectness test for kLiveSlots slots per thread ----
+    float so[kLiveSlots], vcut[kLiveSlots];
+    uint32_t chan[kLiveSlots], flat0[kLiveSlots];
+    bool alive[kLiveSlots];
+    float tv[kLiveSlots][5];
+    int anc_[kLiveSlots], p_[kLiveSlots];
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        const int slot = tile * kLiveTile + q * kLiveThreads + t;
+        const bool valid = slot < nslots;
+        const int sl = valid ? slot : 0;
+        const int anc = sl / SS, p = sl - anc * SS;
+        anc_[q] = anc;
+        p_[q] = p;
+        alive[q] = valid;
+        const float* src = base + anc * kYoloAttrib * SS + p;
+#pragma unroll
+        for (int c = 0; c < 5; ++c) tv[q][c] = valid ? __ldg(src + c * SS) : 0.0f;
+    }
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        const int anc = anc_[q], p = p_[q];
+        const int gy = p / S, gx = p - gy * S;
+        const float aw = anc == 0 ? P.anchor_w[lvl][0] : (anc == 1 ? P.anchor_w[lvl][1] : P.anchor_w[lvl][2]);
+        const float ah = anc == 0 ? P.anchor_h[lvl][0] : (anc == 1 ? P.anchor_h[lvl][1] : P.anchor_h[lvl][2]);
+        const float cx = __fmul_rn(__fadd_rn(sigmoid_f32(tv[q][0]), static_cast<float>(gx)), stride);
+        const float cy = __fmul_rn(__fadd_rn(sigmoid_f32(tv[q][1]), static_cast<float>(gy)), stride);
+        const float hw = __fmul_rn(__fmul_rn(expf(tv[q][2]), aw), 0.5f);
+        const float hh = __fmul_rn(__fmul_rn(expf(tv[q][3]), ah), 0.5f);
+        so[q] = sigmoid_f32(tv[q][4]);
+        const int box = P.box_begin[lvl] + p * 3 + anc;
+        if (alive[q]) {
+            reinterpret_cast<float4*>(P.boxes)[static_cast<int64_t>(img) * P.num_boxes + box] =
+                make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
+        }
+        // score = so * sigmoid(v) can exceed thr only if sigmoid(v) > thr / so.  The cut sits a relative 1e-5 below
+        // that (hundreds of fp32 ulps: rounding of the sigmoid and of the product) and another 0.02 lower in the
+        // logit domain (rounding of the logit itself), so it never loses a candidate; everything above the cut is
+        // evaluated exactly.
+        alive[q] = alive[q] && so[q] > P.thr;
+        vcut[q] = INFINITY;
+        if (alive[q]) {
+            const float qq = (P.thr / so[q]) * (1.0f - 1.0e-5f);
+            vcut[q] = logf(qq / (1.0f - qq)) - 0.02f;
+        }
+        chan[q] = static_cast<uint32_t>((anc * kYoloAttrib + 5) * SS + p);
+        flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
+    }
+    // compaction: the survivors of a warp stay together (slot order inside each of its kLiveSlots runs)
+    unsigned bal[kLiveSlots];
+    int mine = 0;
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        bal[q] = __ballot_sync(kFullMask, alive[q]);
+        mine += __popc(bal[q]);
+    }
+    if (lane == 0) sm.warp_cnt[warp] = mine;
+    __syncthreads();
+    int wbase = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kLiveThreads / 32; ++w) {
+        const int c = sm.warp_cnt[w];
+        if (w < warp) wbase += c;
+        total += c;
+    }
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        if (alive[q]) {
+            YoloLive e;
+            e.so = so[q];
+            e.v_cut = vcut[q];
+            e.chan = chan[q];
+            e.flat0 = flat0[q];
+            sm.live[wbase + __popc(bal[q] & ((1u << lane) - 1u))] = e;
+        }
+        wbase += __popc(bal[q]);
+    }
+    __syncthreads();
+
+    // ---- phase 2: thread k walks the class logits of survivor k ----
+    YoloLiveWarp& ws = sm.w[warp];
+    uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
+    int32_t* gcount = P.counts + img;
+    int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(img) * kHistBins : nullptr;
+    const unsigned lt = (1u << lane) - 1u;
+    int fill = 0, head = 0, tail = 0;  // warp-uniform
+#pragma unroll 1
+    for (int k0 = warp * 32; k0 < total; k0 += kLiveThreads) {
+        const int k = k0 + lane;
+        const bool has = k < total;
+        YoloLive me;
+        me.so = 0.0f;
+        me.v_cut = INFINITY;
+        me.chan = 0u;
+        me.flat0 = 0u;
+        if (has) me = sm.live[k];
+        const float* __restrict__ csrc = base + me.chan;
+        const uint32_t meta0 = static_cast<uint32_t>(k) << 8;
+        float v[kYoloChunk];
+#pragma unroll
+        for (int u = 0; u < kYoloChunk; ++u) v[u] = has ? __ldg(csrc + u * SS) : 0.0f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
+            float vn[kYoloChunk];
+            if (c0 + kYoloChunk < kYoloClasses) {
+#pragma unroll
+                for (int u = 0; u < kYoloChunk; ++u) vn[u] = has ? __ldg(csrc + (c0 + kYoloChunk + u) * SS) : 0.0f;
+            } else {
+#pragma unroll
+                for (int u = 0; u < kYoloChunk; ++u) vn[u] = 0.0f;
+            }
+#pragma unroll
+            for (int h = 0; h < kYoloChunk; h += kLiveSub) {
+#pragma unroll
+                for (int u = 0; u < kLiveSub; ++u) {
+                    const bool pred = v[h + u] > me.v_cut;
+                    const unsigned m = __ballot_sync(kFullMask, pred);
+                    if (pred) {
+                        YoloHit e;
+                        e.v = v[h + u];
+                        e.meta = meta0 | static_cast<uint32_t>(c0 + h + u);
+                        ws.queue[(tail + __popc(m & lt)) & (kLiveQueue - 1)] = e;
+                    }
+                    tail += __popc(m);
+                }
+                __syncwarp();
+                while (tail - head >= 32) {
+                    live_eval_batch(sm, ws, head, 32, P, ghist, fill, gkeys, gcount);
+                    head += 32;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kYoloChunk; ++u) v[u] = vn[u];
+        }
+    }
+    __syncwarp();
+    if (tail - head > 0) live_eval_batch(sm, ws, head, tail - head, P, ghist, fill, gkeys, gcount);
+    if (fill > 0) live_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+}
+
+// ---- the same with the class planes staged through shared memory by the copy engine -------------------------
+// Levels whose plane size is a multiple of 4 floats (16-byte aligned rows) take this path: the CTA's tile is
+// kStTile (anchor, position) slots; for every step of kStClasses classes one thread issues bulk copies of the
+// tile's piece of each class plane (1 or 2 contiguous segments, a tile can straddle an anchor boundary) into a ring
+// of kStStages buffers, completion on an mbarrier.  The copies of the next steps are in flight while the survivors'
+// logits of the current step are read from shared memory, so DRAM latency is not on the consumers' critical path.
+constexpr int kStTile = 448;     // < 2 * kLiveThreads: about half the slots survive, one survivor per thread
+constexpr int kStClasses = 8;
+constexpr int kStStages = 3;
+constexpr int kStSteps = kYoloClasses / kStClasses;
+constexpr int kStSub = 2;
+constexpr int kStQueue = 128;    // > 32 * kStSub new + 31 left over
+static_assert(kYoloClasses % kStClasses == 0 && kStTile % 4 == 0 && kStTile <= kLiveTile, "staged decode layout");
+
+struct YoloStWarp {
+    uint64_t stage[kLiveStage];
+    YoloHit queue[kStQueue];  // meta = live index << 8 | class
+};
+
+struct __align__(128) YoloStagedSmem {
+    float ring[kStStages][kStClasses][kStTile];
+    YoloLive live[kStTile];  // .chan holds the slot's index inside the tile
+    YoloStWarp w[kLiveThreads / 32];
+    uint64_t full[kStStages];
+    int warp_cnt[kLiveThreads / 32];
+};
+
+__device__ __forceinline__ void st_flush(YoloStWarp& ws, int& fill, uint64_t* gkeys, int32_t* gcount, int64_t capacity,
+                                         int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    __syncwarp();
+    int base = 0;
+    if (lane == 0) base = atomicAdd(gcount, fill);
+    base = __shfl_sync(kFullMask, base, 0);
+    for (int i = lane; i < fill; i += 32) {
+        const int64_t pos = static_cast<int64_t>(base) + i;
+        if (pos < capacity) gkeys[pos] = ws.stage[i];
+        else if (status != nullptr) atomicOr(status, FB_STATUS_CAND_OVERFLOW);
+    }
+    __syncwarp();
+    fill = 0;
+}
+
+__device__ __forceinline__ void st_eval_batch(const YoloStagedSmem& sm, YoloStWarp& ws, int head, int nb,
+                                              const YoloParams& P, int32_t* ghist, int& fill, uint64_t* gkeys,
+                                              int32_t* gcount) {
+    const int lane = threadIdx.x & 31;
+    bool pred = false;
+    float s = 0.0f;
+    uint32_t flat = 0u;
+    if (lane < nb) {
+        const YoloHit e = ws.queue[(head + lane) & (kStQueue - 1)];
+        const YoloLive o = sm.live[e.meta >> 8];
+        s = __fmul_rn(o.so, sigmoid_f32(e.v));
+        flat = o.flat0 + (e.meta & 255u);
+        pred = s > P.thr;
+    }
+    const unsigned m = __ballot_sync(kFullMask, pred);
+    if (pred) {
+        ws.stage[fill + __popc(m & ((1u << lane) - 1u))] = make_key(s, flat);
+        if (ghist != nullptr) atomicAdd(ghist + hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift), 1);
+    }
+    fill += __popc(m);
+    if (fill + 32 > kLiveStage) st_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+}
+
+// One thread: copies of class step `step` of the tile [s0, s0 + n) into ring buffer `buf`.
+__device__ __forceinline__ void st_issue(YoloStagedSmem& sm, const float* base, int SS, int s0, int n, int step, int buf) {
+    mbar_arrive_expect_tx(&sm.full[buf], static_cast<uint32_t>(n) * 4u * kStClasses);
+    const int a0 = s0 / SS;
+    const int pa = s0 - a0 * SS;
+    const int len0 = min(n, SS - pa);  // slots of the first anchor; the rest (if any) starts the next anchor's planes
+#pragma unroll
+    for (int c = 0; c < kStClasses; ++c) {
+        const int ch = 5 + step * kStClasses + c;
+        bulk_copy_g2s(&sm.ring[buf][c][0], base + static_cast<int64_t>(a0 * kYoloAttrib + ch) * SS + pa,
+                      static_cast<uint32_t>(len0) * 4u, &sm.full[buf]);
+        if (len0 < n)
+            bulk_copy_g2s(&sm.ring[buf][c][len0], base + static_cast<int64_t>((a0 + 1) * kYoloAttrib + ch) * SS,
+                          static_cast<uint32_t>(n - len0) * 4u, &sm.full[buf]);
+    }
+}
+
+template <int S_T>
+__device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int lvl, const int local, YoloStagedSmem& sm) {
+    const int S = S_T > 0 ? S_T : P.size[lvl];
+    const int SS = S * S;
+    const int nslots = 3 * SS;
+    const int tiles = (nslots + kStTile - 1) / kStTile;
+    const int img = local / tiles;
+    const int tile = local - img * tiles;
+    const int s0 = tile * kStTile;
+    const int n = min(kStTile, nslots - s0);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const float* __restrict__ base = P.map[lvl] + static_cast<int64_t>(img) * 255 * SS;
+    const float stride = P.stride[lvl];
+
+    if (t == 0) {
+#pragma unroll
+        for (int b = 0; b < kStStages; ++b) mbar_init(&sm.full[b], 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (t == 0) {
+#pragma unroll
+        for (int b = 0; b < kStStages; ++b) st_issue(sm, base, SS, s0, n, b, b);
+    }
+
+    // ---- phase 1: box decode + objectness test, two slots per thread (plain loads: 5 of the 85 channels) ----
+    float so[kLiveSlots], vcut[kLiveSlots];
+    uint32_t flat0[kLiveSlots];
+    bool alive[kLiveSlots];
+    float tv[kLiveSlots][5];
+    int anc_[kLiveSlots], p_[kLiveSlots];
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        const int ls = q * kLiveThreads + t;
+        const bool valid = ls < n;
+        const int sl = valid ? s0 + ls : s0;
+        const int anc = sl / SS, p = sl - anc * SS;
+        anc_[q] = anc;
+        p_[q] = p;
+        alive[q] = valid;
+        const float* src = base + anc * kYoloAttrib * SS + p;
+#pragma unroll
+        for (int c = 0; c < 5; ++c) tv[q][c] = valid ? __ldg(src + c * SS) : 0.0f;
+    }
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        const int anc = anc_[q], p = p_[q];
+        const int gy = p / S, gx = p - gy * S;
+        const float aw = anc == 0 ? P.anchor_w[lvl][0] : (anc == 1 ? P.anchor_w[lvl][1] : P.anchor_w[lvl][2]);
+        const float ah = anc == 0 ? P.anchor_h[lvl][0] : (anc == 1 ? P.anchor_h[lvl][1] : P.anchor_h[lvl][2]);
+        const float cx = __fmul_rn(__fadd_rn(sigmoid_f32(tv[q][0]), static_cast<float>(gx)), stride);
+        const float cy = __fmul_rn(__fadd_rn(sigmoid_f32(tv[q][1]), static_cast<float>(gy)), stride);
+        const float hw = __fmul_rn(__fmul_rn(expf(tv[q][2]), aw), 0.5f);
+        const float hh = __fmul_rn(__fmul_rn(expf(tv[q][3]), ah), 0.5f);
+        so[q] = sigmoid_f32(tv[q][4]);
+        const int box = P.box_begin[lvl] + p * 3 + anc;
+        if (alive[q]) {
+            reinterpret_cast<float4*>(P.boxes)[static_cast<int64_t>(img) * P.num_boxes + box] =
+                make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
+        }
+        alive[q] = alive[q] && so[q] > P.thr;
+        vcut[q] = INFINITY;
+        if (alive[q]) {  // same logit cut as in the plain-load form above
+            const float qq = (P.thr / so[q]) * (1.0f - 1.0e-5f);
+            vcut[q] = logf(qq / (1.0f - qq)) - 0.02f;
+        }
+        flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
+    }
+    unsigned bal[kLiveSlots];
+    int mine = 0;
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        bal[q] = __ballot_sync(kFullMask, alive[q]);
+        mine += __popc(bal[q]);
+    }
+    if (lane == 0) sm.warp_cnt[warp] = mine;
+    __syncthreads();
+    int wbase = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kLiveThreads / 32; ++w) {
+        const int c = sm.warp_cnt[w];
+        if (w < warp) wbase += c;
+        total += c;
+    }
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
+        if (alive[q]) {
+            YoloLive e;
+            e.so = so[q];
+            e.v_cut = vcut[q];
+            e.chan = static_cast<uint32_t>(q * kLiveThreads + t);
+            e.flat0 = flat0[q];
+            sm.live[wbase + __popc(bal[q] & ((1u << lane) - 1u))] = e;
+        }
+        wbase += __popc(bal[q]);
+    }
+    __syncthreads();
+
+    // ---- phase 2: per class step, thread k reads the logits of survivor k (k + 256, ... if more survive) ----
+    YoloStWarp& ws = sm.w[warp];
+    uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
+    int32_t* gcount = P.counts + img;
+    int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(img) * kHistBins : nullptr;
+    const unsigned lt = (1u << lane) - 1u;
+    int fill = 0, head = 0, tail = 0;  // warp-uniform
+    bool failed = false;
+#pragma unroll 1
+    for (int step = 0; step < kStSteps; ++step) {
+        const int buf = step % kStStages;
+        if (!failed && !mbar_wait_bounded(&sm.full[buf], static_cast<uint32_t>((step / kStStages) & 1), 100000u)) {
+            failed = true;  // the copy never landed: flag the call, read nothing more
+            if (P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
+        }
+        const bool go = __all_sync(kFullMask, !failed);
+        if (go) {
+#pragma unroll 1
+            for (int k0 = warp * 32; k0 < total; k0 += kLiveThreads) {
+                const int k = k0 + lane;
+                const bool has = k < total;
+                float vc = INFINITY;
+                int ls = 0;
+                if (has) {
+                    const YoloLive me = sm.live[k];
+                    vc = me.v_cut;
+                    ls = static_cast<int>(me.chan);
+                }
+                const uint32_t meta0 = (static_cast<uint32_t>(k) << 8) | static_cast<uint32_t>(step * kStClasses);
+                float v[kStClasses];
+#pragma unroll
+                for (int u = 0; u < kStClasses; ++u) v[u] = sm.ring[buf][u][ls];
+#pragma unroll
+                for (int h = 0; h < kStClasses; h += kStSub) {
+#pragma unroll
+                    for (int u = 0; u < kStSub; ++u) {
+                        const bool pred = v[h + u] > vc;
+                        const unsigned m = __ballot_sync(kFullMask, pred);
+                        if (pred) {
+                            YoloHit e;
+                            e.v = v[h + u];
+                            e.meta = meta0 + static_cast<uint32_t>(h + u);
+                            ws.queue[(tail + __popc(m & lt)) & (kStQueue - 1)] = e;
+                        }
+                        tail += __popc(m);
+                    }
+                    __syncwarp();
+                    while (tail - head >= 32) {
+                        st_eval_batch(sm, ws, head, 32, P, ghist, fill, gkeys, gcount);
+                        head += 32;
+                    }
+                }
+            }
+        }
+        failed = __syncthreads_or(failed ? 1 : 0) != 0;  // every warp is done with ring[buf]; a timeout ends the CTA's reads
+        if (t == 0 && step + kStStages < kStSteps && !failed) st_issue(sm, base, SS, s0, n, step + kStStages, buf);
+    }
+    __syncwarp();
+    if (tail - head > 0) st_eval_batch(sm, ws, head, tail - head, P, ghist, fill, gkeys, gcount);
+    if (fill > 0) st_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+}
+
+// Levels with 16-byte aligned planes go through the staged path, the others (13 x 13) through plain loads.
+template <int S0, int S1, int S2>
+__global__ void __launch_bounds__(kLiveThreads)
+yolo_decode_staged_kernel(const YoloParams P) {
+    extern __shared__ __align__(128) unsigned char st_raw[];
+    const int cta = blockIdx.x;
+    const int lvl = cta >= P.live_begin[2] ? 2 : (cta >= P.live_begin[1] ? 1 : 0);
+    const int local = cta - P.live_begin[lvl];
+    if (P.staged[lvl]) {
+        YoloStagedSmem& sm = *reinterpret_cast<YoloStagedSmem*>(st_raw);
+        if (lvl == 2) yolo_staged_level<S2>(P, 2, local, sm);
+        else if (lvl == 1) yolo_staged_level<S1>(P, 1, local, sm);
+        else yolo_staged_level<S0>(P, 0, local, sm);
+    } else {
+        YoloLiveSmem& sm = *reinterpret_cast<YoloLiveSmem*>(st_raw);
+        if (lvl == 2) yolo_live_level<S2>(P, 2, local, sm);
+        else if (lvl == 1) yolo_live_level<S1>(P, 1, local, sm);
+        else yolo_live_level<S0>(P, 0, local, sm);
     }
 }
 
@@ -300,12 +797,37 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     if (dense) {
         if (std_sizes) yolo_decode_kernel<13, 26, 52, true><<<nblk, kYoloThreads, 0, st>>>(P);
         else yolo_decode_kernel<0, 0, 0, true><<<nblk, kYoloThreads, 0, st>>>(P);
+        count_launch();
+        return check_launch("yolo_decode_kernel");
+    }
+    int64_t live_acc = 0;
+    for (int l = 0; l < 3; ++l) {
+        // a plane of S * S floats keeps every row 16-byte aligned iff S * S is a multiple of 4 (and the map itself is)
+        // (and a plane at least as long as a tile, so that a tile touches at most two anchors)
+        P.staged[l] = ((S[l] * S[l]) % 4 == 0 && S[l] * S[l] >= kStTile && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 1 : 0;
+        const int tile = P.staged[l] ? kStTile : kLiveTile;
+        P.live_begin[l] = static_cast<int>(live_acc);
+        live_acc += static_cast<int64_t>((3 * S[l] * S[l] + tile - 1) / tile) * batch;
+    }
+    FB_REQUIRE(live_acc < (1ll << 31), "yolo_decode: too many tiles");
+    FB_REQUIRE(255ll * S[0] * S[0] < (1ll << 32) && 255ll * S[1] * S[1] < (1ll << 32) && 255ll * S[2] * S[2] < (1ll << 32),
+               "yolo_decode: level map too large");
+    P.live_begin[3] = static_cast<int>(live_acc);
+    const unsigned nlive = static_cast<unsigned>(live_acc);
+    const size_t smem = sizeof(YoloStagedSmem) > sizeof(YoloLiveSmem) ? sizeof(YoloStagedSmem) : sizeof(YoloLiveSmem);
+    if (std_sizes) {
+        FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<13, 26, 52>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                          "yolo_decode attr"));
+        yolo_decode_staged_kernel<13, 26, 52><<<nlive, kLiveThreads, smem, st>>>(P);
     } else {
-        if (std_sizes) yolo_decode_kernel<13, 26, 52, false><<<nblk, kYoloThreads, 0, st>>>(P);
-        else yolo_decode_kernel<0, 0, 0, false><<<nblk, kYoloThreads, 0, st>>>(P);
+        FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<0, 0, 0>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                          "yolo_decode attr"));
+        yolo_decode_staged_kernel<0, 0, 0><<<nlive, kLiveThreads, smem, st>>>(P);
     }
     count_launch();
-    return check_launch("yolo_decode_kernel");
+    return check_launch("yolo_decode_staged_kernel");
 }
 
 static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }

@@ -47,17 +47,18 @@ __device__ __forceinline__ int hist_digit(uint64_t key, uint32_t base, int shift
 // ---- bitonic sort, descending, on `n` (power of two) 64-bit keys in shared memory -------------------
 template <int NT>
 __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
+    // one thread per compare-exchange pair: pair p of a (k, j) step is (i, i | j) with bit j of i clear
+    const int pairs = n >> 1;
     for (int k = 2; k <= n; k <<= 1) {
         for (int j = k >> 1; j > 0; j >>= 1) {
-            for (int i = threadIdx.x; i < n; i += NT) {
-                int ixj = i ^ j;
-                if (ixj > i) {
-                    uint64_t a = s[i], b = s[ixj];
-                    bool desc_seg = (i & k) == 0;
-                    if (desc_seg ? (a < b) : (a > b)) {
-                        s[i] = b;
-                        s[ixj] = a;
-                    }
+            for (int p = threadIdx.x; p < pairs; p += NT) {
+                const int i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
+                const int ixj = i | j;
+                const uint64_t a = s[i], b = s[ixj];
+                const bool desc_seg = (i & k) == 0;
+                if (desc_seg ? (a < b) : (a > b)) {
+                    s[i] = b;
+                    s[ixj] = a;
                 }
             }
             __syncthreads();
@@ -326,6 +327,7 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
     }
     __syncthreads();
+    FB_PHASE(1);
     if (warp == 0) {
         constexpr int per = kHistBins / 32;
         const int lo = lane * per, hi = lo + per;
@@ -353,6 +355,7 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
     }
     __syncthreads();
+    FB_PHASE(2);
     const int nvalid = sm.nvalid;
     if (nvalid == 0) return 0;
     const int dstar = sm.digit;  // -1: everything is selected
@@ -382,6 +385,7 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
     }
     __syncthreads();
+    FB_PHASE(3);
     const int result = nvalid < topk ? nvalid : topk;
     if (dstar >= 0) {
         const int bc = sm.bin_cnt;
@@ -396,10 +400,12 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
         __syncthreads();
     }
+    FB_PHASE(4);
     const int sort_n = next_pow2(result);
     for (int i = result + tid; i < sort_n; i += NT) sm.sel[i] = 0ull;
     __syncthreads();
     bitonic_sort_desc<NT>(sm.sel, sort_n);
+    FB_PHASE(5);
     return result;
 }
 
@@ -469,14 +475,28 @@ __device__ __forceinline__ void warp_nms_scan(const uint32_t* mask, int row_stri
             diag[b] = in ? mask[(base + b) * row_stride + w] : 0u;
             col[b] = (in && lane < words) ? mask[(base + b) * row_stride + lane] : 0u;
         }
-        // 32 serial decisions, branch-free: box b is kept iff its bit of r is still clear
-        uint32_t keepw = 0u;
+        // Serial part.  Row b can only set bits above b, so bit b of r is final once the rows before b are done and
+        // keepw = ~r (valid rows) at the end.  Only rows with a non-empty diagonal word can change r: when there
+        // are few of them they are walked in order (re-read from shared memory by index), otherwise all 32 rows go
+        // through the unrolled register chain.
+        uint32_t nz = 0u;
 #pragma unroll
-        for (int b = 0; b < 32; ++b) {
-            const uint32_t alive = (b < rows && !(r & (1u << b))) ? 0xffffffffu : 0u;
-            keepw |= alive & (1u << b);
-            r |= diag[b] & alive;
+        for (int b = 0; b < 32; ++b) nz |= (diag[b] != 0u) ? (1u << b) : 0u;
+        if (__popc(nz) <= 10) {
+            while (nz) {
+                const int b = __ffs(nz) - 1;
+                nz &= nz - 1u;
+                if (!(r & (1u << b))) r |= mask[(base + b) * row_stride + w];
+            }
+        } else {
+#pragma unroll
+            for (int b = 0; b < 32; ++b) {
+                const uint32_t alive = (r & (1u << b)) ? 0u : 0xffffffffu;
+                r |= diag[b] & alive;
+            }
         }
+        const uint32_t valid_rows = rows >= 32 ? 0xffffffffu : ((1u << rows) - 1u);
+        const uint32_t keepw = ~r & valid_rows;
         // kept rows of this block remove columns in the later words
 #pragma unroll
         for (int b = 0; b < 32; ++b) removed |= (keepw & (1u << b)) ? col[b] : 0u;

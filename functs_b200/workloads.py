@@ -29,7 +29,7 @@ def get_started(a: torch.Tensor, b: torch.Tensor, n: int, device="cuda") -> torc
 
 
 class YOLOV3BBox:
-    """Decode three [B, 255, S, S] maps, score mask, top-k, class-wise NMS.  4 kernel launches (+1 memset) per call."""
+    """Decode three [B, 255, S, S] maps, score mask, top-k, class-wise NMS.  5 kernel launches (+1 memset) per call."""
 
     def __init__(self, sizes=(13, 26, 52), score_thr: float = 0.5, topk: int = 1000, iou_thr: float = 0.45,
                  device="cuda"):
@@ -115,7 +115,7 @@ class SSDBBox:
 
 
 class LSTM:
-    """One-layer LSTM with per-step outputs written by slice assignment (hs[t] = h, cs[t] = c).  2 launches."""
+    """One-layer LSTM with per-step outputs written by slice assignment (hs[t] = h, cs[t] = c).  2 launches (3 when the tensor-core projection runs: operand split, GEMM, recurrence)."""
 
     def __init__(self, w_ih: torch.Tensor, w_hh: torch.Tensor, b_ih: torch.Tensor, b_hh: torch.Tensor, device="cuda"):
         self.device = _dev(device)

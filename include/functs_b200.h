@@ -80,9 +80,10 @@ int functs_b200_threshold_compact(const float* scores, int32_t groups, int64_t n
 int functs_b200_select_topk(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, int32_t groups,
                             int32_t topk, uint64_t* out_keys, int32_t* out_counts, void* stream);
 
-/* The same selection for long candidate lists: 16 CTAs per group collect the keys above / inside the boundary
+/* The same selection for long candidate lists: 8 CTAs per group collect the keys above / inside the boundary
  * bucket of the score histogram `hist` (filled by the candidate producer with the same thr), the CTA that finishes
- * last sorts.  Falls back to the exact generic selection when the boundary bucket holds more than 2048 keys.
+ * last sorts.  A second, normally idle launch redoes a group with the exact generic selection when its boundary
+ * bucket holds more keys than the sort buffer or the histogram and the keys disagree (2 launches in all).
  * scratch: functs_b200_select_binned_scratch_bytes(groups), 256-byte aligned. */
 int64_t functs_b200_select_binned_scratch_bytes(int32_t groups);
 int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity,
@@ -117,7 +118,8 @@ int functs_b200_yolo_decode(const float* map0, const float* map1, const float* m
                             uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
                             int32_t* status, void* stream);
 
-/* Whole post-process: one memset + decode -> select_topk_binned -> batched_nms(class_offset=1): 4 launches.
+/* Whole post-process: one memset + decode -> select_topk_binned -> batched_nms(class_offset=1): 5 kernel launches
+ * (decode, binned select, its fallback pass, NMS bit matrix, NMS scan).
  * Outputs as in batched_nms.
  * scratch: functs_b200_yolo_scratch_bytes(batch, s0, s1, s2, capacity, topk). */
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,

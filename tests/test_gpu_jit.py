@@ -1,6 +1,6 @@
 """Functionalized TorchScript graphs executed on the GPU: the immut:: operators run as CUDA launches of the C-ABI
 library.  Programs restate the reference's test/test_basic.py:6-38 and examples/get_started.py:10-15; the result must
-equal the eager program (pure data movement + identical fp32 arithmetic: bit-exact)."""
+equal the eager program run on the same device bit for bit (and the CPU eager program within 1e-5)."""
 import pytest
 import torch
 
@@ -63,9 +63,11 @@ def run(fjit, fn, *args):
     fjit.functionalize_graph(g)
     kinds = [n.kind() for n in g.nodes()]
     f = torch._C._create_function_from_graph(fn.__name__, g)
-    want = fn(*args)
-    got = f(*[a.cuda() if isinstance(a, torch.Tensor) else a for a in args])
-    assert got.is_cuda and torch.equal(got.cpu(), want), fn.__name__
+    dev_args = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+    want = fn(*[a.clone() if isinstance(a, torch.Tensor) else a for a in dev_args])  # eager program on the same device
+    got = f(*dev_args)
+    assert got.is_cuda and torch.equal(got, want), fn.__name__
+    assert torch.allclose(got.cpu(), fn(*args), rtol=1e-5, atol=1e-6), fn.__name__
     return kinds
 
 
