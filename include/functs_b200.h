@@ -104,6 +104,21 @@ int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_c
                             int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids, int64_t* keep,
                             int32_t* out_counts, void* scratch, void* stream);
 
+/* The same NMS for callers that cannot provide scratch memory.  No counterpart in the reference (its executor always
+ * allocates through torch's caching allocator).  Meant for hosts that bind only this C ABI and own no device allocator
+ * — all device memory belongs to another framework's pool, or a cudaMalloc (a device-wide synchronisation) is not
+ * acceptable inside their loop.  The suppression matrix lives in a 1 MB __device__ array inside the library (held on
+ * every GPU that loads the library, until exit), so groups <= functs_b200_batched_nms_static_max_groups() (8); more
+ * groups are rejected with FB_ERR_INVALID_ARGUMENT.  The entry point calls no cudaMalloc / cudaFree or any allocating
+ * routine.  The first call on a device looks the array's address up (cudaGetSymbolAddress) with that device current:
+ * make that first call before any stream capture.  All calls share the array; calls whose kernels can overlap on
+ * the GPU race on it.  Inputs and outputs exactly as functs_b200_batched_nms. */
+int32_t functs_b200_batched_nms_static_max_groups(void);
+int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_t num_classes, const uint64_t* sel_keys,
+                                   const int32_t* sel_counts, int32_t groups, int32_t topk, float iou_thr,
+                                   int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids,
+                                   int64_t* keep, int32_t* out_counts, void* stream);
+
 /* ---- C2: YOLOv3-style decode + score mask + top-k + class-wise NMS ----------------------- */
 /* Follows functs/benchmark/ai_model/yolov3/yolov3_bbox.py:195-243 at the configured shapes:
  * three NCHW logit maps [batch, 255, S, S]; box order is level, y, x, anchor. */
