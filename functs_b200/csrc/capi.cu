@@ -36,9 +36,9 @@ void record_stage_event(int index, cudaStream_t st) {
 }
 
 #ifdef FB_PHASE_PROBE
-static struct { const char* file; void (*fn)(unsigned long long*, int); } g_phase_readers[32];
+static struct { const char* file; void (*fn)(unsigned long long*, int, int); } g_phase_readers[32];
 static int g_num_phase_readers = 0;
-void register_phase_reader(const char* file, void (*fn)(unsigned long long*, int)) {
+void register_phase_reader(const char* file, void (*fn)(unsigned long long*, int, int)) {
     if (g_num_phase_readers < 32) g_phase_readers[g_num_phase_readers++] = {file, fn};
 }
 }  // namespace fb
@@ -46,7 +46,18 @@ extern "C" int functs_b200_phase_read(const char* file_part, unsigned long long*
     for (int i = 0; i < fb::g_num_phase_readers; ++i) {
         if (strstr(fb::g_phase_readers[i].file, file_part) != nullptr) {
             cudaDeviceSynchronize();
-            fb::g_phase_readers[i].fn(out32, reset);
+            fb::g_phase_readers[i].fn(out32, reset, 0);
+            return 0;
+        }
+    }
+    return 1;
+}
+// out: 8192 x 8 words
+extern "C" int functs_b200_trace_read(const char* file_part, unsigned long long* out) {
+    for (int i = 0; i < fb::g_num_phase_readers; ++i) {
+        if (strstr(fb::g_phase_readers[i].file, file_part) != nullptr) {
+            cudaDeviceSynchronize();
+            fb::g_phase_readers[i].fn(out, 0, 1);
             return 0;
         }
     }

@@ -224,6 +224,14 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 
 }  // namespace fb
 
+namespace fb {
+void yolo_set_prune(int on);
+void yolo_set_tile_major(int on);
+void yolo_set_refresh_all(int on);
+void yolo_set_stream(int on);
+void yolo_set_mode(int m);
+}
+
 extern "C" {
 
 int64_t functs_b200_lstm_scratch_bytes(int32_t seq_len, int32_t batch, int32_t input, int32_t hidden) {
@@ -293,6 +301,26 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
 int functs_b200_debug_set(const char* name, int32_t value) {
     if (name != nullptr && std::strcmp(name, "lstm_tc_swap_lbo_sbo") == 0) {
         fb::lstm_tc_set_swap(value);
+        return FB_OK;
+    }
+    if (name != nullptr && std::strcmp(name, "yolo_prune") == 0) {
+        fb::yolo_set_prune(value);
+        return FB_OK;
+    }
+    if (name != nullptr && std::strcmp(name, "yolo_tile_major") == 0) {
+        fb::yolo_set_tile_major(value);
+        return FB_OK;
+    }
+    if (name != nullptr && std::strcmp(name, "yolo_mode") == 0) {
+        fb::yolo_set_mode(value);
+        return FB_OK;
+    }
+    if (name != nullptr && std::strcmp(name, "yolo_stream") == 0) {
+        fb::yolo_set_stream(value);
+        return FB_OK;
+    }
+    if (name != nullptr && std::strcmp(name, "yolo_refresh_all") == 0) {
+        fb::yolo_set_refresh_all(value);
         return FB_OK;
     }
     fb::set_error("debug_set: unknown switch");

@@ -5,6 +5,8 @@
 // score mask" of functs/benchmark/ai_model/yolov3/yolov3_bbox.py:209-220 and :122-127, in one pass over the NCHW
 // logits: threads run along the contiguous spatial axis (coalesced), every thread walks the 85 channels of one
 // box, and the hits of a warp are staged in shared memory and appended to the image's candidate list.
+#include <cstddef>
+
 #include "select_nms.cuh"
 
 namespace fb {
@@ -35,6 +37,14 @@ struct YoloParams {
     int tile_begin[4];  // first CTA of every level, [3] = total
     int live_begin[4];  // the same for the candidate-only kernel (tiles of (anchor, position) slots per image)
     int staged[3];      // level goes through the bulk-copy staged path (16-byte aligned planes)
+    int prune_topk;     // > 0: the caller only needs the prune_topk best candidates per image (see prune_digit)
+    int refresh_all;
+    int num_direct;            // persistent kernel: leading CTAs that run the plain-load form
+    int st_tiles[3];           // persistent kernel: tiles per image of every staged level (0: not staged)
+    int st_tiles_per_image;
+    int st_total_tiles;
+    int32_t* work_counter;     // persistent kernel: next tile to hand out (zero at launch)
+    int tile_major;     // CTA order of the staged levels: 1 = all images' first tiles, then all second tiles, ...
     int box_begin[3];   // first box index of every level inside an image
     float stride[3];
     float anchor_w[3][3];
@@ -260,6 +270,56 @@ constexpr int kLiveSub = 4;     // class steps between two looks at the queue: <
 constexpr int kLiveQueue = 256;  // > 128 new + 31 left over
 constexpr int kLiveStage = 96;
 
+// Pruning for callers that keep only the `need` best candidates of an image.  The image's score histogram only ever
+// grows, so once some bucket d has at least `need` recorded candidates in the buckets >= d, a candidate of a lower
+// bucket can never be among the `need` best and may be dropped unrecorded.  This returns such a d (0 = no pruning
+// yet) from a possibly stale look at the histogram: stale counts are smaller, which only makes d more conservative.
+// The second look (the owner lane's 64 buckets, two per lane) can only see larger counts than the first, which keeps
+// the result conservative as well.  Called by one full warp; nothing waits for anybody.
+__device__ __noinline__ int prune_digit_regs(const int32_t* __restrict__ h, int need) {
+    const int lane = threadIdx.x & 31;
+    constexpr int per = kHistBins / 32;
+    static_assert(per == 64, "two buckets per lane in the second look");
+    const int4* h4 = reinterpret_cast<const int4*>(h + lane * per);
+    int sum = 0;
+#pragma unroll 4
+    for (int i = 0; i < per / 4; ++i) {
+        const int4 x = __ldcg(h4 + i);
+        sum += (x.x + x.y) + (x.z + x.w);
+    }
+    int incl = sum;  // this lane's buckets and all higher ones
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(kFullMask, incl, o);
+        if (lane + o < 32) incl += v;
+    }
+    const unsigned who = __ballot_sync(kFullMask, incl - sum < need && incl >= need);
+    if (who == 0u) return 0;  // fewer than `need` candidates recorded so far
+    const int owner = __ffs(who) - 1;
+    const int above = __shfl_sync(kFullMask, incl - sum, owner);
+    const int b0 = owner * per + 2 * lane;
+    const int2 c = __ldcg(reinterpret_cast<const int2*>(h + b0));
+    int incl2 = c.x + c.y;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(kFullMask, incl2, o);
+        if (lane + o < 32) incl2 += v;
+    }
+    const int hi = above + incl2 - (c.x + c.y);  // recorded candidates in the buckets above this lane's pair
+    int d = 0;
+    if (hi < need && hi + c.x + c.y >= need) d = (hi + c.y >= need) ? b0 + 1 : b0;
+    return __reduce_max_sync(kFullMask, d);
+}
+
+// v > cut is necessary for so * sigmoid(v) to reach `floor_score` (> 0).  The cut sits a relative 1e-5 below the
+// exact bound (hundreds of fp32 ulps: rounding of the sigmoid and of the product) and another 0.02 lower in the
+// logit domain (rounding of the logit itself), so it never loses a candidate.
+__device__ __forceinline__ float logit_cut(float so, float floor_score) {
+    const float q = (floor_score / so) * (1.0f - 1.0e-5f);
+    if (!(q < 1.0f)) return INFINITY;
+    return logf(q / (1.0f - q)) - 0.02f;
+}
+
 struct __align__(16) YoloLive {
     float so;        // objectness score
     float v_cut;     // class logits at or below this cannot reach the threshold
@@ -273,6 +333,7 @@ struct YoloLiveWarp {
 };
 
 struct YoloLiveSmem {
+    int prune;  // latest pruning bucket published for this CTA
     YoloLive live[kLiveTile];
     YoloLiveWarp w[kLiveThreads / 32];
     int warp_cnt[kLiveThreads / 32];
@@ -296,24 +357,26 @@ __device__ __forceinline__ void live_flush(YoloLiveWarp& ws, int& fill, uint64_t
 
 // lane i evaluates queue entry head + i (nb <= 32 entries): exact score, threshold, key, histogram.
 __device__ __forceinline__ void live_eval_batch(const YoloLiveSmem& sm, YoloLiveWarp& ws, int head, int nb,
-                                                const YoloParams& P, int32_t* ghist, int& fill, uint64_t* gkeys,
-                                                int32_t* gcount) {
+                                                const YoloParams& P, int32_t* ghist, int prune, int& fill,
+                                                uint64_t* gkeys, int32_t* gcount) {
     const int lane = threadIdx.x & 31;
     const bool act = lane < nb;
     bool pred = false;
     float s = 0.0f;
     uint32_t flat = 0u;
+    int digit = 0;
     if (act) {
         const YoloHit e = ws.queue[(head + lane) & (kLiveQueue - 1)];
         const YoloLive o = sm.live[e.meta >> 8];
         s = __fmul_rn(o.so, sigmoid_f32(e.v));
         flat = o.flat0 + (e.meta & 255u);
-        pred = s > P.thr;
+        digit = hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift);
+        pred = s > P.thr && digit >= prune;
     }
     const unsigned m = __ballot_sync(kFullMask, pred);
     if (pred) {
         ws.stage[fill + __popc(m & ((1u << lane) - 1u))] = make_key(s, flat);
-        if (ghist != nullptr) atomicAdd(ghist + hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift), 1);
+        if (ghist != nullptr) atomicAdd(ghist + digit, 1);
     }
     fill += __popc(m);
     if (fill + 32 > kLiveStage) live_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
@@ -350,6 +413,16 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
 #pragma unroll
         for (int c = 0; c < 5; ++c) tv[q][c] = valid ? __ldg(src + c * SS) : 0.0f;
     }
+    int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(img) * kHistBins : nullptr;
+    const bool pruning = P.prune_topk > 0 && ghist != nullptr;
+    if (warp == 0) {
+        const int d = pruning ? prune_digit_regs(ghist, P.prune_topk) : 0;
+        if (lane == 0) sm.prune = d;
+    }
+    __syncthreads();
+    int prune = sm.prune;  // candidates of buckets below this are dropped
+    // lowest score of bucket `prune`; 0 while nothing is pruned
+    float floor_score = prune > 0 ? __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift)) : 0.0f;
 #pragma unroll
     for (int q = 0; q < kLiveSlots; ++q) {
         const int anc = anc_[q], p = p_[q];
@@ -366,16 +439,10 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
             reinterpret_cast<float4*>(P.boxes)[static_cast<int64_t>(img) * P.num_boxes + box] =
                 make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
         }
-        // score = so * sigmoid(v) can exceed thr only if sigmoid(v) > thr / so.  The cut sits a relative 1e-5 below
-        // that (hundreds of fp32 ulps: rounding of the sigmoid and of the product) and another 0.02 lower in the
-        // logit domain (rounding of the logit itself), so it never loses a candidate; everything above the cut is
-        // evaluated exactly.
-        alive[q] = alive[q] && so[q] > P.thr;
-        vcut[q] = INFINITY;
-        if (alive[q]) {
-            const float qq = (P.thr / so[q]) * (1.0f - 1.0e-5f);
-            vcut[q] = logf(qq / (1.0f - qq)) - 0.02f;
-        }
+        // a score is so * sigmoid(v) <= so: the box can only yield candidates if so itself clears both bars; the
+        // class logits above logit_cut() are then evaluated exactly
+        alive[q] = alive[q] && so[q] > P.thr && so[q] >= floor_score;
+        vcut[q] = alive[q] ? logit_cut(so[q], fmaxf(P.thr, floor_score)) : INFINITY;
         chan[q] = static_cast<uint32_t>((anc * kYoloAttrib + 5) * SS + p);
         flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
     }
@@ -414,7 +481,6 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
     YoloLiveWarp& ws = sm.w[warp];
     uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
     int32_t* gcount = P.counts + img;
-    int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(img) * kHistBins : nullptr;
     const unsigned lt = (1u << lane) - 1u;
     int fill = 0, head = 0, tail = 0;  // warp-uniform
 #pragma unroll 1
@@ -434,10 +500,26 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
         for (int u = 0; u < kYoloChunk; ++u) v[u] = has ? __ldg(csrc + u * SS) : 0.0f;
 #pragma unroll 1
         for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
+            if (pruning) {
+                // warp 0 takes a fresh look at the histogram twice per pass; every warp picks the result up when it
+                // gets there (a plain shared-memory word: late or early, any published bucket is valid)
+                if (warp == 0 && (c0 == 2 * kYoloChunk || c0 == 5 * kYoloChunk)) {
+                    const int d = prune_digit_regs(ghist, P.prune_topk);
+                    if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
+                    __syncwarp();
+                }
+                const int now = *reinterpret_cast<volatile int*>(&sm.prune);
+                if (now > prune) {
+                    prune = now;
+                    floor_score = __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift));
+                    me.v_cut = (has && me.so >= floor_score) ? logit_cut(me.so, fmaxf(P.thr, floor_score)) : INFINITY;
+                }
+            }
             float vn[kYoloChunk];
             if (c0 + kYoloChunk < kYoloClasses) {
 #pragma unroll
-                for (int u = 0; u < kYoloChunk; ++u) vn[u] = has ? __ldg(csrc + (c0 + kYoloChunk + u) * SS) : 0.0f;
+                for (int u = 0; u < kYoloChunk; ++u)
+                    vn[u] = (has && me.v_cut < INFINITY) ? __ldg(csrc + (c0 + kYoloChunk + u) * SS) : 0.0f;
             } else {
 #pragma unroll
                 for (int u = 0; u < kYoloChunk; ++u) vn[u] = 0.0f;
@@ -458,7 +540,7 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
                 }
                 __syncwarp();
                 while (tail - head >= 32) {
-                    live_eval_batch(sm, ws, head, 32, P, ghist, fill, gkeys, gcount);
+                    live_eval_batch(sm, ws, head, 32, P, ghist, prune, fill, gkeys, gcount);
                     head += 32;
                 }
             }
@@ -467,7 +549,7 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
         }
     }
     __syncwarp();
-    if (tail - head > 0) live_eval_batch(sm, ws, head, tail - head, P, ghist, fill, gkeys, gcount);
+    if (tail - head > 0) live_eval_batch(sm, ws, head, tail - head, P, ghist, prune, fill, gkeys, gcount);
     if (fill > 0) live_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
 }
 
@@ -483,10 +565,14 @@ constexpr int kStStages = 3;
 constexpr int kStSteps = kYoloClasses / kStClasses;
 constexpr int kStSub = 2;
 constexpr int kStQueue = 128;    // > 32 * kStSub new + 31 left over
+constexpr int kStConsumerWarps = kLiveThreads / 32;
+constexpr int kStThreads = kLiveThreads + 32;  // + the producer warp
 static_assert(kYoloClasses % kStClasses == 0 && kStTile % 4 == 0 && kStTile <= kLiveTile, "staged decode layout");
 
+constexpr int kStKeyStage = 64;  // staged candidate keys per warp (flushed when fewer than 32 slots remain)
+
 struct YoloStWarp {
-    uint64_t stage[kLiveStage];
+    uint64_t stage[kStKeyStage];
     YoloHit queue[kStQueue];  // meta = live index << 8 | class
 };
 
@@ -494,9 +580,61 @@ struct __align__(128) YoloStagedSmem {
     float ring[kStStages][kStClasses][kStTile];
     YoloLive live[kStTile];  // .chan holds the slot's index inside the tile
     YoloStWarp w[kLiveThreads / 32];
-    uint64_t full[kStStages];
+    uint64_t full[kStStages];   // copy engine -> consumers: the buffer's bytes have landed
+    uint64_t empty[kStStages];  // consumers -> producer warp: every consumer warp is done with the buffer
     int warp_cnt[kLiveThreads / 32];
+    int prune;  // latest pruning bucket published for this CTA
+    __align__(16) int hist_snapshot[kHistBins];  // written with 16-byte stores
 };
+
+// Pruning for callers that keep only the `need` best candidates of an image.  The image's score histogram only ever
+// grows, so once some bucket d has at least `need` recorded candidates in the buckets >= d, a candidate of a lower
+// bucket can never be among the `need` best and may be dropped unrecorded.  This returns such a d (0 = no pruning
+// yet) from a possibly stale look at the histogram: stale counts are smaller, which only makes d more conservative.
+// Called by one full warp; nothing waits for anybody.
+__device__ __noinline__ int prune_digit(const int32_t* __restrict__ h, int need, int* tmp) {
+    const int lane = threadIdx.x & 31;
+    constexpr int per = kHistBins / 32;
+    // snapshot into shared memory (coalesced 16-byte loads that bypass L1), then work on the snapshot
+    const int4* h4 = reinterpret_cast<const int4*>(h);
+    int4* t4 = reinterpret_cast<int4*>(tmp);
+#pragma unroll 8
+    for (int i = 0; i < kHistBins / 4 / 32; ++i) t4[i * 32 + lane] = __ldcg(h4 + i * 32 + lane);
+    __syncwarp();
+    int sum = 0;  // lane owns buckets [lane * per, lane * per + per); rotated reads keep the banks apart
+#pragma unroll 8
+    for (int i = 0; i < per; ++i) sum += tmp[lane * per + ((i + lane) & (per - 1))];
+    int incl = sum;  // this lane's buckets and all higher ones
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(kFullMask, incl, o);
+        if (lane + o < 32) incl += v;
+    }
+    const bool mine = incl - sum < need && incl >= need;  // the crossing lies in this lane's buckets (one lane at most)
+    const unsigned who = __ballot_sync(kFullMask, mine);
+    if (who == 0u) return 0;  // fewer than `need` candidates recorded so far
+    const int owner = __ffs(who) - 1;
+    const int above = __shfl_sync(kFullMask, incl - sum, owner);
+    // second level: the owner's `per` buckets, two per lane
+    static_assert(per == 64, "two buckets per lane");
+    const int b0 = owner * per + 2 * lane;
+    const int c0 = tmp[b0], c1 = tmp[b0 + 1];
+    int incl2 = c0 + c1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(kFullMask, incl2, o);
+        if (lane + o < 32) incl2 += v;
+    }
+    const int hi = above + incl2 - (c0 + c1);  // recorded candidates in the buckets above this lane's pair
+    int d = 0;
+    if (hi < need && hi + c0 + c1 >= need) d = (hi + c1 >= need) ? b0 + 1 : b0;
+    __syncwarp();
+    return __reduce_max_sync(kFullMask, d);
+}
+
+static_assert(offsetof(YoloStagedSmem, hist_snapshot) % 16 == 0 && offsetof(YoloStagedSmem, live) % 16 == 0 &&
+                  offsetof(YoloStagedSmem, full) % 8 == 0 && offsetof(YoloStagedSmem, empty) % 8 == 0 && offsetof(YoloStagedSmem, w) % 8 == 0,
+              "shared-memory layout of the staged decode");
 
 __device__ __forceinline__ void st_flush(YoloStWarp& ws, int& fill, uint64_t* gkeys, int32_t* gcount, int64_t capacity,
                                          int32_t* status) {
@@ -514,27 +652,45 @@ __device__ __forceinline__ void st_flush(YoloStWarp& ws, int& fill, uint64_t* gk
     fill = 0;
 }
 
-__device__ __forceinline__ void st_eval_batch(const YoloStagedSmem& sm, YoloStWarp& ws, int head, int nb,
-                                              const YoloParams& P, int32_t* ghist, int& fill, uint64_t* gkeys,
-                                              int32_t* gcount) {
+// Everything the evaluation of queued hits needs, by value (the function below is not inlined).
+struct StEvalArgs {
+    float thr;
+    uint32_t hist_base;
+    int hist_shift;
+    int32_t* ghist;
+    uint64_t* gkeys;
+    int32_t* gcount;
+    int64_t capacity;
+    int32_t* status;
+};
+
+// Lane i evaluates queue entry head + i (nb <= 32 entries): exact score, threshold and pruning bucket, key,
+// histogram.  Returns the new fill level of the warp's key stage.  Kept out of line: it is called from several
+// places of an unrolled loop and the copies would only bloat the instruction footprint.
+__device__ __noinline__ int st_eval_batch(const YoloLive* live, YoloStWarp* wsp, int head, int nb, StEvalArgs a, int prune,
+                                          int fill) {
+    YoloStWarp& ws = *wsp;
     const int lane = threadIdx.x & 31;
     bool pred = false;
     float s = 0.0f;
     uint32_t flat = 0u;
+    int digit = 0;
     if (lane < nb) {
         const YoloHit e = ws.queue[(head + lane) & (kStQueue - 1)];
-        const YoloLive o = sm.live[e.meta >> 8];
+        const YoloLive o = live[e.meta >> 8];
         s = __fmul_rn(o.so, sigmoid_f32(e.v));
         flat = o.flat0 + (e.meta & 255u);
-        pred = s > P.thr;
+        digit = hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, a.hist_base, a.hist_shift);
+        pred = s > a.thr && digit >= prune;
     }
     const unsigned m = __ballot_sync(kFullMask, pred);
     if (pred) {
         ws.stage[fill + __popc(m & ((1u << lane) - 1u))] = make_key(s, flat);
-        if (ghist != nullptr) atomicAdd(ghist + hist_digit(static_cast<uint64_t>(__float_as_uint(s)) << 32, P.hist_base, P.hist_shift), 1);
+        if (a.ghist != nullptr) atomicAdd(a.ghist + digit, 1);
     }
     fill += __popc(m);
-    if (fill + 32 > kLiveStage) st_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+    if (fill + 32 > kStKeyStage) st_flush(ws, fill, a.gkeys, a.gcount, a.capacity, a.status);
+    return fill;
 }
 
 // One thread: copies of class step `step` of the tile [s0, s0 + n) into ring buffer `buf`.
@@ -559,27 +715,36 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     const int S = S_T > 0 ? S_T : P.size[lvl];
     const int SS = S * S;
     const int nslots = 3 * SS;
+    // tile-major CTA order: the CTAs of one image are spread over the whole launch, so that the later ones find the
+    // image's histogram filled by the earlier ones (see prune_digit)
     const int tiles = (nslots + kStTile - 1) / kStTile;
-    const int img = local / tiles;
-    const int tile = local - img * tiles;
+    const int tile = P.tile_major ? local / P.batch : local % tiles;
+    const int img = P.tile_major ? local - tile * P.batch : local / tiles;
     const int s0 = tile * kStTile;
     const int n = min(kStTile, nslots - s0);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const bool producer = warp == kStConsumerWarps;  // the ninth warp only feeds the ring
     const float* __restrict__ base = P.map[lvl] + static_cast<int64_t>(img) * 255 * SS;
     const float stride = P.stride[lvl];
+    int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(img) * kHistBins : nullptr;
+    const bool pruning = P.prune_topk > 0 && ghist != nullptr;
 
     if (t == 0) {
+        FB_TRACE(0, global_ns());
 #pragma unroll
-        for (int b = 0; b < kStStages; ++b) mbar_init(&sm.full[b], 1);
+        for (int b = 0; b < kStStages; ++b) {
+            mbar_init(&sm.full[b], 1);
+            mbar_init(&sm.empty[b], kStConsumerWarps);
+        }
         fence_barrier_init();
     }
     __syncthreads();
-    if (t == 0) {
+    if (producer && lane == 0) {
 #pragma unroll
         for (int b = 0; b < kStStages; ++b) st_issue(sm, base, SS, s0, n, b, b);
     }
 
-    // ---- phase 1: box decode + objectness test, two slots per thread (plain loads: 5 of the 85 channels) ----
+    // ---- phase 1 (consumer warps): box decode + objectness test, two slots per thread, plain loads ----
     float so[kLiveSlots], vcut[kLiveSlots];
     uint32_t flat0[kLiveSlots];
     bool alive[kLiveSlots];
@@ -588,7 +753,7 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
 #pragma unroll
     for (int q = 0; q < kLiveSlots; ++q) {
         const int ls = q * kLiveThreads + t;
-        const bool valid = ls < n;
+        const bool valid = !producer && ls < n;
         const int sl = valid ? s0 + ls : s0;
         const int anc = sl / SS, p = sl - anc * SS;
         anc_[q] = anc;
@@ -598,6 +763,14 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
 #pragma unroll
         for (int c = 0; c < 5; ++c) tv[q][c] = valid ? __ldg(src + c * SS) : 0.0f;
     }
+    if (warp == 0) {
+        const int d = pruning ? prune_digit(ghist, P.prune_topk, sm.hist_snapshot) : 0;
+        if (lane == 0) sm.prune = d;
+    }
+    __syncthreads();
+    int prune = sm.prune;  // candidates of buckets below this are dropped
+    // lowest score of bucket `prune`; 0 while nothing is pruned
+    float floor_score = prune > 0 ? __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift)) : 0.0f;
 #pragma unroll
     for (int q = 0; q < kLiveSlots; ++q) {
         const int anc = anc_[q], p = p_[q];
@@ -614,12 +787,9 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             reinterpret_cast<float4*>(P.boxes)[static_cast<int64_t>(img) * P.num_boxes + box] =
                 make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
         }
-        alive[q] = alive[q] && so[q] > P.thr;
-        vcut[q] = INFINITY;
-        if (alive[q]) {  // same logit cut as in the plain-load form above
-            const float qq = (P.thr / so[q]) * (1.0f - 1.0e-5f);
-            vcut[q] = logf(qq / (1.0f - qq)) - 0.02f;
-        }
+        // a score is so * sigmoid(v) <= so: the box can only yield candidates if so itself clears both bars
+        alive[q] = alive[q] && so[q] > P.thr && so[q] >= floor_score;
+        vcut[q] = alive[q] ? logit_cut(so[q], fmaxf(P.thr, floor_score)) : INFINITY;
         flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
     }
     unsigned bal[kLiveSlots];
@@ -629,11 +799,11 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
         bal[q] = __ballot_sync(kFullMask, alive[q]);
         mine += __popc(bal[q]);
     }
-    if (lane == 0) sm.warp_cnt[warp] = mine;
+    if (lane == 0 && !producer) sm.warp_cnt[warp] = mine;
     __syncthreads();
     int wbase = 0, total = 0;
 #pragma unroll
-    for (int w = 0; w < kLiveThreads / 32; ++w) {
+    for (int w = 0; w < kStConsumerWarps; ++w) {
         const int c = sm.warp_cnt[w];
         if (w < warp) wbase += c;
         total += c;
@@ -650,73 +820,111 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
         }
         wbase += __popc(bal[q]);
     }
-    __syncthreads();
+    __syncthreads();  // the last CTA-wide barrier: from here on the warps only meet through the ring's mbarriers
+    if (t == 0) {
+        FB_TRACE(1, global_ns());
+        FB_TRACE(3, static_cast<unsigned long long>(total));
+        FB_TRACE(4, static_cast<unsigned long long>(prune));
+    }
 
-    // ---- phase 2: per class step, thread k reads the logits of survivor k (k + 256, ... if more survive) ----
+    if (producer) {
+        // refill a buffer as soon as all consumer warps have released it; in between, refresh the pruning bucket
+#pragma unroll 1
+        for (int step = kStStages; step < kStSteps; ++step) {
+            const int buf = step % kStStages;
+            int ok = 1;
+            if (lane == 0) {
+                ok = mbar_wait_bounded(&sm.empty[buf], static_cast<uint32_t>((step / kStStages - 1) & 1), 100000u) ? 1 : 0;
+                if (ok) st_issue(sm, base, SS, s0, n, step, buf);
+                else if (P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
+            }
+            ok = __shfl_sync(kFullMask, ok, 0);
+            if (!ok) break;
+            if (pruning && (P.refresh_all || step == 4 || step == 7)) {
+                const int d = prune_digit(ghist, P.prune_topk, sm.hist_snapshot);
+                if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
+            }
+        }
+        return;
+    }
+
+    // ---- phase 2 (consumer warps): per class step, lane k reads the logits of survivor k (k + 256, ... if more) ----
     YoloStWarp& ws = sm.w[warp];
     uint64_t* gkeys = P.keys + static_cast<int64_t>(img) * P.capacity;
     int32_t* gcount = P.counts + img;
-    int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(img) * kHistBins : nullptr;
     const unsigned lt = (1u << lane) - 1u;
+    const StEvalArgs ea{P.thr, P.hist_base, P.hist_shift, ghist, gkeys, gcount, P.capacity, P.status};
     int fill = 0, head = 0, tail = 0;  // warp-uniform
-    bool failed = false;
 #pragma unroll 1
     for (int step = 0; step < kStSteps; ++step) {
         const int buf = step % kStStages;
-        if (!failed && !mbar_wait_bounded(&sm.full[buf], static_cast<uint32_t>((step / kStStages) & 1), 100000u)) {
-            failed = true;  // the copy never landed: flag the call, read nothing more
-            if (P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
-        }
-        const bool go = __all_sync(kFullMask, !failed);
-        if (go) {
-#pragma unroll 1
-            for (int k0 = warp * 32; k0 < total; k0 += kLiveThreads) {
-                const int k = k0 + lane;
-                const bool has = k < total;
-                float vc = INFINITY;
-                int ls = 0;
-                if (has) {
-                    const YoloLive me = sm.live[k];
-                    vc = me.v_cut;
-                    ls = static_cast<int>(me.chan);
-                }
-                const uint32_t meta0 = (static_cast<uint32_t>(k) << 8) | static_cast<uint32_t>(step * kStClasses);
-                float v[kStClasses];
-#pragma unroll
-                for (int u = 0; u < kStClasses; ++u) v[u] = sm.ring[buf][u][ls];
-#pragma unroll
-                for (int h = 0; h < kStClasses; h += kStSub) {
-#pragma unroll
-                    for (int u = 0; u < kStSub; ++u) {
-                        const bool pred = v[h + u] > vc;
-                        const unsigned m = __ballot_sync(kFullMask, pred);
-                        if (pred) {
-                            YoloHit e;
-                            e.v = v[h + u];
-                            e.meta = meta0 + static_cast<uint32_t>(h + u);
-                            ws.queue[(tail + __popc(m & lt)) & (kStQueue - 1)] = e;
-                        }
-                        tail += __popc(m);
-                    }
-                    __syncwarp();
-                    while (tail - head >= 32) {
-                        st_eval_batch(sm, ws, head, 32, P, ghist, fill, gkeys, gcount);
-                        head += 32;
-                    }
+        if (pruning) {
+            const int now = *reinterpret_cast<volatile int*>(&sm.prune);  // one broadcast read: the same for all lanes
+            if (now > prune) {  // raise the cuts of this thread's survivors
+                prune = now;
+                floor_score = __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift));
+                for (int k = t; k < total; k += kLiveThreads) {
+                    const float so_k = sm.live[k].so;
+                    sm.live[k].v_cut = so_k >= floor_score ? logit_cut(so_k, fmaxf(P.thr, floor_score)) : INFINITY;
                 }
             }
         }
-        failed = __syncthreads_or(failed ? 1 : 0) != 0;  // every warp is done with ring[buf]; a timeout ends the CTA's reads
-        if (t == 0 && step + kStStages < kStSteps && !failed) st_issue(sm, base, SS, s0, n, step + kStStages, buf);
+        const bool landed = mbar_wait_bounded(&sm.full[buf], static_cast<uint32_t>((step / kStStages) & 1), 100000u);
+        if (!__all_sync(kFullMask, landed)) {  // the copy never landed: flag the call, read nothing more
+            if (lane == 0 && P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
+            break;
+        }
+#pragma unroll 1
+        for (int k0 = warp * 32; k0 < total; k0 += kLiveThreads) {
+            const int k = k0 + lane;
+            const bool has = k < total;
+            float vc = INFINITY;
+            int ls = 0;
+            if (has) {
+                const YoloLive me = sm.live[k];
+                vc = me.v_cut;
+                ls = static_cast<int>(me.chan);
+            }
+            const uint32_t meta0 = (static_cast<uint32_t>(k) << 8) | static_cast<uint32_t>(step * kStClasses);
+            float v[kStClasses];
+#pragma unroll
+            for (int u = 0; u < kStClasses; ++u) v[u] = sm.ring[buf][u][ls];
+#pragma unroll
+            for (int h = 0; h < kStClasses; h += kStSub) {
+#pragma unroll
+                for (int u = 0; u < kStSub; ++u) {
+                    const bool pred = v[h + u] > vc;
+                    const unsigned m = __ballot_sync(kFullMask, pred);
+                    if (pred) {
+                        YoloHit e;
+                        e.v = v[h + u];
+                        e.meta = meta0 + static_cast<uint32_t>(h + u);
+                        ws.queue[(tail + __popc(m & lt)) & (kStQueue - 1)] = e;
+                    }
+                    tail += __popc(m);
+                }
+                __syncwarp();
+                while (tail - head >= 32) {
+                    fill = st_eval_batch(sm.live, &ws, head, 32, ea, prune, fill);
+                    head += 32;
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.empty[buf]);  // this warp is done with ring[buf]
     }
     __syncwarp();
-    if (tail - head > 0) st_eval_batch(sm, ws, head, tail - head, P, ghist, fill, gkeys, gcount);
+    if (tail - head > 0) fill = st_eval_batch(sm.live, &ws, head, tail - head, ea, prune, fill);
     if (fill > 0) st_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+    if (t == 0) {
+        FB_TRACE(2, global_ns());
+        FB_TRACE(5, static_cast<unsigned long long>(prune));
+    }
 }
 
 // Levels with 16-byte aligned planes go through the staged path, the others (13 x 13) through plain loads.
 template <int S0, int S1, int S2>
-__global__ void __launch_bounds__(kLiveThreads)
+__global__ void __launch_bounds__(kStThreads, 3)
 yolo_decode_staged_kernel(const YoloParams P) {
     extern __shared__ __align__(128) unsigned char st_raw[];
     const int cta = blockIdx.x;
@@ -728,12 +936,367 @@ yolo_decode_staged_kernel(const YoloParams P) {
         else if (lvl == 1) yolo_staged_level<S1>(P, 1, local, sm);
         else yolo_staged_level<S0>(P, 0, local, sm);
     } else {
+        if (threadIdx.x >= kLiveThreads) return;  // the plain-load form has no producer warp
         YoloLiveSmem& sm = *reinterpret_cast<YoloLiveSmem*>(st_raw);
         if (lvl == 2) yolo_live_level<S2>(P, 2, local, sm);
         else if (lvl == 1) yolo_live_level<S1>(P, 1, local, sm);
         else yolo_live_level<S0>(P, 0, local, sm);
     }
 }
+
+// ---- persistent form of the staged decode ------------------------------------------------------------------
+// Used by the one-call post-process.  About three CTAs per SM stay resident and fetch tiles from a work counter.
+// The producer warp keeps the ring filled ACROSS tiles (it already streams the next tile while the consumer warps
+// finish the current one); the five box channels of a tile travel through the ring as well ("box step": ring step 0
+// of a tile, class step c is ring step c + 1), so the consumer warps never wait for a plain global load, and the
+// producer warp also looks up the tile's pruning bucket ahead of time.  The ring is finer and deeper than in the
+// one-tile-per-CTA form (5 channel planes per step, 6 buffers): the producer may only refill a buffer once ALL
+// consumer warps have released it, and more, smaller buffers keep more bytes in flight under that rule.
+// The consumer warps meet at tile boundaries through an mbarrier (bounded waits like everywhere else).
+constexpr int kSmRows = 5;
+constexpr int kSmStages = 6;
+constexpr int kSmSteps = kYoloClasses / kSmRows;  // class steps per tile
+constexpr int kSmRingSteps = kSmSteps + 1;        // + the box step
+static_assert(kYoloClasses % kSmRows == 0 && kSmRows >= 5, "the box step carries 5 channels");
+
+struct __align__(128) YoloStreamSmem {
+    float ring[kSmStages][kSmRows][kStTile];
+    YoloLive live[kStTile];  // .chan holds the slot's index inside the tile
+    YoloStWarp w[kStConsumerWarps];
+    uint64_t full[kSmStages];
+    uint64_t empty[kSmStages];
+    uint64_t meet;                // consumer warps: one arrival per warp
+    int slot_tile[kSmStages];   // tile carried by the box step in this ring buffer (-1: no more work)
+    int slot_prune[kSmStages];  // pruning bucket the producer warp found for that tile's image
+    int warp_cnt[2][kStConsumerWarps];  // by tile parity
+    int prune;                    // mid-tile refresh of the current tile's bucket
+};
+static_assert(offsetof(YoloStreamSmem, live) % 16 == 0 && offsetof(YoloStreamSmem, full) % 8 == 0 &&
+                  offsetof(YoloStreamSmem, empty) % 8 == 0 && offsetof(YoloStreamSmem, meet) % 8 == 0 &&
+                  offsetof(YoloStreamSmem, w) % 8 == 0,
+              "shared-memory layout of the persistent decode");
+static_assert(sizeof(YoloStreamSmem) <= 75 * 1024, "three CTAs per SM");
+
+constexpr uint32_t kStWaitLimit = 100000u;
+
+struct StreamTile {
+    int img, lvl, S, SS, s0, n;
+    const float* base;
+};
+
+__device__ __forceinline__ StreamTile stream_tile(const YoloParams& P, int tile_id) {
+    StreamTile T;
+    T.img = tile_id / P.st_tiles_per_image;
+    int r = tile_id - T.img * P.st_tiles_per_image;
+    T.lvl = 0;
+    if (r >= P.st_tiles[0]) {
+        r -= P.st_tiles[0];
+        T.lvl = 1;
+        if (r >= P.st_tiles[1]) {
+            r -= P.st_tiles[1];
+            T.lvl = 2;
+        }
+    }
+    T.S = P.size[T.lvl];
+    T.SS = T.S * T.S;
+    T.s0 = r * kStTile;
+    T.n = min(kStTile, 3 * T.SS - T.s0);
+    T.base = P.map[T.lvl] + static_cast<int64_t>(T.img) * 255 * T.SS;
+    return T;
+}
+
+// One thread: copies of kSmRows channel planes starting at channel `ch0` (of the tile's anchor) into ring buffer `buf`.
+__device__ __forceinline__ void stream_issue(YoloStreamSmem& sm, const StreamTile& T, int ch0, int buf) {
+    mbar_arrive_expect_tx(&sm.full[buf], static_cast<uint32_t>(T.n) * 4u * kSmRows);
+    const int a0 = T.s0 / T.SS;
+    const int pa = T.s0 - a0 * T.SS;
+    const int len0 = min(T.n, T.SS - pa);  // slots of the first anchor; the rest (if any) starts the next anchor's planes
+#pragma unroll
+    for (int c = 0; c < kSmRows; ++c) {
+        bulk_copy_g2s(&sm.ring[buf][c][0], T.base + static_cast<int64_t>(a0 * kYoloAttrib + ch0 + c) * T.SS + pa,
+                      static_cast<uint32_t>(len0) * 4u, &sm.full[buf]);
+        if (len0 < T.n)
+            bulk_copy_g2s(&sm.ring[buf][c][len0], T.base + static_cast<int64_t>((a0 + 1) * kYoloAttrib + ch0 + c) * T.SS,
+                          static_cast<uint32_t>(T.n - len0) * 4u, &sm.full[buf]);
+    }
+}
+
+// Consumer warps meet (one arrival per warp).  Returns false when the wait ran out.
+__device__ __forceinline__ bool stream_meet(YoloStreamSmem& sm, uint32_t& phase) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(&sm.meet);
+    const bool ok = mbar_wait_bounded(&sm.meet, phase, kStWaitLimit);
+    phase ^= 1u;
+    return __all_sync(kFullMask, ok);
+}
+
+__global__ void __launch_bounds__(kStThreads, 3)
+yolo_decode_stream_kernel(const YoloParams P) {
+    extern __shared__ __align__(128) unsigned char st_raw[];
+    if (static_cast<int>(blockIdx.x) < P.num_direct) {  // levels whose planes cannot be staged: plain-load form
+        if (threadIdx.x >= kLiveThreads) return;
+        YoloLiveSmem& lsm = *reinterpret_cast<YoloLiveSmem*>(st_raw);
+        const int cta = blockIdx.x;
+        const int lvl = cta >= P.live_begin[2] ? 2 : (cta >= P.live_begin[1] ? 1 : 0);
+        yolo_live_level<0>(P, lvl, cta - P.live_begin[lvl], lsm);
+        return;
+    }
+    YoloStreamSmem& sm = *reinterpret_cast<YoloStreamSmem*>(st_raw);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const bool pruning = P.prune_topk > 0 && P.hist != nullptr;
+    if (t == 0) {
+#pragma unroll
+        for (int b = 0; b < kSmStages; ++b) {
+            mbar_init(&sm.full[b], 1);
+            mbar_init(&sm.empty[b], kStConsumerWarps);
+        }
+        mbar_init(&sm.meet, kStConsumerWarps);
+        fence_barrier_init();
+    }
+    __syncthreads();  // the only CTA-wide barrier
+
+    if (warp == kStConsumerWarps) {
+        // ---- producer warp: lane 0 waits and issues, the whole warp looks up pruning buckets ----
+        uint32_t seq = 0;  // ring steps issued so far
+        int ok = 1;
+        while (ok) {
+            int tile_id = 0;
+            if (lane == 0) tile_id = atomicAdd(P.work_counter, 1);
+            tile_id = __shfl_sync(kFullMask, tile_id, 0);
+            const bool last = tile_id >= P.st_total_tiles;
+            StreamTile T;
+            int bucket = 0;
+            if (!last) {
+                T = stream_tile(P, tile_id);
+                if (pruning) bucket = prune_digit_regs(P.hist + static_cast<int64_t>(T.img) * kHistBins, P.prune_topk);
+            }
+            if (lane == 0) {
+                const int steps = last ? 1 : kSmRingSteps;
+                for (int rs = 0; rs < steps; ++rs, ++seq) {
+                    const int buf = static_cast<int>(seq % kSmStages);
+                    if (seq >= kSmStages && !mbar_wait_bounded(&sm.empty[buf], ((seq / kSmStages) - 1u) & 1u, kStWaitLimit)) {
+                        ok = 0;
+                        break;
+                    }
+                    if (last) {
+                        sm.slot_tile[buf] = -1;
+                        mbar_arrive(&sm.full[buf]);  // nothing to copy: completes the buffer's phase at once
+                    } else if (rs == 0) {
+                        sm.slot_tile[buf] = tile_id;
+                        sm.slot_prune[buf] = bucket;
+                        stream_issue(sm, T, 0, buf);
+                    } else {
+                        stream_issue(sm, T, 5 + (rs - 1) * kSmRows, buf);
+                    }
+                }
+                if (!ok) {
+                    // a consumer never released a buffer: flag the call; do not leave while copies may still land
+                    if (P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
+                    const uint32_t first = seq > kSmStages ? seq - kSmStages : 0u;
+                    for (uint32_t q = first; q < seq; ++q)
+                        mbar_wait_bounded(&sm.full[q % kSmStages], (q / kSmStages) & 1u, kStWaitLimit);
+                }
+            }
+            ok = __shfl_sync(kFullMask, ok, 0);
+            if (last) break;
+        }
+        return;
+    }
+
+    // ---- consumer warps ----
+    YoloStWarp& ws = sm.w[warp];
+    const unsigned lt = (1u << lane) - 1u;
+    uint32_t seq = 0, meet_phase = 0;
+    int fill = 0, head = 0, tail = 0;  // warp-uniform
+    int parity = 0;
+    bool ok = true;
+#ifdef FB_PHASE_PROBE
+    long long tr_wait = 0, tr_p1 = 0, tr_steps = 0, tr_tiles = 0, tr_c0 = clock64(), tr_c1;
+    if (t == 0) FB_TRACE(0, global_ns());
+#define TR_LAP(acc) do { tr_c1 = clock64(); acc += tr_c1 - tr_c0; tr_c0 = tr_c1; } while (0)
+#else
+#define TR_LAP(acc) do { } while (0)
+#endif
+    while (ok) {
+        // box step of the next tile
+        int buf = static_cast<int>(seq % kSmStages);
+        ok = __all_sync(kFullMask, mbar_wait_bounded(&sm.full[buf], (seq / kSmStages) & 1u, kStWaitLimit));
+        if (!ok) break;
+        TR_LAP(tr_wait);
+        const int tile_id = sm.slot_tile[buf];
+#ifdef FB_PHASE_PROBE
+        if (tile_id < 0 && t == 0) {
+            FB_TRACE(1, global_ns());
+            FB_TRACE(2, static_cast<unsigned long long>(tr_wait));
+            FB_TRACE(3, static_cast<unsigned long long>(tr_p1));
+            FB_TRACE(4, static_cast<unsigned long long>(tr_steps));
+            FB_TRACE(5, static_cast<unsigned long long>(tr_tiles));
+        }
+        ++tr_tiles;
+#endif
+        if (tile_id < 0) return;  // no more work (nothing is pending: every tile ends with a flush)
+        int prune = sm.slot_prune[buf];  // candidates of buckets below this are dropped
+        const StreamTile T = stream_tile(P, tile_id);
+        int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(T.img) * kHistBins : nullptr;
+        float floor_score = prune > 0 ? __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift)) : 0.0f;
+
+        float so[kLiveSlots], vcut[kLiveSlots];
+        uint32_t flat0[kLiveSlots];
+        bool alive[kLiveSlots];
+        unsigned bal[kLiveSlots];
+        int mine = 0;
+        const float stride = P.stride[T.lvl];
+#pragma unroll
+        for (int q = 0; q < kLiveSlots; ++q) {
+            const int ls = q * kLiveThreads + t;
+            const bool valid = ls < T.n;
+            const int lsv = valid ? ls : 0;
+            const int sl = T.s0 + lsv;
+            const int anc = sl / T.SS, p = sl - anc * T.SS;
+            const float t0 = sm.ring[buf][0][lsv], t1 = sm.ring[buf][1][lsv], t2 = sm.ring[buf][2][lsv],
+                        t3 = sm.ring[buf][3][lsv], t4 = sm.ring[buf][4][lsv];
+            const int gy = p / T.S, gx = p - gy * T.S;
+            const float aw = anc == 0 ? P.anchor_w[T.lvl][0] : (anc == 1 ? P.anchor_w[T.lvl][1] : P.anchor_w[T.lvl][2]);
+            const float ah = anc == 0 ? P.anchor_h[T.lvl][0] : (anc == 1 ? P.anchor_h[T.lvl][1] : P.anchor_h[T.lvl][2]);
+            const float cx = __fmul_rn(__fadd_rn(sigmoid_f32(t0), static_cast<float>(gx)), stride);
+            const float cy = __fmul_rn(__fadd_rn(sigmoid_f32(t1), static_cast<float>(gy)), stride);
+            const float hw = __fmul_rn(__fmul_rn(expf(t2), aw), 0.5f);
+            const float hh = __fmul_rn(__fmul_rn(expf(t3), ah), 0.5f);
+            so[q] = sigmoid_f32(t4);
+            const int box = P.box_begin[T.lvl] + p * 3 + anc;
+            if (valid) {
+                reinterpret_cast<float4*>(P.boxes)[static_cast<int64_t>(T.img) * P.num_boxes + box] =
+                    make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
+            }
+            flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
+            // a score is so * sigmoid(v) <= so: the box can only yield candidates if so itself clears both bars
+            alive[q] = valid && so[q] > P.thr && so[q] >= floor_score;
+            vcut[q] = alive[q] ? logit_cut(so[q], fmaxf(P.thr, floor_score)) : INFINITY;
+            bal[q] = __ballot_sync(kFullMask, alive[q]);
+            mine += __popc(bal[q]);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(&sm.empty[buf]);  // the box step's buffer is free again
+            sm.warp_cnt[parity][warp] = mine;
+        }
+        ++seq;
+        // meet 1: every warp has finished the previous tile (its survivor list is free) and posted its count
+        ok = stream_meet(sm, meet_phase);
+        if (!ok) break;
+        int wbase = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < kStConsumerWarps; ++w) {
+            const int c = sm.warp_cnt[parity][w];
+            if (w < warp) wbase += c;
+            total += c;
+        }
+        parity ^= 1;
+#pragma unroll
+        for (int q = 0; q < kLiveSlots; ++q) {
+            if (alive[q]) {
+                YoloLive e;
+                e.so = so[q];
+                e.v_cut = vcut[q];
+                e.chan = static_cast<uint32_t>(q * kLiveThreads + t);
+                e.flat0 = flat0[q];
+                sm.live[wbase + __popc(bal[q] & ((1u << lane) - 1u))] = e;
+            }
+            wbase += __popc(bal[q]);
+        }
+        if (t == 0) sm.prune = prune;
+        // meet 2: the survivor list is complete
+        ok = stream_meet(sm, meet_phase);
+        if (!ok) break;
+        TR_LAP(tr_p1);
+
+        // ---- class steps ----
+        uint64_t* gkeys = P.keys + static_cast<int64_t>(T.img) * P.capacity;
+        int32_t* gcount = P.counts + T.img;
+        const StEvalArgs ea{P.thr, P.hist_base, P.hist_shift, ghist, gkeys, gcount, P.capacity, P.status};
+#pragma unroll 1
+        for (int step = 0; step < kSmSteps; ++step, ++seq) {
+            buf = static_cast<int>(seq % kSmStages);
+            if (pruning) {
+                // the last consumer warp (it holds the fewest survivors) refreshes the bucket twice per tile
+                if (warp == kStConsumerWarps - 1 && (step == 4 || step == 9)) {
+                    const int d = prune_digit_regs(ghist, P.prune_topk);
+                    if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
+                    __syncwarp();
+                }
+                const int now = *reinterpret_cast<volatile int*>(&sm.prune);  // one broadcast read
+                if (now > prune) {  // raise the cuts of this thread's survivors
+                    prune = now;
+                    floor_score = __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift));
+                    for (int k = t; k < total; k += kLiveThreads) {
+                        const float so_k = sm.live[k].so;
+                        sm.live[k].v_cut = so_k >= floor_score ? logit_cut(so_k, fmaxf(P.thr, floor_score)) : INFINITY;
+                    }
+                }
+            }
+            ok = __all_sync(kFullMask, mbar_wait_bounded(&sm.full[buf], (seq / kSmStages) & 1u, kStWaitLimit));
+            if (!ok) break;
+            TR_LAP(tr_wait);
+#pragma unroll 1
+            for (int k0 = warp * 32; k0 < total; k0 += kLiveThreads) {
+                const int k = k0 + lane;
+                const bool has = k < total;
+                float vc = INFINITY;
+                int ls = 0;
+                if (has) {
+                    const YoloLive me = sm.live[k];
+                    vc = me.v_cut;
+                    ls = static_cast<int>(me.chan);
+                }
+                const uint32_t meta0 = (static_cast<uint32_t>(k) << 8) | static_cast<uint32_t>(step * kSmRows);
+                float v[kSmRows];
+#pragma unroll
+                for (int u = 0; u < kSmRows; ++u) v[u] = sm.ring[buf][u][ls];
+#pragma unroll
+                for (int u = 0; u < kSmRows; ++u) {
+                    const bool pred = v[u] > vc;
+                    const unsigned m = __ballot_sync(kFullMask, pred);
+                    if (pred) {
+                        YoloHit e;
+                        e.v = v[u];
+                        e.meta = meta0 + static_cast<uint32_t>(u);
+                        ws.queue[(tail + __popc(m & lt)) & (kStQueue - 1)] = e;
+                    }
+                    tail += __popc(m);
+                    if ((u & 1) == 1 || u == kSmRows - 1) {  // at most 64 new entries between two looks at the queue
+                        __syncwarp();
+                        while (tail - head >= 32) {
+                            fill = st_eval_batch(sm.live, &ws, head, 32, ea, prune, fill);
+                            head += 32;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.empty[buf]);  // this warp is done with the buffer
+            TR_LAP(tr_steps);
+        }
+        if (!ok) break;
+        // the queue refers to this tile's survivor list and the key stage to this image: drain both
+        __syncwarp();
+        if (tail - head > 0) {
+            fill = st_eval_batch(sm.live, &ws, head, tail - head, ea, prune, fill);
+            head = tail;
+        }
+        if (fill > 0) st_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+    }
+    // only reached when a wait ran out
+    if (lane == 0 && P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
+}
+
+// Development switch (functs_b200_debug_set "yolo_prune"): 0 keeps every candidate above the score threshold.
+static int g_yolo_prune = 1;
+void yolo_set_prune(int on) { g_yolo_prune = on ? 1 : 0; }
+static int g_yolo_tile_major = 1, g_yolo_refresh_all = 0, g_yolo_mode = 1;  // mode: 0 persistent, 1 one tile per CTA, 2 plain loads
+void yolo_set_stream(int on) { g_yolo_mode = on ? 0 : 1; }
+void yolo_set_mode(int m) { g_yolo_mode = m; }
+void yolo_set_tile_major(int on) { g_yolo_tile_major = on ? 1 : 0; }
+void yolo_set_refresh_all(int on) { g_yolo_refresh_all = on ? 1 : 0; }
 
 static const float kAnchors[3][3][2] = {{{116, 90}, {156, 198}, {373, 326}},
                                         {{30, 61}, {62, 45}, {59, 119}},
@@ -742,8 +1305,8 @@ static const float kStrides[3] = {32.f, 16.f, 8.f};
 
 int launch_yolo_decode(const float* map0, const float* map1, const float* map2, int batch, int s0, int s1, int s2,
                        float score_thr, float* boxes, float* obj_out, float* cls_out, uint64_t* cand_keys,
-                       int32_t* cand_counts, int64_t capacity, int32_t* hist, int zero_first, int32_t* status,
-                       cudaStream_t st) {
+                       int32_t* cand_counts, int64_t capacity, int32_t* hist, int zero_first, int prune_topk,
+                       int32_t* work_counter, int32_t* status, cudaStream_t st) {
     FB_REQUIRE(map0 && map1 && map2 && boxes && cand_keys && cand_counts, "yolo_decode: null pointer");
     FB_REQUIRE(batch > 0 && s0 > 0 && s1 > 0 && s2 > 0 && s0 <= 1024 && s1 <= 1024 && s2 <= 1024 && capacity > 0,
                "yolo_decode: bad sizes");
@@ -783,6 +1346,9 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     P.capacity = capacity;
     P.status = status;
     P.hist = hist;
+    P.prune_topk = (hist != nullptr && prune_topk > 0) ? prune_topk : 0;
+    P.tile_major = g_yolo_tile_major;
+    P.refresh_all = g_yolo_refresh_all;
     const HistParams hp = hist_params_for(score_thr);
     P.hist_base = hp.base;
     P.hist_shift = hp.shift;
@@ -800,18 +1366,53 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
         count_launch();
         return check_launch("yolo_decode_kernel");
     }
+    FB_REQUIRE(255ll * S[0] * S[0] < (1ll << 32) && 255ll * S[1] * S[1] < (1ll << 32) && 255ll * S[2] * S[2] < (1ll << 32),
+               "yolo_decode: level map too large");
+    if (work_counter != nullptr && g_yolo_mode == 0) {
+        // persistent form: CTAs of the plain-load levels first, then about three resident CTAs per SM that fetch tiles
+        int64_t direct_acc = 0;
+        int per_image = 0;
+        for (int l = 0; l < 3; ++l) {
+            P.staged[l] = ((S[l] * S[l]) % 4 == 0 && S[l] * S[l] >= kStTile && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 1 : 0;
+            P.live_begin[l] = static_cast<int>(direct_acc);
+            P.st_tiles[l] = 0;
+            if (P.staged[l]) {
+                P.st_tiles[l] = (3 * S[l] * S[l] + kStTile - 1) / kStTile;
+                per_image += P.st_tiles[l];
+            } else {
+                direct_acc += static_cast<int64_t>((3 * S[l] * S[l] + kLiveTile - 1) / kLiveTile) * batch;
+            }
+        }
+        P.live_begin[3] = static_cast<int>(direct_acc);
+        const int64_t total_tiles = static_cast<int64_t>(per_image) * batch;
+        FB_REQUIRE(direct_acc + total_tiles < (1ll << 30), "yolo_decode: too many tiles");
+        P.num_direct = static_cast<int>(direct_acc);
+        P.st_tiles_per_image = per_image > 0 ? per_image : 1;
+        P.st_total_tiles = static_cast<int>(total_tiles);
+        P.work_counter = work_counter;
+        int dev = 0, sms = 0;
+        FB_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
+        FB_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"));
+        const int64_t resident = 3ll * sms;
+        const int64_t workers = total_tiles < resident ? total_tiles : resident;
+        const size_t smem_s = sizeof(YoloStreamSmem) > sizeof(YoloLiveSmem) ? sizeof(YoloStreamSmem) : sizeof(YoloLiveSmem);
+        FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem_s)),
+                          "yolo_decode attr"));
+        yolo_decode_stream_kernel<<<static_cast<unsigned>(direct_acc + workers), kStThreads, smem_s, st>>>(P);
+        count_launch();
+        return check_launch("yolo_decode_stream_kernel");
+    }
     int64_t live_acc = 0;
     for (int l = 0; l < 3; ++l) {
         // a plane of S * S floats keeps every row 16-byte aligned iff S * S is a multiple of 4 (and the map itself is)
         // (and a plane at least as long as a tile, so that a tile touches at most two anchors)
-        P.staged[l] = ((S[l] * S[l]) % 4 == 0 && S[l] * S[l] >= kStTile && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 1 : 0;
+        P.staged[l] = (g_yolo_mode != 2 && (S[l] * S[l]) % 4 == 0 && S[l] * S[l] >= kStTile && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 1 : 0;
         const int tile = P.staged[l] ? kStTile : kLiveTile;
         P.live_begin[l] = static_cast<int>(live_acc);
         live_acc += static_cast<int64_t>((3 * S[l] * S[l] + tile - 1) / tile) * batch;
     }
     FB_REQUIRE(live_acc < (1ll << 31), "yolo_decode: too many tiles");
-    FB_REQUIRE(255ll * S[0] * S[0] < (1ll << 32) && 255ll * S[1] * S[1] < (1ll << 32) && 255ll * S[2] * S[2] < (1ll << 32),
-               "yolo_decode: level map too large");
     P.live_begin[3] = static_cast<int>(live_acc);
     const unsigned nlive = static_cast<unsigned>(live_acc);
     const size_t smem = sizeof(YoloStagedSmem) > sizeof(YoloLiveSmem) ? sizeof(YoloStagedSmem) : sizeof(YoloLiveSmem);
@@ -819,12 +1420,12 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
         FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<13, 26, 52>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
                           "yolo_decode attr"));
-        yolo_decode_staged_kernel<13, 26, 52><<<nlive, kLiveThreads, smem, st>>>(P);
+        yolo_decode_staged_kernel<13, 26, 52><<<nlive, kStThreads, smem, st>>>(P);
     } else {
         FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<0, 0, 0>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
                           "yolo_decode attr"));
-        yolo_decode_staged_kernel<0, 0, 0><<<nlive, kLiveThreads, smem, st>>>(P);
+        yolo_decode_staged_kernel<0, 0, 0><<<nlive, kStThreads, smem, st>>>(P);
     }
     count_launch();
     return check_launch("yolo_decode_staged_kernel");
@@ -835,7 +1436,7 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 // Scratch of the one-call post-process.  The first `zero_bytes` bytes hold everything that must be zero when a
 // call starts (candidate counts, score histogram, selection counters) and are cleared by ONE memset.
 struct YoloScratch {
-    int64_t counts_off, hist_off, ctr_off, zero_bytes;
+    int64_t counts_off, hist_off, ctr_off, work_off, zero_bytes;
     int64_t keys_off, sel_keys_off, sel_counts_off, lists_off, mask_off, total;
 };
 
@@ -848,6 +1449,8 @@ static YoloScratch yolo_scratch_layout(int batch, int64_t capacity, int topk) {
     off = align_up(off + static_cast<int64_t>(batch) * kHistBins * 4, 256);
     L.ctr_off = off;
     off = align_up(off + select_binned_ctr_bytes(batch), 256);
+    L.work_off = off;  // tile counter of the persistent decode kernel
+    off += 256;
     L.zero_bytes = off;
     L.keys_off = off;
     off = align_up(off + static_cast<int64_t>(batch) * capacity * 8, 256);
@@ -872,7 +1475,7 @@ int functs_b200_yolo_decode(const float* map0, const float* map1, const float* m
                             uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
                             int32_t* status, void* stream) {
     return fb::launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, obj_out, cls_out, cand_keys,
-                                  cand_counts, capacity, hist, 1, status, fb::as_stream(stream));
+                                  cand_counts, capacity, hist, 1, 0, nullptr, status, fb::as_stream(stream));
 }
 
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
@@ -903,8 +1506,9 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
     const int num_boxes = 3 * (s0 * s0 + s1 * s1 + s2 * s2);
     FB_TRY(check_cuda(cudaMemsetAsync(base, 0, static_cast<size_t>(L.zero_bytes), st), "memset yolo counters"));
     record_stage_event(0, st);
+    // only the topk best candidates of an image are used below: let the decode kernel drop hopeless ones early
     FB_TRY(launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, nullptr, nullptr, keys, counts,
-                              capacity, hist, 0, status, st));
+                              capacity, hist, 0, g_yolo_prune ? topk : 0, reinterpret_cast<int32_t*>(base + L.work_off), status, st));
     record_stage_event(1, st);
     FB_TRY(launch_select_binned(keys, counts, capacity, hist, score_thr, batch, topk, sel_keys, sel_counts,
                                 base + L.ctr_off, base + L.lists_off, 0, st));

@@ -177,7 +177,10 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
                                   float* hs, float* cs, int32_t* status, void* scratch, void* stream, int32_t mode);
 
 /* Debugging switches (name -> value); returns FB_ERR_NOT_FOUND for an unknown name.
- *   "lstm_tc_swap_lbo_sbo": exchange the two stride fields of the tensor-core shared-memory descriptors. */
+ *   "lstm_tc_swap_lbo_sbo": exchange the two stride fields of the tensor-core shared-memory descriptors.
+ *   "yolo_prune": 0 makes functs_b200_yolo_postprocess keep every candidate above the score threshold instead of
+ *                 dropping, inside the decode kernel, those that can no longer reach the top-k (default 1; the
+ *                 outputs are the same either way). */
 int functs_b200_debug_set(const char* name, int32_t value);
 
 /* ---- C5: YOLACT-style mask assembly ------------------------------------------------------------ */
