@@ -226,10 +226,6 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 
 namespace fb {
 void yolo_set_prune(int on);
-void yolo_set_tile_major(int on);
-void yolo_set_refresh_all(int on);
-void yolo_set_stream(int on);
-void yolo_set_mode(int m);
 }
 
 extern "C" {
@@ -305,22 +301,6 @@ int functs_b200_debug_set(const char* name, int32_t value) {
     }
     if (name != nullptr && std::strcmp(name, "yolo_prune") == 0) {
         fb::yolo_set_prune(value);
-        return FB_OK;
-    }
-    if (name != nullptr && std::strcmp(name, "yolo_tile_major") == 0) {
-        fb::yolo_set_tile_major(value);
-        return FB_OK;
-    }
-    if (name != nullptr && std::strcmp(name, "yolo_mode") == 0) {
-        fb::yolo_set_mode(value);
-        return FB_OK;
-    }
-    if (name != nullptr && std::strcmp(name, "yolo_stream") == 0) {
-        fb::yolo_set_stream(value);
-        return FB_OK;
-    }
-    if (name != nullptr && std::strcmp(name, "yolo_refresh_all") == 0) {
-        fb::yolo_set_refresh_all(value);
         return FB_OK;
     }
     fb::set_error("debug_set: unknown switch");

@@ -94,11 +94,192 @@ select_topk_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restri
     if (threadIdx.x == 0) out_counts[g] = m;
 }
 
+// ---- NMS ----------------------------------------------------------------------------------------------------------
+// The kernels work on the NMS-space boxes rebuilt from the selected keys: gather the box of every selected candidate,
+// take the maximum coordinate over them, shift each box by label * (max + 1).
+constexpr int kNmsMaxN = 1024;
+constexpr int kNmsWords = kNmsMaxN / 32;
+constexpr int kMaskThreads = 256;
+constexpr int kMaskCtas = 12;          // CTAs per group in the matrix kernel (rows interleaved)
+constexpr int kMaskMaxBuckets = 1024; // class buckets used for pruning (more classes than this: one bucket)
+constexpr int kScanChunk = 256;       // non-empty matrix rows staged in shared memory at a time
+
+// ---- suppression matrix ------------------------------------------------------------------------------------------
+// Class pruning.  With class offsets, class c occupies the coordinate range [c*M + lo, c*M + hi] (M = hi + 1, lo / hi the
+// extreme coordinates of the selected boxes), so boxes whose labels differ by more than K = floor((hi - lo) / M) + 1
+// cannot intersect.  The candidates are bucketed by label (counting sort) and a row only tests the members of the
+// buckets within K of its own label; every pair that can intersect is still tested with the exact IoU expression, so
+// the matrix is the same as the one an all-pairs loop produces.
+//
+// nms_prepare_block (run by the CTA that finishes a group's top-k selection, or by nms_prepare_kernel when the selected
+// keys come from elsewhere) gathers the selected boxes, applies the class offsets, and leaves the boxes, their buckets
+// and the bucket order in scratch; nms_mask_scan_kernel (kMaskCtas CTAs per group) copies that into shared memory and
+// computes its share of the rows; the CTA of a group that finishes last then runs the greedy scan.
+struct NmsPrepHeader {
+    int n, nb, reach, pad;
+};
+constexpr int64_t kPrepBoxesOff = 16;
+constexpr int64_t kPrepLabelOff = kPrepBoxesOff + static_cast<int64_t>(kNmsMaxN) * sizeof(NmsBox);
+constexpr int64_t kPrepOrderOff = kPrepLabelOff + kNmsMaxN * 2;
+constexpr int64_t kPrepStartOff = kPrepOrderOff + kNmsMaxN * 2;
+constexpr int64_t kPrepBytes = (kPrepStartOff + (kMaskMaxBuckets + 1) * 4 + 255) / 256 * 256;
+static_assert(sizeof(NmsBox) == 20 && kPrepBoxesOff % 16 == 0 && kPrepLabelOff % 16 == 0 && kPrepOrderOff % 16 == 0 &&
+                  kPrepStartOff % 4 == 0 && kPrepBytes % 256 == 0,
+              "prepared NMS input layout");
+
+template <int NT>
+struct NmsPrepSmem {
+    uint16_t slabel[kNmsMaxN];
+    int bcursor[kMaskMaxBuckets];
+    float red_hi[NT / 32 + 1], red_lo[NT / 32 + 1];
+};
+
+// All NT threads of a CTA.  sel: the group's n selected keys, sorted (shared or global memory); boxes_g: the group's
+// boxes; prep: the group's prepared-input record; ticket: the group's arrival counter of the matrix kernel (cleared).
+template <int NT>
+__device__ __forceinline__ void nms_prepare_block(const float* __restrict__ boxes_g, int num_classes, int class_offset,
+                                                  const uint64_t* sel, int n, unsigned char* __restrict__ prep,
+                                                  int32_t* ticket, NmsPrepSmem<NT>& ps) {
+    uint16_t* slabel = ps.slabel;
+    int* bcursor = ps.bcursor;
+    float* red_hi = ps.red_hi;
+    float* red_lo = ps.red_lo;
+    const int t = threadIdx.x;
+    const int lane = t & 31, warp = t >> 5;
+    NmsBox* pb = reinterpret_cast<NmsBox*>(prep + kPrepBoxesOff);
+    uint16_t* plabel = reinterpret_cast<uint16_t*>(prep + kPrepLabelOff);
+    uint16_t* porder = reinterpret_cast<uint16_t*>(prep + kPrepOrderOff);
+    int* pstart = reinterpret_cast<int*>(prep + kPrepStartOff);
+    const int nb = (class_offset && num_classes <= kMaskMaxBuckets) ? num_classes : 1;
+
+    // gather: thread t owns candidates t, t + NT, ...
+    constexpr int kPer = kNmsMaxN / NT;
+    float4 bx[kPer];
+    int label[kPer];
+    float lmax = -INFINITY, lmin = INFINITY;
+    for (int i = t; i < nb; i += NT) bcursor[i] = 0;
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+        const int c = t + q * NT;
+        bx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        label[q] = 0;
+        if (c < n) {
+            const uint32_t flat = key_index(sel[c]);
+            const uint32_t box = flat / static_cast<uint32_t>(num_classes);
+            label[q] = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
+            bx[q] = reinterpret_cast<const float4*>(boxes_g)[box];
+            lmax = fmaxf(lmax, fmaxf(fmaxf(bx[q].x, bx[q].y), fmaxf(bx[q].z, bx[q].w)));
+            lmin = fminf(lmin, fminf(fminf(bx[q].x, bx[q].y), fminf(bx[q].z, bx[q].w)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
+        lmin = fminf(lmin, __shfl_xor_sync(kFullMask, lmin, o));
+    }
+    if (lane == 0) {
+        red_hi[warp] = lmax;
+        red_lo[warp] = lmin;
+    }
+    __syncthreads();
+    if (t < 32) {
+        float v = (t < NT / 32) ? red_hi[t] : -INFINITY;
+        float u = (t < NT / 32) ? red_lo[t] : INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
+            u = fminf(u, __shfl_xor_sync(kFullMask, u, o));
+        }
+        if (t == 0) {
+            red_hi[NT / 32] = v;
+            red_lo[NT / 32] = u;
+        }
+    }
+    __syncthreads();
+    const float hi = red_hi[NT / 32], lo = red_lo[NT / 32];
+    const float scale = __fadd_rn(hi, 1.0f);
+    // label distance beyond which two boxes cannot intersect (one extra bucket covers the fp32 rounding of the shifts)
+    int reach = nb;
+    if (nb > 1 && scale > 0.0f) {
+        const float r = floorf((hi - lo) / scale) + 1.0f;
+        if (r < static_cast<float>(nb)) reach = static_cast<int>(r);
+    }
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+        const int c = t + q * NT;
+        if (c < n) {
+            const float off = class_offset ? __fmul_rn(static_cast<float>(label[q]), scale) : 0.0f;
+            pb[c] = make_nms_box(__fadd_rn(bx[q].x, off), __fadd_rn(bx[q].y, off), __fadd_rn(bx[q].z, off),
+                                 __fadd_rn(bx[q].w, off));
+            const int bucket = nb > 1 ? label[q] : 0;
+            slabel[c] = static_cast<uint16_t>(bucket);
+            plabel[c] = static_cast<uint16_t>(bucket);
+            atomicAdd(&bcursor[bucket], 1);
+        }
+    }
+    __syncthreads();
+    // exclusive prefix of the bucket counts (one warp, contiguous chunk per lane), then the scatter
+    if (warp == 0) {
+        const int per = (nb + 31) / 32;
+        const int b0 = lane * per, b1 = min(nb, b0 + per);
+        int s = 0;
+        for (int i = b0; i < b1; ++i) s += bcursor[i];
+        int incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += v;
+        }
+        int run = incl - s;
+        for (int i = b0; i < b1; ++i) {
+            const int c = bcursor[i];
+            pstart[i] = run;
+            bcursor[i] = run;
+            run += c;
+        }
+        if (lane == 31) pstart[nb] = incl;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) {
+        const int c = t + q * NT;
+        if (c < n) porder[atomicAdd(&bcursor[slabel[c]], 1)] = static_cast<uint16_t>(c);
+    }
+    if (t == 0) {
+        NmsPrepHeader h;
+        h.n = n;
+        h.nb = nb;
+        h.reach = reach;
+        h.pad = 0;
+        *reinterpret_cast<NmsPrepHeader*>(prep) = h;
+        *ticket = 0;
+    }
+}
+
+// grid = groups; block = 256.  For selected keys that did not come from select_binned_kernel.
+__global__ void __launch_bounds__(kMaskThreads)
+nms_prepare_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
+                   const int32_t* __restrict__ sel_counts, int topk, int class_offset, unsigned char* __restrict__ prep_g,
+                   int32_t* __restrict__ ticket_g) {
+    __shared__ NmsPrepSmem<kMaskThreads> ps;
+    const int g = blockIdx.x;
+    int n = sel_counts[g];
+    if (n > topk) n = topk;
+    if (n < 0) n = 0;
+    nms_prepare_block<kMaskThreads>(boxes + static_cast<int64_t>(g) * num_boxes * 4, num_classes, class_offset,
+                                    sel_keys + static_cast<int64_t>(g) * topk, n, prep_g + static_cast<int64_t>(g) * kPrepBytes,
+                                    ticket_g + g, ps);
+}
+
+
+
 // ---- binned top-k: many CTAs per group collect, the last one to finish sorts --------------------------------
 // Needs the coarse score histogram that the candidate producer filled (hist[g][kHistBins]).  Every CTA finds the
 // boundary bucket d* (the largest d with count(digit >= d) >= topk), scans its share of the candidate list and
 // appends keys above d* to the group's `sel` list and keys inside d* to its `bin` list.  CTAs then take a ticket;
-// the one that draws the last ticket sorts the bin list, tops `sel` up from it and writes the sorted result.
+// the one that draws the last ticket sorts the bin list, tops `sel` up from it and writes the sorted result (if the
+// lists turn out not to fit the histogram, or the boundary bucket is too crowded, it runs the exact generic selection
+// over the whole candidate list instead), and, when asked to, prepares the group's NMS input (nms_prepare_block).
 // No CTA ever waits for another one.
 constexpr int kBinThreads = 512;
 constexpr int kBinSplit = 8;         // CTAs per group
@@ -119,8 +300,12 @@ __global__ void __launch_bounds__(kBinThreads, 2)
 select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restrict__ in_counts, int64_t capacity,
                      const int32_t* __restrict__ hist, uint32_t hist_base, int hist_shift, int32_t topk,
                      SelectCtr* ctr, uint64_t* sel_tmp, uint64_t* bin_tmp, uint64_t* __restrict__ out_keys,
-                     int32_t* __restrict__ out_counts) {
-    __shared__ __align__(16) BinnedSmem sm;
+                     int32_t* __restrict__ out_counts, const float* __restrict__ nms_boxes, int64_t num_boxes,
+                     int num_classes, int class_offset, unsigned char* __restrict__ prep_g, int32_t* __restrict__ ticket_g) {
+    constexpr size_t kRaw = sizeof(BinnedSmem) > sizeof(SelectSmem<kSelCap>) ? sizeof(BinnedSmem) : sizeof(SelectSmem<kSelCap>);
+    static_assert(sizeof(uint64_t) * kSelCap + sizeof(NmsPrepSmem<kBinThreads>) <= kRaw, "NMS preparation reuses the buffer");
+    __shared__ __align__(16) unsigned char raw[kRaw];
+    BinnedSmem& sm = *reinterpret_cast<BinnedSmem*>(raw);  // .sel is the first member of both views
     __shared__ int s_dstar, s_above, s_inbin, s_last;
     const int g = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -145,8 +330,9 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
         if (warp == 0) {
             constexpr int per = kHistBins / 32;
             const int lo = lane * per, hi = lo + per;
-            int s = 0;
-            for (int i = lo; i < hi; ++i) s += sh[i];
+            int s = 0;  // rotated reads: lane l starts at its bucket l, which keeps the 32 lanes on different banks
+#pragma unroll 8
+            for (int i = 0; i < per; ++i) s += sh[lo + ((i + lane) & (per - 1))];
             int incl = s;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -227,273 +413,226 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     // ---- the last CTA of the group finishes the selection ----
     const int sel_cnt = *reinterpret_cast<volatile int32_t*>(&c->sel_cnt);
     const int bin_cnt = *reinterpret_cast<volatile int32_t*>(&c->bin_cnt);
-    const int result = n < topk ? n : topk;
     const bool consistent = (n <= topk) ? (sel_cnt == n && sel_cnt <= kSelCap)
                                         : (sel_cnt == s_above && bin_cnt == s_inbin && sel_cnt < topk &&
                                            sel_cnt + bin_cnt >= topk && bin_cnt <= kBinListGlobal);
+    int result = n < topk ? n : topk;
     if (!consistent) {
         // the boundary bucket is too crowded (many equal scores) or the histogram does not describe this list:
-        // leave the group to the exact generic selection (select_fixup_kernel, launched right after this kernel)
+        // exact generic selection over the whole list (rare, slow)
         if (tid == 0) c->fallback = 1;
-        return;
-    }
-    for (int i = tid; i < sel_cnt; i += kBinThreads) sm.sel[i] = __ldcg(gsel + i);
-    if (n > topk) {
-        const int bn = next_pow2(bin_cnt);
-        for (int i = tid; i < bn; i += kBinThreads) sm.bin[i] = (i < bin_cnt) ? __ldcg(gbin + i) : 0ull;
         __syncthreads();
-        bitonic_sort_desc<kBinThreads>(sm.bin, bn);
-        const int want = topk - sel_cnt;
-        for (int i = tid; i < want; i += kBinThreads) sm.sel[sel_cnt + i] = sm.bin[i];
+        GlobalKeys kf{keys};
+        result = block_select_topk<kBinThreads, kSelCap, 4>(kf, n, topk, *reinterpret_cast<SelectSmem<kSelCap>*>(raw));
+        __syncthreads();
+    } else {
+        for (int i = tid; i < sel_cnt; i += kBinThreads) sm.sel[i] = __ldcg(gsel + i);
+        if (n > topk) {
+            const int bn = next_pow2(bin_cnt);
+            for (int i = tid; i < bn; i += kBinThreads) sm.bin[i] = (i < bin_cnt) ? __ldcg(gbin + i) : 0ull;
+            __syncthreads();
+            bitonic_sort_desc<kBinThreads>(sm.bin, bn);
+            const int want = topk - sel_cnt;
+            for (int i = tid; i < want; i += kBinThreads) sm.sel[sel_cnt + i] = sm.bin[i];
+        }
+        FB_PHASE(13);
+        const int sn = next_pow2(result);
+        for (int i = result + tid; i < sn; i += kBinThreads) sm.sel[i] = 0ull;
+        __syncthreads();
+        bitonic_sort_desc<kBinThreads>(sm.sel, sn);
     }
-    FB_PHASE(13);
-    const int sn = next_pow2(result);
-    for (int i = result + tid; i < sn; i += kBinThreads) sm.sel[i] = 0ull;
-    __syncthreads();
-    bitonic_sort_desc<kBinThreads>(sm.sel, sn);
     FB_PHASE(14);
     for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < result) ? sm.sel[i] : 0ull;
     if (tid == 0) out_counts[g] = result;
     FB_PHASE(15);
+    if (prep_g != nullptr) {
+        __syncthreads();
+        NmsPrepSmem<kBinThreads>& ps = *reinterpret_cast<NmsPrepSmem<kBinThreads>*>(raw + sizeof(uint64_t) * kSelCap);
+        nms_prepare_block<kBinThreads>(nms_boxes + static_cast<int64_t>(g) * num_boxes * 4, num_classes, class_offset, sm.sel,
+                                       result, prep_g + static_cast<int64_t>(g) * kPrepBytes, ticket_g + g, ps);
+        FB_PHASE(16);
+    }
 }
 
-// Groups that the binned kernel handed back (SelectCtr::fallback) are selected by the generic block-wide routine;
-// for every other group the CTA exits at once.
-__global__ void __launch_bounds__(kSelectThreads)
-select_fixup_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restrict__ in_counts, int64_t capacity,
-                    int32_t topk, const SelectCtr* __restrict__ ctr, uint64_t* __restrict__ out_keys,
-                    int32_t* __restrict__ out_counts) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int g = blockIdx.x;
-    if (ctr[g].fallback == 0) return;
-    SelectSmem<kSelCap>& sm = *reinterpret_cast<SelectSmem<kSelCap>*>(smem_raw);
-    int64_t cnt = in_counts[g];
-    if (cnt > capacity) cnt = capacity;
-    if (cnt < 0) cnt = 0;
-    GlobalKeys kf{in_keys + static_cast<int64_t>(g) * capacity};
-    const int m = block_select_topk<kSelectThreads, kSelCap, 4>(kf, static_cast<int>(cnt), topk, sm);
-    __syncthreads();
-    for (int i = threadIdx.x; i < topk; i += kSelectThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < m) ? sm.sel[i] : 0ull;
-    if (threadIdx.x == 0) out_counts[g] = m;
-}
+// grid = (kMaskCtas, groups); block = 256.  Rows are interleaved over the CTAs of a group (i = k * kMaskCtas +
+// blockIdx.x).  Each CTA writes its rows of the suppression matrix (and one flag per row: does the row suppress
+// anything at all?), then takes a ticket; the CTA that draws the group's last ticket runs the greedy scan: only rows
+// with at least one set bit can remove anything, so the flagged rows are listed in ascending order, staged in shared
+// memory kScanChunk at a time, and one warp walks them (row i is applied unless box i has been removed already; lane l
+// keeps the removed bits of boxes 32l .. 32l+31).  All threads of that CTA then write the compacted outputs.
+// No CTA waits for another one.
+struct NmsRowsSmem {
+    __align__(16) NmsBox sb[kNmsMaxN];
+    __align__(16) uint16_t slabel[kNmsMaxN];  // bucket of every candidate
+    __align__(16) uint16_t order[kNmsMaxN];   // candidates grouped by bucket
+    int bstart[kMaskMaxBuckets + 1];
+    uint32_t rowbuf[kMaskThreads / 32][kNmsWords];
+};
+struct NmsScanSmem {
+    uint32_t srow[kScanChunk][kNmsWords];
+    uint16_t nzrow[kNmsMaxN];
+    int part[kNmsMaxN / 32 + 1];
+    uint32_t keep_words[kNmsWords];
+    int word_prefix[kNmsWords + 1];
+};
 
-// ---- NMS: suppression bit matrix (many small CTAs per group) + serial keep-scan (one CTA per group) ------------
-// Both kernels work on the NMS-space boxes rebuilt from the selected keys: gather the box of every selected
-// candidate, take the maximum coordinate over them, shift each box by label * (max + 1).
-constexpr int kNmsMaxN = 1024;
-constexpr int kNmsWords = kNmsMaxN / 32;
-constexpr int kMaskThreads = 256;
-constexpr int kMaskRowsPerCta = 128;  // 16 rows per warp, interleaved over the CTAs of a group
-constexpr int kMaskMaxBuckets = 1024; // class buckets used for pruning (more classes than this: one bucket)
-constexpr int kScanThreads = 1024;
-
-// grid = (ceil(topk / 128), groups); block = 256.
-// Class pruning.  With class offsets, class c occupies the coordinate range [c*M + lo, c*M + hi] (M = hi + 1, lo / hi the
-// extreme coordinates of the selected boxes), so boxes whose labels differ by more than K = floor((hi - lo) / M) + 1
-// cannot intersect.  The candidates are bucketed by label (counting sort in shared memory) and a row only tests the
-// members of the buckets within K of its own label; every pair that can intersect is still tested with the exact
-// IoU expression, so the matrix is the same as the one an all-pairs loop produces.
 __global__ void __launch_bounds__(kMaskThreads)
-nms_mask_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
-                const int32_t* __restrict__ sel_counts, int topk, float thr, float thr_lo, float thr_hi, int class_offset,
-                uint32_t* __restrict__ mask_g) {
-    __shared__ NmsBox sb[kNmsMaxN];
-    __shared__ uint16_t slabel[kNmsMaxN];   // bucket of every candidate
-    __shared__ uint16_t order[kNmsMaxN];    // candidates grouped by bucket
-    __shared__ int bstart[kMaskMaxBuckets + 1];
-    __shared__ int bcursor[kMaskMaxBuckets];
-    __shared__ uint32_t rowbuf[kMaskThreads / 32][kNmsWords];
-    __shared__ float red_hi[kMaskThreads / 32 + 1], red_lo[kMaskThreads / 32 + 1];
+nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float thr_lo, float thr_hi,
+                     uint32_t* __restrict__ mask_g, uint8_t* __restrict__ rowflag_g, int32_t* __restrict__ ticket_g,
+                     const float* __restrict__ boxes, int64_t num_boxes, int num_classes,
+                     const uint64_t* __restrict__ sel_keys, int topk, float* __restrict__ dets,
+                     int64_t* __restrict__ labels, int64_t* __restrict__ flat_ids, int64_t* __restrict__ keep,
+                     int32_t* __restrict__ out_counts) {
+    constexpr size_t kRaw = sizeof(NmsRowsSmem) > sizeof(NmsScanSmem) ? sizeof(NmsRowsSmem) : sizeof(NmsScanSmem);
+    __shared__ __align__(16) unsigned char raw[kRaw];
+    __shared__ int s_last;
+    NmsRowsSmem& rs = *reinterpret_cast<NmsRowsSmem*>(raw);
     const int g = blockIdx.y;
     const int t = threadIdx.x;
     const int lane = t & 31, warp = t >> 5;
-    int n = sel_counts[g];
-    if (n > topk) n = topk;
+    const unsigned char* prep = prep_g + static_cast<int64_t>(g) * kPrepBytes;
+    const NmsPrepHeader h = *reinterpret_cast<const NmsPrepHeader*>(prep);
+    const int n = h.n, nb = h.nb, reach = h.reach;
     const int rt = gridDim.x;
-    if (static_cast<int>(blockIdx.x) >= n) return;  // rows are interleaved: i = k * rt + blockIdx.x
     FB_PHASE_BEGIN();
+    uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
+    uint8_t* gflag = rowflag_g + static_cast<int64_t>(g) * kNmsMaxN;
+    if (static_cast<int>(blockIdx.x) < n) {  // otherwise this CTA owns no row
+        {
+            // boxes (5 words each), buckets and order (8 candidates per 16 bytes), bucket starts: 16-byte copies
+            // (rounded up: the record and the shared arrays are padded to multiples of 16 bytes)
+            const uint4* src = reinterpret_cast<const uint4*>(prep + kPrepBoxesOff);
+            uint4* dst = reinterpret_cast<uint4*>(rs.sb);
+            for (int i = t; i < (n * 5 + 3) / 4; i += kMaskThreads) dst[i] = __ldg(src + i);
+            const uint4* lsrc = reinterpret_cast<const uint4*>(prep + kPrepLabelOff);
+            const uint4* osrc = reinterpret_cast<const uint4*>(prep + kPrepOrderOff);
+            uint4* ldst = reinterpret_cast<uint4*>(rs.slabel);
+            uint4* odst = reinterpret_cast<uint4*>(rs.order);
+            for (int i = t; i < (n + 7) / 8; i += kMaskThreads) {
+                ldst[i] = __ldg(lsrc + i);
+                odst[i] = __ldg(osrc + i);
+            }
+            const int* ssrc = reinterpret_cast<const int*>(prep + kPrepStartOff);
+            for (int i = t; i <= nb; i += kMaskThreads) rs.bstart[i] = __ldg(ssrc + i);
+        }
+        __syncthreads();
+        FB_PHASE(24);
+        uint32_t* myrow = rs.rowbuf[warp];
+        for (int i = warp * rt + static_cast<int>(blockIdx.x); i < n; i += (kMaskThreads / 32) * rt) {
+            const NmsBox bi = rs.sb[i];
+            const int li = rs.slabel[i];
+            const int p0 = rs.bstart[max(li - reach, 0)], p1 = rs.bstart[min(li + reach + 1, nb)];
+            myrow[lane] = 0u;
+            __syncwarp();
+            for (int base = p0; base < p1; base += 32) {
+                const int p = base + lane;
+                if (p < p1) {
+                    const int j = rs.order[p];
+                    if (j > i && iou_exceeds(bi, rs.sb[j], thr, thr_lo, thr_hi)) atomicOr(&myrow[j >> 5], 1u << (j & 31));
+                }
+            }
+            __syncwarp();
+            const uint32_t mw = myrow[lane];
+            gmask[i * kNmsWords + lane] = mw;
+            const bool any = __any_sync(kFullMask, mw != 0u);
+            if (lane == 0) gflag[i] = any ? 1 : 0;
+            __syncwarp();
+        }
+        FB_PHASE(27);
+    }
+    __threadfence();
+    __syncthreads();
+    if (t == 0) s_last = (atomicAdd(ticket_g + g, 1) == rt - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    // ---- the group's last CTA: greedy scan + outputs ----
+    NmsScanSmem& ss = *reinterpret_cast<NmsScanSmem*>(raw);
     const float* boxes_g = boxes + static_cast<int64_t>(g) * num_boxes * 4;
     const uint64_t* sel = sel_keys + static_cast<int64_t>(g) * topk;
-    uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
-    const int nb = (class_offset && num_classes <= kMaskMaxBuckets) ? num_classes : 1;
-
-    // gather: thread t owns candidates t, t + 256, ...
-    constexpr int kPer = kNmsMaxN / kMaskThreads;
-    float4 bx[kPer];
-    int label[kPer];
-    float lmax = -INFINITY, lmin = INFINITY;
-    for (int i = t; i < nb; i += kMaskThreads) bcursor[i] = 0;
+    // ascending list of the non-empty rows (candidate c = q * 256 + t)
+    constexpr int kRounds = kNmsMaxN / kMaskThreads;
+    bool nz[kRounds];
+    unsigned nzm[kRounds];
 #pragma unroll
-    for (int q = 0; q < kPer; ++q) {
-        const int c = t + q * kMaskThreads;
-        bx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        label[q] = 0;
-        if (c < n) {
-            const uint32_t flat = key_index(sel[c]);
-            const uint32_t box = flat / static_cast<uint32_t>(num_classes);
-            label[q] = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
-            bx[q] = reinterpret_cast<const float4*>(boxes_g)[box];
-            lmax = fmaxf(lmax, fmaxf(fmaxf(bx[q].x, bx[q].y), fmaxf(bx[q].z, bx[q].w)));
-            lmin = fminf(lmin, fminf(fminf(bx[q].x, bx[q].y), fminf(bx[q].z, bx[q].w)));
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        lmax = fmaxf(lmax, __shfl_xor_sync(kFullMask, lmax, o));
-        lmin = fminf(lmin, __shfl_xor_sync(kFullMask, lmin, o));
-    }
-    if (lane == 0) {
-        red_hi[warp] = lmax;
-        red_lo[warp] = lmin;
+    for (int q = 0; q < kRounds; ++q) {
+        const int c = q * kMaskThreads + t;
+        nz[q] = c < n && __ldcg(gflag + c) != 0;
+        nzm[q] = __ballot_sync(kFullMask, nz[q]);
+        if (lane == 0) ss.part[q * (kMaskThreads / 32) + warp] = __popc(nzm[q]);
     }
     __syncthreads();
-    if (t < 32) {
-        float v = (t < kMaskThreads / 32) ? red_hi[t] : -INFINITY;
-        float u = (t < kMaskThreads / 32) ? red_lo[t] : INFINITY;
+    int nz_total = 0;
+    int before[kRounds];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
-            u = fminf(u, __shfl_xor_sync(kFullMask, u, o));
-        }
-        if (t == 0) {
-            red_hi[kMaskThreads / 32] = v;
-            red_lo[kMaskThreads / 32] = u;
-        }
-    }
-    __syncthreads();
-    FB_PHASE(25);
-    const float hi = red_hi[kMaskThreads / 32], lo = red_lo[kMaskThreads / 32];
-    const float scale = __fadd_rn(hi, 1.0f);
-    // label distance beyond which two boxes cannot intersect (one extra bucket covers the fp32 rounding of the shifts)
-    int reach = nb;
-    if (nb > 1 && scale > 0.0f) {
-        const float r = floorf((hi - lo) / scale) + 1.0f;
-        if (r < static_cast<float>(nb)) reach = static_cast<int>(r);
+    for (int q = 0; q < kRounds; ++q) before[q] = 0;
+    for (int w = 0; w < kNmsMaxN / 32; ++w) {
+        const int cnt = ss.part[w];
+#pragma unroll
+        for (int q = 0; q < kRounds; ++q) before[q] += (w < q * (kMaskThreads / 32) + warp) ? cnt : 0;
+        nz_total += cnt;
     }
 #pragma unroll
-    for (int q = 0; q < kPer; ++q) {
-        const int c = t + q * kMaskThreads;
-        if (c < n) {
-            const float off = class_offset ? __fmul_rn(static_cast<float>(label[q]), scale) : 0.0f;
-            sb[c] = make_nms_box(__fadd_rn(bx[q].x, off), __fadd_rn(bx[q].y, off), __fadd_rn(bx[q].z, off),
-                                 __fadd_rn(bx[q].w, off));
-            const int bucket = nb > 1 ? label[q] : 0;
-            slabel[c] = static_cast<uint16_t>(bucket);
-            atomicAdd(&bcursor[bucket], 1);
-        }
-    }
+    for (int q = 0; q < kRounds; ++q)
+        if (nz[q]) ss.nzrow[before[q] + __popc(nzm[q] & ((1u << lane) - 1u))] = static_cast<uint16_t>(q * kMaskThreads + t);
     __syncthreads();
-    // exclusive prefix of the bucket counts (one warp, contiguous chunk per lane), then the scatter
+    FB_PHASE(20);
+    uint32_t removed = 0u;  // warp 0: lane l holds the removed bits of boxes 32l .. 32l+31
+    for (int c0 = 0; c0 < nz_total; c0 += kScanChunk) {
+        const int rows = min(kScanChunk, nz_total - c0);
+        if (t < rows) {  // one thread per row: eight 16-byte loads (L2-resident: just written)
+            const uint4* src = reinterpret_cast<const uint4*>(gmask + static_cast<int64_t>(ss.nzrow[c0 + t]) * kNmsWords);
+            uint4* dst = reinterpret_cast<uint4*>(&ss.srow[t][0]);
+#pragma unroll
+            for (int q = 0; q < kNmsWords / 4; ++q) dst[q] = __ldcg(src + q);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            for (int j0 = 0; j0 < rows; j0 += 32) {
+                const int mine = (j0 + lane < rows) ? ss.nzrow[c0 + j0 + lane] : 0;  // row numbers of the next 32 entries
+                const int cnt = min(32, rows - j0);
+                for (int j = 0; j < cnt; ++j) {
+                    const int i = __shfl_sync(kFullMask, mine, j);
+                    const uint32_t rw = __shfl_sync(kFullMask, removed, i >> 5);
+                    const uint32_t row = ss.srow[j0 + j][lane];
+                    if (!((rw >> (i & 31)) & 1u)) removed |= row;
+                }
+            }
+        }
+        __syncthreads();
+    }
     if (warp == 0) {
-        const int per = (nb + 31) / 32;
-        const int b0 = lane * per, b1 = min(nb, b0 + per);
-        int s = 0;
-        for (int i = b0; i < b1; ++i) s += bcursor[i];
-        int incl = s;
+        const int lo = lane * 32;
+        const uint32_t valid = n >= lo + 32 ? 0xffffffffu : (n > lo ? ((1u << (n - lo)) - 1u) : 0u);
+        const uint32_t kw = ~removed & valid;
+        ss.keep_words[lane] = kw;
+        // exclusive prefix of the kept counts
+        int incl = __popc(kw);
+        const int own = incl;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int v = __shfl_up_sync(kFullMask, incl, o);
             if (lane >= o) incl += v;
         }
-        int run = incl - s;
-        for (int i = b0; i < b1; ++i) {
-            const int c = bcursor[i];
-            bstart[i] = run;
-            bcursor[i] = run;
-            run += c;
+        ss.word_prefix[lane] = incl - own;
+        if (lane == 31) {
+            ss.word_prefix[kNmsWords] = incl;
+            out_counts[g] = incl;
         }
-        if (lane == 31) bstart[nb] = incl;
     }
-    __syncthreads();
-#pragma unroll
-    for (int q = 0; q < kPer; ++q) {
-        const int c = t + q * kMaskThreads;
-        if (c < n) order[atomicAdd(&bcursor[slabel[c]], 1)] = static_cast<uint16_t>(c);
-    }
-    __syncthreads();
-    FB_PHASE(26);
-
-    uint32_t* myrow = rowbuf[warp];
-    for (int rr = 0; rr < kMaskRowsPerCta / (kMaskThreads / 32); ++rr) {
-        const int i = (warp * (kMaskRowsPerCta / (kMaskThreads / 32)) + rr) * rt + blockIdx.x;
-        if (i >= n) continue;  // warp-uniform
-        const NmsBox bi = sb[i];
-        const int li = slabel[i];
-        const int p0 = bstart[max(li - reach, 0)], p1 = bstart[min(li + reach + 1, nb)];
-        myrow[lane] = 0u;
-        __syncwarp();
-        for (int base = p0; base < p1; base += 32) {
-            const int p = base + lane;
-            if (p < p1) {
-                const int j = order[p];
-                if (j > i && iou_exceeds(bi, sb[j], thr, thr_lo, thr_hi)) atomicOr(&myrow[j >> 5], 1u << (j & 31));
-            }
-        }
-        __syncwarp();
-        gmask[i * kNmsWords + lane] = myrow[lane];
-        __syncwarp();
-    }
-    FB_PHASE(27);
-}
-
-// grid = groups; block = 1024; dynamic smem = 1024 x 32 words.  Stages the group's bit matrix in shared memory, one
-// warp scans, all threads write the compacted outputs.
-__global__ void __launch_bounds__(kScanThreads)
-nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
-                const int32_t* __restrict__ sel_counts, int topk, const uint32_t* __restrict__ mask_g,
-                float* __restrict__ dets, int64_t* __restrict__ labels, int64_t* __restrict__ flat_ids,
-                int64_t* __restrict__ keep, int32_t* __restrict__ out_counts) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t* smask = reinterpret_cast<uint32_t*>(smem_raw);  // [n][32]
-    __shared__ uint32_t keep_words[kNmsWords];
-    __shared__ int word_prefix[kNmsWords + 1];
-    const int g = blockIdx.x;
-    const int t = threadIdx.x;
-    FB_PHASE_BEGIN();
-    int n = sel_counts[g];
-    if (n > topk) n = topk;
-    if (n < 0) n = 0;
-    const int words = (n + 31) >> 5;
-    const float* boxes_g = boxes + static_cast<int64_t>(g) * num_boxes * 4;
-    const uint64_t* sel = sel_keys + static_cast<int64_t>(g) * topk;
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords);
-        uint4* dst = reinterpret_cast<uint4*>(smask);
-        const int total = n * (kNmsWords / 4);
-        for (int i = t; i < total; i += kScanThreads) dst[i] = __ldg(src + i);
-    }
-    // the gathers for the output rows do not depend on the scan: issue them before it
-    uint64_t k = 0ull;
-    float4 bx = make_float4(0.f, 0.f, 0.f, 0.f);
-    uint32_t flat = 0u, box = 0u;
-    if (t < n) {
-        k = sel[t];
-        flat = key_index(k);
-        box = flat / static_cast<uint32_t>(num_classes);
-        bx = reinterpret_cast<const float4*>(boxes_g)[box];
-    }
-    if (t < kNmsWords) keep_words[t] = 0u;
-    __syncthreads();
-    FB_PHASE(20);
-    if (t < 32) warp_nms_scan(smask, kNmsWords, n, words, keep_words);
     __syncthreads();
     FB_PHASE(21);
-    if (t == 0) {
-        int acc = 0;
-        for (int w = 0; w < kNmsWords; ++w) {
-            word_prefix[w] = acc;
-            acc += __popc(keep_words[w]);
-        }
-        word_prefix[kNmsWords] = acc;
-        out_counts[g] = acc;
-    }
-    __syncthreads();
     const int64_t obase = static_cast<int64_t>(g) * topk;
-    if (t < n) {
-        const uint32_t kw = keep_words[t >> 5];
-        const int b = t & 31;
+    for (int c = t; c < n; c += kMaskThreads) {
+        const uint32_t kw = ss.keep_words[c >> 5];
+        const int b = c & 31;
         if ((kw >> b) & 1u) {
-            const int rank = word_prefix[t >> 5] + __popc(kw & ((1u << b) - 1u));
+            const uint64_t k = sel[c];
+            const uint32_t flat = key_index(k);
+            const uint32_t box = flat / static_cast<uint32_t>(num_classes);
+            const float4 bx = reinterpret_cast<const float4*>(boxes_g)[box];
+            const int rank = ss.word_prefix[c >> 5] + __popc(kw & ((1u << b) - 1u));
             float* d = dets + (obase + rank) * 5;
             d[0] = bx.x;
             d[1] = bx.y;
@@ -502,12 +641,12 @@ nms_scan_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_clas
             d[4] = key_score(k);
             labels[obase + rank] = static_cast<int64_t>(flat - box * static_cast<uint32_t>(num_classes));
             flat_ids[obase + rank] = static_cast<int64_t>(flat);
-            if (keep != nullptr) keep[obase + rank] = t;
+            if (keep != nullptr) keep[obase + rank] = c;
         }
     }
     // zero the tail so that the padded outputs are deterministic
-    const int total_kept = word_prefix[kNmsWords];
-    for (int i = total_kept + t; i < topk; i += kScanThreads) {
+    const int total_kept = ss.word_prefix[kNmsWords];
+    for (int i = total_kept + t; i < topk; i += kMaskThreads) {
         float* d = dets + (obase + i) * 5;
         d[0] = d[1] = d[2] = d[3] = d[4] = 0.0f;
         labels[obase + i] = -1;
@@ -557,39 +696,64 @@ int64_t select_binned_lists_bytes(int groups) {
     return static_cast<int64_t>(groups) * (kSelCap + kBinListGlobal) * sizeof(uint64_t);
 }
 
-// ctr must be zero when the kernel starts (zero_ctr != 0 makes this call clear it).
-int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, const int32_t* hist,
-                         float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
-                         void* lists, int zero_ctr, cudaStream_t st) {
-    FB_REQUIRE(in_keys && in_counts && hist && out_keys && out_counts && ctr && lists, "select_topk_binned: null pointer");
-    FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kSelCap && capacity > 0 && capacity < (1ll << 31),
-               "select_topk_binned: bad sizes (topk must be in [1, %d])", kSelCap);
-    FB_REQUIRE(thr > 0.0f, "select_topk_binned: the threshold must be positive");
-    if (zero_ctr) FB_TRY(check_cuda(cudaMemsetAsync(ctr, 0, select_binned_ctr_bytes(groups), st), "memset select counters"));
-    const HistParams hp = hist_params_for(thr);
-    uint64_t* sel_tmp = static_cast<uint64_t*>(lists);
-    uint64_t* bin_tmp = sel_tmp + static_cast<int64_t>(groups) * kSelCap;
-    dim3 grid(kBinSplit, groups);
-    select_binned_kernel<<<grid, kBinThreads, 0, st>>>(in_keys, in_counts, capacity, hist, hp.base, hp.shift, topk,
-                                                       static_cast<SelectCtr*>(ctr), sel_tmp, bin_tmp, out_keys, out_counts);
-    count_launch();
-    FB_TRY(check_launch("select_binned_kernel"));
-    const size_t smem = sizeof(SelectSmem<kSelCap>);
-    select_fixup_kernel<<<groups, kSelectThreads, smem, st>>>(in_keys, in_counts, capacity, topk,
-                                                               static_cast<const SelectCtr*>(ctr), out_keys, out_counts);
-    count_launch();
-    return check_launch("select_fixup_kernel");
+// Work area of batched NMS: [bit matrix: groups x 1024 x 32 words][row flags: groups x 1024 bytes]
+// [prepared input: groups x kPrepBytes, 256-byte aligned][tickets: groups x int32].
+struct NmsScratch {
+    uint32_t* mask;
+    uint8_t* rowflag;
+    unsigned char* prep;
+    int32_t* ticket;
+};
+static NmsScratch nms_scratch_views(void* base, int groups) {
+    NmsScratch v;
+    v.mask = static_cast<uint32_t*>(base);
+    v.rowflag = reinterpret_cast<uint8_t*>(v.mask) + static_cast<int64_t>(groups) * kNmsMaxN * kNmsWords * sizeof(uint32_t);
+    unsigned char* p = v.rowflag + static_cast<int64_t>(groups) * kNmsMaxN;
+    p += (256 - (reinterpret_cast<uintptr_t>(p) & 255)) & 255;
+    v.prep = p;
+    v.ticket = reinterpret_cast<int32_t*>(p + static_cast<int64_t>(groups) * kPrepBytes);
+    return v;
 }
-
-int64_t nms_mask_bytes(int groups) { return static_cast<int64_t>(groups) * kNmsMaxN * kNmsWords * sizeof(uint32_t); }
+int64_t nms_mask_bytes(int groups) {
+    return static_cast<int64_t>(groups) * (kNmsMaxN * kNmsWords * sizeof(uint32_t) + kNmsMaxN + kPrepBytes + 4) + 256;
+}
 int64_t nms_scratch_bytes(int groups, int topk) {
     (void)topk;
     return nms_mask_bytes(groups);
 }
 
+// ctr must be zero when the kernel starts (zero_ctr != 0 makes this call clear it).  With nms_scratch != nullptr the
+// CTA that finishes a group also prepares the group's NMS input there (boxes [groups, num_boxes, 4], flat index =
+// box * num_classes + label), so that launch_batched_nms(..., prepared = 1) can follow directly.
+int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, const int32_t* hist,
+                         float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
+                         void* lists, int zero_ctr, const float* nms_boxes, int64_t num_boxes, int num_classes,
+                         int class_offset, void* nms_scratch, cudaStream_t st) {
+    FB_REQUIRE(in_keys && in_counts && hist && out_keys && out_counts && ctr && lists, "select_topk_binned: null pointer");
+    FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kSelCap && capacity > 0 && capacity < (1ll << 31),
+               "select_topk_binned: bad sizes (topk must be in [1, %d])", kSelCap);
+    FB_REQUIRE(thr > 0.0f, "select_topk_binned: the threshold must be positive");
+    FB_REQUIRE(nms_scratch == nullptr || (nms_boxes != nullptr && num_boxes > 0 && num_classes > 0 &&
+                                          (reinterpret_cast<uintptr_t>(nms_boxes) & 15) == 0),
+               "select_topk_binned: NMS preparation needs 16-byte aligned boxes");
+    if (zero_ctr) FB_TRY(check_cuda(cudaMemsetAsync(ctr, 0, select_binned_ctr_bytes(groups), st), "memset select counters"));
+    const HistParams hp = hist_params_for(thr);
+    uint64_t* sel_tmp = static_cast<uint64_t*>(lists);
+    uint64_t* bin_tmp = sel_tmp + static_cast<int64_t>(groups) * kSelCap;
+    NmsScratch v{nullptr, nullptr, nullptr, nullptr};
+    if (nms_scratch != nullptr) v = nms_scratch_views(nms_scratch, groups);
+    dim3 grid(kBinSplit, groups);
+    select_binned_kernel<<<grid, kBinThreads, 0, st>>>(in_keys, in_counts, capacity, hist, hp.base, hp.shift, topk,
+                                                       static_cast<SelectCtr*>(ctr), sel_tmp, bin_tmp, out_keys, out_counts,
+                                                       nms_boxes, num_boxes, num_classes, class_offset, v.prep, v.ticket);
+    count_launch();
+    return check_launch("select_binned_kernel");
+}
+
+// prepared != 0: the group's NMS input is in the scratch already (launch_select_binned with the same scratch).
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
-                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask,
+                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
                        cudaStream_t st) {
     FB_REQUIRE(boxes && sel_keys && sel_counts && dets && labels && flat_ids && out_counts && mask,
                "batched_nms: null pointer");
@@ -599,20 +763,19 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
     FB_REQUIRE((reinterpret_cast<uintptr_t>(boxes) & 15) == 0 && (reinterpret_cast<uintptr_t>(mask) & 15) == 0,
                "batched_nms: boxes and scratch must be 16-byte aligned");
     const float thr_lo = iou_thr * (1.0f - 1.0e-6f), thr_hi = iou_thr * (1.0f + 1.0e-6f);
-    dim3 grid((topk + kMaskRowsPerCta - 1) / kMaskRowsPerCta, groups);
-    nms_mask_kernel<<<grid, kMaskThreads, 0, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk, iou_thr,
-                                                   thr_lo, thr_hi, class_offset, static_cast<uint32_t*>(mask));
-    count_launch();
-    FB_TRY(check_launch("nms_mask_kernel"));
-    const size_t smem = static_cast<size_t>(kNmsMaxN) * kNmsWords * sizeof(uint32_t);
-    FB_TRY(check_cuda(cudaFuncSetAttribute(nms_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem)),
-                      "nms_scan attr"));
-    nms_scan_kernel<<<groups, kScanThreads, smem, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk,
-                                                        static_cast<const uint32_t*>(mask), dets, labels, flat_ids, keep,
+    const NmsScratch v = nms_scratch_views(mask, groups);
+    if (!prepared) {
+        nms_prepare_kernel<<<groups, kMaskThreads, 0, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk,
+                                                            class_offset, v.prep, v.ticket);
+        count_launch();
+        FB_TRY(check_launch("nms_prepare_kernel"));
+    }
+    dim3 grid(kMaskCtas, groups);
+    nms_mask_scan_kernel<<<grid, kMaskThreads, 0, st>>>(v.prep, iou_thr, thr_lo, thr_hi, v.mask, v.rowflag, v.ticket, boxes,
+                                                        num_boxes, num_classes, sel_keys, topk, dets, labels, flat_ids, keep,
                                                         out_counts);
     count_launch();
-    return check_launch("nms_scan_kernel");
+    return check_launch("nms_mask_scan_kernel");
 }
 
 }  // namespace fb
@@ -649,7 +812,8 @@ int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_co
     }
     unsigned char* base = static_cast<unsigned char*>(scratch);
     return fb::launch_select_binned(in_keys, in_counts, capacity, hist, thr, groups, topk, out_keys, out_counts, base,
-                                    base + fb::select_binned_ctr_bytes(groups > 0 ? groups : 1), 1, fb::as_stream(stream));
+                                    base + fb::select_binned_ctr_bytes(groups > 0 ? groups : 1), 1, nullptr, 0, 0, 0, nullptr,
+                                    fb::as_stream(stream));
 }
 
 int64_t functs_b200_nms_scratch_bytes(int32_t groups, int32_t topk) {
@@ -666,7 +830,7 @@ int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_c
         return FB_ERR_INVALID_ARGUMENT;
     }
     return fb::launch_batched_nms(boxes, num_boxes, num_classes, sel_keys, sel_counts, groups, topk, iou_thr,
-                                  class_offset, dets, labels, flat_ids, keep, out_counts, scratch,
+                                  class_offset, dets, labels, flat_ids, keep, out_counts, scratch, 0,
                                   fb::as_stream(stream));
 }
 

@@ -15,11 +15,12 @@ int64_t select_binned_ctr_bytes(int groups);
 int64_t select_binned_lists_bytes(int groups);
 int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, const int32_t* hist,
                          float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
-                         void* lists, int zero_ctr, cudaStream_t st);
+                         void* lists, int zero_ctr, const float* nms_boxes, int64_t num_boxes, int num_classes,
+                         int class_offset, void* nms_scratch, cudaStream_t st);
 int64_t nms_mask_bytes(int groups);
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
-                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask,
+                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
                        cudaStream_t st);
 
 constexpr int kYoloThreads = 128;
@@ -38,13 +39,6 @@ struct YoloParams {
     int live_begin[4];  // the same for the candidate-only kernel (tiles of (anchor, position) slots per image)
     int staged[3];      // level goes through the bulk-copy staged path (16-byte aligned planes)
     int prune_topk;     // > 0: the caller only needs the prune_topk best candidates per image (see prune_digit)
-    int refresh_all;
-    int num_direct;            // persistent kernel: leading CTAs that run the plain-load form
-    int st_tiles[3];           // persistent kernel: tiles per image of every staged level (0: not staged)
-    int st_tiles_per_image;
-    int st_total_tiles;
-    int32_t* work_counter;     // persistent kernel: next tile to hand out (zero at launch)
-    int tile_major;     // CTA order of the staged levels: 1 = all images' first tiles, then all second tiles, ...
     int box_begin[3];   // first box index of every level inside an image
     float stride[3];
     float anchor_w[3][3];
@@ -715,11 +709,9 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     const int S = S_T > 0 ? S_T : P.size[lvl];
     const int SS = S * S;
     const int nslots = 3 * SS;
-    // tile-major CTA order: the CTAs of one image are spread over the whole launch, so that the later ones find the
-    // image's histogram filled by the earlier ones (see prune_digit)
     const int tiles = (nslots + kStTile - 1) / kStTile;
-    const int tile = P.tile_major ? local / P.batch : local % tiles;
-    const int img = P.tile_major ? local - tile * P.batch : local / tiles;
+    const int img = local / tiles;
+    const int tile = local - img * tiles;
     const int s0 = tile * kStTile;
     const int n = min(kStTile, nslots - s0);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -763,14 +755,11 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
 #pragma unroll
         for (int c = 0; c < 5; ++c) tv[q][c] = valid ? __ldg(src + c * SS) : 0.0f;
     }
-    if (warp == 0) {
+    if (producer) {  // idle until the first buffer comes back: look up the image's pruning bucket meanwhile
         const int d = pruning ? prune_digit(ghist, P.prune_topk, sm.hist_snapshot) : 0;
         if (lane == 0) sm.prune = d;
     }
-    __syncthreads();
-    int prune = sm.prune;  // candidates of buckets below this are dropped
-    // lowest score of bucket `prune`; 0 while nothing is pruned
-    float floor_score = prune > 0 ? __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift)) : 0.0f;
+    // box decode (does not need the bucket)
 #pragma unroll
     for (int q = 0; q < kLiveSlots; ++q) {
         const int anc = anc_[q], p = p_[q];
@@ -787,10 +776,17 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             reinterpret_cast<float4*>(P.boxes)[static_cast<int64_t>(img) * P.num_boxes + box] =
                 make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
         }
+        flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
+    }
+    __syncthreads();
+    int prune = sm.prune;  // candidates of buckets below this are dropped
+    // lowest score of bucket `prune`; 0 while nothing is pruned
+    float floor_score = prune > 0 ? __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift)) : 0.0f;
+#pragma unroll
+    for (int q = 0; q < kLiveSlots; ++q) {
         // a score is so * sigmoid(v) <= so: the box can only yield candidates if so itself clears both bars
         alive[q] = alive[q] && so[q] > P.thr && so[q] >= floor_score;
         vcut[q] = alive[q] ? logit_cut(so[q], fmaxf(P.thr, floor_score)) : INFINITY;
-        flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
     }
     unsigned bal[kLiveSlots];
     int mine = 0;
@@ -840,7 +836,7 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             }
             ok = __shfl_sync(kFullMask, ok, 0);
             if (!ok) break;
-            if (pruning && (P.refresh_all || step == 4 || step == 7)) {
+            if (pruning && (step == 4 || step == 7)) {
                 const int d = prune_digit(ghist, P.prune_topk, sm.hist_snapshot);
                 if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
             }
@@ -944,359 +940,9 @@ yolo_decode_staged_kernel(const YoloParams P) {
     }
 }
 
-// ---- persistent form of the staged decode ------------------------------------------------------------------
-// Used by the one-call post-process.  About three CTAs per SM stay resident and fetch tiles from a work counter.
-// The producer warp keeps the ring filled ACROSS tiles (it already streams the next tile while the consumer warps
-// finish the current one); the five box channels of a tile travel through the ring as well ("box step": ring step 0
-// of a tile, class step c is ring step c + 1), so the consumer warps never wait for a plain global load, and the
-// producer warp also looks up the tile's pruning bucket ahead of time.  The ring is finer and deeper than in the
-// one-tile-per-CTA form (5 channel planes per step, 6 buffers): the producer may only refill a buffer once ALL
-// consumer warps have released it, and more, smaller buffers keep more bytes in flight under that rule.
-// The consumer warps meet at tile boundaries through an mbarrier (bounded waits like everywhere else).
-constexpr int kSmRows = 5;
-constexpr int kSmStages = 6;
-constexpr int kSmSteps = kYoloClasses / kSmRows;  // class steps per tile
-constexpr int kSmRingSteps = kSmSteps + 1;        // + the box step
-static_assert(kYoloClasses % kSmRows == 0 && kSmRows >= 5, "the box step carries 5 channels");
-
-struct __align__(128) YoloStreamSmem {
-    float ring[kSmStages][kSmRows][kStTile];
-    YoloLive live[kStTile];  // .chan holds the slot's index inside the tile
-    YoloStWarp w[kStConsumerWarps];
-    uint64_t full[kSmStages];
-    uint64_t empty[kSmStages];
-    uint64_t meet;                // consumer warps: one arrival per warp
-    int slot_tile[kSmStages];   // tile carried by the box step in this ring buffer (-1: no more work)
-    int slot_prune[kSmStages];  // pruning bucket the producer warp found for that tile's image
-    int warp_cnt[2][kStConsumerWarps];  // by tile parity
-    int prune;                    // mid-tile refresh of the current tile's bucket
-};
-static_assert(offsetof(YoloStreamSmem, live) % 16 == 0 && offsetof(YoloStreamSmem, full) % 8 == 0 &&
-                  offsetof(YoloStreamSmem, empty) % 8 == 0 && offsetof(YoloStreamSmem, meet) % 8 == 0 &&
-                  offsetof(YoloStreamSmem, w) % 8 == 0,
-              "shared-memory layout of the persistent decode");
-static_assert(sizeof(YoloStreamSmem) <= 75 * 1024, "three CTAs per SM");
-
-constexpr uint32_t kStWaitLimit = 100000u;
-
-struct StreamTile {
-    int img, lvl, S, SS, s0, n;
-    const float* base;
-};
-
-__device__ __forceinline__ StreamTile stream_tile(const YoloParams& P, int tile_id) {
-    StreamTile T;
-    T.img = tile_id / P.st_tiles_per_image;
-    int r = tile_id - T.img * P.st_tiles_per_image;
-    T.lvl = 0;
-    if (r >= P.st_tiles[0]) {
-        r -= P.st_tiles[0];
-        T.lvl = 1;
-        if (r >= P.st_tiles[1]) {
-            r -= P.st_tiles[1];
-            T.lvl = 2;
-        }
-    }
-    T.S = P.size[T.lvl];
-    T.SS = T.S * T.S;
-    T.s0 = r * kStTile;
-    T.n = min(kStTile, 3 * T.SS - T.s0);
-    T.base = P.map[T.lvl] + static_cast<int64_t>(T.img) * 255 * T.SS;
-    return T;
-}
-
-// One thread: copies of kSmRows channel planes starting at channel `ch0` (of the tile's anchor) into ring buffer `buf`.
-__device__ __forceinline__ void stream_issue(YoloStreamSmem& sm, const StreamTile& T, int ch0, int buf) {
-    mbar_arrive_expect_tx(&sm.full[buf], static_cast<uint32_t>(T.n) * 4u * kSmRows);
-    const int a0 = T.s0 / T.SS;
-    const int pa = T.s0 - a0 * T.SS;
-    const int len0 = min(T.n, T.SS - pa);  // slots of the first anchor; the rest (if any) starts the next anchor's planes
-#pragma unroll
-    for (int c = 0; c < kSmRows; ++c) {
-        bulk_copy_g2s(&sm.ring[buf][c][0], T.base + static_cast<int64_t>(a0 * kYoloAttrib + ch0 + c) * T.SS + pa,
-                      static_cast<uint32_t>(len0) * 4u, &sm.full[buf]);
-        if (len0 < T.n)
-            bulk_copy_g2s(&sm.ring[buf][c][len0], T.base + static_cast<int64_t>((a0 + 1) * kYoloAttrib + ch0 + c) * T.SS,
-                          static_cast<uint32_t>(T.n - len0) * 4u, &sm.full[buf]);
-    }
-}
-
-// Consumer warps meet (one arrival per warp).  Returns false when the wait ran out.
-__device__ __forceinline__ bool stream_meet(YoloStreamSmem& sm, uint32_t& phase) {
-    __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(&sm.meet);
-    const bool ok = mbar_wait_bounded(&sm.meet, phase, kStWaitLimit);
-    phase ^= 1u;
-    return __all_sync(kFullMask, ok);
-}
-
-__global__ void __launch_bounds__(kStThreads, 3)
-yolo_decode_stream_kernel(const YoloParams P) {
-    extern __shared__ __align__(128) unsigned char st_raw[];
-    if (static_cast<int>(blockIdx.x) < P.num_direct) {  // levels whose planes cannot be staged: plain-load form
-        if (threadIdx.x >= kLiveThreads) return;
-        YoloLiveSmem& lsm = *reinterpret_cast<YoloLiveSmem*>(st_raw);
-        const int cta = blockIdx.x;
-        const int lvl = cta >= P.live_begin[2] ? 2 : (cta >= P.live_begin[1] ? 1 : 0);
-        yolo_live_level<0>(P, lvl, cta - P.live_begin[lvl], lsm);
-        return;
-    }
-    YoloStreamSmem& sm = *reinterpret_cast<YoloStreamSmem*>(st_raw);
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const bool pruning = P.prune_topk > 0 && P.hist != nullptr;
-    if (t == 0) {
-#pragma unroll
-        for (int b = 0; b < kSmStages; ++b) {
-            mbar_init(&sm.full[b], 1);
-            mbar_init(&sm.empty[b], kStConsumerWarps);
-        }
-        mbar_init(&sm.meet, kStConsumerWarps);
-        fence_barrier_init();
-    }
-    __syncthreads();  // the only CTA-wide barrier
-
-    if (warp == kStConsumerWarps) {
-        // ---- producer warp: lane 0 waits and issues, the whole warp looks up pruning buckets ----
-        uint32_t seq = 0;  // ring steps issued so far
-        int ok = 1;
-        while (ok) {
-            int tile_id = 0;
-            if (lane == 0) tile_id = atomicAdd(P.work_counter, 1);
-            tile_id = __shfl_sync(kFullMask, tile_id, 0);
-            const bool last = tile_id >= P.st_total_tiles;
-            StreamTile T;
-            int bucket = 0;
-            if (!last) {
-                T = stream_tile(P, tile_id);
-                if (pruning) bucket = prune_digit_regs(P.hist + static_cast<int64_t>(T.img) * kHistBins, P.prune_topk);
-            }
-            if (lane == 0) {
-                const int steps = last ? 1 : kSmRingSteps;
-                for (int rs = 0; rs < steps; ++rs, ++seq) {
-                    const int buf = static_cast<int>(seq % kSmStages);
-                    if (seq >= kSmStages && !mbar_wait_bounded(&sm.empty[buf], ((seq / kSmStages) - 1u) & 1u, kStWaitLimit)) {
-                        ok = 0;
-                        break;
-                    }
-                    if (last) {
-                        sm.slot_tile[buf] = -1;
-                        mbar_arrive(&sm.full[buf]);  // nothing to copy: completes the buffer's phase at once
-                    } else if (rs == 0) {
-                        sm.slot_tile[buf] = tile_id;
-                        sm.slot_prune[buf] = bucket;
-                        stream_issue(sm, T, 0, buf);
-                    } else {
-                        stream_issue(sm, T, 5 + (rs - 1) * kSmRows, buf);
-                    }
-                }
-                if (!ok) {
-                    // a consumer never released a buffer: flag the call; do not leave while copies may still land
-                    if (P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
-                    const uint32_t first = seq > kSmStages ? seq - kSmStages : 0u;
-                    for (uint32_t q = first; q < seq; ++q)
-                        mbar_wait_bounded(&sm.full[q % kSmStages], (q / kSmStages) & 1u, kStWaitLimit);
-                }
-            }
-            ok = __shfl_sync(kFullMask, ok, 0);
-            if (last) break;
-        }
-        return;
-    }
-
-    // ---- consumer warps ----
-    YoloStWarp& ws = sm.w[warp];
-    const unsigned lt = (1u << lane) - 1u;
-    uint32_t seq = 0, meet_phase = 0;
-    int fill = 0, head = 0, tail = 0;  // warp-uniform
-    int parity = 0;
-    bool ok = true;
-#ifdef FB_PHASE_PROBE
-    long long tr_wait = 0, tr_p1 = 0, tr_steps = 0, tr_tiles = 0, tr_c0 = clock64(), tr_c1;
-    if (t == 0) FB_TRACE(0, global_ns());
-#define TR_LAP(acc) do { tr_c1 = clock64(); acc += tr_c1 - tr_c0; tr_c0 = tr_c1; } while (0)
-#else
-#define TR_LAP(acc) do { } while (0)
-#endif
-    while (ok) {
-        // box step of the next tile
-        int buf = static_cast<int>(seq % kSmStages);
-        ok = __all_sync(kFullMask, mbar_wait_bounded(&sm.full[buf], (seq / kSmStages) & 1u, kStWaitLimit));
-        if (!ok) break;
-        TR_LAP(tr_wait);
-        const int tile_id = sm.slot_tile[buf];
-#ifdef FB_PHASE_PROBE
-        if (tile_id < 0 && t == 0) {
-            FB_TRACE(1, global_ns());
-            FB_TRACE(2, static_cast<unsigned long long>(tr_wait));
-            FB_TRACE(3, static_cast<unsigned long long>(tr_p1));
-            FB_TRACE(4, static_cast<unsigned long long>(tr_steps));
-            FB_TRACE(5, static_cast<unsigned long long>(tr_tiles));
-        }
-        ++tr_tiles;
-#endif
-        if (tile_id < 0) return;  // no more work (nothing is pending: every tile ends with a flush)
-        int prune = sm.slot_prune[buf];  // candidates of buckets below this are dropped
-        const StreamTile T = stream_tile(P, tile_id);
-        int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(T.img) * kHistBins : nullptr;
-        float floor_score = prune > 0 ? __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift)) : 0.0f;
-
-        float so[kLiveSlots], vcut[kLiveSlots];
-        uint32_t flat0[kLiveSlots];
-        bool alive[kLiveSlots];
-        unsigned bal[kLiveSlots];
-        int mine = 0;
-        const float stride = P.stride[T.lvl];
-#pragma unroll
-        for (int q = 0; q < kLiveSlots; ++q) {
-            const int ls = q * kLiveThreads + t;
-            const bool valid = ls < T.n;
-            const int lsv = valid ? ls : 0;
-            const int sl = T.s0 + lsv;
-            const int anc = sl / T.SS, p = sl - anc * T.SS;
-            const float t0 = sm.ring[buf][0][lsv], t1 = sm.ring[buf][1][lsv], t2 = sm.ring[buf][2][lsv],
-                        t3 = sm.ring[buf][3][lsv], t4 = sm.ring[buf][4][lsv];
-            const int gy = p / T.S, gx = p - gy * T.S;
-            const float aw = anc == 0 ? P.anchor_w[T.lvl][0] : (anc == 1 ? P.anchor_w[T.lvl][1] : P.anchor_w[T.lvl][2]);
-            const float ah = anc == 0 ? P.anchor_h[T.lvl][0] : (anc == 1 ? P.anchor_h[T.lvl][1] : P.anchor_h[T.lvl][2]);
-            const float cx = __fmul_rn(__fadd_rn(sigmoid_f32(t0), static_cast<float>(gx)), stride);
-            const float cy = __fmul_rn(__fadd_rn(sigmoid_f32(t1), static_cast<float>(gy)), stride);
-            const float hw = __fmul_rn(__fmul_rn(expf(t2), aw), 0.5f);
-            const float hh = __fmul_rn(__fmul_rn(expf(t3), ah), 0.5f);
-            so[q] = sigmoid_f32(t4);
-            const int box = P.box_begin[T.lvl] + p * 3 + anc;
-            if (valid) {
-                reinterpret_cast<float4*>(P.boxes)[static_cast<int64_t>(T.img) * P.num_boxes + box] =
-                    make_float4(__fsub_rn(cx, hw), __fsub_rn(cy, hh), __fadd_rn(cx, hw), __fadd_rn(cy, hh));
-            }
-            flat0[q] = static_cast<uint32_t>(box) * kYoloClasses;
-            // a score is so * sigmoid(v) <= so: the box can only yield candidates if so itself clears both bars
-            alive[q] = valid && so[q] > P.thr && so[q] >= floor_score;
-            vcut[q] = alive[q] ? logit_cut(so[q], fmaxf(P.thr, floor_score)) : INFINITY;
-            bal[q] = __ballot_sync(kFullMask, alive[q]);
-            mine += __popc(bal[q]);
-        }
-        __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(&sm.empty[buf]);  // the box step's buffer is free again
-            sm.warp_cnt[parity][warp] = mine;
-        }
-        ++seq;
-        // meet 1: every warp has finished the previous tile (its survivor list is free) and posted its count
-        ok = stream_meet(sm, meet_phase);
-        if (!ok) break;
-        int wbase = 0, total = 0;
-#pragma unroll
-        for (int w = 0; w < kStConsumerWarps; ++w) {
-            const int c = sm.warp_cnt[parity][w];
-            if (w < warp) wbase += c;
-            total += c;
-        }
-        parity ^= 1;
-#pragma unroll
-        for (int q = 0; q < kLiveSlots; ++q) {
-            if (alive[q]) {
-                YoloLive e;
-                e.so = so[q];
-                e.v_cut = vcut[q];
-                e.chan = static_cast<uint32_t>(q * kLiveThreads + t);
-                e.flat0 = flat0[q];
-                sm.live[wbase + __popc(bal[q] & ((1u << lane) - 1u))] = e;
-            }
-            wbase += __popc(bal[q]);
-        }
-        if (t == 0) sm.prune = prune;
-        // meet 2: the survivor list is complete
-        ok = stream_meet(sm, meet_phase);
-        if (!ok) break;
-        TR_LAP(tr_p1);
-
-        // ---- class steps ----
-        uint64_t* gkeys = P.keys + static_cast<int64_t>(T.img) * P.capacity;
-        int32_t* gcount = P.counts + T.img;
-        const StEvalArgs ea{P.thr, P.hist_base, P.hist_shift, ghist, gkeys, gcount, P.capacity, P.status};
-#pragma unroll 1
-        for (int step = 0; step < kSmSteps; ++step, ++seq) {
-            buf = static_cast<int>(seq % kSmStages);
-            if (pruning) {
-                // the last consumer warp (it holds the fewest survivors) refreshes the bucket twice per tile
-                if (warp == kStConsumerWarps - 1 && (step == 4 || step == 9)) {
-                    const int d = prune_digit_regs(ghist, P.prune_topk);
-                    if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
-                    __syncwarp();
-                }
-                const int now = *reinterpret_cast<volatile int*>(&sm.prune);  // one broadcast read
-                if (now > prune) {  // raise the cuts of this thread's survivors
-                    prune = now;
-                    floor_score = __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift));
-                    for (int k = t; k < total; k += kLiveThreads) {
-                        const float so_k = sm.live[k].so;
-                        sm.live[k].v_cut = so_k >= floor_score ? logit_cut(so_k, fmaxf(P.thr, floor_score)) : INFINITY;
-                    }
-                }
-            }
-            ok = __all_sync(kFullMask, mbar_wait_bounded(&sm.full[buf], (seq / kSmStages) & 1u, kStWaitLimit));
-            if (!ok) break;
-            TR_LAP(tr_wait);
-#pragma unroll 1
-            for (int k0 = warp * 32; k0 < total; k0 += kLiveThreads) {
-                const int k = k0 + lane;
-                const bool has = k < total;
-                float vc = INFINITY;
-                int ls = 0;
-                if (has) {
-                    const YoloLive me = sm.live[k];
-                    vc = me.v_cut;
-                    ls = static_cast<int>(me.chan);
-                }
-                const uint32_t meta0 = (static_cast<uint32_t>(k) << 8) | static_cast<uint32_t>(step * kSmRows);
-                float v[kSmRows];
-#pragma unroll
-                for (int u = 0; u < kSmRows; ++u) v[u] = sm.ring[buf][u][ls];
-#pragma unroll
-                for (int u = 0; u < kSmRows; ++u) {
-                    const bool pred = v[u] > vc;
-                    const unsigned m = __ballot_sync(kFullMask, pred);
-                    if (pred) {
-                        YoloHit e;
-                        e.v = v[u];
-                        e.meta = meta0 + static_cast<uint32_t>(u);
-                        ws.queue[(tail + __popc(m & lt)) & (kStQueue - 1)] = e;
-                    }
-                    tail += __popc(m);
-                    if ((u & 1) == 1 || u == kSmRows - 1) {  // at most 64 new entries between two looks at the queue
-                        __syncwarp();
-                        while (tail - head >= 32) {
-                            fill = st_eval_batch(sm.live, &ws, head, 32, ea, prune, fill);
-                            head += 32;
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.empty[buf]);  // this warp is done with the buffer
-            TR_LAP(tr_steps);
-        }
-        if (!ok) break;
-        // the queue refers to this tile's survivor list and the key stage to this image: drain both
-        __syncwarp();
-        if (tail - head > 0) {
-            fill = st_eval_batch(sm.live, &ws, head, tail - head, ea, prune, fill);
-            head = tail;
-        }
-        if (fill > 0) st_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
-    }
-    // only reached when a wait ran out
-    if (lane == 0 && P.status != nullptr) atomicOr(P.status, FB_STATUS_WAIT_TIMEOUT);
-}
-
 // Development switch (functs_b200_debug_set "yolo_prune"): 0 keeps every candidate above the score threshold.
 static int g_yolo_prune = 1;
 void yolo_set_prune(int on) { g_yolo_prune = on ? 1 : 0; }
-static int g_yolo_tile_major = 1, g_yolo_refresh_all = 0, g_yolo_mode = 1;  // mode: 0 persistent, 1 one tile per CTA, 2 plain loads
-void yolo_set_stream(int on) { g_yolo_mode = on ? 0 : 1; }
-void yolo_set_mode(int m) { g_yolo_mode = m; }
-void yolo_set_tile_major(int on) { g_yolo_tile_major = on ? 1 : 0; }
-void yolo_set_refresh_all(int on) { g_yolo_refresh_all = on ? 1 : 0; }
 
 static const float kAnchors[3][3][2] = {{{116, 90}, {156, 198}, {373, 326}},
                                         {{30, 61}, {62, 45}, {59, 119}},
@@ -1306,7 +952,7 @@ static const float kStrides[3] = {32.f, 16.f, 8.f};
 int launch_yolo_decode(const float* map0, const float* map1, const float* map2, int batch, int s0, int s1, int s2,
                        float score_thr, float* boxes, float* obj_out, float* cls_out, uint64_t* cand_keys,
                        int32_t* cand_counts, int64_t capacity, int32_t* hist, int zero_first, int prune_topk,
-                       int32_t* work_counter, int32_t* status, cudaStream_t st) {
+                       int32_t* status, cudaStream_t st) {
     FB_REQUIRE(map0 && map1 && map2 && boxes && cand_keys && cand_counts, "yolo_decode: null pointer");
     FB_REQUIRE(batch > 0 && s0 > 0 && s1 > 0 && s2 > 0 && s0 <= 1024 && s1 <= 1024 && s2 <= 1024 && capacity > 0,
                "yolo_decode: bad sizes");
@@ -1347,8 +993,6 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     P.status = status;
     P.hist = hist;
     P.prune_topk = (hist != nullptr && prune_topk > 0) ? prune_topk : 0;
-    P.tile_major = g_yolo_tile_major;
-    P.refresh_all = g_yolo_refresh_all;
     const HistParams hp = hist_params_for(score_thr);
     P.hist_base = hp.base;
     P.hist_shift = hp.shift;
@@ -1368,46 +1012,11 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     }
     FB_REQUIRE(255ll * S[0] * S[0] < (1ll << 32) && 255ll * S[1] * S[1] < (1ll << 32) && 255ll * S[2] * S[2] < (1ll << 32),
                "yolo_decode: level map too large");
-    if (work_counter != nullptr && g_yolo_mode == 0) {
-        // persistent form: CTAs of the plain-load levels first, then about three resident CTAs per SM that fetch tiles
-        int64_t direct_acc = 0;
-        int per_image = 0;
-        for (int l = 0; l < 3; ++l) {
-            P.staged[l] = ((S[l] * S[l]) % 4 == 0 && S[l] * S[l] >= kStTile && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 1 : 0;
-            P.live_begin[l] = static_cast<int>(direct_acc);
-            P.st_tiles[l] = 0;
-            if (P.staged[l]) {
-                P.st_tiles[l] = (3 * S[l] * S[l] + kStTile - 1) / kStTile;
-                per_image += P.st_tiles[l];
-            } else {
-                direct_acc += static_cast<int64_t>((3 * S[l] * S[l] + kLiveTile - 1) / kLiveTile) * batch;
-            }
-        }
-        P.live_begin[3] = static_cast<int>(direct_acc);
-        const int64_t total_tiles = static_cast<int64_t>(per_image) * batch;
-        FB_REQUIRE(direct_acc + total_tiles < (1ll << 30), "yolo_decode: too many tiles");
-        P.num_direct = static_cast<int>(direct_acc);
-        P.st_tiles_per_image = per_image > 0 ? per_image : 1;
-        P.st_total_tiles = static_cast<int>(total_tiles);
-        P.work_counter = work_counter;
-        int dev = 0, sms = 0;
-        FB_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
-        FB_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"));
-        const int64_t resident = 3ll * sms;
-        const int64_t workers = total_tiles < resident ? total_tiles : resident;
-        const size_t smem_s = sizeof(YoloStreamSmem) > sizeof(YoloLiveSmem) ? sizeof(YoloStreamSmem) : sizeof(YoloLiveSmem);
-        FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(smem_s)),
-                          "yolo_decode attr"));
-        yolo_decode_stream_kernel<<<static_cast<unsigned>(direct_acc + workers), kStThreads, smem_s, st>>>(P);
-        count_launch();
-        return check_launch("yolo_decode_stream_kernel");
-    }
     int64_t live_acc = 0;
     for (int l = 0; l < 3; ++l) {
         // a plane of S * S floats keeps every row 16-byte aligned iff S * S is a multiple of 4 (and the map itself is)
         // (and a plane at least as long as a tile, so that a tile touches at most two anchors)
-        P.staged[l] = (g_yolo_mode != 2 && (S[l] * S[l]) % 4 == 0 && S[l] * S[l] >= kStTile && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 1 : 0;
+        P.staged[l] = ((S[l] * S[l]) % 4 == 0 && S[l] * S[l] >= kStTile && (reinterpret_cast<uintptr_t>(P.map[l]) & 15) == 0) ? 1 : 0;
         const int tile = P.staged[l] ? kStTile : kLiveTile;
         P.live_begin[l] = static_cast<int>(live_acc);
         live_acc += static_cast<int64_t>((3 * S[l] * S[l] + tile - 1) / tile) * batch;
@@ -1436,7 +1045,7 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 // Scratch of the one-call post-process.  The first `zero_bytes` bytes hold everything that must be zero when a
 // call starts (candidate counts, score histogram, selection counters) and are cleared by ONE memset.
 struct YoloScratch {
-    int64_t counts_off, hist_off, ctr_off, work_off, zero_bytes;
+    int64_t counts_off, hist_off, ctr_off, zero_bytes;
     int64_t keys_off, sel_keys_off, sel_counts_off, lists_off, mask_off, total;
 };
 
@@ -1449,8 +1058,6 @@ static YoloScratch yolo_scratch_layout(int batch, int64_t capacity, int topk) {
     off = align_up(off + static_cast<int64_t>(batch) * kHistBins * 4, 256);
     L.ctr_off = off;
     off = align_up(off + select_binned_ctr_bytes(batch), 256);
-    L.work_off = off;  // tile counter of the persistent decode kernel
-    off += 256;
     L.zero_bytes = off;
     L.keys_off = off;
     off = align_up(off + static_cast<int64_t>(batch) * capacity * 8, 256);
@@ -1475,7 +1082,7 @@ int functs_b200_yolo_decode(const float* map0, const float* map1, const float* m
                             uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
                             int32_t* status, void* stream) {
     return fb::launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, obj_out, cls_out, cand_keys,
-                                  cand_counts, capacity, hist, 1, 0, nullptr, status, fb::as_stream(stream));
+                                  cand_counts, capacity, hist, 1, 0, status, fb::as_stream(stream));
 }
 
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
@@ -1508,13 +1115,15 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
     record_stage_event(0, st);
     // only the topk best candidates of an image are used below: let the decode kernel drop hopeless ones early
     FB_TRY(launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, nullptr, nullptr, keys, counts,
-                              capacity, hist, 0, g_yolo_prune ? topk : 0, reinterpret_cast<int32_t*>(base + L.work_off), status, st));
+                              capacity, hist, 0, g_yolo_prune ? topk : 0, status, st));
     record_stage_event(1, st);
+    // the CTA that finishes an image's selection also prepares the image's NMS input in the NMS work area
     FB_TRY(launch_select_binned(keys, counts, capacity, hist, score_thr, batch, topk, sel_keys, sel_counts,
-                                base + L.ctr_off, base + L.lists_off, 0, st));
+                                base + L.ctr_off, base + L.lists_off, 0, boxes, num_boxes, kYoloClasses, 1,
+                                base + L.mask_off, st));
     record_stage_event(2, st);
     const int rc = launch_batched_nms(boxes, num_boxes, kYoloClasses, sel_keys, sel_counts, batch, topk, iou_thr, 1, dets,
-                                      labels, flat_ids, nullptr, out_counts, base + L.mask_off, st);
+                                      labels, flat_ids, nullptr, out_counts, base + L.mask_off, 1, st);
     record_stage_event(3, st);
     return rc;
 }

@@ -4,13 +4,14 @@
 // process whose whole device memory was given to another framework's pool at start-up, or a post-processing step
 // that runs in a latency-critical loop where a cudaMalloc (which synchronises the whole device) is not acceptable.
 // Such a caller can still provide inputs and outputs (they are part of its fixed memory plan) but has nowhere to
-// take the 128 KB-per-group suppression matrix from.  Here the matrix lives in a file-scope __device__ array.
+// take the 157 KB-per-group work area (suppression matrix, row flags, prepared boxes) from.  Here it lives in a
+// file-scope __device__ array.
 //
-// Cost and limits: the array is kStaticNmsGroups * 128 KB = 1 MB of device memory on EVERY GPU that loads the
+// Cost and limits: the array is kStaticNmsGroups * 157 KB = 1258 KB (about 1.3 MB) of device memory on EVERY GPU that loads the
 // library, held until the process exits.  At most kStaticNmsGroups groups per call.  All calls share the array:
 // two calls whose kernels can overlap on the GPU (different streams, different host threads) race on it — serialise
-// them.  Nothing in the array has to start at zero: the matrix kernel writes every word of every row that the scan
-// kernel later reads, so stale contents of an earlier call are never observed.
+// them.  Nothing in the array has to start at zero: the kernels write every word, flag and prepared box that a
+// later kernel of the same call reads, so stale contents of an earlier call are never observed.
 #include <mutex>
 
 #include "common.cuh"
@@ -19,12 +20,14 @@ namespace fb {
 
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
-                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask,
+                       int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
                        cudaStream_t st);
 int64_t nms_mask_bytes(int groups);
 
 constexpr int kStaticNmsGroups = 8;
-constexpr size_t kStaticNmsBytes = static_cast<size_t>(kStaticNmsGroups) * 1024 * 32 * sizeof(uint32_t);  // 1 MB
+// per group: the 1024 x 1024 bit matrix (128 KB), one flag byte per row (1 KB) and the prepared boxes / class buckets
+// (28928 bytes) and an arrival counter (4 bytes); plus 256 bytes of alignment slack.  Checked against nms_mask_bytes() at every call.
+constexpr size_t kStaticNmsBytes = static_cast<size_t>(kStaticNmsGroups) * (1024 * 32 * sizeof(uint32_t) + 1024 + 28928 + 4) + 256;  // 1258 KB
 
 // In host code this name is only a handle for the symbol, not a device address: the address is looked up per device.
 static __device__ __align__(256) unsigned char g_static_nms_scratch[kStaticNmsBytes];
@@ -68,7 +71,7 @@ int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_
     void* scratch = nullptr;
     FB_TRY(static_nms_scratch(&scratch));
     return launch_batched_nms(boxes, num_boxes, num_classes, sel_keys, sel_counts, groups, topk, iou_thr, class_offset,
-                              dets, labels, flat_ids, keep, out_counts, scratch, as_stream(stream));
+                              dets, labels, flat_ids, keep, out_counts, scratch, 0, as_stream(stream));
 }
 
 }  // extern "C"

@@ -29,7 +29,7 @@ def get_started(a: torch.Tensor, b: torch.Tensor, n: int, device="cuda") -> torc
 
 
 class YOLOV3BBox:
-    """Decode three [B, 255, S, S] maps, score mask, top-k, class-wise NMS.  5 kernel launches (+1 memset) per call."""
+    """Decode three [B, 255, S, S] maps, score mask, top-k, class-wise NMS.  3 kernel launches (+1 memset) per call."""
 
     def __init__(self, sizes=(13, 26, 52), score_thr: float = 0.5, topk: int = 1000, iou_thr: float = 0.45,
                  device="cuda"):

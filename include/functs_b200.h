@@ -82,8 +82,8 @@ int functs_b200_select_topk(const uint64_t* in_keys, const int32_t* in_counts, i
 
 /* The same selection for long candidate lists: 8 CTAs per group collect the keys above / inside the boundary
  * bucket of the score histogram `hist` (filled by the candidate producer with the same thr), the CTA that finishes
- * last sorts.  A second, normally idle launch redoes a group with the exact generic selection when its boundary
- * bucket holds more keys than the sort buffer or the histogram and the keys disagree (2 launches in all).
+ * last sorts; if a group's boundary bucket holds more keys than the sort buffer, or the histogram and the keys
+ * disagree, that CTA runs the exact generic selection over the whole list instead (1 launch either way).
  * scratch: functs_b200_select_binned_scratch_bytes(groups), 256-byte aligned. */
 int64_t functs_b200_select_binned_scratch_bytes(int32_t groups);
 int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity,
@@ -107,7 +107,7 @@ int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_c
 /* The same NMS for callers that cannot provide scratch memory.  No counterpart in the reference (its executor always
  * allocates through torch's caching allocator).  Meant for hosts that bind only this C ABI and own no device allocator
  * — all device memory belongs to another framework's pool, or a cudaMalloc (a device-wide synchronisation) is not
- * acceptable inside their loop.  The suppression matrix lives in a 1 MB __device__ array inside the library (held on
+ * acceptable inside their loop.  The suppression matrix lives in a 1258 KB (about 1.3 MB) __device__ array inside the library (held on
  * every GPU that loads the library, until exit), so groups <= functs_b200_batched_nms_static_max_groups() (8); more
  * groups are rejected with FB_ERR_INVALID_ARGUMENT.  The entry point calls no cudaMalloc / cudaFree or any allocating
  * routine.  The first call on a device looks the array's address up (cudaGetSymbolAddress) with that device current:
@@ -133,8 +133,8 @@ int functs_b200_yolo_decode(const float* map0, const float* map1, const float* m
                             uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
                             int32_t* status, void* stream);
 
-/* Whole post-process: one memset + decode -> select_topk_binned -> batched_nms(class_offset=1): 5 kernel launches
- * (decode, binned select, its fallback pass, NMS bit matrix, NMS scan).
+/* Whole post-process: one memset + decode -> select_topk_binned -> batched_nms(class_offset=1): 3 kernel launches
+ * (decode + mask + compaction; top-k selection, which also lays out the NMS input; NMS bit matrix + greedy scan).
  * Outputs as in batched_nms.
  * scratch: functs_b200_yolo_scratch_bytes(batch, s0, s1, s2, capacity, topk). */
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,

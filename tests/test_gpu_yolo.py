@@ -64,7 +64,7 @@ def check_batch(fb, oracle_mod, maps, sizes, thr=0.5, topk=1000, iou=0.45):
     # full pipeline
     mod = fb.workloads.YOLOV3BBox(sizes=sizes, score_thr=thr, topk=topk, iou_thr=iou)
     dets, labels, flat_ids, cnt = mod.forward_padded(cmaps)
-    assert mod.kernels_last_call == 5  # decode, select, select fallback pass, NMS matrix, NMS scan
+    assert mod.kernels_last_call == 3  # decode; top-k selection (+ NMS input); NMS matrix + scan
     fb.ops.raise_on_status(mod._plan.status, "yolo")
     dets, labels, flat_ids, cnt = dets.cpu(), labels.cpu(), flat_ids.cpu(), cnt.cpu()
     o_eager = W.YOLOV3Post(sizes=sizes, score_thr=thr, topk=topk, iou_thr=iou)

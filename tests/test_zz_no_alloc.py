@@ -2,7 +2,7 @@
 
 It serves hosts that bind only the C ABI and have no device allocator to take scratch from (all device memory is in
 another framework's pool, or an allocation call would stall their loop); the suppression matrix lives in a fixed
-1 MB array inside the library instead.  The test feeds the same selected candidates to the regular entry point (with
+1258 KB (about 1.3 MB) array inside the library instead.  The test feeds the same selected candidates to the regular entry point (with
 caller-provided scratch) and to the static one, twice in a row with different data — the second call runs on the
 array the first one left behind — and requires identical outputs (integer work: exact equality).  This file sorts
 last on purpose, so that a run that stops at the first failure has already run everything else.
