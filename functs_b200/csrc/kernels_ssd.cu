@@ -91,30 +91,30 @@ ssd_softmax_decode_kernel(const float* __restrict__ loc, const float* __restrict
 }
 
 // ---- group 2 ------------------------------------------------------------------------------------------------
-constexpr int kSsdNmsThreads = 512;
+constexpr int kSsdNmsThreads = 256;
 constexpr int kSsdSelCap = 256;
 constexpr int kSsdWords = kSsdSelCap / 32;
 
-struct SmemScores {
+// The class's scores are read twice (histogram pass, collection pass) straight from global memory: the second pass
+// hits in L2, and not staging them keeps the CTA small enough for four CTAs per SM.
+struct ClassScores {
     const float* s;
     float thr;
     __device__ __forceinline__ uint64_t operator()(int i) const {
-        float v = s[i];
+        float v = __ldg(s + i);
         return (v > thr) ? make_key(v, static_cast<uint32_t>(i)) : 0ull;
     }
 };
 
-// dynamic smem: [num_priors floats (padded to 16 B)][SelectSmem<256>][NmsBox[256]][mask 256 x 8 words]
-__global__ void __launch_bounds__(kSsdNmsThreads)
+// dynamic smem: [SelectSmem<256>][NmsBox[256]][mask 256 x 8 words]
+__global__ void __launch_bounds__(kSsdNmsThreads, 3)
 ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ scores_cm, int num_priors, int num_classes,
                      float score_thr, uint32_t hist_base, int hist_shift, int topk, float iou_thr, float thr_lo,
                      float thr_hi, float* __restrict__ dets, int64_t* __restrict__ prior_ids,
                      int32_t* __restrict__ out_counts) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const size_t sc_bytes = (static_cast<size_t>(num_priors) * 4 + 15) / 16 * 16;
-    float* sc = reinterpret_cast<float*>(smem_raw);
-    SelectSmem<kSsdSelCap>& sm = *reinterpret_cast<SelectSmem<kSsdSelCap>*>(smem_raw + sc_bytes);
-    NmsBox* sb = reinterpret_cast<NmsBox*>(smem_raw + sc_bytes + sizeof(SelectSmem<kSsdSelCap>));
+    SelectSmem<kSsdSelCap>& sm = *reinterpret_cast<SelectSmem<kSsdSelCap>*>(smem_raw);
+    NmsBox* sb = reinterpret_cast<NmsBox*>(smem_raw + sizeof(SelectSmem<kSsdSelCap>));
     uint32_t* smask = reinterpret_cast<uint32_t*>(sb + kSsdSelCap);
     __shared__ uint32_t keep_words[kSsdWords];
     __shared__ int word_prefix[kSsdWords + 1];
@@ -123,18 +123,8 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     const int t = threadIdx.x;
     FB_PHASE_BEGIN();
     const float* src = scores_cm + (static_cast<int64_t>(img) * num_classes + cls) * num_priors;
-    if ((num_priors & 3) == 0) {
-        const float4* s4 = reinterpret_cast<const float4*>(src);
-        float4* d4 = reinterpret_cast<float4*>(sc);
-        for (int i = t; i < (num_priors >> 2); i += kSsdNmsThreads) d4[i] = __ldg(s4 + i);
-    } else {
-        for (int i = t; i < num_priors; i += kSsdNmsThreads) sc[i] = __ldg(src + i);
-    }
-    __syncthreads();
-    FB_PHASE(0);
-
-    SmemScores kf{sc, score_thr};
-    const int n = block_select_topk_binned<kSsdNmsThreads, kSsdSelCap, 4>(kf, num_priors, topk, hist_base, hist_shift, sm);
+    ClassScores kf{src, score_thr};
+    const int n = block_select_topk_binned<kSsdNmsThreads, kSsdSelCap, 8>(kf, num_priors, topk, hist_base, hist_shift, sm);
     // (block_select_topk ends with a barrier when n > 1; make the hand-over explicit)
     __syncthreads();
 
@@ -150,18 +140,18 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     __syncthreads();
     FB_PHASE(6);
 
-    // suppression bit matrix: warp r handles rows r, r + 8, ...; lane b tests box 32w + b
+    // suppression bit matrix: warp r handles rows r, r + 8, ...; lane b tests boxes i + 1 + b, i + 33 + b, ...
+    // (independent tests, set bits go in with shared-memory atomics: no vote or barrier inside a row)
     const int lane = t & 31, warp = t >> 5;
     const int words = (n + 31) >> 5;
+    for (int i = t; i < n * kSsdWords; i += kSsdNmsThreads) smask[i] = 0u;
+    __syncthreads();
     for (int i = warp; i < n; i += kSsdNmsThreads / 32) {
         const NmsBox bi = sb[i];
-        uint32_t bits = 0u;
-        for (int w = i >> 5; w < words; ++w) {
-            const int j = w * 32 + lane;
-            const unsigned m = nms_row_word(bi, sb, j, j > i && j < n, iou_thr, thr_lo, thr_hi);
-            if (lane == w) bits = m;
+        uint32_t* row = smask + i * kSsdWords;
+        for (int j = i + 1 + lane; j < n; j += 32) {
+            if (iou_exceeds(bi, sb[j], iou_thr, thr_lo, thr_hi)) atomicOr(&row[j >> 5], 1u << (j & 31));
         }
-        if (lane < kSsdWords) smask[i * kSsdWords + lane] = bits;
     }
     __syncthreads();
     FB_PHASE(7);
@@ -242,10 +232,7 @@ int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_
     FB_REQUIRE(iou_thr > 0.0f && iou_thr < 1.0f, "ssd_class_nms: iou threshold must be in (0, 1)");
     FB_REQUIRE(((reinterpret_cast<uintptr_t>(boxes) | reinterpret_cast<uintptr_t>(scores_cm)) & 15) == 0,
                "ssd_class_nms: boxes and scores must be 16-byte aligned");
-    const size_t sc_bytes = (static_cast<size_t>(num_priors) * 4 + 15) / 16 * 16;
-    const size_t smem = sc_bytes + sizeof(SelectSmem<kSsdSelCap>) + sizeof(NmsBox) * kSsdSelCap +
-                        sizeof(uint32_t) * kSsdSelCap * kSsdWords;
-    FB_REQUIRE(smem <= 200 * 1024, "ssd_class_nms: %d priors do not fit in shared memory", num_priors);
+    const size_t smem = sizeof(SelectSmem<kSsdSelCap>) + sizeof(NmsBox) * kSsdSelCap + sizeof(uint32_t) * kSsdSelCap * kSsdWords;
     FB_TRY(check_cuda(cudaFuncSetAttribute(ssd_class_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem)),
                       "ssd_class_nms attr"));

@@ -66,6 +66,25 @@ __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
     }
 }
 
+// Rank sort, descending, of n <= NT distinct keys: thread t counts the keys larger than s[t] (broadcast reads) and
+// drops its key at that rank.  Cheaper than the bitonic network for a few hundred keys (no barrier per step).
+// tmp: n more keys of shared memory.  Ends with a barrier; the sorted keys are back in s.
+template <int NT>
+__device__ __forceinline__ void rank_sort_desc(uint64_t* s, int n, uint64_t* tmp) {
+    const int t = threadIdx.x;
+    uint64_t mine = 0ull;
+    int rank = 0;
+    if (t < n) {
+        mine = s[t];
+#pragma unroll 8
+        for (int j = 0; j < n; ++j) rank += (s[j] > mine) ? 1 : 0;
+        tmp[rank] = mine;
+    }
+    __syncthreads();
+    if (t < n) s[t] = tmp[t];
+    __syncthreads();
+}
+
 __device__ __forceinline__ int next_pow2(int v) {
     int p = 1;
     while (p < v) p <<= 1;
@@ -401,10 +420,14 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         __syncthreads();
     }
     FB_PHASE(4);
-    const int sort_n = next_pow2(result);
-    for (int i = result + tid; i < sort_n; i += NT) sm.sel[i] = 0ull;
-    __syncthreads();
-    bitonic_sort_desc<NT>(sm.sel, sort_n);
+    if (result <= NT && result <= kBinListCap) {
+        rank_sort_desc<NT>(sm.sel, result, sm.binlist);  // the boundary list is not needed any more
+    } else {
+        const int sort_n = next_pow2(result);
+        for (int i = result + tid; i < sort_n; i += NT) sm.sel[i] = 0ull;
+        __syncthreads();
+        bitonic_sort_desc<NT>(sm.sel, sort_n);
+    }
     FB_PHASE(5);
     return result;
 }
