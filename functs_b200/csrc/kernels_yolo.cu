@@ -38,7 +38,7 @@ struct YoloParams {
     int tile_begin[4];  // first CTA of every level, [3] = total
     int live_begin[4];  // the same for the candidate-only kernel (tiles of (anchor, position) slots per image)
     int staged[3];      // level goes through the bulk-copy staged path (16-byte aligned planes)
-    int prune_topk;     // > 0: the caller only needs the prune_topk best candidates per image (see prune_digit)
+    int prune_topk;     // > 0: the caller only needs the prune_topk best candidates per image (see prune_digit_regs)
     int box_begin[3];   // first box index of every level inside an image
     float stride[3];
     float anchor_w[3][3];
@@ -563,7 +563,7 @@ constexpr int kStConsumerWarps = kLiveThreads / 32;
 constexpr int kStThreads = kLiveThreads + 32;  // + the producer warp
 static_assert(kYoloClasses % kStClasses == 0 && kStTile % 4 == 0 && kStTile <= kLiveTile, "staged decode layout");
 
-constexpr int kStKeyStage = 64;  // staged candidate keys per warp (flushed when fewer than 32 slots remain)
+constexpr int kStKeyStage = 96;  // staged candidate keys per warp (flushed when fewer than 32 slots remain)
 
 struct YoloStWarp {
     uint64_t stage[kStKeyStage];
@@ -578,55 +578,10 @@ struct __align__(128) YoloStagedSmem {
     uint64_t empty[kStStages];  // consumers -> producer warp: every consumer warp is done with the buffer
     int warp_cnt[kLiveThreads / 32];
     int prune;  // latest pruning bucket published for this CTA
-    __align__(16) int hist_snapshot[kHistBins];  // written with 16-byte stores
 };
+static_assert(sizeof(YoloStagedSmem) <= 75 * 1024, "three CTAs per SM");
 
-// Pruning for callers that keep only the `need` best candidates of an image.  The image's score histogram only ever
-// grows, so once some bucket d has at least `need` recorded candidates in the buckets >= d, a candidate of a lower
-// bucket can never be among the `need` best and may be dropped unrecorded.  This returns such a d (0 = no pruning
-// yet) from a possibly stale look at the histogram: stale counts are smaller, which only makes d more conservative.
-// Called by one full warp; nothing waits for anybody.
-__device__ __noinline__ int prune_digit(const int32_t* __restrict__ h, int need, int* tmp) {
-    const int lane = threadIdx.x & 31;
-    constexpr int per = kHistBins / 32;
-    // snapshot into shared memory (coalesced 16-byte loads that bypass L1), then work on the snapshot
-    const int4* h4 = reinterpret_cast<const int4*>(h);
-    int4* t4 = reinterpret_cast<int4*>(tmp);
-#pragma unroll 8
-    for (int i = 0; i < kHistBins / 4 / 32; ++i) t4[i * 32 + lane] = __ldcg(h4 + i * 32 + lane);
-    __syncwarp();
-    int sum = 0;  // lane owns buckets [lane * per, lane * per + per); rotated reads keep the banks apart
-#pragma unroll 8
-    for (int i = 0; i < per; ++i) sum += tmp[lane * per + ((i + lane) & (per - 1))];
-    int incl = sum;  // this lane's buckets and all higher ones
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_down_sync(kFullMask, incl, o);
-        if (lane + o < 32) incl += v;
-    }
-    const bool mine = incl - sum < need && incl >= need;  // the crossing lies in this lane's buckets (one lane at most)
-    const unsigned who = __ballot_sync(kFullMask, mine);
-    if (who == 0u) return 0;  // fewer than `need` candidates recorded so far
-    const int owner = __ffs(who) - 1;
-    const int above = __shfl_sync(kFullMask, incl - sum, owner);
-    // second level: the owner's `per` buckets, two per lane
-    static_assert(per == 64, "two buckets per lane");
-    const int b0 = owner * per + 2 * lane;
-    const int c0 = tmp[b0], c1 = tmp[b0 + 1];
-    int incl2 = c0 + c1;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_down_sync(kFullMask, incl2, o);
-        if (lane + o < 32) incl2 += v;
-    }
-    const int hi = above + incl2 - (c0 + c1);  // recorded candidates in the buckets above this lane's pair
-    int d = 0;
-    if (hi < need && hi + c0 + c1 >= need) d = (hi + c1 >= need) ? b0 + 1 : b0;
-    __syncwarp();
-    return __reduce_max_sync(kFullMask, d);
-}
-
-static_assert(offsetof(YoloStagedSmem, hist_snapshot) % 16 == 0 && offsetof(YoloStagedSmem, live) % 16 == 0 &&
+static_assert(offsetof(YoloStagedSmem, live) % 16 == 0 &&
                   offsetof(YoloStagedSmem, full) % 8 == 0 && offsetof(YoloStagedSmem, empty) % 8 == 0 && offsetof(YoloStagedSmem, w) % 8 == 0,
               "shared-memory layout of the staged decode");
 
@@ -756,7 +711,7 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
         for (int c = 0; c < 5; ++c) tv[q][c] = valid ? __ldg(src + c * SS) : 0.0f;
     }
     if (producer) {  // idle until the first buffer comes back: look up the image's pruning bucket meanwhile
-        const int d = pruning ? prune_digit(ghist, P.prune_topk, sm.hist_snapshot) : 0;
+        const int d = pruning ? prune_digit_regs(ghist, P.prune_topk) : 0;
         if (lane == 0) sm.prune = d;
     }
     // box decode (does not need the bucket)
@@ -837,7 +792,7 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             ok = __shfl_sync(kFullMask, ok, 0);
             if (!ok) break;
             if (pruning && (step == 4 || step == 7)) {
-                const int d = prune_digit(ghist, P.prune_topk, sm.hist_snapshot);
+                const int d = prune_digit_regs(ghist, P.prune_topk);
                 if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
             }
         }
