@@ -157,3 +157,25 @@ def test_yolo_full_batch_properties(fb):
     # determinism: a second run gives identical bits
     d2, l2, f2, c2 = mod.forward_padded(maps)
     assert torch.equal(d2, dets) and torch.equal(f2, flat_ids) and torch.equal(c2, cnt)
+
+
+def test_yolo_topk_pruning_does_not_change_results(fb):
+    """The one-call post-process lets the decode kernel drop candidates that can no longer reach the top-k (it reads
+    the running score histogram).  With that switched off every candidate above the threshold goes through the
+    selection; detections, labels, ids and counts must be identical bit for bit, and pruning must shorten the list."""
+    from functs_b200._lib import check, lib
+    sizes = (13, 26, 52)
+    maps = [m.cuda() for m in W.make_yolo_inputs(16)]
+    mod = fb.workloads.YOLOV3BBox(sizes=sizes)
+    results, cand = {}, {}
+    try:
+        for on in (1, 0):
+            check(lib.functs_b200_debug_set(b"yolo_prune", on), "debug_set")
+            results[on] = [t.clone() for t in mod.forward_padded(maps)]
+            fb.ops.raise_on_status(mod._plan.status, "yolo")
+            cand[on] = int(mod._plan.scratch[: 16 * 4].view(torch.int32).sum())
+    finally:
+        check(lib.functs_b200_debug_set(b"yolo_prune", 1), "debug_set")
+    for a, b in zip(results[1], results[0]):
+        assert torch.equal(a, b)
+    assert cand[1] < cand[0]
