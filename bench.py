@@ -250,6 +250,15 @@ def run_ours(args):
     plan = fb.ops.YoloPostprocessPlan(BATCH, SIZES, topk, cap, device=dev)
     rec = torch.empty(BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
     rec_all = torch.empty(world * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev) if world > 1 else None
+    # multi-GPU: the gather of step i runs on a second stream while step i + 1 computes (two record buffers)
+    if world > 1:
+        comm_stream = torch.cuda.Stream(dev)
+        recs = [rec, torch.empty_like(rec)]
+        rec_alls = [rec_all, torch.empty_like(rec_all)]
+        packed_ev = [torch.cuda.Event(), torch.cuda.Event()]
+        gathered_ev = [torch.cuda.Event(), torch.cuda.Event()]
+        for e in gathered_ev:
+            e.record()
     # per-step stage events, recorded inside the one-call entry point through its profiling hook
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     for row in ev:
@@ -266,8 +275,15 @@ def run_ours(args):
         if handles is not None:
             lib.functs_b200_set_stage_events(None, 0)
         if world > 1:
-            fdist.pack_detections(plan.dets, plan.labels, plan.flat_ids, plan.counts, out=rec)
-            fdist.gather_records(rec, out=rec_all)
+            j = i & 1
+            main = torch.cuda.current_stream()
+            main.wait_event(gathered_ev[j])     # the gather that used this buffer pair two steps ago is done
+            fdist.pack_detections(plan.dets, plan.labels, plan.flat_ids, plan.counts, out=recs[j])   # 1 kernel
+            packed_ev[j].record(main)
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(packed_ev[j])
+                fdist.gather_records(recs[j], out=rec_alls[j])
+                gathered_ev[j].record(comm_stream)
 
     def barrier():
         if world > 1:
@@ -286,6 +302,8 @@ def run_ours(args):
     t_start.record()
     for i in range(args.steps):
         step(i, ev_handles[i])
+    if world > 1:
+        torch.cuda.current_stream().wait_stream(comm_stream)   # the timed region ends when the last gather has landed
     t_end.record()
     barrier()
     launches = launch_count() - launches0
@@ -334,7 +352,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "YOLOv3-style decode + score>0.5 mask + top-1000 + class-wise NMS 0.45, 3 scales 13/26/52, batch 64 per GPU",
                        "batch_per_gpu": BATCH, "l2": f"inputs 231.7 MB per step > 126 MB L2, {n_sets} input sets rotated",
-                       "collective": "none" if world == 1 else "NCCL all-gather of padded detection records every step"},
+                       "collective": "none" if world == 1 else "NCCL all-gather of the 2 MB detection records of every step, on a second stream while the next step computes"},
             "latency_us": ms_per_step * 1e3, "kernels_per_call": launches / args.steps,
             "images_per_s": world * BATCH * 1e3 / ms_per_step,
             "stage_us": {"decode_mask_compact": decode_ms * 1e3, "select_topk": select_ms * 1e3, "nms": nms_ms * 1e3},

@@ -139,6 +139,34 @@ static int dispatch_elem(int elem_size, F&& f) {
 
 }  // namespace fb
 
+namespace fb {
+
+// Detection records for the multi-GPU gather: one 32-byte record per output row, bit-preserving:
+// words 0..4 = (x1, y1, x2, y2, score) as fp32 bits, 5 = label, 6 = flat id, 7 = 1 for a valid row / 0 for padding.
+__global__ void __launch_bounds__(256)
+pack_detections_kernel(const float* __restrict__ dets, const int64_t* __restrict__ labels,
+                       const int64_t* __restrict__ flat_ids, const int32_t* __restrict__ counts, int topk, int64_t total,
+                       int4* __restrict__ rec) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int g = static_cast<int>(i / topk);
+    const int k = static_cast<int>(i - static_cast<int64_t>(g) * topk);
+    const float* d = dets + i * 5;
+    int4 lo, hi;
+    lo.x = __float_as_int(d[0]);
+    lo.y = __float_as_int(d[1]);
+    lo.z = __float_as_int(d[2]);
+    lo.w = __float_as_int(d[3]);
+    hi.x = __float_as_int(d[4]);
+    hi.y = static_cast<int>(labels[i]);
+    hi.z = static_cast<int>(flat_ids[i]);
+    hi.w = k < counts[g] ? 1 : 0;
+    rec[2 * i] = lo;
+    rec[2 * i + 1] = hi;
+}
+
+}  // namespace fb
+
 extern "C" {
 
 int functs_b200_rows_select_add_select_rev(const float* b, float* out, int64_t rows, int64_t cols, int64_t n,
@@ -277,6 +305,19 @@ int functs_b200_index_rows_rev(const void* self, const void* src, const int64_t*
     FB_TRY(rc);
     count_launch();
     return check_launch("scatter_rows_kernel");
+}
+
+int functs_b200_pack_detections(const float* dets, const int64_t* labels, const int64_t* flat_ids, const int32_t* counts,
+                                int32_t groups, int32_t topk, int32_t* records, void* stream) {
+    using namespace fb;
+    FB_REQUIRE(dets && labels && flat_ids && counts && records, "pack_detections: null pointer");
+    FB_REQUIRE(groups > 0 && topk > 0, "pack_detections: bad sizes");
+    FB_REQUIRE((reinterpret_cast<uintptr_t>(records) & 15) == 0, "pack_detections: records must be 16-byte aligned");
+    const int64_t total = static_cast<int64_t>(groups) * topk;
+    pack_detections_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+        dets, labels, flat_ids, counts, topk, total, reinterpret_cast<int4*>(records));
+    count_launch();
+    return check_launch("pack_detections_kernel");
 }
 
 }  // extern "C"

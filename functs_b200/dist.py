@@ -26,6 +26,15 @@ def pack_detections(dets: torch.Tensor, labels: torch.Tensor, flat_ids: torch.Te
     """[B,K,5] fp32 + [B,K] int64 + [B,K] int64 + [B] int32 -> [B,K,8] int32 records (bit-preserving)."""
     b, k, _ = dets.shape
     rec = out if out is not None else torch.empty(b, k, RECORD_WORDS, dtype=torch.int32, device=dets.device)
+    if dets.is_cuda:  # one launch of the library's pack kernel on the current stream
+        from ._lib import check, lib
+        if not (dets.is_contiguous() and labels.is_contiguous() and flat_ids.is_contiguous() and rec.is_contiguous()
+                and counts.is_contiguous() and counts.dtype == torch.int32):
+            raise ValueError("pack_detections: contiguous tensors (counts int32) expected")
+        check(lib.functs_b200_pack_detections(dets.data_ptr(), labels.data_ptr(), flat_ids.data_ptr(), counts.data_ptr(), b, k,
+                                              rec.data_ptr(), torch.cuda.current_stream(dets.device).cuda_stream),
+              "pack_detections")
+        return rec
     rec[:, :, 0:5] = dets.view(torch.int32)
     rec[:, :, 5] = labels.to(torch.int32)
     rec[:, :, 6] = flat_ids.to(torch.int32)

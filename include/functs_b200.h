@@ -119,6 +119,14 @@ int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_
                                    int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids,
                                    int64_t* keep, int32_t* out_counts, void* stream);
 
+/* Packs the padded outputs of batched_nms / yolo_postprocess into 32-byte records for the multi-GPU gather of final
+ * detections (the step that follows the reference's per-image loop when the batch is sharded over GPUs; the reference
+ * itself is single-device, its callers concatenate per-image results on the host: yolov3_bbox.py:236-243).
+ * records [groups, topk, 8] int32: words 0..4 = x1, y1, x2, y2, score (fp32 bits), 5 = label, 6 = flat id,
+ * 7 = 1 for a valid row (k < counts[g]) and 0 for padding.  16-byte aligned. */
+int functs_b200_pack_detections(const float* dets, const int64_t* labels, const int64_t* flat_ids, const int32_t* counts,
+                                int32_t groups, int32_t topk, int32_t* records, void* stream);
+
 /* ---- C2: YOLOv3-style decode + score mask + top-k + class-wise NMS ----------------------- */
 /* Follows functs/benchmark/ai_model/yolov3/yolov3_bbox.py:195-243 at the configured shapes:
  * three NCHW logit maps [batch, 255, S, S]; box order is level, y, x, anchor. */

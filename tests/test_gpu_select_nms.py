@@ -198,3 +198,20 @@ def test_argument_errors(fb, cuda_device):
         fb.ops.select_topk(torch.zeros(1, 8, dtype=torch.int64, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"), 2000)
     with pytest.raises(ValueError):
         fb.ops.threshold_compact(torch.zeros(1, 8), 0.5)  # CPU tensor: no CPU path
+
+
+def test_pack_detections_matches_host_packing(fb, cuda_device):
+    """The pack kernel (records for the multi-GPU gather) against the tensor-op packing that the gloo tests use."""
+    from functs_b200 import dist as fdist
+    g = torch.Generator().manual_seed(5)
+    b, k = 3, 37
+    dets = torch.randn(b, k, 5, generator=g)
+    labels = torch.randint(0, 80, (b, k), generator=g)
+    ids = torch.randint(0, 10647 * 80, (b, k), generator=g)
+    counts = torch.tensor([0, 17, 37], dtype=torch.int32)
+    want = fdist.pack_detections(dets, labels, ids, counts)
+    got = fdist.pack_detections(dets.cuda(), labels.cuda(), ids.cuda(), counts.cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(got.cpu(), want)
+    d2, l2, i2, c2 = fdist.unpack_detections(got.cpu())
+    assert torch.equal(d2, dets) and torch.equal(l2, labels) and torch.equal(i2, ids) and torch.equal(c2, counts)
