@@ -54,6 +54,7 @@ struct YoloParams {
     int64_t capacity;
     int32_t* status;
     int32_t* hist;       // optional [batch][kHistBins] histogram of candidate scores (for the binned top-k), or null
+    int32_t* floor;      // optional [batch]: highest pruning bucket any CTA has found for the image so far (zero at launch)
     uint32_t hist_base;  // float bits of the score threshold
     int hist_shift;
 };
@@ -410,7 +411,9 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
     int32_t* ghist = P.hist != nullptr ? P.hist + static_cast<int64_t>(img) * kHistBins : nullptr;
     const bool pruning = P.prune_topk > 0 && ghist != nullptr;
     if (warp == 0) {
-        const int d = pruning ? prune_digit_regs(ghist, P.prune_topk) : 0;
+        // a bucket that an earlier CTA derived from the image's histogram stays valid: one load instead of a scan
+        int d = 0;
+        if (pruning) d = P.floor != nullptr ? __ldcg(P.floor + img) : prune_digit_regs(ghist, P.prune_topk);
         if (lane == 0) sm.prune = d;
     }
     __syncthreads();
@@ -499,7 +502,10 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
                 // gets there (a plain shared-memory word: late or early, any published bucket is valid)
                 if (warp == 0 && (c0 == 2 * kYoloChunk || c0 == 5 * kYoloChunk)) {
                     const int d = prune_digit_regs(ghist, P.prune_topk);
-                    if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
+                    if (lane == 0 && d > sm.prune) {
+                        *reinterpret_cast<volatile int*>(&sm.prune) = d;
+                        if (P.floor != nullptr) atomicMax(P.floor + img, d);
+                    }
                     __syncwarp();
                 }
                 const int now = *reinterpret_cast<volatile int*>(&sm.prune);
@@ -711,7 +717,9 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
         for (int c = 0; c < 5; ++c) tv[q][c] = valid ? __ldg(src + c * SS) : 0.0f;
     }
     if (producer) {  // idle until the first buffer comes back: look up the image's pruning bucket meanwhile
-        const int d = pruning ? prune_digit_regs(ghist, P.prune_topk) : 0;
+        // a bucket that an earlier CTA derived from the image's histogram stays valid: one load instead of a scan
+        int d = 0;
+        if (pruning) d = P.floor != nullptr ? __ldcg(P.floor + img) : prune_digit_regs(ghist, P.prune_topk);
         if (lane == 0) sm.prune = d;
     }
     // box decode (does not need the bucket)
@@ -793,7 +801,10 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             if (!ok) break;
             if (pruning && (step == 4 || step == 7)) {
                 const int d = prune_digit_regs(ghist, P.prune_topk);
-                if (lane == 0 && d > sm.prune) *reinterpret_cast<volatile int*>(&sm.prune) = d;
+                if (lane == 0 && d > sm.prune) {
+                    *reinterpret_cast<volatile int*>(&sm.prune) = d;
+                    if (P.floor != nullptr) atomicMax(P.floor + img, d);
+                }
             }
         }
         return;
@@ -907,7 +918,7 @@ static const float kStrides[3] = {32.f, 16.f, 8.f};
 int launch_yolo_decode(const float* map0, const float* map1, const float* map2, int batch, int s0, int s1, int s2,
                        float score_thr, float* boxes, float* obj_out, float* cls_out, uint64_t* cand_keys,
                        int32_t* cand_counts, int64_t capacity, int32_t* hist, int zero_first, int prune_topk,
-                       int32_t* status, cudaStream_t st) {
+                       int32_t* floor, int32_t* status, cudaStream_t st) {
     FB_REQUIRE(map0 && map1 && map2 && boxes && cand_keys && cand_counts, "yolo_decode: null pointer");
     FB_REQUIRE(batch > 0 && s0 > 0 && s1 > 0 && s2 > 0 && s0 <= 1024 && s1 <= 1024 && s2 <= 1024 && capacity > 0,
                "yolo_decode: bad sizes");
@@ -948,6 +959,7 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     P.status = status;
     P.hist = hist;
     P.prune_topk = (hist != nullptr && prune_topk > 0) ? prune_topk : 0;
+    P.floor = P.prune_topk > 0 ? floor : nullptr;
     const HistParams hp = hist_params_for(score_thr);
     P.hist_base = hp.base;
     P.hist_shift = hp.shift;
@@ -1000,7 +1012,7 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 // Scratch of the one-call post-process.  The first `zero_bytes` bytes hold everything that must be zero when a
 // call starts (candidate counts, score histogram, selection counters) and are cleared by ONE memset.
 struct YoloScratch {
-    int64_t counts_off, hist_off, ctr_off, zero_bytes;
+    int64_t counts_off, hist_off, ctr_off, floor_off, zero_bytes;
     int64_t keys_off, sel_keys_off, sel_counts_off, lists_off, mask_off, total;
 };
 
@@ -1013,6 +1025,8 @@ static YoloScratch yolo_scratch_layout(int batch, int64_t capacity, int topk) {
     off = align_up(off + static_cast<int64_t>(batch) * kHistBins * 4, 256);
     L.ctr_off = off;
     off = align_up(off + select_binned_ctr_bytes(batch), 256);
+    L.floor_off = off;  // per image: the pruning bucket published by the decode kernel's CTAs
+    off = align_up(off + static_cast<int64_t>(batch) * 4, 256);
     L.zero_bytes = off;
     L.keys_off = off;
     off = align_up(off + static_cast<int64_t>(batch) * capacity * 8, 256);
@@ -1037,7 +1051,7 @@ int functs_b200_yolo_decode(const float* map0, const float* map1, const float* m
                             uint64_t* cand_keys, int32_t* cand_counts, int64_t capacity, int32_t* hist,
                             int32_t* status, void* stream) {
     return fb::launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, obj_out, cls_out, cand_keys,
-                                  cand_counts, capacity, hist, 1, 0, status, fb::as_stream(stream));
+                                  cand_counts, capacity, hist, 1, 0, nullptr, status, fb::as_stream(stream));
 }
 
 int64_t functs_b200_yolo_scratch_bytes(int32_t batch, int32_t s0, int32_t s1, int32_t s2, int64_t capacity,
@@ -1070,7 +1084,7 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
     record_stage_event(0, st);
     // only the topk best candidates of an image are used below: let the decode kernel drop hopeless ones early
     FB_TRY(launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, nullptr, nullptr, keys, counts,
-                              capacity, hist, 0, g_yolo_prune ? topk : 0, status, st));
+                              capacity, hist, 0, g_yolo_prune ? topk : 0, reinterpret_cast<int32_t*>(base + L.floor_off), status, st));
     record_stage_event(1, st);
     // the CTA that finishes an image's selection also prepares the image's NMS input in the NMS work area
     FB_TRY(launch_select_binned(keys, counts, capacity, hist, score_thr, batch, topk, sel_keys, sel_counts,
