@@ -8,14 +8,14 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(os.path.dirname(HERE))
 OUT = os.path.join(PKG, "_C" + sysconfig.get_config_var("EXT_SUFFIX"))
-SOURCES = ["immut_ops.cpp", "tensorssa.cpp", "module.cpp"]
+SOURCES = ["immut_ops.cpp", "tensorssa.cpp", "fusion.cpp", "module.cpp"]
 
 
 def stale() -> bool:
     if not os.path.exists(OUT):
         return True
     built = os.path.getmtime(OUT)
-    deps = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".cpp", ".h"))]
+    deps = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".cpp", ".h", ".inc"))]
     deps.append(os.path.join(PKG, "..", "include", "functs_b200.h"))
     return any(os.path.getmtime(d) > built for d in deps)
 

@@ -1,0 +1,31 @@
+// Loop parallelization, op grouping and the tssa::ParallelFunctor operator (see fusion.cpp).
+//
+// These passes play the role of the reference's fait/passes/{parallelize_loops,fuse_ops,te_op}.cpp on a graph that
+// the TensorSSA passes have already made free of tensor mutation:
+//   ParallelizeLoops         prim::Loop without carried values, whose outer lists are only read by list[i] and written by
+//                            one append each            ->  tssa::ParallelMap(n, in lists...) -> out lists
+//   FuseOps                  contiguous runs of fusable tensor ops (>= 2 working ops)  ->  prim::FusionGroup
+//   LowerToParallelFunctors  map whose body is one group -> tssa::ParallelFunctor(is_parallel_map = 1);
+//                            other groups -> tssa::ParallelFunctor(is_parallel_map = 0); other maps -> loops again
+//   MatchPrecompiledLoops    known whole-loop patterns -> tssa::ParallelFunctor carrying a kernel signature
+// tssa::ParallelFunctor is a registered JIT operator: it launches the precompiled kernel of libfuncts_b200.so when the
+// node carries the signature of one, and otherwise interprets its subgraph (per parallel index) on the immut:: kernels.
+#pragma once
+
+#include <torch/csrc/jit/ir/ir.h>
+
+#include <memory>
+
+namespace functs_b200 {
+
+void ParallelizeLoops(const std::shared_ptr<torch::jit::Graph>& graph);
+// whole loops that a precompiled kernel of the C-ABI library covers -> tssa::ParallelFunctor carrying its signature
+void MatchPrecompiledLoops(const std::shared_ptr<torch::jit::Graph>& graph);
+void FuseOps(const std::shared_ptr<torch::jit::Graph>& graph);
+void LowerToParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
+// TensorSSA conversion (+ marker removal) followed by the three passes above and dead-code elimination
+void FaitPipeline(const std::shared_ptr<torch::jit::Graph>& graph);
+// number of tssa::ParallelFunctor nodes in the graph (all blocks): the unit the launch-count metric counts
+int64_t CountParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
+
+}  // namespace functs_b200

@@ -3,6 +3,12 @@
 #include <torch/csrc/jit/python/pybind_utils.h>
 #include <torch/extension.h>
 
+#include <torch/csrc/jit/api/compilation_unit.h>
+#include <torch/csrc/jit/api/module.h>
+#include <torch/csrc/jit/passes/freeze_module.h>
+#include <torch/csrc/jit/passes/shape_analysis.h>
+
+#include "fusion.h"
 #include "tensorssa.h"
 
 namespace py = pybind11;
@@ -26,4 +32,35 @@ PYBIND11_MODULE(_C, m) {
         functs_b200::TensorSSAPropagation(g, *info);
     });
     m.def("_jit_pass_rename", [](std::shared_ptr<Graph> g) { functs_b200::TensorSSARename(g); });
+    // loop parallelization, grouping, functor lowering (reference: fait passes behind _jit_pass_fait_pipeline)
+    m.def("_jit_pass_parallelize_loops", [](std::shared_ptr<Graph> g) { functs_b200::ParallelizeLoops(g); });
+    m.def("_jit_pass_fait_fuse_ops", [](std::shared_ptr<Graph> g, py::object /*refined_types*/) { functs_b200::FuseOps(g); },
+          py::arg("graph"), py::arg("refined_types") = py::none());
+    m.def("_jit_pass_match_precompiled_loops", [](std::shared_ptr<Graph> g) { functs_b200::MatchPrecompiledLoops(g); });
+    m.def("_jit_pass_lower_to_parallel_functors", [](std::shared_ptr<Graph> g) { functs_b200::LowerToParallelFunctors(g); });
+    m.def("_jit_pass_fait_pipeline",
+          [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint) {
+              // the type hints refine the graph inputs (shapes / dtypes), as the reference's pipeline does first
+              for (size_t i = 0; i < type_hint.size() && i < g->inputs().size(); ++i) {
+                  if (type_hint[i]) g->inputs()[i]->setType(type_hint[i]);
+              }
+              functs_b200::FaitPipeline(g);
+          },
+          py::arg("graph"), py::arg("type_hint") = std::vector<c10::TypePtr>());
+    m.def("_jit_pass_fait_shape_infer",
+          [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint, py::object /*refined_types*/) {
+              for (size_t i = 0; i < type_hint.size() && i < g->inputs().size(); ++i) {
+                  if (type_hint[i]) g->inputs()[i]->setType(type_hint[i]);
+              }
+              torch::jit::PropagateInputShapes(g);
+          },
+          py::arg("graph"), py::arg("type_hint") = std::vector<c10::TypePtr>(), py::arg("refined_types") = py::none());
+    m.def("_count_parallel_functors", [](std::shared_ptr<Graph> g) { return functs_b200::CountParallelFunctors(g); });
+    m.def("_jit_pass_freeze", [](torch::jit::Module& module) { return torch::jit::freeze_module(module); });
+    m.def("_jit_pass_clone", [](torch::jit::Module& module) { return module.clone(); });
+    m.def("_create_function_from_graph", [](const std::string& qualname, std::shared_ptr<Graph> graph) {
+        auto cu = std::make_shared<torch::jit::CompilationUnit>();
+        auto* fn = cu->create_function(c10::QualifiedName(qualname), graph);
+        return torch::jit::StrongFunctionPtr(std::move(cu), fn);
+    });
 }

@@ -35,3 +35,39 @@ def script(fn, backend: str = "jit", remove_update: bool = True, enable_dce_cse:
         jit_fn = torch.jit.freeze(jit_fn.cuda().eval())
     functionalize_graph(jit_fn.graph, remove_update, enable_dce_cse, add_clone)
     return jit_fn
+
+
+def fait_pipeline(g: torch.Graph, type_hint=()) -> None:
+    """Functionalize `g` (already inlined), turn independent loops into maps, group fusable ops and lower everything to
+    tssa::ParallelFunctor nodes: the counterpart of the reference's _jit_pass_fait_pipeline (fait/fait.cpp pipeline
+    order: TensorSSA -> ParallelizeLoops -> FuseOps -> functor nodes)."""
+    torch._C._jit_pass_inline(g)
+    _C._jit_pass_fait_pipeline(g, list(type_hint))
+
+
+def build(fn, example_inputs=(), add_clone: bool = False):
+    """Counterpart of the reference's functs.jit.build(fn, example_inputs) (functs/jit/_build.py): script, optionally
+    clone tensor inputs, run the pipeline with the example inputs' types as hints.  Returns the scripted function; its
+    graph holds tssa::ParallelFunctor nodes, which launch a precompiled kernel of libfuncts_b200.so when their signature
+    names one and otherwise run their subgraph on the immut:: kernels."""
+    jit_fn = torch.jit.script(fn)
+    if not inspect.isfunction(fn):
+        jit_fn = torch.jit.freeze(jit_fn.eval())
+    else:
+        # torch.jit.script caches per Python function: work on a private copy of the graph
+        jit_fn = _C._create_function_from_graph(jit_fn.qualified_name.split(".")[-1], jit_fn.graph.copy())
+    g = jit_fn.graph
+    if add_clone:
+        _C._jit_pass_dumb_remove_inter_precedure_mutation(g)
+    hints = []
+    for v in example_inputs:
+        hints.append(torch._C.TensorType.create_from_tensor(v) if isinstance(v, torch.Tensor) else None)
+    if not inspect.isfunction(fn):
+        hints = [None] + hints  # self
+    fait_pipeline(g, hints)
+    return jit_fn
+
+
+def count_groups(g: torch.Graph) -> int:
+    """Number of tssa::ParallelFunctor nodes: the unit the kernels-per-call metric counts."""
+    return int(_C._count_parallel_functors(g))

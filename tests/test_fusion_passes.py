@@ -1,0 +1,163 @@
+"""ParallelizeLoops / FuseOps / functor lowering and the tssa::ParallelFunctor operator, on CPU graphs.
+
+The passes only rewrite graphs; the functor operator interprets its subgraph through a GraphExecutor, for which the
+test-only CPU kernels of the immut:: operators (oracle/immut_cpu.py) are enough.  Results are compared with eager
+execution of the same Python function."""
+from typing import List
+
+import pytest
+import torch
+
+import oracle.immut_cpu  # noqa: F401  (test-only CPU implementations of immut::)
+
+fjit = pytest.importorskip("functs_b200.jit")
+from functs_b200 import _C  # noqa: E402
+
+
+def kinds(g, recursive=True):
+    out = []
+
+    def walk(block):
+        for n in block.nodes():
+            out.append(n.kind())
+            if recursive:
+                for b in n.blocks():
+                    walk(b)
+    walk(g)
+    return out
+
+
+def scales_decode(feats: List[torch.Tensor], offs: List[torch.Tensor]):
+    outs: List[torch.Tensor] = []
+    for i in range(3):
+        x = feats[i].clone()
+        x[:, 0:2] = torch.sigmoid(x[:, 0:2]) + offs[i]
+        x[:, 2:4] = torch.exp(x[:, 2:4]) * 2.0
+        outs.append(x * 8.0)  # the mutated tensor itself does not escape into the list
+    return outs
+
+
+def carried(b: torch.Tensor, n: int):
+    b = b.clone()
+    for i in range(n):
+        b[i] = b[i] + 1
+    return b
+
+
+def dependent(xs: List[torch.Tensor]):
+    outs: List[torch.Tensor] = []
+    acc = torch.zeros_like(xs[0])
+    for i in range(len(xs)):
+        acc = acc + xs[i]
+        outs.append(acc * 2.0)
+    return outs
+
+
+def reads_own_output(xs: List[torch.Tensor]):
+    outs: List[torch.Tensor] = [xs[0]]
+    for i in range(1, len(xs)):
+        outs.append(outs[i - 1] + xs[i])
+    return outs
+
+
+def make_lists():
+    g = torch.Generator().manual_seed(3)
+    feats = [torch.randn(5 + i, 6, generator=g) for i in range(3)]
+    offs = [torch.randn(5 + i, 2, generator=g) for i in range(3)]
+    return feats, offs
+
+
+def test_independent_loop_becomes_one_parallel_functor():
+    feats, offs = make_lists()
+    want = scales_decode(feats, offs)
+    fn = fjit.build(scales_decode, (feats, offs))
+    ks = kinds(fn.graph)
+    assert "prim::Loop" not in ks and "tssa::ParallelMap" not in ks
+    assert ks.count("tssa::ParallelFunctor") == 1 and fjit.count_groups(fn.graph) == 1
+    node = [n for n in fn.graph.nodes() if n.kind() == "tssa::ParallelFunctor"][0]
+    assert node.i("is_parallel_map") == 1 and node.i("parallel_degree") == 3
+    assert list(getattr(node, "is")("is_parallel_args")) == [1, 1]
+    sub = node.g("Subgraph")
+    assert str(list(sub.inputs())[0].type()) == "int"
+    sub_kinds = [n.kind() for n in sub.nodes()]
+    assert "immut::slice_rev" in sub_kinds and "aten::sigmoid" in sub_kinds and "aten::copy_" not in sub_kinds
+    got = fn(feats, offs)
+    assert len(got) == 3
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    # inputs are not modified (the clone inside the loop is part of the group)
+    feats2, _ = make_lists()
+    for a, b in zip(feats, feats2):
+        assert torch.equal(a, b)
+
+
+def test_parallelize_loops_alone_and_back():
+    g = torch.jit.script(scales_decode).graph.copy()  # torch.jit.script caches: never edit the cached graph
+    torch._C._jit_pass_inline(g)
+    _C._jit_pass_convert_to_tensorssa(g)
+    _C._jit_pass_tensorssa_remove_update(g)
+    _C._jit_pass_parallelize_loops(g)
+    ks = kinds(g, recursive=False)
+    assert "tssa::ParallelMap" in ks and "prim::Loop" not in ks
+    m = [n for n in g.nodes() if n.kind() == "tssa::ParallelMap"][0]
+    assert len(list(m.inputs())) == 3 and len(list(m.outputs())) == 1  # trip count + two lists -> one list
+    body = list(m.blocks())[0]
+    assert len(list(body.inputs())) == 3 and len(list(body.outputs())) == 1
+    assert "aten::__getitem__" not in kinds(g) and "aten::append" not in kinds(g)
+    # without grouping, lowering turns the map back into an equivalent loop
+    _C._jit_pass_lower_to_parallel_functors(g)
+    ks = kinds(g)
+    assert "tssa::ParallelMap" not in ks and "prim::Loop" in ks and "aten::append" in ks
+    feats, offs = make_lists()
+    want = scales_decode(feats, offs)
+    got = _C._create_function_from_graph("lowered", g)(feats, offs)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("fn", [dependent, reads_own_output])
+def test_loops_with_dependences_stay_loops(fn):
+    g = torch.Generator().manual_seed(4)
+    xs = [torch.randn(4, 3, generator=g) for _ in range(4)]
+    want = fn(xs)
+    built = fjit.build(fn, (xs,))
+    ks = kinds(built.graph)
+    assert "prim::Loop" in ks and "tssa::ParallelMap" not in ks
+    got = built(xs)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
+def test_carried_row_loop_is_matched_to_the_precompiled_group():
+    b = torch.randn(6, 5)
+    fn = fjit.build(carried, (b, 6))
+    nodes = [n for n in fn.graph.nodes() if n.kind() == "tssa::ParallelFunctor"]
+    assert len(nodes) == 1 and "prim::Loop" not in kinds(fn.graph, recursive=False)
+    assert nodes[0].s("kernel_signature") == "loop[i<n]{immut::select(b,0,i)->aten::add(.,c)->immut::select_rev(b,.,0,i)}"
+    assert nodes[0].i("is_parallel_map") == 0
+    # CPU tensors: the operator interprets the subgraph (the precompiled kernel only takes CUDA fp32 matrices)
+    assert torch.equal(fn(b, 6), carried(b, 6))
+    assert torch.equal(fn(b, 4), carried(b, 4))
+
+
+def test_plain_group_outside_loops():
+    def f(x: torch.Tensor, y: torch.Tensor):
+        z = x.clone()
+        z[1] = torch.sigmoid(y[0]) * 3.0
+        return z + 1.0
+
+    x, y = torch.randn(4, 3), torch.randn(2, 3)
+    fn = fjit.build(f, (x, y))
+    nodes = [n for n in fn.graph.nodes() if n.kind() == "tssa::ParallelFunctor"]
+    assert len(nodes) == 1 and nodes[0].i("is_parallel_map") == 0
+    assert str(list(nodes[0].g("Subgraph").inputs())[0].type()) == "NoneType"
+    assert torch.equal(fn(x, y), f(x, y))
+
+
+def test_pass_api_names():
+    for name in ("_jit_pass_fait_pipeline", "_jit_pass_fait_fuse_ops", "_jit_pass_fait_shape_infer", "_jit_pass_freeze",
+                 "_jit_pass_clone", "_create_function_from_graph", "_jit_pass_parallelize_loops"):
+        assert hasattr(_C, name), name
+    g = torch.jit.script(carried).graph.copy()
+    f = _C._create_function_from_graph("roundtrip", g)
+    assert torch.equal(f(torch.ones(3, 2), 2), carried(torch.ones(3, 2), 2))

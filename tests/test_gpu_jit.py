@@ -1,6 +1,8 @@
 """Functionalized TorchScript graphs executed on the GPU: the immut:: operators run as CUDA launches of the C-ABI
 library.  Programs restate the reference's test/test_basic.py:6-38 and examples/get_started.py:10-15; the result must
 equal the eager program run on the same device bit for bit (and the CPU eager program within 1e-5)."""
+from typing import List
+
 import pytest
 import torch
 
@@ -87,3 +89,50 @@ def test_script_front_door(fjit):
     f = fjit.script(get_started)
     a, b = rnd(8, 16), rnd(8, 16, seed=1)
     assert torch.equal(f(a.cuda(), b.cuda(), 5).cpu(), get_started(a, b, 5))
+
+
+def scales(feats: List[torch.Tensor], offs: List[torch.Tensor]):
+    outs: List[torch.Tensor] = []
+    for i in range(3):
+        x = feats[i].clone()
+        x[:, 0:2] = torch.sigmoid(x[:, 0:2]) + offs[i]
+        x[:, 2:4] = torch.exp(x[:, 2:4]) * 2.0
+        outs.append(x * 8.0)
+    return outs
+
+
+def test_build_launches_the_precompiled_group(fjit):
+    """jit.build: the get_started loop becomes ONE tssa::ParallelFunctor that launches the library's kernel (one launch
+    for the whole loop), with the bit-exact result of the eager program."""
+    from functs_b200._lib import launch_count
+    fn = fjit.build(get_started, (rnd(64, 1024), rnd(64, 1024, seed=1), 64))
+    nodes = [n for n in fn.graph.nodes() if n.kind() == "tssa::ParallelFunctor"]
+    assert len(nodes) == 1 and fjit.count_groups(fn.graph) == 1
+    assert "prim::Loop" not in [n.kind() for n in fn.graph.nodes()]
+    a, b = rnd(64, 1024), rnd(64, 1024, seed=1)
+    ca, cb = a.cuda(), b.cuda()
+    fn(ca, cb, 64)  # warm-up (first run of the graph executor)
+    torch.cuda.synchronize()
+    before = launch_count()
+    got = fn(ca, cb, 64)
+    torch.cuda.synchronize()
+    assert launch_count() - before == 1
+    assert torch.equal(got.cpu(), get_started(a, b, 64))
+    assert torch.equal(fn(ca, cb, 17).cpu(), get_started(a, b, 17))
+
+
+def test_build_parallel_map_on_gpu(fjit):
+    """A loop over three scales becomes one tssa::ParallelFunctor(is_parallel_map); without a precompiled kernel for its
+    signature the operator runs the subgraph per index on the immut:: CUDA kernels: same bits as eager on the device."""
+    g = torch.Generator().manual_seed(3)
+    feats = [torch.randn(50 + i, 6, generator=g).cuda() for i in range(3)]
+    offs = [torch.randn(50 + i, 2, generator=g).cuda() for i in range(3)]
+    fn = fjit.build(scales, (feats, offs))
+    nodes = [n for n in fn.graph.nodes() if n.kind() == "tssa::ParallelFunctor"]
+    assert len(nodes) == 1 and nodes[0].i("is_parallel_map") == 1 and nodes[0].i("parallel_degree") == 3
+    want = scales(feats, offs)
+    got = fn(feats, offs)
+    torch.cuda.synchronize()
+    assert len(got) == 3
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
