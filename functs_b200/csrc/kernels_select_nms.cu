@@ -282,7 +282,7 @@ nms_prepare_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_c
 // over the whole candidate list instead), and, when asked to, prepares the group's NMS input (nms_prepare_block).
 // No CTA ever waits for another one.
 constexpr int kBinThreads = 512;
-constexpr int kBinSplit = 8;         // CTAs per group
+constexpr int kBinSplit = 4;         // CTAs per group
 constexpr int kBinListGlobal = 2048; // capacity of the boundary-bucket list; beyond it the generic selection runs
 
 struct SelectCtr {
@@ -436,10 +436,70 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
             for (int i = tid; i < want; i += kBinThreads) sm.sel[sel_cnt + i] = sm.bin[i];
         }
         FB_PHASE(13);
-        const int sn = next_pow2(result);
-        for (int i = result + tid; i < sn; i += kBinThreads) sm.sel[i] = 0ull;
+        // sm.sel[0 .. sel_cnt) holds the keys above the boundary bucket in arrival order, the sorted tail from the
+        // boundary bucket follows.  Order the head by counting sort on the score buckets (higher bucket = higher
+        // score) plus a rank count inside every bucket; a crowded bucket falls back to the bitonic network.
         __syncthreads();
-        bitonic_sort_desc<kBinThreads>(sm.sel, sn);
+        int* cnt = sm.hist;                                     // the staged histogram is not needed any more
+        uint64_t* tmp = sm.bin;                                 // nor the boundary list: first half = keys,
+        int* cursor = reinterpret_cast<int*>(sm.bin + kSelCap);  // second half = running positions
+        for (int i = tid; i < kHistBins; i += kBinThreads) cnt[i] = 0;
+        __syncthreads();
+        for (int i = tid; i < sel_cnt; i += kBinThreads) atomicAdd(&cnt[hist_digit(sm.sel[i], hist_base, hist_shift)], 1);
+        __syncthreads();
+        constexpr int kPerThread = kHistBins / kBinThreads;
+        int c[kPerThread];
+        int mine = 0, crowded = 0;
+#pragma unroll
+        for (int q = 0; q < kPerThread; ++q) {
+            c[q] = cnt[tid * kPerThread + q];
+            mine += c[q];
+            crowded |= c[q] > 32 ? 1 : 0;
+        }
+        // keys in higher buckets come first: exclusive suffix sum over threads (buckets ascend with tid)
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_down_sync(kFullMask, incl, o);
+            if (lane + o < 32) incl += v;
+        }
+        __shared__ int warp_sum[kBinThreads / 32];
+        if (lane == 0) warp_sum[warp] = incl;
+        crowded = __syncthreads_or(crowded);
+        int above = incl - mine;
+        for (int w = warp + 1; w < kBinThreads / 32; ++w) above += warp_sum[w];
+#pragma unroll
+        for (int q = kPerThread - 1; q >= 0; --q) {
+            cursor[tid * kPerThread + q] = above;
+            above += c[q];
+        }
+        __syncthreads();
+        FB_PHASE(17);
+        if (!crowded) {
+            for (int i = tid; i < sel_cnt; i += kBinThreads) {
+                const uint64_t k = sm.sel[i];
+                tmp[atomicAdd(&cursor[hist_digit(k, hist_base, hist_shift)], 1)] = k;
+            }
+            __syncthreads();
+            FB_PHASE(18);
+            // inside a bucket: every key counts the larger keys of its bucket's segment (keys are distinct) and
+            // goes straight to its final place
+            for (int i = tid; i < sel_cnt; i += kBinThreads) {
+                const uint64_t k = tmp[i];
+                const int bkt = hist_digit(k, hist_base, hist_shift);
+                const int end = cursor[bkt], begin = end - cnt[bkt];
+                int r = begin;
+                for (int j = begin; j < end; ++j) r += tmp[j] > k ? 1 : 0;
+                sm.sel[r] = k;
+            }
+            __syncthreads();
+            FB_PHASE(19);
+        } else {
+            const int sn = next_pow2(result);
+            for (int i = result + tid; i < sn; i += kBinThreads) sm.sel[i] = 0ull;
+            __syncthreads();
+            bitonic_sort_desc<kBinThreads>(sm.sel, sn);
+        }
     }
     FB_PHASE(14);
     for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < result) ? sm.sel[i] : 0ull;
