@@ -100,7 +100,8 @@ select_topk_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __restri
 constexpr int kNmsMaxN = 1024;
 constexpr int kNmsWords = kNmsMaxN / 32;
 constexpr int kMaskThreads = 256;
-constexpr int kMaskCtas = 12;          // CTAs per group in the matrix kernel (rows interleaved)
+constexpr int kMaskCtasMax = 16;       // CTAs per group in the matrix kernel (rows interleaved); the launcher picks
+                                       // the largest count that keeps the whole grid resident at once
 constexpr int kMaskMaxBuckets = 1024; // class buckets used for pruning (more classes than this: one bucket)
 constexpr int kScanChunk = 256;       // non-empty matrix rows staged in shared memory at a time
 
@@ -113,7 +114,7 @@ constexpr int kScanChunk = 256;       // non-empty matrix rows staged in shared 
 //
 // nms_prepare_block (run by the CTA that finishes a group's top-k selection, or by nms_prepare_kernel when the selected
 // keys come from elsewhere) gathers the selected boxes, applies the class offsets, and leaves the boxes, their buckets
-// and the bucket order in scratch; nms_mask_scan_kernel (kMaskCtas CTAs per group) copies that into shared memory and
+// and the bucket order in scratch; nms_mask_scan_kernel (up to kMaskCtasMax CTAs per group) copies that into shared memory and
 // computes its share of the rows; the CTA of a group that finishes last then runs the greedy scan.
 struct NmsPrepHeader {
     int n, nb, reach, pad;
@@ -514,7 +515,7 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     }
 }
 
-// grid = (kMaskCtas, groups); block = 256.  Rows are interleaved over the CTAs of a group (i = k * kMaskCtas +
+// grid = (CTAs per group, groups); block = 256.  Rows are interleaved over the CTAs of a group (i = k * gridDim.x +
 // blockIdx.x).  Each CTA writes its rows of the suppression matrix (and one flag per row: does the row suppress
 // anything at all?), then takes a ticket; the CTA that draws the group's last ticket runs the greedy scan: only rows
 // with at least one set bit can remove anything, so the flagged rows are listed in ascending order, staged in shared
@@ -615,6 +616,20 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
     constexpr int kRounds = kNmsMaxN / kMaskThreads;
     bool nz[kRounds];
     unsigned nzm[kRounds];
+    // the output rows of this thread's candidates do not depend on the scan: fetch key and box now, use them after it
+    uint64_t okey[kRounds];
+    float4 obox[kRounds];
+#pragma unroll
+    for (int q = 0; q < kRounds; ++q) {
+        const int c = q * kMaskThreads + t;
+        okey[q] = c < n ? sel[c] : 0ull;
+    }
+#pragma unroll
+    for (int q = 0; q < kRounds; ++q) {
+        const int c = q * kMaskThreads + t;
+        obox[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < n) obox[q] = reinterpret_cast<const float4*>(boxes_g)[key_index(okey[q]) / static_cast<uint32_t>(num_classes)];
+    }
 #pragma unroll
     for (int q = 0; q < kRounds; ++q) {
         const int c = q * kMaskThreads + t;
@@ -684,14 +699,17 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
     __syncthreads();
     FB_PHASE(21);
     const int64_t obase = static_cast<int64_t>(g) * topk;
-    for (int c = t; c < n; c += kMaskThreads) {
+#pragma unroll
+    for (int q = 0; q < kRounds; ++q) {
+        const int c = q * kMaskThreads + t;
+        if (c >= n) continue;
         const uint32_t kw = ss.keep_words[c >> 5];
         const int b = c & 31;
         if ((kw >> b) & 1u) {
-            const uint64_t k = sel[c];
+            const uint64_t k = okey[q];
             const uint32_t flat = key_index(k);
             const uint32_t box = flat / static_cast<uint32_t>(num_classes);
-            const float4 bx = reinterpret_cast<const float4*>(boxes_g)[box];
+            const float4 bx = obox[q];
             const int rank = ss.word_prefix[c >> 5] + __popc(kw & ((1u << b) - 1u));
             float* d = dets + (obase + rank) * 5;
             d[0] = bx.x;
@@ -830,7 +848,15 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
         count_launch();
         FB_TRY(check_launch("nms_prepare_kernel"));
     }
-    dim3 grid(kMaskCtas, groups);
+    // one wave: a second, partly filled wave costs more than longer row loops per warp
+    int dev = 0, sms = 0, per_sm = 0;
+    FB_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
+    FB_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"));
+    FB_TRY(check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nms_mask_scan_kernel, kMaskThreads, 0),
+                      "occupancy"));
+    int ctas = (sms * per_sm) / groups;
+    ctas = ctas < 1 ? 1 : (ctas > kMaskCtasMax ? kMaskCtasMax : ctas);
+    dim3 grid(ctas, groups);
     nms_mask_scan_kernel<<<grid, kMaskThreads, 0, st>>>(v.prep, iou_thr, thr_lo, thr_hi, v.mask, v.rowflag, v.ticket, boxes,
                                                         num_boxes, num_classes, sel_keys, topk, dets, labels, flat_ids, keep,
                                                         out_counts);
