@@ -25,6 +25,9 @@ void FuseOps(const std::shared_ptr<torch::jit::Graph>& graph);
 void LowerToParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
 // TensorSSA conversion (+ marker removal) followed by the three passes above and dead-code elimination
 void FaitPipeline(const std::shared_ptr<torch::jit::Graph>& graph);
+// graph inputs take `type_hint` (null entries are skipped); shapes, dtypes and devices are then propagated through the
+// aten:: operators (TorchScript's own propagation) and the immut:: family (shape_infer.cpp)
+void InferShapes(const std::shared_ptr<torch::jit::Graph>& graph, const std::vector<c10::TypePtr>& type_hint);
 // number of tssa::ParallelFunctor nodes in the graph (all blocks): the unit the launch-count metric counts
 int64_t CountParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
 

@@ -49,10 +49,7 @@ PYBIND11_MODULE(_C, m) {
           py::arg("graph"), py::arg("type_hint") = std::vector<c10::TypePtr>());
     m.def("_jit_pass_fait_shape_infer",
           [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint, py::object /*refined_types*/) {
-              for (size_t i = 0; i < type_hint.size() && i < g->inputs().size(); ++i) {
-                  if (type_hint[i]) g->inputs()[i]->setType(type_hint[i]);
-              }
-              torch::jit::PropagateInputShapes(g);
+              functs_b200::InferShapes(g, type_hint);
           },
           py::arg("graph"), py::arg("type_hint") = std::vector<c10::TypePtr>(), py::arg("refined_types") = py::none());
     m.def("_count_parallel_functors", [](std::shared_ptr<Graph> g) { return functs_b200::CountParallelFunctors(g); });

@@ -161,3 +161,39 @@ def test_pass_api_names():
     g = torch.jit.script(carried).graph.copy()
     f = _C._create_function_from_graph("roundtrip", g)
     assert torch.equal(f(torch.ones(3, 2), 2), carried(torch.ones(3, 2), 2))
+
+
+def test_shape_inference_through_immut_ops():
+    """_jit_pass_fait_shape_infer: type hints on the inputs, TorchScript's propagation for aten:: ops and the immut::
+    table for the Access / Assign family; the inferred sizes must be those of an actual run."""
+    def f(x: torch.Tensor, y: torch.Tensor):
+        z = x.clone()
+        z[:, 1:7:2] = torch.sigmoid(y).unsqueeze(1).expand(-1, 3)
+        w = z.permute(1, 0)[2:5]
+        return w * 2.0, z[3] + 1.0  # only values of pure ops leave the graph
+
+    x, y = torch.randn(10, 8), torch.randn(10)
+    g = torch.jit.script(f).graph.copy()
+    torch._C._jit_pass_inline(g)
+    _C._jit_pass_convert_to_tensorssa(g)
+    _C._jit_pass_tensorssa_remove_update(g)
+    torch._C._jit_pass_dce(g)
+    torch._C._jit_pass_constant_propagation(g)
+    hints = [torch._C.TensorType.create_from_tensor(t) for t in (x, y)]
+    _C._jit_pass_fait_shape_infer(g, hints)
+    seen = {}
+    for n in g.nodes():
+        if n.kind().startswith("immut::"):
+            sizes = n.output().type().sizes()
+            assert sizes is not None, f"{n.kind()} has no static shape"
+            seen.setdefault(n.kind(), []).append(tuple(sizes))
+    assert "immut::slice_rev" in seen and all(s == (10, 8) for s in seen["immut::slice_rev"])
+    assert (8, 10) in seen.get("immut::permute", [])
+    assert (3, 10) in seen.get("immut::slice", [])
+    assert (8,) in seen.get("immut::select", [])
+    out_sizes = [tuple(o.type().sizes()) for o in g.outputs()] if len(list(g.outputs())) > 1 else None
+    fn = _C._create_function_from_graph("shapes", g)
+    got = fn(x, y)
+    want = f(x, y)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b) and a.shape == b.shape
