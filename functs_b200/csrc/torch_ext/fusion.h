@@ -21,6 +21,8 @@ namespace functs_b200 {
 void ParallelizeLoops(const std::shared_ptr<torch::jit::Graph>& graph);
 // whole loops that a precompiled kernel of the C-ABI library covers -> tssa::ParallelFunctor carrying its signature
 void MatchPrecompiledLoops(const std::shared_ptr<torch::jit::Graph>& graph);
+// loops with carried values, a constant trip count (<= 16) and a small body are unrolled completely
+void UnrollLoopsWithDeps(const std::shared_ptr<torch::jit::Graph>& graph);
 void FuseOps(const std::shared_ptr<torch::jit::Graph>& graph);
 void LowerToParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
 // TensorSSA conversion (+ marker removal) followed by the three passes above and dead-code elimination

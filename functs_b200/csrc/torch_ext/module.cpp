@@ -37,6 +37,7 @@ PYBIND11_MODULE(_C, m) {
     m.def("_jit_pass_fait_fuse_ops", [](std::shared_ptr<Graph> g, py::object /*refined_types*/) { functs_b200::FuseOps(g); },
           py::arg("graph"), py::arg("refined_types") = py::none());
     m.def("_jit_pass_match_precompiled_loops", [](std::shared_ptr<Graph> g) { functs_b200::MatchPrecompiledLoops(g); });
+    m.def("_jit_pass_unroll_loops_with_deps", [](std::shared_ptr<Graph> g) { functs_b200::UnrollLoopsWithDeps(g); });
     m.def("_jit_pass_lower_to_parallel_functors", [](std::shared_ptr<Graph> g) { functs_b200::LowerToParallelFunctors(g); });
     m.def("_jit_pass_fait_pipeline",
           [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint) {

@@ -197,3 +197,18 @@ def test_shape_inference_through_immut_ops():
     want = f(x, y)
     for a, b in zip(got, want):
         assert torch.equal(a, b) and a.shape == b.shape
+
+
+def test_constant_trip_loop_with_carried_tensor_is_unrolled_into_one_group():
+    def f(x: torch.Tensor, w: torch.Tensor):
+        acc = x.clone()
+        for i in range(4):
+            acc[i] = torch.tanh(acc[i] * w[i]) + 1.0
+        return acc * 0.5
+
+    x, w = torch.randn(6, 5), torch.randn(4, 5)
+    fn = fjit.build(f, (x, w))
+    ks = kinds(fn.graph)
+    assert "prim::Loop" not in ks
+    assert fjit.count_groups(fn.graph) == 1  # all four iterations and the epilogue in one fusion group
+    assert torch.equal(fn(x, w), f(x, w))
