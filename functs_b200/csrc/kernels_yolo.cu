@@ -54,6 +54,7 @@ struct YoloParams {
     int64_t capacity;
     int32_t* status;
     int32_t* hist;       // optional [batch][kHistBins] histogram of candidate scores (for the binned top-k), or null
+    int scan_in_staged;  // no level takes the plain-load form: the staged CTAs have to look at the histogram themselves
     int32_t* floor;      // optional [batch]: highest pruning bucket any CTA has found for the image so far (zero at launch)
     uint32_t hist_base;  // float bits of the score threshold
     int hist_shift;
@@ -308,11 +309,13 @@ __device__ __noinline__ int prune_digit_regs(const int32_t* __restrict__ h, int 
 
 // v > cut is necessary for so * sigmoid(v) to reach `floor_score` (> 0).  The cut sits a relative 1e-5 below the
 // exact bound (hundreds of fp32 ulps: rounding of the sigmoid and of the product) and another 0.02 lower in the
-// logit domain (rounding of the logit itself), so it never loses a candidate.
+// logit domain, so it never loses a candidate.  The 0.02 also covers the fast division and logarithm used here
+// (errors of a few ulps, i.e. below 1e-5 in the logit): the cut is recomputed whenever the pruning floor rises, for
+// every survivor, and must be cheap.
 __device__ __forceinline__ float logit_cut(float so, float floor_score) {
-    const float q = (floor_score / so) * (1.0f - 1.0e-5f);
+    const float q = __fdividef(floor_score, so) * (1.0f - 1.0e-5f);
     if (!(q < 1.0f)) return INFINITY;
-    return logf(q / (1.0f - q)) - 0.02f;
+    return __logf(__fdividef(q, 1.0f - q)) - 0.02f;
 }
 
 struct __align__(16) YoloLive {
@@ -787,7 +790,7 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     }
 
     if (producer) {
-        // refill a buffer as soon as all consumer warps have released it; in between, refresh the pruning bucket
+        // refill a buffer as soon as all consumer warps have released it
 #pragma unroll 1
         for (int step = kStStages; step < kStSteps; ++step) {
             const int buf = step % kStStages;
@@ -799,7 +802,11 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             }
             ok = __shfl_sync(kFullMask, ok, 0);
             if (!ok) break;
-            if (pruning && (step == 4 || step == 7)) {
+            // A look at the histogram delays this warp's next refill by several memory round trips, and measured end to
+            // end it costs more than it saves; the CTAs of the plain-load levels take the looks instead and every other
+            // CTA reads the bucket they publish (P.floor).  Only a pyramid without a plain-load level scans here (first
+            // tile of every image and level, twice).
+            if (pruning && P.scan_in_staged && tile == 0 && (step == 4 || step == 7)) {
                 const int d = prune_digit_regs(ghist, P.prune_topk);
                 if (lane == 0 && d > sm.prune) {
                     *reinterpret_cast<volatile int*>(&sm.prune) = d;
@@ -817,11 +824,16 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     const unsigned lt = (1u << lane) - 1u;
     const StEvalArgs ea{P.thr, P.hist_base, P.hist_shift, ghist, gkeys, gcount, P.capacity, P.status};
     int fill = 0, head = 0, tail = 0;  // warp-uniform
+    int published = 0;  // the image's bucket as other CTAs published it: loaded during one step, used at the next
 #pragma unroll 1
     for (int step = 0; step < kStSteps; ++step) {
         const int buf = step % kStStages;
         if (pruning) {
-            const int now = *reinterpret_cast<volatile int*>(&sm.prune);  // one broadcast read: the same for all lanes
+            int now = *reinterpret_cast<volatile int*>(&sm.prune);  // one broadcast read: the same for all lanes
+            if (P.floor != nullptr) {
+                now = max(now, __shfl_sync(kFullMask, published, 0));
+                if (lane == 0) published = __ldcg(P.floor + img);  // consumed one step later: the latency is hidden
+            }
             if (now > prune) {  // raise the cuts of this thread's survivors
                 prune = now;
                 floor_score = __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift));
@@ -851,6 +863,11 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             float v[kStClasses];
 #pragma unroll
             for (int u = 0; u < kStClasses; ++u) v[u] = sm.ring[buf][u][ls];
+            // once the pruning floor is up most steps have no hit at all in a warp: one vote then skips the packing
+            float vmax = v[0];
+#pragma unroll
+            for (int u = 1; u < kStClasses; ++u) vmax = fmaxf(vmax, v[u]);
+            if (!__any_sync(kFullMask, vmax > vc)) continue;
 #pragma unroll
             for (int h = 0; h < kStClasses; h += kStSub) {
 #pragma unroll
@@ -990,6 +1007,7 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     }
     FB_REQUIRE(live_acc < (1ll << 31), "yolo_decode: too many tiles");
     P.live_begin[3] = static_cast<int>(live_acc);
+    P.scan_in_staged = (P.staged[0] && P.staged[1] && P.staged[2]) ? 1 : 0;
     const unsigned nlive = static_cast<unsigned>(live_acc);
     const size_t smem = sizeof(YoloStagedSmem) > sizeof(YoloLiveSmem) ? sizeof(YoloStagedSmem) : sizeof(YoloLiveSmem);
     if (std_sizes) {
