@@ -95,35 +95,75 @@ constexpr int kSsdNmsThreads = 256;
 constexpr int kSsdSelCap = 256;
 constexpr int kSsdWords = kSsdSelCap / 32;
 
-// The class's scores are read twice (histogram pass, collection pass) straight from global memory: the second pass
-// hits in L2, and not staging them keeps the CTA small enough for four CTAs per SM.
+// The class's scores (one contiguous run of the class-major array) are staged in shared memory by one bulk copy and
+// then read twice (histogram pass, collection pass).  A class with more scores than the staging area holds is read
+// from global memory both times.
 struct ClassScores {
-    const float* s;
+    static constexpr bool kDenseScores = true;
+    const float* s;  // shared or global
     float thr;
+    bool vec4;       // s is 16-byte aligned
     __device__ __forceinline__ uint64_t operator()(int i) const {
-        float v = __ldg(s + i);
+        float v = s[i];
         return (v > thr) ? make_key(v, static_cast<uint32_t>(i)) : 0ull;
     }
 };
 
-// dynamic smem: [SelectSmem<256>][NmsBox[256]][mask 256 x 8 words]
-__global__ void __launch_bounds__(kSsdNmsThreads, 3)
+constexpr int kSsdStageMax = 16384;  // scores of one class that the staging area may hold (64 KB)
+constexpr size_t kSsdSelBytes = (sizeof(SelectSmem<kSsdSelCap>) + 127) / 128 * 128;
+constexpr int kSsdRowBatch = 8;  // rows of the suppression matrix one warp tests at a time
+
+// dynamic smem: [SelectSmem<256>][staged scores]; after the selection the NMS boxes and the 256 x 8 mask words live in
+// the selection's boundary list and histogram, which are not needed any more
+__global__ void __launch_bounds__(kSsdNmsThreads, 4)
 ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ scores_cm, int num_priors, int num_classes,
                      float score_thr, uint32_t hist_base, int hist_shift, int topk, float iou_thr, float thr_lo,
                      float thr_hi, float* __restrict__ dets, int64_t* __restrict__ prior_ids,
-                     int32_t* __restrict__ out_counts) {
+                     int32_t* __restrict__ out_counts, int stage) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     SelectSmem<kSsdSelCap>& sm = *reinterpret_cast<SelectSmem<kSsdSelCap>*>(smem_raw);
-    NmsBox* sb = reinterpret_cast<NmsBox*>(smem_raw + sizeof(SelectSmem<kSsdSelCap>));
-    uint32_t* smask = reinterpret_cast<uint32_t*>(sb + kSsdSelCap);
+    static_assert(sizeof(NmsBox) * kSsdSelCap <= sizeof(sm.binlist) && sizeof(uint32_t) * kSsdSelCap * kSsdWords <= sizeof(sm.hist),
+                  "the NMS work area must fit the parts of the selection state it reuses");
+    NmsBox* sb = reinterpret_cast<NmsBox*>(sm.binlist);
+    uint32_t* smask = reinterpret_cast<uint32_t*>(sm.hist);
+    float* sscore = reinterpret_cast<float*>(smem_raw + kSsdSelBytes);
     __shared__ uint32_t keep_words[kSsdWords];
     __shared__ int word_prefix[kSsdWords + 1];
+    __shared__ uint32_t or_words[2 * kSsdWords];
+    __shared__ __align__(8) uint64_t bar;
 
     const int cls = blockIdx.x, img = blockIdx.y;
     const int t = threadIdx.x;
     FB_PHASE_BEGIN();
     const float* src = scores_cm + (static_cast<int64_t>(img) * num_classes + cls) * num_priors;
-    ClassScores kf{src, score_thr};
+    const float* score_ptr = src;
+    if (stage != 0) {
+        bool staged = false;
+        if (stage == 2) {  // the run starts on a 16-byte boundary and is a multiple of 16 bytes long
+            if (t == 0) {
+                mbar_init(&bar, 1);
+                fence_barrier_init();
+            }
+            __syncthreads();
+            if (t == 0) {
+                mbar_arrive_expect_tx(&bar, static_cast<uint32_t>(num_priors) * 4u);
+                bulk_copy_g2s(sscore, src, static_cast<uint32_t>(num_priors) * 4u, &bar);
+            }
+            staged = mbar_wait_bounded(&bar, 0, 400000u);
+            staged = __syncthreads_and(staged ? 1 : 0) != 0;
+        }
+        if (staged) {
+            score_ptr = sscore;
+        } else if (stage == 1) {
+            for (int i = t; i < num_priors; i += kSsdNmsThreads) sscore[i] = __ldg(src + i);
+            __syncthreads();
+            score_ptr = sscore;
+        }
+        // a copy that did not land in time (never observed): the scores are read from global memory instead; the
+        // landing zone is not used for anything else
+    }
+    FB_PHASE(0);
+    ClassScores kf{score_ptr, score_thr, (reinterpret_cast<uintptr_t>(score_ptr) & 15) == 0};
     const int n = block_select_topk_binned<kSsdNmsThreads, kSsdSelCap, 8>(kf, num_priors, topk, hist_base, hist_shift, sm);
     // (block_select_topk ends with a barrier when n > 1; make the hand-over explicit)
     __syncthreads();
@@ -140,22 +180,52 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     __syncthreads();
     FB_PHASE(6);
 
-    // suppression bit matrix: warp r handles rows r, r + 8, ...; lane b tests boxes i + 1 + b, i + 33 + b, ...
-    // (independent tests, set bits go in with shared-memory atomics: no vote or barrier inside a row)
+    // suppression bit matrix.  A task is (column word w, batch of rows): lane b holds box j = 32w + b, the rows' boxes
+    // are broadcast reads, the tests of a batch are independent and branch-free, and one ballot per row yields the
+    // word, which a single lane stores: no atomics.  Word w only needs the rows i < 32w + 31; tasks are dealt
+    // round-robin to the warps.
     const int lane = t & 31, warp = t >> 5;
     const int words = (n + 31) >> 5;
     for (int i = t; i < n * kSsdWords; i += kSsdNmsThreads) smask[i] = 0u;
     __syncthreads();
-    for (int i = warp; i < n; i += kSsdNmsThreads / 32) {
-        const NmsBox bi = sb[i];
-        uint32_t* row = smask + i * kSsdWords;
-        for (int j = i + 1 + lane; j < n; j += 32) {
-            if (iou_exceeds(bi, sb[j], iou_thr, thr_lo, thr_hi)) atomicOr(&row[j >> 5], 1u << (j & 31));
+    {
+        int total = 0;
+        for (int w = 0; w < words; ++w) total += (min(n, 32 * w + 31) + kSsdRowBatch - 1) / kSsdRowBatch;
+        for (int task = warp; task < total; task += kSsdNmsThreads / 32) {
+            int w = 0, rb = task;
+            for (;; ++w) {
+                const int nb = (min(n, 32 * w + 31) + kSsdRowBatch - 1) / kSsdRowBatch;
+                if (rb < nb) break;
+                rb -= nb;
+            }
+            const int j = 32 * w + lane;
+            const bool jv = j < n;
+            const NmsBox bj = sb[jv ? j : 0];
+            const int i0 = rb * kSsdRowBatch;
+            uint32_t hitm = 0u, unsure = 0u;  // bit u: row i0 + u
+#pragma unroll
+            for (int u = 0; u < kSsdRowBatch; ++u) {
+                const int i = i0 + u;
+                const bool valid = jv && i < j;  // implies i < n
+                const IouQuick q = iou_quick(sb[i < n ? i : 0], bj, thr_lo, thr_hi);
+                hitm |= (valid && q.verdict == 1) ? (1u << u) : 0u;
+                unsure |= (valid && q.verdict == 2) ? (1u << u) : 0u;
+            }
+            if (__any_sync(kFullMask, unsure != 0u)) {  // inside the rounding bracket of the threshold: exact quotient
+                for (int u = 0; u < kSsdRowBatch; ++u) {
+                    if (((unsure >> u) & 1u) && iou_exceeds(sb[i0 + u], bj, iou_thr, thr_lo, thr_hi)) hitm |= 1u << u;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kSsdRowBatch; ++u) {
+                const uint32_t bits = __ballot_sync(kFullMask, (hitm >> u) & 1u);
+                if (lane == u && i0 + u < n && bits != 0u) smask[(i0 + u) * kSsdWords + w] = bits;
+            }
         }
     }
     __syncthreads();
     FB_PHASE(7);
-    if (warp == 0) warp_nms_scan(smask, kSsdWords, n, words, keep_words);
+    block_nms_resolve<kSsdNmsThreads, kSsdWords>(smask, n, keep_words, or_words);
     __syncthreads();
     FB_PHASE(8);
     if (t == 0) {
@@ -232,7 +302,11 @@ int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_
     FB_REQUIRE(iou_thr > 0.0f && iou_thr < 1.0f, "ssd_class_nms: iou threshold must be in (0, 1)");
     FB_REQUIRE(((reinterpret_cast<uintptr_t>(boxes) | reinterpret_cast<uintptr_t>(scores_cm)) & 15) == 0,
                "ssd_class_nms: boxes and scores must be 16-byte aligned");
-    const size_t smem = sizeof(SelectSmem<kSsdSelCap>) + sizeof(NmsBox) * kSsdSelCap + sizeof(uint32_t) * kSsdSelCap * kSsdWords;
+    // stage: 0 = scores read from global memory twice, 1 = staged by plain loads, 2 = staged by one bulk copy
+    const int stage = num_priors > kSsdStageMax ? 0
+                      : ((reinterpret_cast<uintptr_t>(scores_cm) & 15) == 0 && num_priors % 4 == 0) ? 2 : 1;
+    const size_t stage_bytes = stage ? (static_cast<size_t>(num_priors) * 4 + 15) / 16 * 16 : 0;
+    const size_t smem = kSsdSelBytes + stage_bytes;
     FB_TRY(check_cuda(cudaFuncSetAttribute(ssd_class_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem)),
                       "ssd_class_nms attr"));
@@ -241,7 +315,8 @@ int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_
     const HistParams hp = hist_params_for(score_thr);
     ssd_class_nms_kernel<<<grid, kSsdNmsThreads, smem, as_stream(stream)>>>(boxes, scores_cm, num_priors, num_classes,
                                                                             score_thr, hp.base, hp.shift, topk, iou_thr,
-                                                                            thr_lo, thr_hi, dets, prior_ids, out_counts);
+                                                                            thr_lo, thr_hi, dets, prior_ids, out_counts,
+                                                                            stage);
     count_launch();
     return check_launch("ssd_class_nms_kernel");
 }

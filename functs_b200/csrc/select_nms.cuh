@@ -68,7 +68,7 @@ __device__ __forceinline__ void bitonic_sort_desc(uint64_t* s, int n) {
 
 // Rank sort, descending, of n <= NT distinct keys: thread t counts the keys larger than s[t] (broadcast reads) and
 // drops its key at that rank.  Cheaper than the bitonic network for a few hundred keys (no barrier per step).
-// tmp: n more keys of shared memory.  Ends with a barrier; the sorted keys are back in s.
+// tmp: n more keys of shared memory; s must be 16-byte aligned.  Ends with a barrier; the sorted keys are back in s.
 template <int NT>
 __device__ __forceinline__ void rank_sort_desc(uint64_t* s, int n, uint64_t* tmp) {
     const int t = threadIdx.x;
@@ -76,8 +76,14 @@ __device__ __forceinline__ void rank_sort_desc(uint64_t* s, int n, uint64_t* tmp
     int rank = 0;
     if (t < n) {
         mine = s[t];
-#pragma unroll 8
-        for (int j = 0; j < n; ++j) rank += (s[j] > mine) ? 1 : 0;
+        const ulonglong2* s2 = reinterpret_cast<const ulonglong2*>(s);  // two keys per (broadcast) load
+#pragma unroll 4
+        for (int j = 0; j < (n >> 1); ++j) {
+            const ulonglong2 k = s2[j];
+            rank += (k.x > mine) ? 1 : 0;
+            rank += (k.y > mine) ? 1 : 0;
+        }
+        if (n & 1) rank += (s[n - 1] > mine) ? 1 : 0;
         tmp[rank] = mine;
     }
     __syncthreads();
@@ -93,7 +99,7 @@ __device__ __forceinline__ int next_pow2(int v) {
 
 template <int SELCAP>
 struct SelectSmem {
-    uint64_t sel[SELCAP];
+    __align__(16) uint64_t sel[SELCAP];
     uint64_t binlist[kBinListCap];
     int hist[kHistBins];
     uint64_t red_min[32];
@@ -318,6 +324,8 @@ __device__ int block_select_topk(KeyFn key, int n, int topk, SelectSmem<SELCAP>&
 // Same result as block_select_topk, but in two passes for keys whose scores lie above a known threshold: one pass
 // fills the coarse score histogram (hist_digit), the second collects the keys above / inside the boundary bucket,
 // and only the boundary bucket is sorted.  Falls back to block_select_topk when that bucket exceeds kBinListCap.
+// KeyFn::kDenseScores marks a key function over a plain fp32 score array (members s, thr, vec4: the array may be read
+// four at a time): the two passes then read the scores directly and build keys only for the elements they keep.
 template <int NT, int SELCAP, int UNROLL, class KeyFn>
 __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t hist_base, int hist_shift,
                                         SelectSmem<SELCAP>& sm) {
@@ -333,44 +341,87 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         sm.nvalid = 0;
     }
     __syncthreads();
-    for (int base = 0; base < n; base += NT * UNROLL) {
-        uint64_t k[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int i = base + u * NT + tid;
-            k[u] = (i < n) ? key(i) : 0ull;
+    if constexpr (KeyFn::kDenseScores) {
+        // fp32 scores, four per load: an element below the threshold costs a compare, nothing else
+        const float thr = key.thr;
+        auto add = [&](float v) {
+            if (v > thr) atomicAdd(&sm.hist[hist_digit(static_cast<uint64_t>(__float_as_uint(v)) << 32, hist_base, hist_shift)], 1);
+        };
+        const int n4 = key.vec4 ? (n >> 2) : 0;
+        const float4* s4 = reinterpret_cast<const float4*>(key.s);
+        for (int c = tid; c < n4; c += NT) {
+            const float4 q = s4[c];
+            add(q.x);
+            add(q.y);
+            add(q.z);
+            add(q.w);
         }
+        for (int i = 4 * n4 + tid; i < n; i += NT) add(key.s[i]);
+    } else {
+        for (int base = 0; base < n; base += NT * UNROLL) {
+            uint64_t k[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            if (k[u] != 0ull) atomicAdd(&sm.hist[hist_digit(k[u], hist_base, hist_shift)], 1);
+            for (int u = 0; u < UNROLL; ++u) {
+                const int i = base + u * NT + tid;
+                k[u] = (i < n) ? key(i) : 0ull;
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (k[u] != 0ull) atomicAdd(&sm.hist[hist_digit(k[u], hist_base, hist_shift)], 1);
+            }
         }
     }
     __syncthreads();
     FB_PHASE(1);
-    if (warp == 0) {
-        constexpr int per = kHistBins / 32;
-        const int lo = lane * per, hi = lo + per;
+    // boundary bucket: the largest digit d with (keys in buckets >= d) >= topk.  Every thread sums its share of the
+    // buckets (higher thread = higher buckets), suffix sums over the block locate the thread that holds the boundary
+    {
+        static_assert(kHistBins % NT == 0, "the histogram must split evenly over the block");
+        constexpr int per = kHistBins / NT;
+        int h[per];
         int s = 0;
-        for (int i = lo; i < hi; ++i) s += sm.hist[i];
+#pragma unroll
+        for (int k = 0; k < per; ++k) {
+            h[k] = sm.hist[tid * per + k];
+            s += h[k];
+        }
         int incl = s;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int t = __shfl_down_sync(kFullMask, incl, o);
             if (lane + o < 32) incl += t;
         }
-        const int total = __shfl_sync(kFullMask, incl, 0);
-        if (lane == 0) sm.nvalid = total;
+        if (lane == 0) sm.red_cnt[warp] = incl;
+        __syncthreads();
+        int higher = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < NT / 32; ++w) {
+            const int c = sm.red_cnt[w];
+            total += c;
+            higher += (w > warp) ? c : 0;
+        }
+        incl += higher;
         const int suf = incl - s;
+        if (tid == 0) sm.nvalid = total;
         if (total > topk && suf < topk && incl >= topk) {
-            int cum = suf, d = hi - 1;
-            for (; d >= lo; --d) {
-                const int h = sm.hist[d];
-                if (cum + h >= topk) break;
-                cum += h;
+            int cum = suf, dsel = 0, hsel = 0, above = 0;
+            bool found = false;
+#pragma unroll
+            for (int k = per - 1; k >= 0; --k) {  // incl >= topk: one of the buckets is the boundary
+                if (!found) {
+                    if (cum + h[k] >= topk) {
+                        found = true;
+                        dsel = k;
+                        hsel = h[k];
+                        above = cum;
+                    } else {
+                        cum += h[k];
+                    }
+                }
             }
-            sm.digit = d;
-            sm.above = cum;
-            sm.inbin = sm.hist[d];
+            sm.digit = tid * per + dsel;
+            sm.above = above;
+            sm.inbin = hsel;
         }
     }
     __syncthreads();
@@ -382,24 +433,45 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         __syncthreads();
         return block_select_topk<NT, SELCAP, UNROLL>(key, n, topk, sm);
     }
-    for (int base = 0; base < n; base += NT * UNROLL) {
-        uint64_t k[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int i = base + u * NT + tid;
-            k[u] = (i < n) ? key(i) : 0ull;
+    auto place = [&](uint64_t k) {
+        const int d = hist_digit(k, hist_base, hist_shift);
+        if (d > dstar) {
+            const int pos = atomicAdd(&sm.sel_cnt, 1);
+            if (pos < SELCAP) sm.sel[pos] = k;
+        } else if (d == dstar) {
+            const int pos = atomicAdd(&sm.bin_cnt, 1);
+            if (pos < kBinListCap) sm.binlist[pos] = k;
         }
+    };
+    if constexpr (KeyFn::kDenseScores) {
+        // a score can only reach bucket dstar or above if its bits reach the bucket's first value: one integer
+        // compare per element, the few that pass take the exact path
+        const float thr = key.thr;
+        const uint32_t lo_bits = dstar > 0 ? hist_base + (static_cast<uint32_t>(dstar) << hist_shift) : 0u;
+        auto look = [&](float v, int i) {
+            if (v > thr && __float_as_uint(v) >= lo_bits) place(make_key(v, static_cast<uint32_t>(i)));
+        };
+        const int n4 = key.vec4 ? (n >> 2) : 0;
+        const float4* s4 = reinterpret_cast<const float4*>(key.s);
+        for (int c = tid; c < n4; c += NT) {
+            const float4 q = s4[c];
+            look(q.x, 4 * c);
+            look(q.y, 4 * c + 1);
+            look(q.z, 4 * c + 2);
+            look(q.w, 4 * c + 3);
+        }
+        for (int i = 4 * n4 + tid; i < n; i += NT) look(key.s[i], i);
+    } else {
+        for (int base = 0; base < n; base += NT * UNROLL) {
+            uint64_t k[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            if (k[u] != 0ull) {
-                const int d = hist_digit(k[u], hist_base, hist_shift);
-                if (d > dstar) {
-                    const int pos = atomicAdd(&sm.sel_cnt, 1);
-                    if (pos < SELCAP) sm.sel[pos] = k[u];
-                } else if (d == dstar) {
-                    const int pos = atomicAdd(&sm.bin_cnt, 1);
-                    if (pos < kBinListCap) sm.binlist[pos] = k[u];
-                }
+            for (int u = 0; u < UNROLL; ++u) {
+                const int i = base + u * NT + tid;
+                k[u] = (i < n) ? key(i) : 0ull;
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (k[u] != 0ull) place(k[u]);
             }
         }
     }
@@ -465,6 +537,27 @@ __device__ __forceinline__ bool iou_exceeds(const NmsBox& a, const NmsBox& b, fl
     return __fdiv_rn(inter, uni) > thr;
 }
 
+// The same decision without branches, for callers that run several independent tests at once: verdict 0 = not above,
+// 1 = above, 2 = inside the bracket (the caller forms the correctly rounded quotient inter / uni and compares it
+// with thr, as iou_exceeds does).
+struct IouQuick {
+    float inter, uni;
+    int verdict;
+};
+__device__ __forceinline__ IouQuick iou_quick(const NmsBox& a, const NmsBox& b, float thr_lo, float thr_hi) {
+    IouQuick q;
+    const float w = fmaxf(0.0f, __fsub_rn(fminf(a.x2, b.x2), fmaxf(a.x1, b.x1)));
+    const float h = fmaxf(0.0f, __fsub_rn(fminf(a.y2, b.y2), fmaxf(a.y1, b.y1)));
+    q.inter = __fmul_rn(w, h);
+    q.uni = __fsub_rn(__fadd_rn(a.area, b.area), q.inter);
+    const bool pos = (w > 0.0f) && (q.inter > 0.0f);
+    const bool safe = q.uni > 0.0f && q.uni < 3.0e38f && q.inter < 3.0e38f;
+    const bool yes = pos && safe && q.inter > __fmul_rn(q.uni, thr_hi);
+    const bool no = !pos || (safe && q.inter < __fmul_rn(q.uni, thr_lo));
+    q.verdict = yes ? 1 : (no ? 0 : 2);
+    return q;
+}
+
 // One word of a row of the suppression matrix: lane b tests box j = 32w + b against box i (valid = j > i && j < n).
 // The x extents are compared first for the whole warp; only if some lane overlaps in x is the full test run.
 // Must be called by all 32 lanes.
@@ -525,6 +618,53 @@ __device__ __forceinline__ void warp_nms_scan(const uint32_t* mask, int row_stri
         for (int b = 0; b < 32; ++b) removed |= (keepw & (1u << b)) ? col[b] : 0u;
         if (lane == 0) keep_words[w] = keepw;
     }
+}
+
+// Greedy NMS over a precomputed suppression bit matrix, resolved by the whole block in parallel rounds instead of a
+// serial walk.  Thread i owns row i (NT == 32 * WORDS, n <= NT).  A box is certainly kept once every box that could
+// suppress it is certainly removed, and certainly removed once a certainly kept box suppresses it; both sets only
+// grow, every round settles at least the first undecided box, and the fixed point is the greedy result.  Random boxes
+// need a handful of rounds.  or_words: 2 * WORDS words of shared memory.  keep_words[w] receives the keep bits.
+template <int NT, int WORDS>
+__device__ __forceinline__ void block_nms_resolve(const uint32_t* mask, int n, uint32_t* keep_words, uint32_t* or_words) {
+    static_assert(NT == 32 * WORDS, "one thread per row, one warp per word");
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const bool valid = t < n;
+    uint32_t row[WORDS];
+    uint32_t any = 0u;
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) {
+        row[w] = valid ? mask[t * WORDS + w] : 0u;
+        any |= row[w];
+    }
+    uint32_t* maybe = or_words;            // boxes that a not-yet-removed box suppresses
+    uint32_t* gone = or_words + WORDS;     // boxes that a kept box suppresses
+    bool kept = false, removed = false;
+    for (int round = 0; round <= n; ++round) {
+        if (t < 2 * WORDS) or_words[t] = 0u;
+        __syncthreads();
+        if (__any_sync(kFullMask, any != 0u && !removed)) {
+#pragma unroll
+            for (int w = 0; w < WORDS; ++w) {
+                const uint32_t v = __reduce_or_sync(kFullMask, removed ? 0u : row[w]);
+                if (lane == w && v != 0u) atomicOr(&maybe[w], v);
+            }
+        }
+        __syncthreads();
+        kept = valid && !removed && ((maybe[warp] >> lane) & 1u) == 0u;
+        if (__any_sync(kFullMask, any != 0u && kept)) {
+#pragma unroll
+            for (int w = 0; w < WORDS; ++w) {
+                const uint32_t v = __reduce_or_sync(kFullMask, kept ? row[w] : 0u);
+                if (lane == w && v != 0u) atomicOr(&gone[w], v);
+            }
+        }
+        __syncthreads();
+        removed = valid && ((gone[warp] >> lane) & 1u) != 0u;
+        if (__syncthreads_or((valid && !kept && !removed) ? 1 : 0) == 0) break;
+    }
+    const uint32_t kw = __ballot_sync(kFullMask, kept);
+    if (lane == 0) keep_words[warp] = kw;
 }
 
 }  // namespace fb
