@@ -171,13 +171,16 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     const float* bimg = boxes + static_cast<int64_t>(img) * num_priors * 4;
     float4 mybox = make_float4(0.f, 0.f, 0.f, 0.f);
     uint64_t mykey = 0ull;
+    bool tame_box = true;
     if (t < n) {
         mykey = sm.sel[t];
         mybox = __ldg(reinterpret_cast<const float4*>(bimg) + key_index(mykey));
-        sb[t] = make_nms_box(mybox.x, mybox.y, mybox.z, mybox.w);
+        const NmsBox nb = make_nms_box(mybox.x, mybox.y, mybox.z, mybox.w);
+        tame_box = nms_box_is_tame(nb);
+        sb[t] = nb;
     }
     if (t < kSsdWords) keep_words[t] = 0u;
-    __syncthreads();
+    const bool tame = __syncthreads_and(tame_box ? 1 : 0) != 0;  // also the barrier behind the box stores
     FB_PHASE(6);
 
     // suppression bit matrix.  A task is (column word w, batch of rows): lane b holds box j = 32w + b, the rows' boxes
@@ -202,25 +205,33 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
             const bool jv = j < n;
             const NmsBox bj = sb[jv ? j : 0];
             const int i0 = rb * kSsdRowBatch;
-            uint32_t hitm = 0u, unsure = 0u;  // bit u: row i0 + u
+            uint32_t myword = 0u;  // lane u: the word of row i0 + u
+            if (tame) {
+                // one vote per row gives the word; pairs inside the rounding bracket of the threshold (rare) take the
+                // exact quotient
 #pragma unroll
-            for (int u = 0; u < kSsdRowBatch; ++u) {
-                const int i = i0 + u;
-                const bool valid = jv && i < j;  // implies i < n
-                const IouQuick q = iou_quick(sb[i < n ? i : 0], bj, thr_lo, thr_hi);
-                hitm |= (valid && q.verdict == 1) ? (1u << u) : 0u;
-                unsure |= (valid && q.verdict == 2) ? (1u << u) : 0u;
-            }
-            if (__any_sync(kFullMask, unsure != 0u)) {  // inside the rounding bracket of the threshold: exact quotient
                 for (int u = 0; u < kSsdRowBatch; ++u) {
-                    if (((unsure >> u) & 1u) && iou_exceeds(sb[i0 + u], bj, iou_thr, thr_lo, thr_hi)) hitm |= 1u << u;
+                    const int i = i0 + u;
+                    const bool valid = jv && i < j;  // implies i < n
+                    bool yes, unsure;
+                    iou_quick_tame(sb[i < n ? i : 0], bj, thr_lo, thr_hi, yes, unsure);
+                    uint32_t bits = __ballot_sync(kFullMask, valid && yes);
+                    if (__any_sync(kFullMask, valid && unsure)) {
+                        const bool late = valid && unsure && iou_exceeds(sb[i], bj, iou_thr, thr_lo, thr_hi);
+                        bits |= __ballot_sync(kFullMask, late);
+                    }
+                    if (lane == u) myword = bits;
+                }
+            } else {
+#pragma unroll 1
+                for (int u = 0; u < kSsdRowBatch; ++u) {
+                    const int i = i0 + u;
+                    const bool hit = jv && i < j && iou_exceeds(sb[i], bj, iou_thr, thr_lo, thr_hi);
+                    const uint32_t bits = __ballot_sync(kFullMask, hit);
+                    if (lane == u) myword = bits;
                 }
             }
-#pragma unroll
-            for (int u = 0; u < kSsdRowBatch; ++u) {
-                const uint32_t bits = __ballot_sync(kFullMask, (hitm >> u) & 1u);
-                if (lane == u && i0 + u < n && bits != 0u) smask[(i0 + u) * kSsdWords + w] = bits;
-            }
+            if (lane < kSsdRowBatch && i0 + lane < n && myword != 0u) smask[(i0 + lane) * kSsdWords + w] = myword;
         }
     }
     __syncthreads();

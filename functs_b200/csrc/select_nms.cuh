@@ -403,6 +403,16 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         incl += higher;
         const int suf = incl - s;
         if (tid == 0) sm.nvalid = total;
+        // the counts are not needed again: every bucket now holds the number of keys in the buckets above it, which
+        // is where its keys start in the final descending order
+        {
+            int above_k = suf;
+#pragma unroll
+            for (int k = per - 1; k >= 0; --k) {
+                sm.hist[tid * per + k] = above_k;
+                above_k += h[k];
+            }
+        }
         if (total > topk && suf < topk && incl >= topk) {
             int cum = suf, dsel = 0, hsel = 0, above = 0;
             bool found = false;
@@ -492,13 +502,29 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         __syncthreads();
     }
     FB_PHASE(4);
-    if (result <= NT && result <= kBinListCap) {
-        rank_sort_desc<NT>(sm.sel, result, sm.binlist);  // the boundary list is not needed any more
-    } else {
-        const int sort_n = next_pow2(result);
-        for (int i = result + tid; i < sort_n; i += NT) sm.sel[i] = 0ull;
+    // Final order.  The boundary bucket's share already sits sorted behind the `have` keys of the higher buckets.
+    // Those are ordered by a counting sort: a key of bucket d goes to the run that starts at hist[d] (keys in higher
+    // buckets), in arrival order; afterwards hist[d] is the run's end and hist[d + 1] its start, and every key
+    // counts the larger keys of its own run (a run holds a key or two unless many scores are nearly equal).
+    static_assert(SELCAP <= kBinListCap, "the boundary list doubles as the scatter target");
+    {
+        const int have = dstar >= 0 ? (sm.sel_cnt < SELCAP ? sm.sel_cnt : SELCAP) : result;
+        uint64_t* tmp = sm.binlist;  // not needed any more
         __syncthreads();
-        bitonic_sort_desc<NT>(sm.sel, sort_n);
+        for (int i = tid; i < have; i += NT) {
+            const uint64_t k = sm.sel[i];
+            tmp[atomicAdd(&sm.hist[hist_digit(k, hist_base, hist_shift)], 1)] = k;
+        }
+        __syncthreads();
+        for (int i = tid; i < have; i += NT) {
+            const uint64_t mine = tmp[i];
+            const int d = hist_digit(mine, hist_base, hist_shift);
+            const int lo = d + 1 < kHistBins ? sm.hist[d + 1] : 0, hi = sm.hist[d];
+            int rank = lo;
+            for (int q = lo; q < hi; ++q) rank += (tmp[q] > mine) ? 1 : 0;
+            sm.sel[rank] = mine;
+        }
+        __syncthreads();
     }
     FB_PHASE(5);
     return result;
@@ -556,6 +582,22 @@ __device__ __forceinline__ IouQuick iou_quick(const NmsBox& a, const NmsBox& b, 
     const bool no = !pos || (safe && q.inter < __fmul_rn(q.uni, thr_lo));
     q.verdict = yes ? 1 : (no ? 0 : 2);
     return q;
+}
+
+// For boxes with finite coordinates and areas below 1e37 (nms_box_is_tame) the guards of iou_exceeds are implied by a
+// positive intersection: inter <= min(area) and max(area) <= union <= 2e37.  yes / unsure as in iou_quick.
+__device__ __forceinline__ bool nms_box_is_tame(const NmsBox& b) {
+    return fabsf(b.x1) < 1.0e18f && fabsf(b.y1) < 1.0e18f && fabsf(b.x2) < 1.0e18f && fabsf(b.y2) < 1.0e18f && b.area < 1.0e37f;
+}
+__device__ __forceinline__ void iou_quick_tame(const NmsBox& a, const NmsBox& b, float thr_lo, float thr_hi, bool& yes,
+                                               bool& unsure) {
+    const float w = __fsub_rn(fminf(a.x2, b.x2), fmaxf(a.x1, b.x1));
+    const float h = __fsub_rn(fminf(a.y2, b.y2), fmaxf(a.y1, b.y1));
+    const float inter = __fmul_rn(w, h);
+    const float uni = __fsub_rn(__fadd_rn(a.area, b.area), inter);
+    const bool pos = w > 0.0f && h > 0.0f && inter > 0.0f;
+    yes = pos && inter > __fmul_rn(uni, thr_hi);
+    unsure = pos && !yes && !(inter < __fmul_rn(uni, thr_lo));
 }
 
 // One word of a row of the suppression matrix: lane b tests box j = 32w + b against box i (valid = j > i && j < n).
