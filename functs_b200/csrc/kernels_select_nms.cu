@@ -311,48 +311,70 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     const int g = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     FB_PHASE_BEGIN();
+    // the group's histogram (four buckets per thread) does not depend on anything: ask for it first, together with
+    // the candidate count, so that the two round trips overlap
+    static_assert(kHistBins == 4 * kBinThreads, "four histogram buckets per thread");
+    const int4 hv = __ldcg(reinterpret_cast<const int4*>(hist + static_cast<int64_t>(g) * kHistBins) + tid);
     int64_t cnt64 = in_counts[g];
     if (cnt64 > capacity) cnt64 = capacity;
     if (cnt64 < 0) cnt64 = 0;
     const int n = static_cast<int>(cnt64);
     const uint64_t* keys = in_keys + static_cast<int64_t>(g) * capacity;
+    // this CTA's share of the keys: the first two batches are requested now and looked at once the boundary is known
+    const int lo = static_cast<int>(static_cast<int64_t>(n) * blockIdx.x / gridDim.x);
+    const int hi = static_cast<int>(static_cast<int64_t>(n) * (blockIdx.x + 1) / gridDim.x);
+    constexpr int kPre = 8;
+    uint64_t pre[kPre];
+#pragma unroll
+    for (int u = 0; u < kPre; ++u) {
+        const int i = lo + u * kBinThreads + tid;
+        pre[u] = (i < hi) ? __ldg(keys + i) : 0ull;
+    }
+    __shared__ int s_wsum[kBinThreads / 32];
     if (tid == 0) {
         s_dstar = -1;  // n <= topk: everything is "above"
         s_above = n;
         s_inbin = 0;
     }
-    __syncthreads();
-    if (n > topk) {
-        // stage the group's histogram (coalesced), then one warp finds the boundary bucket
-        int* sh = sm.hist;
-        const int32_t* h = hist + static_cast<int64_t>(g) * kHistBins;
-        for (int i = tid; i < kHistBins; i += kBinThreads) sh[i] = __ldcg(h + i);
-        __syncthreads();
-        if (warp == 0) {
-            constexpr int per = kHistBins / 32;
-            const int lo = lane * per, hi = lo + per;
-            int s = 0;  // rotated reads: lane l starts at its bucket l, which keeps the 32 lanes on different banks
-#pragma unroll 8
-            for (int i = 0; i < per; ++i) s += sh[lo + ((i + lane) & (per - 1))];
-            int incl = s;
+    {
+        // boundary bucket: the largest d with (keys in buckets >= d) >= topk; suffix sums over the block
+        const int s4 = hv.x + hv.y + hv.z + hv.w;
+        int incl = s4;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                int t = __shfl_down_sync(kFullMask, incl, o);
-                if (lane + o < 32) incl += t;
-            }
-            const int suf = incl - s;
-            if (suf < topk && incl >= topk) {
-                int cum = suf, d = hi - 1;
-                for (; d >= lo; --d) {
-                    const int c = sh[d];
-                    if (cum + c >= topk) break;
-                    cum += c;
-                }
-                s_dstar = d;
-                s_above = cum;
-                s_inbin = sh[d];
-            }
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_down_sync(kFullMask, incl, o);
+            if (lane + o < 32) incl += v;
         }
+        if (lane == 0) s_wsum[warp] = incl;
+        __syncthreads();
+        for (int w = warp + 1; w < kBinThreads / 32; ++w) incl += s_wsum[w];
+        const int suf = incl - s4;
+        if (n > topk && suf < topk && incl >= topk) {
+            int cum = suf, d = 3, inb = hv.w;
+            if (cum + hv.w < topk) {
+                cum += hv.w;
+                d = 2;
+                inb = hv.z;
+                if (cum + hv.z < topk) {
+                    cum += hv.z;
+                    d = 1;
+                    inb = hv.y;
+                    if (cum + hv.y < topk) {
+                        cum += hv.y;
+                        d = 0;
+                        inb = hv.x;
+                    }
+                }
+            }
+            s_dstar = tid * 4 + d;
+            s_above = cum;
+            s_inbin = inb;
+        }
+    }
+    __shared__ int s_nsel, s_nbin, s_bsel, s_bbin;
+    if (tid == 0) {
+        s_nsel = 0;
+        s_nbin = 0;
     }
     __syncthreads();
     FB_PHASE(10);
@@ -360,18 +382,32 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     SelectCtr* c = ctr + g;
     uint64_t* gsel = sel_tmp + static_cast<int64_t>(g) * kSelCap;
     uint64_t* gbin = bin_tmp + static_cast<int64_t>(g) * kBinListGlobal;
-    // collect this CTA's share into shared-memory lists first (shared atomics), then reserve space in the group's
-    // global lists with ONE atomic per list and copy
-    __shared__ int s_nsel, s_nbin, s_bsel, s_bbin;
-    if (tid == 0) {
-        s_nsel = 0;
-        s_nbin = 0;
-    }
-    __syncthreads();
+    // collect this CTA's share into shared-memory lists first (one shared atomic per warp and list), then reserve
+    // space in the group's global lists with ONE atomic per list and copy
     {
-        const int lo = static_cast<int>(static_cast<int64_t>(n) * blockIdx.x / gridDim.x);
-        const int hi = static_cast<int>(static_cast<int64_t>(n) * (blockIdx.x + 1) / gridDim.x);
-        for (int base = lo; base < hi; base += kBinThreads * 4) {
+        const unsigned lt = (1u << lane) - 1u;
+        auto place = [&](uint64_t k) {  // called by whole warps
+            const int d = k != 0ull ? hist_digit(k, hist_base, hist_shift) : -2;
+            const bool up = d > dstar, in = d == dstar;
+            const unsigned mu = __ballot_sync(kFullMask, up), mi = __ballot_sync(kFullMask, in);
+            if (mu != 0u) {
+                int base = 0;
+                if (lane == 0) base = atomicAdd(&s_nsel, __popc(mu));
+                base = __shfl_sync(kFullMask, base, 0);
+                const int pos = base + __popc(mu & lt);
+                if (up && pos < kSelCap) sm.sel[pos] = k;
+            }
+            if (mi != 0u) {
+                int base = 0;
+                if (lane == 0) base = atomicAdd(&s_nbin, __popc(mi));
+                base = __shfl_sync(kFullMask, base, 0);
+                const int pos = base + __popc(mi & lt);
+                if (in && pos < kBinListGlobal) sm.bin[pos] = k;
+            }
+        };
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) place(pre[u]);
+        for (int base = lo + kPre * kBinThreads; base < hi; base += kBinThreads * 4) {
             uint64_t k[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -379,17 +415,7 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
                 k[u] = (i < hi) ? __ldg(keys + i) : 0ull;
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (k[u] == 0ull) continue;
-                const int d = hist_digit(k[u], hist_base, hist_shift);
-                if (d > dstar) {
-                    const int pos = atomicAdd(&s_nsel, 1);
-                    if (pos < kSelCap) sm.sel[pos] = k[u];
-                } else if (d == dstar) {
-                    const int pos = atomicAdd(&s_nbin, 1);
-                    if (pos < kBinListGlobal) sm.bin[pos] = k[u];
-                }
-            }
+            for (int u = 0; u < 4; ++u) place(k[u]);
         }
     }
     __syncthreads();
@@ -811,6 +837,7 @@ int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int6
     FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kSelCap && capacity > 0 && capacity < (1ll << 31),
                "select_topk_binned: bad sizes (topk must be in [1, %d])", kSelCap);
     FB_REQUIRE(thr > 0.0f, "select_topk_binned: the threshold must be positive");
+    FB_REQUIRE((reinterpret_cast<uintptr_t>(hist) & 15) == 0, "select_topk_binned: the histogram must be 16-byte aligned");
     FB_REQUIRE(nms_scratch == nullptr || (nms_boxes != nullptr && num_boxes > 0 && num_classes > 0 &&
                                           (reinterpret_cast<uintptr_t>(nms_boxes) & 15) == 0),
                "select_topk_binned: NMS preparation needs 16-byte aligned boxes");

@@ -909,7 +909,14 @@ yolo_decode_staged_kernel(const YoloParams P) {
     const int cta = blockIdx.x;
     const int lvl = cta >= P.live_begin[2] ? 2 : (cta >= P.live_begin[1] ? 1 : 0);
     const int local = cta - P.live_begin[lvl];
-    if (P.staged[lvl]) {
+    if constexpr (S0 == 0 && S1 == 0 && S2 == 0) {  // sizes known only at run time: one body serves every level
+        if (P.staged[lvl]) {
+            yolo_staged_level<0>(P, lvl, local, *reinterpret_cast<YoloStagedSmem*>(st_raw));
+        } else {
+            if (threadIdx.x >= kLiveThreads) return;
+            yolo_live_level<0>(P, lvl, local, *reinterpret_cast<YoloLiveSmem*>(st_raw));
+        }
+    } else if (P.staged[lvl]) {
         YoloStagedSmem& sm = *reinterpret_cast<YoloStagedSmem*>(st_raw);
         if (lvl == 2) yolo_staged_level<S2>(P, 2, local, sm);
         else if (lvl == 1) yolo_staged_level<S1>(P, 1, local, sm);

@@ -80,11 +80,11 @@ int functs_b200_threshold_compact(const float* scores, int32_t groups, int64_t n
 int functs_b200_select_topk(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, int32_t groups,
                             int32_t topk, uint64_t* out_keys, int32_t* out_counts, void* stream);
 
-/* The same selection for long candidate lists: 8 CTAs per group collect the keys above / inside the boundary
+/* The same selection for long candidate lists: 4 CTAs per group collect the keys above / inside the boundary
  * bucket of the score histogram `hist` (filled by the candidate producer with the same thr), the CTA that finishes
  * last sorts; if a group's boundary bucket holds more keys than the sort buffer, or the histogram and the keys
  * disagree, that CTA runs the exact generic selection over the whole list instead (1 launch either way).
- * scratch: functs_b200_select_binned_scratch_bytes(groups), 256-byte aligned. */
+ * hist must be 16-byte aligned.  scratch: functs_b200_select_binned_scratch_bytes(groups), 256-byte aligned. */
 int64_t functs_b200_select_binned_scratch_bytes(int32_t groups);
 int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity,
                                    const int32_t* hist, float thr, int32_t groups, int32_t topk, uint64_t* out_keys,

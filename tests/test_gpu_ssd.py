@@ -90,3 +90,65 @@ def test_ssd_no_candidates_and_all_candidates(fb):
     _, _, res = o(loc, conf)
     got = mod.unpad(dets, ids, counts)[0]
     assert torch.equal(got[2].cpu(), res[0][2])
+
+
+def _class_nms_case(fb, boxes, scores, thr=0.01, topk=200, iou=0.45):
+    """boxes [P,4], scores [P,C] (CPU): the GPU per-class kernel against the oracle's per-class loop, bit for bit."""
+    o = W.SSDPost(score_thr=thr, topk=topk, iou_thr=iou)
+    wd, wl, wi = o.post_single(boxes, scores)
+    dev = torch.device("cuda:0")
+    scores_cm = scores.t().contiguous()[None].to(dev)
+    dets, ids, counts = fb.ops.ssd_class_nms(boxes[None].contiguous().to(dev), scores_cm, thr, topk, iou)
+    torch.cuda.synchronize()
+    gd, gl, gi = [], [], []
+    for c in range(scores.size(1)):
+        k = int(counts[0, c])
+        gd.append(dets[0, c, :k].cpu())
+        gi.append(ids[0, c, :k].cpu())
+        gl.append(torch.full([k], c, dtype=torch.long))
+    gd, gl, gi = torch.cat(gd), torch.cat(gl), torch.cat(gi)
+    assert torch.equal(gi, wi) and torch.equal(gl, wl) and torch.equal(gd, wd)
+    return counts[0].cpu()
+
+
+def test_ssd_class_nms_suppression_chain(fb):
+    """Box k overlaps box k + 1 above the threshold and box k + 2 below it: the greedy result alternates and every
+    decision depends on the one before (the deepest dependency chain the parallel resolve can meet)."""
+    n = 200
+    x0 = torch.arange(n, dtype=torch.float32) * 3.0      # width 10, shift 3: IoU 7/13 = 0.54, shift 6: 4/16 = 0.25
+    boxes = torch.stack([x0, torch.zeros(n), x0 + 10.0, torch.full([n], 10.0)], dim=1)
+    scores = torch.zeros(n, 2)
+    scores[:, 0] = torch.linspace(0.9, 0.1, n)           # class 0: score order = chain order
+    scores[:, 1] = torch.linspace(0.1, 0.9, n)           # class 1: the chain runs the other way
+    counts = _class_nms_case(fb, boxes, scores)
+    assert counts.tolist() == [100, 100]
+
+
+def test_ssd_class_nms_ties_and_duplicates(fb):
+    """Equal scores fill one histogram bucket (order falls back to the prior index), identical boxes are all
+    suppressed by the first, and more candidates than top-k tie at the boundary."""
+    g = torch.Generator().manual_seed(21)
+    p = 600
+    xy = torch.rand(p, 2, generator=g) * 250.0
+    wh = torch.rand(p, 2, generator=g) * 40.0 + 5.0
+    boxes = torch.cat([xy, xy + wh], dim=1)
+    boxes[100:140] = boxes[100]                            # forty copies of one box
+    scores = torch.zeros(p, 3)
+    scores[:, 0] = 0.5                                     # all tie: top-k takes priors 0..199
+    scores[:, 1] = (torch.randint(0, 4, (p,), generator=g).float() + 1.0) * 0.125   # four score levels
+    scores[:, 2] = torch.rand(p, generator=g)
+    scores[100:140, 2] = 0.99
+    _class_nms_case(fb, boxes, scores)
+
+
+def test_ssd_class_nms_wild_boxes(fb):
+    """Coordinates far outside the tame range take the guarded IoU path; degenerate boxes never suppress."""
+    g = torch.Generator().manual_seed(5)
+    p = 300
+    xy = torch.rand(p, 2, generator=g) * 100.0
+    wh = torch.rand(p, 2, generator=g) * 30.0 + 1.0
+    boxes = torch.cat([xy, xy + wh], dim=1)
+    boxes[7] = torch.tensor([0.0, 0.0, 3.0e19, 3.0e19])    # area overflows to inf
+    boxes[9] = torch.tensor([50.0, 50.0, 40.0, 40.0])      # negative extent
+    scores = torch.rand(p, 2, generator=g)
+    _class_nms_case(fb, boxes, scores)
