@@ -234,7 +234,11 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # the gather shares the GPU with the next step's kernels: its (few) CTAs must not queue behind theirs
+        opts = None
+        if args.comm_priority == "high":
+            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     hbm_peak, peak_kind = measured_peaks()
 
     # ---- inputs: this rank's 64 images; three sets rotated so that no step finds its logits in L2 ----
@@ -252,7 +256,7 @@ def run_ours(args):
     rec_all = torch.empty(world * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev) if world > 1 else None
     # multi-GPU: the gather of step i runs on a second stream while step i + 1 computes (two record buffers)
     if world > 1:
-        comm_stream = torch.cuda.Stream(dev)
+        comm_stream = torch.cuda.Stream(dev, priority=-1 if args.comm_priority == "high" else 0)
         recs = [rec, torch.empty_like(rec)]
         rec_alls = [rec_all, torch.empty_like(rec_all)]
         packed_ev = [torch.cuda.Event(), torch.cuda.Event()]
@@ -424,6 +428,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--comm-priority", default="high", choices=["high", "normal"],
+                    help="stream priority of the multi-GPU gather (N > 1)")
     ap.add_argument("--no-extra", action="store_true", help="skip the cpu_baseline leg and the other workloads")
     ap.add_argument("--only", default=None, choices=["yolo", "ssd", "yolact", "lstm", "get_started"],
                     help="run a few calls of one workload and exit (for profiler captures)")

@@ -19,6 +19,7 @@ SOURCES = [
     "kernels_yolact.cu",
     "kernels_lstm.cu",
     "kernels_lstm_tc.cu",
+    "kernels_peer.cu",
     "no_alloc.cu",
 ]
 

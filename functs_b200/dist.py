@@ -78,3 +78,4 @@ def gather_ragged(rec: torch.Tensor, total: int, group=None) -> torch.Tensor:
     full = gather_records(padded, group)
     parts: List[torch.Tensor] = [full[r * cap:r * cap + (e - s)] for r, (s, e) in enumerate(sizes)]
     return torch.cat(parts, dim=0)
+

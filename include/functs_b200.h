@@ -127,6 +127,28 @@ int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_
 int functs_b200_pack_detections(const float* dets, const int64_t* labels, const int64_t* flat_ids, const int32_t* counts,
                                 int32_t groups, int32_t topk, int32_t* records, void* stream);
 
+/* The same packing fused with the gather itself, without a collective library: every record is stored straight into
+ * the gather buffer of every rank over NVLink (plain peer stores), then one flag per destination says that this rank's
+ * share of step `step` is complete.  peer_records[r]: rank r's gather buffer for this step's slot,
+ * [nranks * groups, topk, 8] int32 (rank q's records start at q * groups); peer_flags[r]: rank r's flag block of
+ * functs_b200_peer_flag_bytes() bytes, zeroed before the first step.  Both are device pointers valid on the calling
+ * GPU (the caller opens the other ranks' allocations, e.g. through CUDA IPC, and calls
+ * functs_b200_peer_enable_access once per peer device).  Steps count from 1 and alternate between two slots: before
+ * it overwrites a slot the kernel waits until every destination has released the step that used it last
+ * (functs_b200_peer_release); a reader waits for a step with functs_b200_peer_wait.  All waits are bounded (about a
+ * second) and report FB_STATUS_WAIT_TIMEOUT in `status` instead of blocking.
+ * Status: compiled and exported; no test of this library runs these entry points on hardware yet, and the benchmark's
+ * gather is the NCCL all-gather of functs_b200_pack_detections records. */
+int32_t functs_b200_peer_flag_bytes(void);
+int functs_b200_peer_enable_access(int32_t peer_device);
+int functs_b200_peer_check_pointer(const void* ptr, int32_t* device);
+int functs_b200_pack_detections_peers(const float* dets, const int64_t* labels, const int64_t* flat_ids,
+                                      const int32_t* counts, int32_t groups, int32_t topk, void* const* peer_records,
+                                      void* const* peer_flags, int32_t rank, int32_t nranks, uint32_t step,
+                                      int32_t* status, void* stream);
+int functs_b200_peer_wait(const void* my_flags, int32_t nranks, uint32_t step, int32_t* status, void* stream);
+int functs_b200_peer_release(void* const* peer_flags, int32_t rank, int32_t nranks, uint32_t step, void* stream);
+
 /* ---- C2: YOLOv3-style decode + score mask + top-k + class-wise NMS ----------------------- */
 /* Follows functs/benchmark/ai_model/yolov3/yolov3_bbox.py:195-243 at the configured shapes:
  * three NCHW logit maps [batch, 255, S, S]; box order is level, y, x, anchor. */
