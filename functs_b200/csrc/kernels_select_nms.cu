@@ -876,12 +876,19 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
         FB_TRY(check_launch("nms_prepare_kernel"));
     }
     // one wave: a second, partly filled wave costs more than longer row loops per warp
-    int dev = 0, sms = 0, per_sm = 0;
+    static int wave_cache[64] = {};  // resident CTAs of this kernel per device: asked once
+    int dev = 0;
     FB_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
-    FB_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"));
-    FB_TRY(check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nms_mask_scan_kernel, kMaskThreads, 0),
-                      "occupancy"));
-    int ctas = (sms * per_sm) / groups;
+    int wave = dev >= 0 && dev < 64 ? wave_cache[dev] : 0;
+    if (wave == 0) {
+        int sms = 0, per_sm = 0;
+        FB_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"));
+        FB_TRY(check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nms_mask_scan_kernel, kMaskThreads, 0),
+                          "occupancy"));
+        wave = sms * per_sm;
+        if (dev >= 0 && dev < 64) wave_cache[dev] = wave;
+    }
+    int ctas = wave / groups;
     ctas = ctas < 1 ? 1 : (ctas > kMaskCtasMax ? kMaskCtasMax : ctas);
     dim3 grid(ctas, groups);
     nms_mask_scan_kernel<<<grid, kMaskThreads, 0, st>>>(v.prep, iou_thr, thr_lo, thr_hi, v.mask, v.rowflag, v.ticket, boxes,

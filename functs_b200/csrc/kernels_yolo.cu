@@ -1017,15 +1017,26 @@ int launch_yolo_decode(const float* map0, const float* map1, const float* map2, 
     P.scan_in_staged = (P.staged[0] && P.staged[1] && P.staged[2]) ? 1 : 0;
     const unsigned nlive = static_cast<unsigned>(live_acc);
     const size_t smem = sizeof(YoloStagedSmem) > sizeof(YoloLiveSmem) ? sizeof(YoloStagedSmem) : sizeof(YoloLiveSmem);
+    // the shared-memory opt-in is a per-device property of the kernel: set once, not on every call
+    static unsigned char attr_done[2][64] = {};
+    int dev = 0;
+    FB_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
+    const int slot = dev >= 0 && dev < 64 ? dev : 0;
     if (std_sizes) {
-        FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<13, 26, 52>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
-                          "yolo_decode attr"));
+        if (!attr_done[0][slot] || dev >= 64) {
+            FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<13, 26, 52>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                              "yolo_decode attr"));
+            attr_done[0][slot] = 1;
+        }
         yolo_decode_staged_kernel<13, 26, 52><<<nlive, kStThreads, smem, st>>>(P);
     } else {
-        FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<0, 0, 0>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
-                          "yolo_decode attr"));
+        if (!attr_done[1][slot] || dev >= 64) {
+            FB_TRY(check_cuda(cudaFuncSetAttribute(yolo_decode_staged_kernel<0, 0, 0>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                              "yolo_decode attr"));
+            attr_done[1][slot] = 1;
+        }
         yolo_decode_staged_kernel<0, 0, 0><<<nlive, kStThreads, smem, st>>>(P);
     }
     count_launch();
