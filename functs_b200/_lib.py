@@ -5,7 +5,7 @@ this module raises.  Nothing here computes on the CPU.
 """
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_double, c_float, c_int32, c_int64, c_uint32, c_uint64, c_void_p
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int32, c_int64, c_uint64, c_void_p
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 # FUNCTS_B200_LIBRARY names another build of the same library (for example one compiled with profiling marks).
@@ -46,16 +46,10 @@ SIGNATURES = {
     "functs_b200_select_topk_binned": (c_int32, [P, P, c_int64, P, c_float, c_int32, c_int32, P, P, P, P]),
     "functs_b200_select_topk": (c_int32, [P, P, c_int64, c_int32, c_int32, P, P, P]),
     "functs_b200_nms_scratch_bytes": (c_int64, [c_int32, c_int32]),
-    "functs_b200_batched_nms": (c_int32, [P, c_int64, c_int32, P, P, c_int32, c_int32, c_float, c_int32, P, P, P, P, P, P, P]),
+    "functs_b200_batched_nms": (c_int32, [P, c_int64, c_int32, P, P, c_int32, c_int32, c_float, c_int32, P, P, P, P, P, P, P, P]),
     "functs_b200_pack_detections": (c_int32, [P, P, P, P, c_int32, c_int32, P, P]),
-    "functs_b200_peer_flag_bytes": (c_int32, []),
-    "functs_b200_peer_enable_access": (c_int32, [c_int32]),
-    "functs_b200_peer_check_pointer": (c_int32, [P, P]),
-    "functs_b200_pack_detections_peers": (c_int32, [P, P, P, P, c_int32, c_int32, P, P, c_int32, c_int32, c_uint32, P, P]),
-    "functs_b200_peer_wait": (c_int32, [P, c_int32, c_uint32, P, P]),
-    "functs_b200_peer_release": (c_int32, [P, c_int32, c_int32, c_uint32, P]),
     "functs_b200_batched_nms_static_max_groups": (c_int32, []),
-    "functs_b200_batched_nms_static": (c_int32, [P, c_int64, c_int32, P, P, c_int32, c_int32, c_float, c_int32, P, P, P, P, P, P]),
+    "functs_b200_batched_nms_static": (c_int32, [P, c_int64, c_int32, P, P, c_int32, c_int32, c_float, c_int32, P, P, P, P, P, P, P]),
     "functs_b200_yolo_decode": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, P, P, P, P, P, c_int64, P, P, P]),
     "functs_b200_yolo_scratch_bytes": (c_int64, [c_int32, c_int32, c_int32, c_int32, c_int64, c_int32]),
     "functs_b200_yolo_postprocess": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, c_float,

@@ -19,7 +19,6 @@ SOURCES = [
     "kernels_yolact.cu",
     "kernels_lstm.cu",
     "kernels_lstm_tc.cu",
-    "kernels_peer.cu",
     "no_alloc.cu",
 ]
 

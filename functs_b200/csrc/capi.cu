@@ -35,37 +35,6 @@ void record_stage_event(int index, cudaStream_t st) {
     if (index >= 0 && index < g_num_stage_events && g_stage_events[index] != nullptr) cudaEventRecord(g_stage_events[index], st);
 }
 
-#ifdef FB_PHASE_PROBE
-static struct { const char* file; void (*fn)(unsigned long long*, int, int); } g_phase_readers[32];
-static int g_num_phase_readers = 0;
-void register_phase_reader(const char* file, void (*fn)(unsigned long long*, int, int)) {
-    if (g_num_phase_readers < 32) g_phase_readers[g_num_phase_readers++] = {file, fn};
-}
-}  // namespace fb
-extern "C" int functs_b200_phase_read(const char* file_part, unsigned long long* out32, int reset) {
-    for (int i = 0; i < fb::g_num_phase_readers; ++i) {
-        if (strstr(fb::g_phase_readers[i].file, file_part) != nullptr) {
-            cudaDeviceSynchronize();
-            fb::g_phase_readers[i].fn(out32, reset, 0);
-            return 0;
-        }
-    }
-    return 1;
-}
-// out: 8192 x 8 words
-extern "C" int functs_b200_trace_read(const char* file_part, unsigned long long* out) {
-    for (int i = 0; i < fb::g_num_phase_readers; ++i) {
-        if (strstr(fb::g_phase_readers[i].file, file_part) != nullptr) {
-            cudaDeviceSynchronize();
-            fb::g_phase_readers[i].fn(out, 0, 1);
-            return 0;
-        }
-    }
-    return 1;
-}
-namespace fb {
-#endif
-
 // ---- group registry -----------------------------------------------------------------------------------
 // A signature names the op sequence of a fusion group the way the group's subgraph prints it, outermost
 // structure first.  Argument conventions are listed per entry; pointers are device pointers.
@@ -101,7 +70,7 @@ static int g_select_topk(const void* const* in, const int64_t* ia, const double*
 }
 
 static int g_batched_nms(const void* const* in, const int64_t* ia, const double* fa, void* const* out, void* scratch,
-                         int32_t*, void* stream) {
+                         int32_t* status, void* stream) {
     // in: boxes, sel_keys, sel_counts; ia: num_boxes, num_classes, groups, topk, class_offset; fa: iou_thr;
     // out: dets, labels, flat_ids, keep (may be null), out_counts
     return functs_b200_batched_nms(static_cast<const float*>(in[0]), ia[0], static_cast<int32_t>(ia[1]),
@@ -109,7 +78,7 @@ static int g_batched_nms(const void* const* in, const int64_t* ia, const double*
                                    static_cast<int32_t>(ia[2]), static_cast<int32_t>(ia[3]), static_cast<float>(fa[0]),
                                    static_cast<int32_t>(ia[4]), static_cast<float*>(out[0]),
                                    static_cast<int64_t*>(out[1]), static_cast<int64_t*>(out[2]),
-                                   static_cast<int64_t*>(out[3]), static_cast<int32_t*>(out[4]), scratch, stream);
+                                   static_cast<int64_t*>(out[3]), static_cast<int32_t*>(out[4]), status, scratch, stream);
 }
 
 static int g_ssd_softmax_decode(const void* const* in, const int64_t* ia, const double* fa, void* const* out, void*,
@@ -171,7 +140,7 @@ static const int kNumGroups = static_cast<int>(sizeof(kGroups) / sizeof(kGroups[
 
 extern "C" {
 
-int functs_b200_abi_version(void) { return 1; }
+int functs_b200_abi_version(void) { return 2; }
 const char* functs_b200_last_error(void) { return fb::g_error; }
 uint64_t functs_b200_launch_count(void) { return fb::g_launches.load(std::memory_order_relaxed); }
 

@@ -98,66 +98,6 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gm
                  : "memory");
 }
 
-// ---- phase clocks (development builds only) ---------------------------------------------------------------
-// Compiled with -DFB_PHASE_PROBE a kernel adds, at every FB_PHASE(k), the cycles its CTA spent since the previous
-// mark to g_phase_cycles[k] (thread 0's clock, after a barrier); functs_b200_phase_read(file name part, out[32], reset)
-// copies the sums of one translation unit to the host; FB_TRACE(word, value) stores a free-form per-CTA record
-// (functs_b200_trace_read).  In the library build the marks expand to nothing.
-#ifdef FB_PHASE_PROBE
-static __device__ unsigned long long g_phase_cycles[32];  // one copy per translation unit
-constexpr int kTraceCtas = 8192, kTraceWords = 8;
-static __device__ unsigned long long g_cta_trace[kTraceCtas * kTraceWords];  // free-form per-CTA records
-void register_phase_reader(const char* file, void (*fn)(unsigned long long*, int, int));
-namespace {
-struct PhaseReader {
-    explicit PhaseReader(const char* file) {
-        register_phase_reader(file, [](unsigned long long* out, int reset, int which) {
-            if (which == 0) {
-                cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(g_phase_cycles));
-                if (reset) {
-                    unsigned long long zero[32] = {0};
-                    cudaMemcpyToSymbol(g_phase_cycles, zero, sizeof(zero));
-                }
-            } else {
-                cudaMemcpyFromSymbol(out, g_cta_trace, sizeof(g_cta_trace));
-            }
-        });
-    }
-};
-static PhaseReader g_phase_reader{__BASE_FILE__};
-}  // namespace
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long v;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
-    return v;
-}
-#define FB_TRACE(word, value)                                                                                  \
-    do {                                                                                                       \
-        if (blockIdx.x < fb::kTraceCtas) fb::g_cta_trace[blockIdx.x * fb::kTraceWords + (word)] = (value);     \
-    } while (0)
-__device__ __forceinline__ long long& phase_prev() {
-    __shared__ long long v;
-    return v;
-}
-#define FB_PHASE_BEGIN()                               \
-    do {                                               \
-        if (threadIdx.x == 0) fb::phase_prev() = clock64(); \
-    } while (0)
-#define FB_PHASE(k)                                                                     \
-    do {                                                                                \
-        __syncthreads();                                                                \
-        if (threadIdx.x == 0) {                                                         \
-            const long long now_ = clock64();                                           \
-            atomicAdd(&fb::g_phase_cycles[k], static_cast<unsigned long long>(now_ - fb::phase_prev())); \
-            fb::phase_prev() = now_;                                                    \
-        }                                                                               \
-    } while (0)
-#else
-#define FB_PHASE_BEGIN() do { } while (0)
-#define FB_PHASE(k) do { } while (0)
-#define FB_TRACE(word, value) do { } while (0)
-#endif
-
 #endif  // __CUDACC__
 
 }  // namespace fb

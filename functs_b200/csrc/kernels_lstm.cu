@@ -17,7 +17,6 @@ namespace fb {
 
 int launch_lstm_input_proj_tc(const float* x, const float* w_ih, const float* b_ih, const float* b_hh, int M, int K,
                               int H, float* pre, void* tc_scratch, int32_t* status, cudaStream_t st);  // kernels_lstm_tc.cu
-void lstm_tc_set_swap(int v);
 int64_t lstm_tc_scratch_bytes(int M, int K, int H);
 bool lstm_tc_supported(int M, int K, int H);
 
@@ -295,10 +294,6 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
 }
 
 int functs_b200_debug_set(const char* name, int32_t value) {
-    if (name != nullptr && std::strcmp(name, "lstm_tc_swap_lbo_sbo") == 0) {
-        fb::lstm_tc_set_swap(value);
-        return FB_OK;
-    }
     if (name != nullptr && std::strcmp(name, "yolo_prune") == 0) {
         fb::yolo_set_prune(value);
         return FB_OK;

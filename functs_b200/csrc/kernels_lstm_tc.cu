@@ -135,7 +135,7 @@ struct TcShared {
 __global__ void __launch_bounds__(kTcThreads, 1)
 lstm_tc_gemm_kernel(const unsigned char* __restrict__ a_tiles, const unsigned char* __restrict__ b_tiles,
                     const float* __restrict__ b_ih, const float* __restrict__ b_hh, int K, int H, float* __restrict__ pre,
-                    int32_t* status, int swap_lbo_sbo) {
+                    int32_t* status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* tiles = smem_raw;
     TcShared& sh = *reinterpret_cast<TcShared*>(smem_raw + kTcStages * kTcStageBytes);
@@ -188,8 +188,9 @@ lstm_tc_gemm_kernel(const unsigned char* __restrict__ a_tiles, const unsigned ch
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t lbo = swap_lbo_sbo ? 1024u : 128u;
-            const uint32_t sbo = swap_lbo_sbo ? 128u : 1024u;
+            // descriptor strides of the pre-tiled layout (tile_offset): core matrices adjacent in K are 128 bytes apart
+            // (leading-dimension offset), 8-row groups 1024 bytes apart (stride-dimension offset)
+            constexpr uint32_t lbo = 128u, sbo = 1024u;
             uint32_t accumulate = 0;
             bool failed = false;
             for (int kt = 0; kt < KT && !failed; ++kt) {
@@ -285,9 +286,6 @@ int64_t lstm_tc_scratch_bytes(int M, int K, int H) {
     return a + b;
 }
 
-static int g_swap_lbo_sbo = 0;  // debugging aid: exchange the two descriptor strides (see functs_b200_debug_set)
-void lstm_tc_set_swap(int v) { g_swap_lbo_sbo = v; }
-
 int launch_lstm_input_proj_tc(const float* x, const float* w_ih, const float* b_ih, const float* b_hh, int M, int K,
                               int H, float* pre, void* tc_scratch, int32_t* status, cudaStream_t st) {
     FB_REQUIRE(lstm_tc_supported(M, K, H), "lstm tensor-core projection: shape not supported");
@@ -308,7 +306,7 @@ int launch_lstm_input_proj_tc(const float* x, const float* w_ih, const float* b_
                                            static_cast<int>(smem)),
                       "lstm_tc_gemm attr"));
     dim3 grid(4 * H / kTcBN, M / kTcBM);
-    lstm_tc_gemm_kernel<<<grid, kTcThreads, smem, st>>>(a_tiles, b_tiles, b_ih, b_hh, K, H, pre, status, g_swap_lbo_sbo);
+    lstm_tc_gemm_kernel<<<grid, kTcThreads, smem, st>>>(a_tiles, b_tiles, b_ih, b_hh, K, H, pre, status);
     count_launch();
     return check_launch("lstm_tc_gemm_kernel");
 }

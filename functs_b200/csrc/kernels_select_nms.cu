@@ -2,6 +2,8 @@
 // These are the un-fused ATen / torchvision steps that sit between the reference's fusion groups
 // (nonzero, bool-mask index, sort, torchvision.ops.nms — reference call sites
 // functs/benchmark/ai_model/yolov3/yolov3_bbox.py:122-134, 144-151, 177 and ssd/ssd_bbox.py:163-172, 212).
+#include <atomic>
+
 #include "select_nms.cuh"
 
 namespace fb {
@@ -123,9 +125,11 @@ constexpr int64_t kPrepBoxesOff = 16;
 constexpr int64_t kPrepLabelOff = kPrepBoxesOff + static_cast<int64_t>(kNmsMaxN) * sizeof(NmsBox);
 constexpr int64_t kPrepOrderOff = kPrepLabelOff + kNmsMaxN * 2;
 constexpr int64_t kPrepStartOff = kPrepOrderOff + kNmsMaxN * 2;
-constexpr int64_t kPrepBytes = (kPrepStartOff + (kMaskMaxBuckets + 1) * 4 + 255) / 256 * 256;
+// one bit per candidate: its key named a box outside [0, num_boxes) (the candidate then takes no part in the NMS)
+constexpr int64_t kPrepInvalidOff = kPrepStartOff + (kMaskMaxBuckets + 1) * 4;
+constexpr int64_t kPrepBytes = (kPrepInvalidOff + kNmsWords * 4 + 255) / 256 * 256;
 static_assert(sizeof(NmsBox) == 20 && kPrepBoxesOff % 16 == 0 && kPrepLabelOff % 16 == 0 && kPrepOrderOff % 16 == 0 &&
-                  kPrepStartOff % 4 == 0 && kPrepBytes % 256 == 0,
+                  kPrepStartOff % 4 == 0 && kPrepInvalidOff % 4 == 0 && kPrepBytes % 256 == 0 && kPrepBytes == 28928,
               "prepared NMS input layout");
 
 template <int NT>
@@ -136,11 +140,15 @@ struct NmsPrepSmem {
 };
 
 // All NT threads of a CTA.  sel: the group's n selected keys, sorted (shared or global memory); boxes_g: the group's
-// boxes; prep: the group's prepared-input record; ticket: the group's arrival counter of the matrix kernel (cleared).
+// num_boxes boxes; prep: the group's prepared-input record; ticket: the group's arrival counter of the matrix kernel
+// (cleared).  A key whose box index is not below num_boxes (a stale or malformed key: the keys are caller-supplied) is
+// never used as an address: the candidate gets a zero box, is marked invalid in the record (the scan treats it as
+// removed from the start, so it neither survives nor suppresses) and FB_STATUS_INDEX_RANGE is set in `status`.
 template <int NT>
-__device__ __forceinline__ void nms_prepare_block(const float* __restrict__ boxes_g, int num_classes, int class_offset,
-                                                  const uint64_t* sel, int n, unsigned char* __restrict__ prep,
-                                                  int32_t* ticket, NmsPrepSmem<NT>& ps) {
+__device__ __forceinline__ void nms_prepare_block(const float* __restrict__ boxes_g, int64_t num_boxes, int num_classes,
+                                                  int class_offset, const uint64_t* sel, int n,
+                                                  unsigned char* __restrict__ prep, int32_t* ticket, int32_t* status,
+                                                  NmsPrepSmem<NT>& ps) {
     uint16_t* slabel = ps.slabel;
     int* bcursor = ps.bcursor;
     float* red_hi = ps.red_hi;
@@ -151,7 +159,9 @@ __device__ __forceinline__ void nms_prepare_block(const float* __restrict__ boxe
     uint16_t* plabel = reinterpret_cast<uint16_t*>(prep + kPrepLabelOff);
     uint16_t* porder = reinterpret_cast<uint16_t*>(prep + kPrepOrderOff);
     int* pstart = reinterpret_cast<int*>(prep + kPrepStartOff);
+    uint32_t* pinvalid = reinterpret_cast<uint32_t*>(prep + kPrepInvalidOff);
     const int nb = (class_offset && num_classes <= kMaskMaxBuckets) ? num_classes : 1;
+    static_assert(NT % 32 == 0, "a warp covers 32 consecutive candidates");
 
     // gather: thread t owns candidates t, t + NT, ...
     constexpr int kPer = kNmsMaxN / NT;
@@ -164,13 +174,22 @@ __device__ __forceinline__ void nms_prepare_block(const float* __restrict__ boxe
         const int c = t + q * NT;
         bx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
         label[q] = 0;
+        bool bad = false;
         if (c < n) {
             const uint32_t flat = key_index(sel[c]);
             const uint32_t box = flat / static_cast<uint32_t>(num_classes);
             label[q] = static_cast<int>(flat - box * static_cast<uint32_t>(num_classes));
-            bx[q] = reinterpret_cast<const float4*>(boxes_g)[box];
-            lmax = fmaxf(lmax, fmaxf(fmaxf(bx[q].x, bx[q].y), fmaxf(bx[q].z, bx[q].w)));
-            lmin = fminf(lmin, fminf(fminf(bx[q].x, bx[q].y), fminf(bx[q].z, bx[q].w)));
+            bad = static_cast<int64_t>(box) >= num_boxes;
+            if (!bad) {
+                bx[q] = reinterpret_cast<const float4*>(boxes_g)[box];
+                lmax = fmaxf(lmax, fmaxf(fmaxf(bx[q].x, bx[q].y), fmaxf(bx[q].z, bx[q].w)));
+                lmin = fminf(lmin, fminf(fminf(bx[q].x, bx[q].y), fminf(bx[q].z, bx[q].w)));
+            }
+        }
+        const unsigned bad_word = __ballot_sync(kFullMask, bad);
+        if (lane == 0) {
+            pinvalid[(t >> 5) + q * (NT / 32)] = bad_word;
+            if (bad_word != 0u && status != nullptr) atomicOr(status, FB_STATUS_INDEX_RANGE);
         }
     }
 #pragma unroll
@@ -261,15 +280,15 @@ __device__ __forceinline__ void nms_prepare_block(const float* __restrict__ boxe
 __global__ void __launch_bounds__(kMaskThreads)
 nms_prepare_kernel(const float* __restrict__ boxes, int64_t num_boxes, int num_classes, const uint64_t* __restrict__ sel_keys,
                    const int32_t* __restrict__ sel_counts, int topk, int class_offset, unsigned char* __restrict__ prep_g,
-                   int32_t* __restrict__ ticket_g) {
+                   int32_t* __restrict__ ticket_g, int32_t* status) {
     __shared__ NmsPrepSmem<kMaskThreads> ps;
     const int g = blockIdx.x;
     int n = sel_counts[g];
     if (n > topk) n = topk;
     if (n < 0) n = 0;
-    nms_prepare_block<kMaskThreads>(boxes + static_cast<int64_t>(g) * num_boxes * 4, num_classes, class_offset,
+    nms_prepare_block<kMaskThreads>(boxes + static_cast<int64_t>(g) * num_boxes * 4, num_boxes, num_classes, class_offset,
                                     sel_keys + static_cast<int64_t>(g) * topk, n, prep_g + static_cast<int64_t>(g) * kPrepBytes,
-                                    ticket_g + g, ps);
+                                    ticket_g + g, status, ps);
 }
 
 
@@ -302,7 +321,8 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
                      const int32_t* __restrict__ hist, uint32_t hist_base, int hist_shift, int32_t topk,
                      SelectCtr* ctr, uint64_t* sel_tmp, uint64_t* bin_tmp, uint64_t* __restrict__ out_keys,
                      int32_t* __restrict__ out_counts, const float* __restrict__ nms_boxes, int64_t num_boxes,
-                     int num_classes, int class_offset, unsigned char* __restrict__ prep_g, int32_t* __restrict__ ticket_g) {
+                     int num_classes, int class_offset, unsigned char* __restrict__ prep_g, int32_t* __restrict__ ticket_g,
+                     int32_t* status) {
     constexpr size_t kRaw = sizeof(BinnedSmem) > sizeof(SelectSmem<kSelCap>) ? sizeof(BinnedSmem) : sizeof(SelectSmem<kSelCap>);
     static_assert(sizeof(uint64_t) * kSelCap + sizeof(NmsPrepSmem<kBinThreads>) <= kRaw, "NMS preparation reuses the buffer");
     __shared__ __align__(16) unsigned char raw[kRaw];
@@ -310,7 +330,6 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     __shared__ int s_dstar, s_above, s_inbin, s_last;
     const int g = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    FB_PHASE_BEGIN();
     // the group's histogram (four buckets per thread) does not depend on anything: ask for it first, together with
     // the candidate count, so that the two round trips overlap
     static_assert(kHistBins == 4 * kBinThreads, "four histogram buckets per thread");
@@ -377,7 +396,6 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
         s_nbin = 0;
     }
     __syncthreads();
-    FB_PHASE(10);
     const int dstar = s_dstar;
     SelectCtr* c = ctr + g;
     uint64_t* gsel = sel_tmp + static_cast<int64_t>(g) * kSelCap;
@@ -419,7 +437,6 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
         }
     }
     __syncthreads();
-    FB_PHASE(11);
     if (tid == 0) {
         s_bsel = s_nsel > 0 ? atomicAdd(&c->sel_cnt, s_nsel) : 0;
         s_bbin = s_nbin > 0 ? atomicAdd(&c->bin_cnt, s_nbin) : 0;
@@ -433,7 +450,6 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
     __syncthreads();
     if (tid == 0) s_last = (atomicAdd(&c->ticket, 1) == static_cast<int>(gridDim.x) - 1) ? 1 : 0;
     __syncthreads();
-    FB_PHASE(12);
     if (!s_last) return;
     __threadfence();
 
@@ -462,7 +478,6 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
             const int want = topk - sel_cnt;
             for (int i = tid; i < want; i += kBinThreads) sm.sel[sel_cnt + i] = sm.bin[i];
         }
-        FB_PHASE(13);
         // sm.sel[0 .. sel_cnt) holds the keys above the boundary bucket in arrival order, the sorted tail from the
         // boundary bucket follows.  Order the head by counting sort on the score buckets (higher bucket = higher
         // score) plus a rank count inside every bucket; a crowded bucket falls back to the bitonic network.
@@ -501,14 +516,12 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
             above += c[q];
         }
         __syncthreads();
-        FB_PHASE(17);
         if (!crowded) {
             for (int i = tid; i < sel_cnt; i += kBinThreads) {
                 const uint64_t k = sm.sel[i];
                 tmp[atomicAdd(&cursor[hist_digit(k, hist_base, hist_shift)], 1)] = k;
             }
             __syncthreads();
-            FB_PHASE(18);
             // inside a bucket: every key counts the larger keys of its bucket's segment (keys are distinct) and
             // goes straight to its final place
             for (int i = tid; i < sel_cnt; i += kBinThreads) {
@@ -520,7 +533,6 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
                 sm.sel[r] = k;
             }
             __syncthreads();
-            FB_PHASE(19);
         } else {
             const int sn = next_pow2(result);
             for (int i = result + tid; i < sn; i += kBinThreads) sm.sel[i] = 0ull;
@@ -528,16 +540,14 @@ select_binned_kernel(const uint64_t* __restrict__ in_keys, const int32_t* __rest
             bitonic_sort_desc<kBinThreads>(sm.sel, sn);
         }
     }
-    FB_PHASE(14);
     for (int i = tid; i < topk; i += kBinThreads) out_keys[static_cast<int64_t>(g) * topk + i] = (i < result) ? sm.sel[i] : 0ull;
     if (tid == 0) out_counts[g] = result;
-    FB_PHASE(15);
     if (prep_g != nullptr) {
         __syncthreads();
         NmsPrepSmem<kBinThreads>& ps = *reinterpret_cast<NmsPrepSmem<kBinThreads>*>(raw + sizeof(uint64_t) * kSelCap);
-        nms_prepare_block<kBinThreads>(nms_boxes + static_cast<int64_t>(g) * num_boxes * 4, num_classes, class_offset, sm.sel,
-                                       result, prep_g + static_cast<int64_t>(g) * kPrepBytes, ticket_g + g, ps);
-        FB_PHASE(16);
+        nms_prepare_block<kBinThreads>(nms_boxes + static_cast<int64_t>(g) * num_boxes * 4, num_boxes, num_classes,
+                                       class_offset, sm.sel, result, prep_g + static_cast<int64_t>(g) * kPrepBytes,
+                                       ticket_g + g, status, ps);
     }
 }
 
@@ -581,7 +591,6 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
     const NmsPrepHeader h = *reinterpret_cast<const NmsPrepHeader*>(prep);
     const int n = h.n, nb = h.nb, reach = h.reach;
     const int rt = gridDim.x;
-    FB_PHASE_BEGIN();
     uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
     uint8_t* gflag = rowflag_g + static_cast<int64_t>(g) * kNmsMaxN;
     if (static_cast<int>(blockIdx.x) < n) {  // otherwise this CTA owns no row
@@ -603,7 +612,6 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
             for (int i = t; i <= nb; i += kMaskThreads) rs.bstart[i] = __ldg(ssrc + i);
         }
         __syncthreads();
-        FB_PHASE(24);
         uint32_t* myrow = rs.rowbuf[warp];
         for (int i = warp * rt + static_cast<int>(blockIdx.x); i < n; i += (kMaskThreads / 32) * rt) {
             const NmsBox bi = rs.sb[i];
@@ -625,7 +633,6 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
             if (lane == 0) gflag[i] = any ? 1 : 0;
             __syncwarp();
         }
-        FB_PHASE(27);
     }
     __threadfence();
     __syncthreads();
@@ -654,7 +661,11 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
     for (int q = 0; q < kRounds; ++q) {
         const int c = q * kMaskThreads + t;
         obox[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < n) obox[q] = reinterpret_cast<const float4*>(boxes_g)[key_index(okey[q]) / static_cast<uint32_t>(num_classes)];
+        if (c < n) {
+            // an out-of-range box index is never dereferenced; such a candidate is marked invalid and not written out
+            const uint32_t box = key_index(okey[q]) / static_cast<uint32_t>(num_classes);
+            if (static_cast<int64_t>(box) < num_boxes) obox[q] = reinterpret_cast<const float4*>(boxes_g)[box];
+        }
     }
 #pragma unroll
     for (int q = 0; q < kRounds; ++q) {
@@ -678,8 +689,8 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
     for (int q = 0; q < kRounds; ++q)
         if (nz[q]) ss.nzrow[before[q] + __popc(nzm[q] & ((1u << lane) - 1u))] = static_cast<uint16_t>(q * kMaskThreads + t);
     __syncthreads();
-    FB_PHASE(20);
-    uint32_t removed = 0u;  // warp 0: lane l holds the removed bits of boxes 32l .. 32l+31
+    // warp 0: lane l holds the removed bits of boxes 32l .. 32l+31; invalid candidates start out removed
+    uint32_t removed = (warp == 0) ? __ldcg(reinterpret_cast<const uint32_t*>(prep + kPrepInvalidOff) + lane) : 0u;
     for (int c0 = 0; c0 < nz_total; c0 += kScanChunk) {
         const int rows = min(kScanChunk, nz_total - c0);
         if (t < rows) {  // one thread per row: eight 16-byte loads (L2-resident: just written)
@@ -723,7 +734,6 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
         }
     }
     __syncthreads();
-    FB_PHASE(21);
     const int64_t obase = static_cast<int64_t>(g) * topk;
 #pragma unroll
     for (int q = 0; q < kRounds; ++q) {
@@ -757,7 +767,6 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
         flat_ids[obase + i] = -1;
         if (keep != nullptr) keep[obase + i] = -1;
     }
-    FB_PHASE(22);
 }
 
 // ---- host launchers (internal C++ API, used by the C ABI and by the YOLO pipeline) ----------------
@@ -832,7 +841,7 @@ int64_t nms_scratch_bytes(int groups, int topk) {
 int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, const int32_t* hist,
                          float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
                          void* lists, int zero_ctr, const float* nms_boxes, int64_t num_boxes, int num_classes,
-                         int class_offset, void* nms_scratch, cudaStream_t st) {
+                         int class_offset, void* nms_scratch, int32_t* status, cudaStream_t st) {
     FB_REQUIRE(in_keys && in_counts && hist && out_keys && out_counts && ctr && lists, "select_topk_binned: null pointer");
     FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kSelCap && capacity > 0 && capacity < (1ll << 31),
                "select_topk_binned: bad sizes (topk must be in [1, %d])", kSelCap);
@@ -850,7 +859,8 @@ int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int6
     dim3 grid(kBinSplit, groups);
     select_binned_kernel<<<grid, kBinThreads, 0, st>>>(in_keys, in_counts, capacity, hist, hp.base, hp.shift, topk,
                                                        static_cast<SelectCtr*>(ctr), sel_tmp, bin_tmp, out_keys, out_counts,
-                                                       nms_boxes, num_boxes, num_classes, class_offset, v.prep, v.ticket);
+                                                       nms_boxes, num_boxes, num_classes, class_offset, v.prep, v.ticket,
+                                                       status);
     count_launch();
     return check_launch("select_binned_kernel");
 }
@@ -859,7 +869,7 @@ int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int6
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
                        int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
-                       cudaStream_t st) {
+                       int32_t* status, cudaStream_t st) {
     FB_REQUIRE(boxes && sel_keys && sel_counts && dets && labels && flat_ids && out_counts && mask,
                "batched_nms: null pointer");
     FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kNmsMaxN && num_classes > 0 && num_boxes > 0,
@@ -871,22 +881,22 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
     const NmsScratch v = nms_scratch_views(mask, groups);
     if (!prepared) {
         nms_prepare_kernel<<<groups, kMaskThreads, 0, st>>>(boxes, num_boxes, num_classes, sel_keys, sel_counts, topk,
-                                                            class_offset, v.prep, v.ticket);
+                                                            class_offset, v.prep, v.ticket, status);
         count_launch();
         FB_TRY(check_launch("nms_prepare_kernel"));
     }
     // one wave: a second, partly filled wave costs more than longer row loops per warp
-    static int wave_cache[64] = {};  // resident CTAs of this kernel per device: asked once
+    static std::atomic<int> wave_cache[64];  // resident CTAs of this kernel per device: asked once (0 = not yet)
     int dev = 0;
     FB_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
-    int wave = dev >= 0 && dev < 64 ? wave_cache[dev] : 0;
+    int wave = dev >= 0 && dev < 64 ? wave_cache[dev].load(std::memory_order_relaxed) : 0;
     if (wave == 0) {
         int sms = 0, per_sm = 0;
         FB_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"));
         FB_TRY(check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nms_mask_scan_kernel, kMaskThreads, 0),
                           "occupancy"));
         wave = sms * per_sm;
-        if (dev >= 0 && dev < 64) wave_cache[dev] = wave;
+        if (dev >= 0 && dev < 64) wave_cache[dev].store(wave, std::memory_order_relaxed);
     }
     int ctas = wave / groups;
     ctas = ctas < 1 ? 1 : (ctas > kMaskCtasMax ? kMaskCtasMax : ctas);
@@ -933,7 +943,7 @@ int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_co
     unsigned char* base = static_cast<unsigned char*>(scratch);
     return fb::launch_select_binned(in_keys, in_counts, capacity, hist, thr, groups, topk, out_keys, out_counts, base,
                                     base + fb::select_binned_ctr_bytes(groups > 0 ? groups : 1), 1, nullptr, 0, 0, 0, nullptr,
-                                    fb::as_stream(stream));
+                                    nullptr, fb::as_stream(stream));
 }
 
 int64_t functs_b200_nms_scratch_bytes(int32_t groups, int32_t topk) {
@@ -944,13 +954,13 @@ int64_t functs_b200_nms_scratch_bytes(int32_t groups, int32_t topk) {
 int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_classes, const uint64_t* sel_keys,
                             const int32_t* sel_counts, int32_t groups, int32_t topk, float iou_thr,
                             int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids, int64_t* keep,
-                            int32_t* out_counts, void* scratch, void* stream) {
+                            int32_t* out_counts, int32_t* status, void* scratch, void* stream) {
     if (scratch == nullptr || groups <= 0) {
         fb::set_error("batched_nms: null scratch or bad group count");
         return FB_ERR_INVALID_ARGUMENT;
     }
     return fb::launch_batched_nms(boxes, num_boxes, num_classes, sel_keys, sel_counts, groups, topk, iou_thr,
-                                  class_offset, dets, labels, flat_ids, keep, out_counts, scratch, 0,
+                                  class_offset, dets, labels, flat_ids, keep, out_counts, scratch, 0, status,
                                   fb::as_stream(stream));
 }
 

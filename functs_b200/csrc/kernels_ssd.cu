@@ -134,7 +134,6 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
 
     const int cls = blockIdx.x, img = blockIdx.y;
     const int t = threadIdx.x;
-    FB_PHASE_BEGIN();
     const float* src = scores_cm + (static_cast<int64_t>(img) * num_classes + cls) * num_priors;
     const float* score_ptr = src;
     if (stage != 0) {
@@ -162,7 +161,6 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
         // a copy that did not land in time (never observed): the scores are read from global memory instead; the
         // landing zone is not used for anything else
     }
-    FB_PHASE(0);
     ClassScores kf{score_ptr, score_thr, (reinterpret_cast<uintptr_t>(score_ptr) & 15) == 0};
     const int n = block_select_topk_binned<kSsdNmsThreads, kSsdSelCap, 8>(kf, num_priors, topk, hist_base, hist_shift, sm);
     // (block_select_topk ends with a barrier when n > 1; make the hand-over explicit)
@@ -181,7 +179,6 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     }
     if (t < kSsdWords) keep_words[t] = 0u;
     const bool tame = __syncthreads_and(tame_box ? 1 : 0) != 0;  // also the barrier behind the box stores
-    FB_PHASE(6);
 
     // suppression bit matrix.  A task is (column word w, batch of rows): lane b holds box j = 32w + b, the rows' boxes
     // are broadcast reads, the tests of a batch are independent and branch-free, and one ballot per row yields the
@@ -235,10 +232,8 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
         }
     }
     __syncthreads();
-    FB_PHASE(7);
     block_nms_resolve<kSsdNmsThreads, kSsdWords>(smask, n, keep_words, or_words);
     __syncthreads();
-    FB_PHASE(8);
     if (t == 0) {
         int acc = 0;
         for (int w = 0; w < kSsdWords; ++w) {
@@ -270,7 +265,6 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
         d[0] = d[1] = d[2] = d[3] = d[4] = 0.0f;
         prior_ids[obase + i] = -1;
     }
-    FB_PHASE(9);
 }
 
 }  // namespace fb

@@ -16,12 +16,12 @@ int64_t select_binned_lists_bytes(int groups);
 int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int64_t capacity, const int32_t* hist,
                          float thr, int groups, int topk, uint64_t* out_keys, int32_t* out_counts, void* ctr,
                          void* lists, int zero_ctr, const float* nms_boxes, int64_t num_boxes, int num_classes,
-                         int class_offset, void* nms_scratch, cudaStream_t st);
+                         int class_offset, void* nms_scratch, int32_t* status, cudaStream_t st);
 int64_t nms_mask_bytes(int groups);
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
                        int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
-                       cudaStream_t st);
+                       int32_t* status, cudaStream_t st);
 
 constexpr int kYoloThreads = 128;
 constexpr int kYoloClasses = 80;
@@ -686,7 +686,6 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     const bool pruning = P.prune_topk > 0 && ghist != nullptr;
 
     if (t == 0) {
-        FB_TRACE(0, global_ns());
 #pragma unroll
         for (int b = 0; b < kStStages; ++b) {
             mbar_init(&sm.full[b], 1);
@@ -784,9 +783,6 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     }
     __syncthreads();  // the last CTA-wide barrier: from here on the warps only meet through the ring's mbarriers
     if (t == 0) {
-        FB_TRACE(1, global_ns());
-        FB_TRACE(3, static_cast<unsigned long long>(total));
-        FB_TRACE(4, static_cast<unsigned long long>(prune));
     }
 
     if (producer) {
@@ -896,8 +892,6 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     if (tail - head > 0) fill = st_eval_batch(sm.live, &ws, head, tail - head, ea, prune, fill);
     if (fill > 0) st_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
     if (t == 0) {
-        FB_TRACE(2, global_ns());
-        FB_TRACE(5, static_cast<unsigned long long>(prune));
     }
 }
 
@@ -1125,10 +1119,10 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
     // the CTA that finishes an image's selection also prepares the image's NMS input in the NMS work area
     FB_TRY(launch_select_binned(keys, counts, capacity, hist, score_thr, batch, topk, sel_keys, sel_counts,
                                 base + L.ctr_off, base + L.lists_off, 0, boxes, num_boxes, kYoloClasses, 1,
-                                base + L.mask_off, st));
+                                base + L.mask_off, status, st));
     record_stage_event(2, st);
     const int rc = launch_batched_nms(boxes, num_boxes, kYoloClasses, sel_keys, sel_counts, batch, topk, iou_thr, 1, dets,
-                                      labels, flat_ids, nullptr, out_counts, base + L.mask_off, 1, st);
+                                      labels, flat_ids, nullptr, out_counts, base + L.mask_off, 1, status, st);
     record_stage_event(3, st);
     return rc;
 }

@@ -21,7 +21,7 @@ namespace fb {
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
                        int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
-                       cudaStream_t st);
+                       int32_t* status, cudaStream_t st);
 int64_t nms_mask_bytes(int groups);
 
 constexpr int kStaticNmsGroups = 8;
@@ -61,7 +61,7 @@ int32_t functs_b200_batched_nms_static_max_groups(void) { return fb::kStaticNmsG
 int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_t num_classes, const uint64_t* sel_keys,
                                    const int32_t* sel_counts, int32_t groups, int32_t topk, float iou_thr,
                                    int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids,
-                                   int64_t* keep, int32_t* out_counts, void* stream) {
+                                   int64_t* keep, int32_t* out_counts, int32_t* status, void* stream) {
     using namespace fb;
     FB_REQUIRE(groups > 0 && groups <= kStaticNmsGroups,
                "batched_nms_static: %d groups requested, the built-in scratch holds at most %d (use "
@@ -71,7 +71,7 @@ int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_
     void* scratch = nullptr;
     FB_TRY(static_nms_scratch(&scratch));
     return launch_batched_nms(boxes, num_boxes, num_classes, sel_keys, sel_counts, groups, topk, iou_thr, class_offset,
-                              dets, labels, flat_ids, keep, out_counts, scratch, 0, as_stream(stream));
+                              dets, labels, flat_ids, keep, out_counts, scratch, 0, status, as_stream(stream));
 }
 
 }  // extern "C"

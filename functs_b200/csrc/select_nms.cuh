@@ -372,7 +372,6 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
     }
     __syncthreads();
-    FB_PHASE(1);
     // boundary bucket: the largest digit d with (keys in buckets >= d) >= topk.  Every thread sums its share of the
     // buckets (higher thread = higher buckets), suffix sums over the block locate the thread that holds the boundary
     {
@@ -435,7 +434,6 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
     }
     __syncthreads();
-    FB_PHASE(2);
     const int nvalid = sm.nvalid;
     if (nvalid == 0) return 0;
     const int dstar = sm.digit;  // -1: everything is selected
@@ -486,7 +484,6 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
     }
     __syncthreads();
-    FB_PHASE(3);
     const int result = nvalid < topk ? nvalid : topk;
     if (dstar >= 0) {
         const int bc = sm.bin_cnt;
@@ -501,7 +498,6 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
         __syncthreads();
     }
-    FB_PHASE(4);
     // Final order.  The boundary bucket's share already sits sorted behind the `have` keys of the higher buckets.
     // Those are ordered by a counting sort: a key of bucket d goes to the run that starts at hist[d] (keys in higher
     // buckets), in arrival order; afterwards hist[d] is the run's end and hist[d + 1] its start, and every key
@@ -526,7 +522,6 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
         }
         __syncthreads();
     }
-    FB_PHASE(5);
     return result;
 }
 

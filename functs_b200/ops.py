@@ -107,7 +107,7 @@ def select_topk(keys: torch.Tensor, counts: torch.Tensor, topk: int) -> Tuple[to
 
 
 def batched_nms(boxes: torch.Tensor, num_classes: int, sel_keys: torch.Tensor, sel_counts: torch.Tensor,
-                iou_thr: float, class_offset: bool):
+                iou_thr: float, class_offset: bool, status: Optional[torch.Tensor] = None):
     """boxes [G, N, 4]; sel_keys [G, K] -> (dets [G,K,5], labels [G,K], flat_ids [G,K], keep [G,K], counts [G])."""
     boxes = _req(boxes, torch.float32, "boxes")
     sel_keys = _req(sel_keys, torch.int64, "sel_keys")
@@ -122,7 +122,7 @@ def batched_nms(boxes: torch.Tensor, num_classes: int, sel_keys: torch.Tensor, s
     scratch = torch.empty(int(lib.functs_b200_nms_scratch_bytes(g, k)), dtype=torch.uint8, device=dev)
     check(lib.functs_b200_batched_nms(_ptr(boxes), boxes.size(1), int(num_classes), _ptr(sel_keys), _ptr(sel_counts), g, k,
                                       float(iou_thr), 1 if class_offset else 0, _ptr(dets), _ptr(labels), _ptr(flat_ids),
-                                      _ptr(keep), _ptr(counts), _ptr(scratch), _stream()), "batched_nms")
+                                      _ptr(keep), _ptr(counts), _ptr(status), _ptr(scratch), _stream()), "batched_nms")
     return dets, labels, flat_ids, keep, counts
 
 

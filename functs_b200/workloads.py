@@ -128,6 +128,12 @@ class LSTM:
         self._status = ops.new_status(self.device)
         self.kernels_last_call = 0
 
+    @staticmethod
+    def expected_launches(seq_len: int, batch: int, hidden: int, mode: int = 0) -> int:
+        """Kernel launches of one call: operand split + tensor-core projection + recurrence, or (mode 1, or a shape the
+        tensor-core projection does not take) CUDA-core projection + recurrence."""
+        return 3 if (mode == 0 and (seq_len * batch) % 128 == 0 and hidden % 128 == 0) else 2
+
     def forward_device(self, x: torch.Tensor, mode: int = 0):
         """x on the device; outputs and scratch are reused across calls; no synchronisation."""
         t, b, i = x.shape

@@ -37,7 +37,7 @@ extern "C" {
 /* bits of the device status word */
 #define FB_STATUS_CAND_OVERFLOW 1 /* a candidate list was longer than its capacity; extra candidates were dropped */
 #define FB_STATUS_WAIT_TIMEOUT 2  /* a bounded device-side wait ran out */
-#define FB_STATUS_INDEX_RANGE 4   /* an index tensor held a row outside the indexed extent */
+#define FB_STATUS_INDEX_RANGE 4   /* an index tensor (or a candidate key) named a row outside the indexed extent */
 
 /* ---- library ------------------------------------------------------------------------- */
 
@@ -97,12 +97,15 @@ int functs_b200_select_topk_binned(const uint64_t* in_keys, const int32_t* in_co
  * Outputs (fixed capacity topk per group, first out_counts[g] rows valid, score-descending):
  *   dets [groups, topk, 5] (x1,y1,x2,y2,score), labels [groups, topk] int64, flat_ids [groups, topk] int64,
  *   keep [groups, topk] int64 (position in the selected list), out_counts [groups] int32.
+ * A key whose box index (flat index / num_classes) is not below num_boxes is never used as an address: that candidate
+ * takes no part in the NMS (it neither survives nor suppresses), and FB_STATUS_INDEX_RANGE is set in `status`
+ * (optional device word, may be NULL).
  * scratch: functs_b200_nms_scratch_bytes(groups, topk). */
 int64_t functs_b200_nms_scratch_bytes(int32_t groups, int32_t topk);
 int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_classes, const uint64_t* sel_keys,
                             const int32_t* sel_counts, int32_t groups, int32_t topk, float iou_thr,
                             int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids, int64_t* keep,
-                            int32_t* out_counts, void* scratch, void* stream);
+                            int32_t* out_counts, int32_t* status, void* scratch, void* stream);
 
 /* The same NMS for callers that cannot provide scratch memory.  No counterpart in the reference (its executor always
  * allocates through torch's caching allocator).  Meant for hosts that bind only this C ABI and own no device allocator
@@ -117,7 +120,7 @@ int32_t functs_b200_batched_nms_static_max_groups(void);
 int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_t num_classes, const uint64_t* sel_keys,
                                    const int32_t* sel_counts, int32_t groups, int32_t topk, float iou_thr,
                                    int32_t class_offset, float* dets, int64_t* labels, int64_t* flat_ids,
-                                   int64_t* keep, int32_t* out_counts, void* stream);
+                                   int64_t* keep, int32_t* out_counts, int32_t* status, void* stream);
 
 /* Packs the padded outputs of batched_nms / yolo_postprocess into 32-byte records for the multi-GPU gather of final
  * detections (the step that follows the reference's per-image loop when the batch is sharded over GPUs; the reference
@@ -126,28 +129,6 @@ int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_
  * 7 = 1 for a valid row (k < counts[g]) and 0 for padding.  16-byte aligned. */
 int functs_b200_pack_detections(const float* dets, const int64_t* labels, const int64_t* flat_ids, const int32_t* counts,
                                 int32_t groups, int32_t topk, int32_t* records, void* stream);
-
-/* The same packing fused with the gather itself, without a collective library: every record is stored straight into
- * the gather buffer of every rank over NVLink (plain peer stores), then one flag per destination says that this rank's
- * share of step `step` is complete.  peer_records[r]: rank r's gather buffer for this step's slot,
- * [nranks * groups, topk, 8] int32 (rank q's records start at q * groups); peer_flags[r]: rank r's flag block of
- * functs_b200_peer_flag_bytes() bytes, zeroed before the first step.  Both are device pointers valid on the calling
- * GPU (the caller opens the other ranks' allocations, e.g. through CUDA IPC, and calls
- * functs_b200_peer_enable_access once per peer device).  Steps count from 1 and alternate between two slots: before
- * it overwrites a slot the kernel waits until every destination has released the step that used it last
- * (functs_b200_peer_release); a reader waits for a step with functs_b200_peer_wait.  All waits are bounded (about a
- * second) and report FB_STATUS_WAIT_TIMEOUT in `status` instead of blocking.
- * Status: compiled and exported; no test of this library runs these entry points on hardware yet, and the benchmark's
- * gather is the NCCL all-gather of functs_b200_pack_detections records. */
-int32_t functs_b200_peer_flag_bytes(void);
-int functs_b200_peer_enable_access(int32_t peer_device);
-int functs_b200_peer_check_pointer(const void* ptr, int32_t* device);
-int functs_b200_pack_detections_peers(const float* dets, const int64_t* labels, const int64_t* flat_ids,
-                                      const int32_t* counts, int32_t groups, int32_t topk, void* const* peer_records,
-                                      void* const* peer_flags, int32_t rank, int32_t nranks, uint32_t step,
-                                      int32_t* status, void* stream);
-int functs_b200_peer_wait(const void* my_flags, int32_t nranks, uint32_t step, int32_t* status, void* stream);
-int functs_b200_peer_release(void* const* peer_flags, int32_t rank, int32_t nranks, uint32_t step, void* stream);
 
 /* ---- C2: YOLOv3-style decode + score mask + top-k + class-wise NMS ----------------------- */
 /* Follows functs/benchmark/ai_model/yolov3/yolov3_bbox.py:195-243 at the configured shapes:
@@ -207,7 +188,6 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
                                   float* hs, float* cs, int32_t* status, void* scratch, void* stream, int32_t mode);
 
 /* Debugging switches (name -> value); returns FB_ERR_NOT_FOUND for an unknown name.
- *   "lstm_tc_swap_lbo_sbo": exchange the two stride fields of the tensor-core shared-memory descriptors.
  *   "yolo_prune": 0 makes functs_b200_yolo_postprocess keep every candidate above the score threshold instead of
  *                 dropping, inside the decode kernel, those that can no longer reach the top-k (default 1; the
  *                 outputs are the same either way). */

@@ -14,8 +14,10 @@ Parity pin status:
   * ``get_started``, ``batched_nms``, ``select_topk``, ``ssd_delta2bbox``, ``lstm_cell`` and
     ``crop_by_slice_assign`` are pinned, bit for bit, against outputs of the reference's own Python
     functions (``tests/golden/make_golden.py`` wrote the fixtures; ``tests/test_oracle_golden.py``
-    checks them).  The YOLOv3 decode formula (sigmoid + grid, exp * anchor) has no counterpart
-    function in the reference files and is pinned only by its definition here.
+    checks them).  The YOLOv3 decode (sigmoid + grid offset, exp * anchor) is pinned to 1e-5 relative, not bit for
+    bit, against the reference's ``decode_bboxes`` on the anchors of its ``YOLOAnchorGenerator``
+    (yolov3_bbox.py:12-100): the reference forms the centre as anchor centre + (sigmoid - 0.5) * stride, this
+    program as (sigmoid + cell) * stride — the same boxes through another operation order.
   * ``torchvision.ops.nms``, ``torch.sort`` and the ATen CPU math kernels are third-party
     arithmetic that the reference's tests do not pin; the installed CPU kernels define the answer.
 
@@ -135,7 +137,7 @@ class YOLOV3Post(torch.nn.Module):
             pred[..., 4:].sigmoid_()
             pred[..., 0:2] = (pred[..., 0:2] + self.grids[lvl]) * self.strides[lvl]
             pred[..., 2:4] = pred[..., 2:4].exp() * self.anchor_whs[lvl]
-            flatten_preds.append(pred)
+            flatten_preds.append(pred.clone())  # a copy goes into the list, as in yolov3_bbox.py:213
         flat = torch.cat(flatten_preds, dim=1)
         xy = flat[..., 0:2]
         half = flat[..., 2:4] * 0.5

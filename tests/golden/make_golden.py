@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this folder by running the REFERENCE's own Python functions on CPU.
 
-Run once, in a container that has the reference checked out (default /root/reference, or pass the path):
-    python tests/golden/make_golden.py [reference_root]
+Run once, in a container that has the reference checked out, with the path of that checkout:
+    python tests/golden/make_golden.py <reference_root>
 The fixtures (small ``.pt`` files: seeded inputs + the reference's outputs) are committed; the tests only read them.
 
 The reference's benchmark modules cannot be instantiated on CPU (their constructors call ``.cuda()`` and load
@@ -67,6 +67,32 @@ def main(ref_root: str) -> None:
     dets, keep = yolo.batched_nms(boxes, scores, labels)
     out["batched_nms"] = {"boxes": boxes, "scores": scores, "labels": labels, "iou_thr": 0.45, "dets": dets, "keep": keep}
 
+    # ---- YOLOv3 box decode: yolov3_bbox.py:12-23 (decode_bboxes) on the anchors of YOLOAnchorGenerator (:26-100), fed as
+    # YOLOV3BBox.forward feeds them (:209-222): permute/reshape, sigmoid on the xy slice, strides expanded per box.
+    # gen_single_level_base_anchors ends in .cuda(); on this CPU-only run that one method is made the identity.
+    g = gen(17)
+    sizes, strides = (2, 3, 5), (32, 16, 8)
+    maps = [torch.randn(1, 255, s, s, generator=g) for s in sizes]
+    cuda_saved = torch.Tensor.cuda
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    try:
+        agen = yolo.YOLOAnchorGenerator(strides=[32, 16, 8], base_sizes=[[(116, 90), (156, 198), (373, 326)],
+                                                                       [(30, 61), (62, 45), (59, 119)],
+                                                                       [(10, 13), (16, 30), (33, 23)]])
+    finally:
+        torch.Tensor.cuda = cuda_saved
+    anchors = torch.cat(agen([(s, s) for s in sizes], dtype=torch.float32, device=torch.device("cpu")))
+    preds, strs = [], []
+    for pred, stride in zip(maps, strides):
+        pred = pred.permute(0, 2, 3, 1).reshape(1, -1, 85).clone()
+        pred[..., :2].sigmoid_()
+        preds.append(pred.clone())
+        strs.append(torch.tensor(stride).expand(pred.size(1)))
+    flat = torch.cat(preds, dim=1)
+    out["yolo_decode"] = {"maps": maps, "sizes": sizes,
+                          "bboxes": yolo.decode_bboxes(anchors, flat[..., :4], torch.cat(strs).unsqueeze(-1)),
+                          "objectness": flat[..., 4].sigmoid(), "cls_scores": flat[..., 5:].sigmoid()}
+
     # ---- mask -> nonzero -> sort -> top-k: ssd_bbox.py:163-172 (filter_scores_and_topk) ----
     ssd = load_module(os.path.join(bench, "ssd", "ssd_bbox.py"), "ref_ssd_bbox")
     g = gen(13)
@@ -119,4 +145,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <reference_root>")
+    main(sys.argv[1])

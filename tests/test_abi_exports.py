@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
 def test_argument_errors_without_gpu():
     from functs_b200 import _lib
     lib = _lib.lib
-    assert lib.functs_b200_abi_version() == 1
+    assert lib.functs_b200_abi_version() == 2
     # invalid arguments are rejected on the host before any CUDA call
     rc = lib.functs_b200_rows_select_add_select_rev(None, None, 4, 4, 1, 1.0, None)
     assert rc == -1 and "null" in _lib.last_error()

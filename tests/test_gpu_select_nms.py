@@ -175,6 +175,41 @@ def test_batched_nms_bit_exact(fb, cuda_device, n, classes, offset, spread):
             assert bool((labels[gi, m:] == -1).all())
 
 
+def test_batched_nms_out_of_range_key_is_skipped_and_reported(fb, cuda_device):
+    """Keys come from the caller.  One whose box index lies beyond num_boxes (and an all-zero key, whose flat index is
+    0xFFFFFFFF) must not be dereferenced: the status word reports it and the other candidates give the oracle's answer."""
+    g = gen(4242)
+    num_boxes, classes, n = 500, 3, 200
+    boxes = random_boxes(num_boxes, g, 40.0)
+    scores = torch.rand(n, generator=g) * 0.5 + 0.5
+    flat = torch.randperm(num_boxes * classes, generator=g)[:n]
+    flat[17] = num_boxes * classes + 5          # box index == num_boxes + 1
+    flat[120] = (1 << 31) + 12345               # far outside
+    keys = make_keys(scores, flat).sort(descending=True).values
+    keys[n - 1] = 0                              # stale row: flat index 0xFFFFFFFF
+    fl = key_index(keys)
+    valid = (fl // classes) < num_boxes
+    assert int((~valid).sum()) == 3
+    s, bi, lab = key_scores(keys)[valid], (fl // classes)[valid], (fl % classes)[valid]
+    wd, wkeep = W.batched_nms(boxes[bi], s, lab, 0.45)
+    pos = torch.nonzero(valid)[:, 0][wkeep]      # positions in the full selected list
+    status = fb.ops.new_status(cuda_device)
+    dets, labels, flat_ids, keep, cnt = fb.ops.batched_nms(boxes[None].cuda(), classes, keys[None].cuda(),
+                                                           torch.tensor([n], dtype=torch.int32).cuda(), 0.45, True,
+                                                           status=status)
+    assert int(status.item()) == 4               # FB_STATUS_INDEX_RANGE
+    m = int(cnt[0])
+    assert m == pos.numel()
+    assert torch.equal(keep[0, :m].cpu(), pos)
+    assert torch.equal(flat_ids[0, :m].cpu(), fl[valid][wkeep])
+    assert torch.equal(dets[0, :m].cpu(), wd)
+    # a clean call leaves the status word alone
+    status.zero_()
+    fb.ops.batched_nms(boxes[None].cuda(), classes, keys[valid][None, :50].contiguous().cuda(),
+                       torch.tensor([50], dtype=torch.int32).cuda(), 0.45, True, status=status)
+    assert int(status.item()) == 0
+
+
 def test_batched_nms_golden_fixture(fb, cuda_device):
     """The fixture produced by the reference's own batched_nms (tests/golden/batched_nms.pt)."""
     import os

@@ -1,10 +1,12 @@
 """GPU parity for C3 (SSD-style softmax + decode, per-class mask / top-k / NMS) against the TorchScript CPU oracle.
-Floats within 1e-5 relative; the per-class integer stages bit-exact on the GPU's own floats; end-to-end identity
-against the oracle's floats reported per (image, class) with near-tie cases counted (see test_gpu_yolo.py)."""
+Floats within 1e-5 relative; the per-class integer stages bit-exact on the GPU's own floats; end to end against the
+oracle's own floats every (image, class) list is identical, or the first decision on which the two runs part is shown
+in fp64 to lie inside the last-ulp band (tests/tieband.py); anything else fails."""
 import pytest
 import torch
 
 from oracle import workloads as W
+from tests import tieband
 from tests.util import close
 
 pytestmark = pytest.mark.gpu
@@ -40,19 +42,49 @@ def run_case(fb, loc, conf, priors, thr=0.01, topk=200, iou=0.45):
         assert torch.equal(gi, wi) and torch.equal(gl, wl) and torch.equal(gd, wd)
         # against the oracle's own floats, class by class
         od, ol, oi = ores[i]
+        score64 = None
         for k in range(c):
             total += 1
             a, bb = gi[gl == k], oi[ol == k]
             if a.numel() == bb.numel() and torch.equal(a, bb):
                 exact += 1
-    print(f"(image, class) pairs identical to the oracle end to end: {exact}/{total}")
-    assert exact >= 0.9 * total
+                continue
+            if score64 is None:
+                score64 = conf[i].double().softmax(-1)
+            ga, gk, gb = class_stages(boxes_c[i], scores_c[i][:, k], thr, topk, iou)
+            ca, ck, cb = class_stages(obox[i], oscores[i][:, k], thr, topk, iou)
+            why = tieband.explain_or_fail(ga, ca, score64[:, k], thr, topk, gk, ck, gb, cb, None, iou)
+            assert why != "identical"
+            print(f"[tie-band] image {i} class {k}: {why}")
+    print(f"(image, class) lists identical to the oracle's own run: {exact}/{total}; the others were explained by the "
+          f"fp64 audit")
     return exact, total
+
+
+def class_stages(bboxes, scores_c, thr, topk, iou):
+    """The oracle's per-class stages (SSDPost.class_single) with the intermediate lists kept: selected prior ids in
+    sorted order, kept positions, selected boxes."""
+    import torchvision
+    mask = scores_c > thr
+    idx = torch.nonzero(mask)[:, 0]
+    s, order = scores_c[mask].sort(descending=True, stable=True)
+    k = min(topk, idx.numel())
+    s, idx = s[:k], idx[order[:k]]
+    bx = bboxes[idx]
+    keep = torchvision.ops.nms(bx, s, iou)
+    return idx, keep.sort().values, bx
 
 
 def test_ssd_config_shapes(fb):
     loc, conf = W.make_ssd_inputs(2)
     run_case(fb, loc, conf, W.ssd_priors())
+
+
+def test_ssd_full_batch_against_oracle(fb):
+    """B = 64 (5120 (image, class) lists) against the oracle's own run."""
+    loc, conf = W.make_ssd_inputs(64)
+    exact, total = run_case(fb, loc, conf, W.ssd_priors())
+    assert total == 64 * 80
 
 
 def test_ssd_ragged_small(fb):

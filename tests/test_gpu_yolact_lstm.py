@@ -15,11 +15,21 @@ def fb(cuda_device):
 
 
 def yolact_case(fb, proto, coef, boxes):
-    want_masks, want_logits = torch.jit.script(W.YolactMasks())(proto, coef, boxes)
     masks, logits = fb.ops.yolact_masks(proto.cuda(), coef.cuda(), boxes.cuda(), with_logits=True)
     masks_fast = fb.ops.yolact_masks(proto.cuda(), coef.cuda(), boxes.cuda())
     assert torch.equal(masks, masks_fast)  # the value-check variant and the product variant agree bit for bit
     masks, logits = masks.cpu(), logits.cpu().permute(0, 2, 3, 1)  # [B,H,W,N]
+    oracle = torch.jit.script(W.YolactMasks())
+    ndiff = 0
+    for s in range(0, proto.size(0), 16):  # the comparison runs in slices of 16 images to bound host memory
+        e = min(s + 16, proto.size(0))
+        ndiff += yolact_compare(oracle, proto[s:e], coef[s:e], boxes[s:e], masks[s:e], logits[s:e])
+    print(f"mask bytes differing from the oracle inside the 1e-5 boundary band: {ndiff} of {masks.numel()}")
+    return ndiff
+
+
+def yolact_compare(oracle, proto, coef, boxes, masks, logits):
+    want_masks, want_logits = oracle(proto, coef, boxes)
     # a dot product is accurate relative to the sum of the magnitudes of its terms
     mag = torch.einsum("bhwk,bnk->bhwn", proto.abs(), coef.abs())
     close(logits, want_logits, rtol=1e-5, scale=mag, what="mask logits")
@@ -29,12 +39,17 @@ def yolact_case(fb, proto, coef, boxes):
     if ndiff:
         l64 = torch.einsum("bhwk,bnk->bnhw", proto.double(), coef.double())
         assert bool((l64[diff].abs() < 1e-5).all()), "mask mismatch away from the threshold boundary"
-    print(f"mask bytes differing from the oracle inside the 1e-5 boundary band: {ndiff} of {masks.numel()}")
     return ndiff
 
 
 def test_yolact_config_shapes(fb):
     proto, coef, boxes = W.make_yolact_inputs(2)
+    yolact_case(fb, proto, coef, boxes)
+
+
+def test_yolact_full_batch_against_oracle(fb):
+    """B = 64 (the configured maximum): 122 M mask bytes against the oracle's own run."""
+    proto, coef, boxes = W.make_yolact_inputs(64)
     yolact_case(fb, proto, coef, boxes)
 
 
@@ -80,39 +95,37 @@ def test_yolact_full_batch_properties(fb):
 
 
 def lstm_case(fb, seq, batch, hidden, mode):
+    """Bar for fp32 values: 1e-5 relative.  h = o * tanh(c) lies in (-1, 1) and passes through zero, so a value is
+    measured against max(|want|, 1): 1 is the bound of the gate activations every h and c is formed from.  No absolute
+    term.  On top of that the device result must be as close to the fp64 evaluation of the same program as the fp32
+    CPU oracle itself is (factor 2), which is the stricter check when errors have compounded over many steps."""
     x, w_ih, w_hh, b_ih, b_hh = W.make_lstm_inputs(seq, batch, hidden)
     want_hs, want_cs = torch.jit.script(W.LSTMSeq(w_ih, w_hh, b_ih, b_hh))(x)
     mod = fb.workloads.LSTM(w_ih, w_hh, b_ih, b_hh)
     hs, cs = mod(x, mode=mode)
-    assert mod.kernels_last_call == (3 if (mode == 0 and (seq * batch) % 128 == 0) else 2)
-    # fp64 restatement bounds the oracle's own rounding
+    assert mod.kernels_last_call == fb.workloads.LSTM.expected_launches(seq, batch, hidden, mode)
     o64 = W.LSTMSeq(w_ih.double(), w_hh.double(), b_ih.double(), b_hh.double())
     hs64, cs64 = o64(x.double())
-    e_or = float((want_hs.double() - hs64).abs().max())
-    e_gpu = float((hs.cpu().double() - hs64).abs().max())
-    print(f"T={seq} B={batch} H={hidden} mode={mode}: max |h - h64| oracle {e_or:.2e}, gpu {e_gpu:.2e}")
-    close(hs.cpu(), want_hs, rtol=1e-5, atol=1e-5, what="hs")
-    close(cs.cpu(), want_cs, rtol=1e-5, atol=1e-5, what="cs")
+    for name, got, want, truth in (("hs", hs, want_hs, hs64), ("cs", cs, want_cs, cs64)):
+        e_or = float((want.double() - truth).abs().max())
+        e_gpu = float((got.cpu().double() - truth).abs().max())
+        print(f"T={seq} B={batch} H={hidden} mode={mode} {name}: max |v - v64| oracle {e_or:.2e}, gpu {e_gpu:.2e}")
+        assert e_gpu <= 2.0 * e_or + 1e-7, (name, e_gpu, e_or)
+        close(got.cpu(), want, rtol=1e-5, atol=0.0, scale=1.0, what=name)
 
 
-def test_lstm_tensor_core_projection_probe(fb):
-    """Runs first among the LSTM tests: checks the tcgen05 projection against the CUDA-core one on a small shape."""
-    from functs_b200._lib import lib
+def test_lstm_tensor_core_projection_matches_cuda_cores(fb):
+    """Runs first among the LSTM tests: the tcgen05 (3xTF32) input projection against the fp32 CUDA-core projection on
+    a small shape.  Agreement to 1e-5 is the evidence that the shared-memory descriptor strides describe the pre-tiled
+    operand layout."""
     x, w_ih, w_hh, b_ih, b_hh = W.make_lstm_inputs(2, 64, 512)
     mod = fb.workloads.LSTM(w_ih, w_hh, b_ih, b_hh)
     ref_hs, _ = mod(x, mode=1)
     ref_hs = ref_hs.clone()
-    errs = {}
-    for swap in (0, 1):
-        assert lib.functs_b200_debug_set(b"lstm_tc_swap_lbo_sbo", swap) == 0
-        try:
-            hs, _ = mod(x, mode=0)
-            errs[swap] = float((hs - ref_hs).abs().max())
-        except fb.FunctsB200Error as exc:
-            errs[swap] = repr(exc)
-    lib.functs_b200_debug_set(b"lstm_tc_swap_lbo_sbo", 0)
-    print(f"tcgen05 projection vs CUDA-core projection, max |dh|: normal strides {errs[0]}, swapped strides {errs[1]}")
-    assert isinstance(errs[0], float) and errs[0] < 1e-5, errs
+    hs, _ = mod(x, mode=0)
+    err = float((hs - ref_hs).abs().max())
+    print(f"tcgen05 projection vs CUDA-core projection, max |dh|: {err:.3e}")
+    assert err < 1e-5
 
 
 @pytest.mark.parametrize("mode", [1, 0])

@@ -69,3 +69,23 @@ def test_scripted_workloads_run_and_edge_cases():
     assert not torch.equal(a[0][0], a[0][1])
     c = W.make_yolo_inputs(1, sizes=(2, 4, 8), first=1)
     assert torch.equal(c[0][0], a[0][1])
+
+
+def test_yolo_decode_matches_reference():
+    """decode_bboxes on the reference's anchor grid gives the same boxes through another operation order (anchor centre
+    + (sigmoid - 0.5) * stride instead of (sigmoid + cell) * stride): 1e-5 relative to the box's own magnitude (centre
+    plus extent; a corner is a difference of the two).  Objectness and class scores are the same sigmoid, evaluated in place
+    on a strided slice here and out of place there (ATen picks different vector kernels): 1e-6 relative."""
+    f = load("yolo_decode")
+    o = W.YOLOV3Post(sizes=tuple(f["sizes"]))
+    bboxes, obj, cls = o.decode(f["maps"])
+    want = f["bboxes"]
+    centre = (want[..., 0:2] + want[..., 2:4]).abs() * 0.5
+    extent = (want[..., 2:4] - want[..., 0:2]).abs()
+    scale = torch.cat([centre + extent, centre + extent], dim=-1)
+    err = (bboxes.double() - want.double()).abs()
+    assert bool((err <= 1e-5 * scale.double()).all()), float((err / scale.double()).max())
+    assert torch.allclose(obj, f["objectness"], rtol=1e-6, atol=0.0)
+    assert torch.allclose(cls, f["cls_scores"], rtol=1e-6, atol=0.0)
+    sb, sobj, scls = torch.jit.script(o).decode(f["maps"])
+    assert torch.equal(sb, bboxes) and torch.equal(sobj, obj) and torch.equal(scls, cls)
