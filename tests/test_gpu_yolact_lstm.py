@@ -97,8 +97,10 @@ def test_yolact_full_batch_properties(fb):
 def lstm_case(fb, seq, batch, hidden, mode):
     """Bar for fp32 values: 1e-5 relative.  h = o * tanh(c) lies in (-1, 1) and passes through zero, so a value is
     measured against max(|want|, 1): 1 is the bound of the gate activations every h and c is formed from.  No absolute
-    term.  On top of that the device result must be as close to the fp64 evaluation of the same program as the fp32
-    CPU oracle itself is (factor 2), which is the stricter check when errors have compounded over many steps."""
+    term.  On top of that the device result is compared with the fp64 evaluation of the same program: the fp32 CUDA-core
+    path (mode 1) must be as close to it as the fp32 CPU oracle itself is (factor 2); the tensor-core path (mode 0)
+    splits every fp32 operand into two TF32 numbers, which carry 22 of the 24 mantissa bits, so its products are about
+    four times less accurate than fp32 products: factor 10, and always below 1e-5."""
     x, w_ih, w_hh, b_ih, b_hh = W.make_lstm_inputs(seq, batch, hidden)
     want_hs, want_cs = torch.jit.script(W.LSTMSeq(w_ih, w_hh, b_ih, b_hh))(x)
     mod = fb.workloads.LSTM(w_ih, w_hh, b_ih, b_hh)
@@ -110,7 +112,7 @@ def lstm_case(fb, seq, batch, hidden, mode):
         e_or = float((want.double() - truth).abs().max())
         e_gpu = float((got.cpu().double() - truth).abs().max())
         print(f"T={seq} B={batch} H={hidden} mode={mode} {name}: max |v - v64| oracle {e_or:.2e}, gpu {e_gpu:.2e}")
-        assert e_gpu <= 2.0 * e_or + 1e-7, (name, e_gpu, e_or)
+        assert e_gpu <= (2.0 if mode == 1 else 10.0) * e_or + 1e-7 and e_gpu < 1e-5, (name, e_gpu, e_or)
         close(got.cpu(), want, rtol=1e-5, atol=0.0, scale=1.0, what=name)
 
 
