@@ -61,6 +61,18 @@ static int g_yolo_decode(const void* const* in, const int64_t* ia, const double*
                                    static_cast<uint64_t*>(out[1]), static_cast<int32_t*>(out[2]), ia[4], nullptr, status, stream);
 }
 
+static int g_yolo_post(const void* const* in, const int64_t* ia, const double* fa, void* const* out, void* scratch,
+                       int32_t* status, void* stream) {
+    // in: map0, map1, map2; ia: batch, s0, s1, s2, topk, capacity; fa: score_thr, iou_thr;
+    // out: boxes, obj (may be null), cls (may be null), dets, labels, flat_ids, counts
+    return functs_b200_yolo_postprocess_dense(
+        static_cast<const float*>(in[0]), static_cast<const float*>(in[1]), static_cast<const float*>(in[2]),
+        static_cast<int32_t>(ia[0]), static_cast<int32_t>(ia[1]), static_cast<int32_t>(ia[2]), static_cast<int32_t>(ia[3]),
+        static_cast<float>(fa[0]), static_cast<int32_t>(ia[4]), static_cast<float>(fa[1]), ia[5],
+        static_cast<float*>(out[0]), static_cast<float*>(out[1]), static_cast<float*>(out[2]), static_cast<float*>(out[3]),
+        static_cast<int64_t*>(out[4]), static_cast<int64_t*>(out[5]), static_cast<int32_t*>(out[6]), status, scratch, stream);
+}
+
 static int g_select_topk(const void* const* in, const int64_t* ia, const double*, void* const* out, void*, int32_t*,
                          void* stream) {
     // in: keys, counts; ia: capacity, groups, topk; out: sel_keys, sel_counts
@@ -104,11 +116,11 @@ static int g_ssd_class_nms(const void* const* in, const int64_t* ia, const doubl
 
 static int g_yolact(const void* const* in, const int64_t* ia, const double* fa, void* const* out, void*, int32_t*,
                     void* stream) {
-    // in: proto, coef, boxes; ia: batch, height, width, num_det; fa: thr; out: masks
+    // in: proto, coef, boxes; ia: batch, height, width, num_det; fa: thr; out: masks, logits [batch, N, H, W] (may be null)
     return functs_b200_yolact_masks(static_cast<const float*>(in[0]), static_cast<const float*>(in[1]),
                                     static_cast<const float*>(in[2]), static_cast<int32_t>(ia[0]),
                                     static_cast<int32_t>(ia[1]), static_cast<int32_t>(ia[2]), static_cast<int32_t>(ia[3]),
-                                    static_cast<float>(fa[0]), static_cast<uint8_t*>(out[0]), nullptr, stream);
+                                    static_cast<float>(fa[0]), static_cast<uint8_t*>(out[0]), static_cast<float*>(out[1]), stream);
 }
 
 static int g_lstm(const void* const* in, const int64_t* ia, const double*, void* const* out, void* scratch,
@@ -126,6 +138,7 @@ static const GroupEntry kGroups[] = {
     {"yolov3{permute->reshape->slice/sigmoid/slice_rev[xy,obj,cls]->add(grid)->mul(stride)->exp*anchor->corners->"
      "mul(obj,cls)->gt(thr)->nonzero}",
      g_yolo_decode},
+    {"yolov3{decode->loop[b<B]{mul(obj,cls)->gt(thr)->nonzero->sort(desc,stable)->slice[:k]->class-offset nms}}", g_yolo_post},
     {"masked{sort(desc,stable)->slice[:k]}", g_select_topk},
     {"nms{max->mul(label)->add->torchvision::nms->index}", g_batched_nms},
     {"ssd{softmax(-1)->slice[:-1]->delta2bbox->slice_rev[0::2,1::2](clamp)}", g_ssd_softmax_decode},

@@ -7,6 +7,8 @@
 // box, and the hits of a warp are staged in shared memory and appended to the image's candidate list.
 #include <cstddef>
 
+#include <atomic>
+
 #include "select_nms.cuh"
 
 namespace fb {
@@ -925,8 +927,8 @@ yolo_decode_staged_kernel(const YoloParams P) {
 }
 
 // Development switch (functs_b200_debug_set "yolo_prune"): 0 keeps every candidate above the score threshold.
-static int g_yolo_prune = 1;
-void yolo_set_prune(int on) { g_yolo_prune = on ? 1 : 0; }
+static std::atomic<int> g_yolo_prune{1};
+void yolo_set_prune(int on) { g_yolo_prune.store(on ? 1 : 0, std::memory_order_relaxed); }
 
 static const float kAnchors[3][3][2] = {{{116, 90}, {156, 198}, {373, 326}},
                                         {{30, 61}, {62, 45}, {59, 119}},
@@ -1097,6 +1099,16 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
                                  int32_t s1, int32_t s2, float score_thr, int32_t topk, float iou_thr,
                                  int64_t capacity, float* boxes, float* dets, int64_t* labels, int64_t* flat_ids,
                                  int32_t* out_counts, int32_t* status, void* scratch, void* stream) {
+    return functs_b200_yolo_postprocess_dense(map0, map1, map2, batch, s0, s1, s2, score_thr, topk, iou_thr, capacity,
+                                              boxes, nullptr, nullptr, dets, labels, flat_ids, out_counts, status,
+                                              scratch, stream);
+}
+
+int functs_b200_yolo_postprocess_dense(const float* map0, const float* map1, const float* map2, int32_t batch,
+                                       int32_t s0, int32_t s1, int32_t s2, float score_thr, int32_t topk,
+                                       float iou_thr, int64_t capacity, float* boxes, float* obj_out, float* cls_out,
+                                       float* dets, int64_t* labels, int64_t* flat_ids, int32_t* out_counts,
+                                       int32_t* status, void* scratch, void* stream) {
     using namespace fb;
     FB_REQUIRE(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 255) == 0,
                "yolo_postprocess: scratch must be non-null and 256-byte aligned");
@@ -1113,8 +1125,10 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
     FB_TRY(check_cuda(cudaMemsetAsync(base, 0, static_cast<size_t>(L.zero_bytes), st), "memset yolo counters"));
     record_stage_event(0, st);
     // only the topk best candidates of an image are used below: let the decode kernel drop hopeless ones early
-    FB_TRY(launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, nullptr, nullptr, keys, counts,
-                              capacity, hist, 0, g_yolo_prune ? topk : 0, reinterpret_cast<int32_t*>(base + L.floor_off), status, st));
+    // (with dense objectness / class-score outputs every score is formed anyway: the thread-per-box kernel, no pruning)
+    FB_TRY(launch_yolo_decode(map0, map1, map2, batch, s0, s1, s2, score_thr, boxes, obj_out, cls_out, keys, counts,
+                              capacity, hist, 0, g_yolo_prune.load(std::memory_order_relaxed) ? topk : 0,
+                              reinterpret_cast<int32_t*>(base + L.floor_off), status, st));
     record_stage_event(1, st);
     // the CTA that finishes an image's selection also prepares the image's NMS input in the NMS work area
     FB_TRY(launch_select_binned(keys, counts, capacity, hist, score_thr, batch, topk, sel_keys, sel_counts,

@@ -13,8 +13,11 @@
 #pragma once
 
 #include <torch/csrc/jit/ir/ir.h>
+#include <torch/csrc/jit/runtime/operator.h>
 
 #include <memory>
+#include <string>
+#include <vector>
 
 namespace functs_b200 {
 
@@ -32,5 +35,35 @@ void FaitPipeline(const std::shared_ptr<torch::jit::Graph>& graph);
 void InferShapes(const std::shared_ptr<torch::jit::Graph>& graph, const std::vector<c10::TypePtr>& type_hint);
 // number of tssa::ParallelFunctor nodes in the graph (all blocks): the unit the launch-count metric counts
 int64_t CountParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
+// the normalisation every graph goes through before regions are matched: TensorSSA conversion, marker removal, CSE,
+// constant propagation, dead-code elimination (pattern programs and user programs alike)
+void PrepareForMatching(const std::shared_ptr<torch::jit::Graph>& graph);
+
+// ---- precompiled regions (regions.cpp) --------------------------------------------------------------------------------
+// Canonical description of the whole top level of `graph` (a pattern program after PrepareForMatching).  fwild / iwild:
+// slots of the float / int constant lists that print as "?" instead of by value.
+struct RegionDescription {
+    std::string signature;
+    int64_t num_nodes = 0, num_inputs = 0, num_outputs = 0, num_tensors = 0;
+    std::vector<double> fconsts;
+    std::vector<int64_t> iconsts;
+};
+RegionDescription DescribeRegion(const std::shared_ptr<torch::jit::Graph>& graph, const std::vector<int64_t>& fwild,
+                                 const std::vector<int64_t>& iwild);
+// `graph`: a pattern program after PrepareForMatching; `name`: the kernel adapter that runs it; froles / iroles: (attribute
+// name, constant slot) of the scalar constants a matching program may choose freely
+void RegisterRegionPattern(const std::string& name, const std::shared_ptr<torch::jit::Graph>& graph,
+                           const std::vector<std::pair<std::string, int64_t>>& froles,
+                           const std::vector<std::pair<std::string, int64_t>>& iroles);
+int64_t RegionPatternCount();
+// windows of top-level nodes whose canonical signature equals a registered pattern -> one tssa::ParallelFunctor each
+bool MatchPrecompiledRegions(const std::shared_ptr<torch::jit::Graph>& graph);
+// name of the kernel adapter a functor node is bound to ("" = none: its subgraph is interpreted)
+std::string RegionSignature(const torch::jit::Node* functor);
+bool isRegionFunctor(const torch::jit::Node* node);
+torch::jit::Operation createRegionOperation(const torch::jit::Node* node);
+// functor runs that went through the subgraph interpreter instead of a precompiled kernel, in this process
+void countInterpretedRun();
+int64_t InterpretedFunctorRuns();
 
 }  // namespace functs_b200

@@ -53,6 +53,40 @@ PYBIND11_MODULE(_C, m) {
               functs_b200::InferShapes(g, type_hint);
           },
           py::arg("graph"), py::arg("type_hint") = std::vector<c10::TypePtr>(), py::arg("refined_types") = py::none());
+    // precompiled regions: pattern programs are registered from Python (functs_b200/patterns.py)
+    m.def("_jit_pass_prepare_for_matching", [](std::shared_ptr<Graph> g) { functs_b200::PrepareForMatching(g); });
+    m.def("_jit_pass_match_precompiled_regions", [](std::shared_ptr<Graph> g) { return functs_b200::MatchPrecompiledRegions(g); });
+    m.def("_describe_region",
+          [](std::shared_ptr<Graph> g, std::vector<int64_t> fwild, std::vector<int64_t> iwild) {
+              auto d = functs_b200::DescribeRegion(g, fwild, iwild);
+              py::dict out;
+              out["signature"] = d.signature;
+              out["num_nodes"] = d.num_nodes;
+              out["num_inputs"] = d.num_inputs;
+              out["num_outputs"] = d.num_outputs;
+              out["num_tensors"] = d.num_tensors;
+              out["fconsts"] = d.fconsts;
+              out["iconsts"] = d.iconsts;
+              return out;
+          },
+          py::arg("graph"), py::arg("fwild") = std::vector<int64_t>(), py::arg("iwild") = std::vector<int64_t>());
+    m.def("_register_region_pattern",
+          [](const std::string& name, std::shared_ptr<Graph> g, std::vector<std::pair<std::string, int64_t>> froles,
+             std::vector<std::pair<std::string, int64_t>> iroles) { functs_b200::RegisterRegionPattern(name, g, froles, iroles); });
+    m.def("_region_pattern_count", []() { return functs_b200::RegionPatternCount(); });
+    m.def("_interpreted_functor_runs", []() { return functs_b200::InterpretedFunctorRuns(); });
+    m.def("_functor_regions", [](std::shared_ptr<Graph> g) {
+        // adapter name of every tssa::ParallelFunctor node ("" = interpreted), in graph order
+        std::vector<std::string> out;
+        std::function<void(torch::jit::Block*)> visit = [&](torch::jit::Block* b) {
+            for (torch::jit::Node* n : b->nodes()) {
+                if (n->kind() == c10::Symbol::fromQualString("tssa::ParallelFunctor")) out.push_back(functs_b200::RegionSignature(n));
+                for (torch::jit::Block* nb : n->blocks()) visit(nb);
+            }
+        };
+        visit(g->block());
+        return out;
+    });
     m.def("_count_parallel_functors", [](std::shared_ptr<Graph> g) { return functs_b200::CountParallelFunctors(g); });
     m.def("_jit_pass_freeze", [](torch::jit::Module& module) { return torch::jit::freeze_module(module); });
     m.def("_jit_pass_clone", [](torch::jit::Module& module) { return module.clone(); });

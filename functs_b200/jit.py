@@ -64,8 +64,20 @@ def build(fn, example_inputs=(), add_clone: bool = False):
         hints.append(torch._C.TensorType.create_from_tensor(v) if isinstance(v, torch.Tensor) else None)
     if not inspect.isfunction(fn):
         hints = [None] + hints  # self
+    from . import patterns
+    patterns.register_all()  # the programs that the precompiled kernel sequences stand for (once per process)
     fait_pipeline(g, hints)
     return jit_fn
+
+
+def functor_regions(g: torch.Graph):
+    """Kernel adapter bound to each tssa::ParallelFunctor node of `g`, in graph order ("" = its subgraph is interpreted)."""
+    return list(_C._functor_regions(g))
+
+
+def interpreted_functor_runs() -> int:
+    """How many functor executions of this process went through the subgraph interpreter instead of a precompiled kernel."""
+    return int(_C._interpreted_functor_runs())
 
 
 def count_groups(g: torch.Graph) -> int:

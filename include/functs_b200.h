@@ -155,6 +155,16 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
                                  int64_t capacity, float* boxes, float* dets, int64_t* labels, int64_t* flat_ids,
                                  int32_t* out_counts, int32_t* status, void* scratch, void* stream);
 
+/* The same with the dense per-box outputs of the decode group kept: obj_out [batch, N] and cls_out [batch, N, 80]
+ * (sigmoid of the objectness / class logits), as a program that returns them needs (the slices flat[..., 4] and
+ * flat[..., 5:] of yolov3_bbox.py:217-219).  Every score is formed in that case, so the decode launch is the
+ * thread-per-box kernel and nothing is pruned; still 3 launches.  NULL for both = functs_b200_yolo_postprocess. */
+int functs_b200_yolo_postprocess_dense(const float* map0, const float* map1, const float* map2, int32_t batch,
+                                       int32_t s0, int32_t s1, int32_t s2, float score_thr, int32_t topk,
+                                       float iou_thr, int64_t capacity, float* boxes, float* obj_out, float* cls_out,
+                                       float* dets, int64_t* labels, int64_t* flat_ids, int32_t* out_counts,
+                                       int32_t* status, void* scratch, void* stream);
+
 /* ---- C3: SSD-style post-process ----------------------------------------------------------- */
 /* Follows functs/benchmark/ai_model/ssd/ssd_bbox.py:121-154 (decode with the strided clamp), :268 (softmax, last
  * column = background dropped) and :163-172 + :212 inside a loop over classes that is mapped onto CTAs. */
