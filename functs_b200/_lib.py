@@ -55,7 +55,7 @@ SIGNATURES = {
     "functs_b200_yolo_postprocess": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, c_float,
                                                c_int64, P, P, P, P, P, P, P, P]),
     "functs_b200_yolo_postprocess_dense": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, c_float,
-                                                     c_int64, P, P, P, P, P, P, P, P, P, P]),
+                                                     c_int64, P, P, P, P, P, P, P, P, P, P, P]),
     "functs_b200_ssd_softmax_decode": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_float, P, P, P]),
     "functs_b200_ssd_class_nms": (c_int32, [P, P, c_int32, c_int32, c_int32, c_float, c_int32, c_float, P, P, P, P]),
     "functs_b200_lstm_scratch_bytes": (c_int64, [c_int32, c_int32, c_int32, c_int32]),

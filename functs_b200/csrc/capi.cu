@@ -64,13 +64,14 @@ static int g_yolo_decode(const void* const* in, const int64_t* ia, const double*
 static int g_yolo_post(const void* const* in, const int64_t* ia, const double* fa, void* const* out, void* scratch,
                        int32_t* status, void* stream) {
     // in: map0, map1, map2; ia: batch, s0, s1, s2, topk, capacity; fa: score_thr, iou_thr;
-    // out: boxes, obj (may be null), cls (may be null), dets, labels, flat_ids, counts
+    // out: boxes, obj (may be null), cls (may be null), dets, labels, flat_ids, counts, records (may be null)
     return functs_b200_yolo_postprocess_dense(
         static_cast<const float*>(in[0]), static_cast<const float*>(in[1]), static_cast<const float*>(in[2]),
         static_cast<int32_t>(ia[0]), static_cast<int32_t>(ia[1]), static_cast<int32_t>(ia[2]), static_cast<int32_t>(ia[3]),
         static_cast<float>(fa[0]), static_cast<int32_t>(ia[4]), static_cast<float>(fa[1]), ia[5],
         static_cast<float*>(out[0]), static_cast<float*>(out[1]), static_cast<float*>(out[2]), static_cast<float*>(out[3]),
-        static_cast<int64_t*>(out[4]), static_cast<int64_t*>(out[5]), static_cast<int32_t*>(out[6]), status, scratch, stream);
+        static_cast<int64_t*>(out[4]), static_cast<int64_t*>(out[5]), static_cast<int32_t*>(out[6]),
+        static_cast<int32_t*>(out[7]), status, scratch, stream);
 }
 
 static int g_select_topk(const void* const* in, const int64_t* ia, const double*, void* const* out, void*, int32_t*,

@@ -62,6 +62,53 @@ access_kernel(const T* __restrict__ src, T* __restrict__ out, const functs_b200_
     }
 }
 
+// The same gather with 32-bit index arithmetic (every extent, stride and offset below 2^31): a 64-bit division costs
+// about ten times a 32-bit one, and a gather of rank r does r of them (plus the modulo) per element.  Dimensions are
+// merged and the innermost run is widened to 16-byte elements on the host (simplify_access), so that a contiguous
+// region moves as 128-bit loads and stores and the divisions are paid once per 16 bytes.
+struct AccessDesc32 {
+    int rank;
+    unsigned shape[8];
+    int stride[8];
+    unsigned mod[8];  // 0 = none
+    int offset;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+access_kernel32(const T* __restrict__ src, T* __restrict__ out, const AccessDesc32 d, unsigned numel) {
+    const unsigned stride = gridDim.x * blockDim.x;
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < numel; e += stride) {
+        unsigned rem = e;
+        int off = d.offset;
+#pragma unroll
+        for (int k = 7; k >= 0; --k) {
+            if (k < d.rank) {
+                const unsigned sz = d.shape[k];
+                unsigned ax = rem % sz;
+                rem /= sz;
+                if (d.mod[k] > 0u) ax %= d.mod[k];
+                off += static_cast<int>(ax) * d.stride[k];
+            }
+        }
+        out[e] = src[off];
+    }
+}
+
+// 16-byte elements of the region form of the Assign family: out = self except where dd = (e / inner) % D lies in the
+// region (inner counted in 16-byte units).
+__global__ void __launch_bounds__(256)
+assign_region_kernel_v16(const uint4* __restrict__ self, const uint4* __restrict__ src, uint4* __restrict__ out,
+                         unsigned numel, unsigned D, unsigned inner, unsigned start, unsigned end, unsigned step, unsigned L) {
+    const unsigned gstride = gridDim.x * blockDim.x;
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < numel; e += gstride) {
+        const unsigned od = e / inner, in = e - od * inner;
+        const unsigned o = od / D, dd = od - o * D;
+        const bool set = dd >= start && dd < end && ((dd - start) % step) == 0u;
+        out[e] = set ? __ldg(src + (o * L + (dd - start) / step) * inner + in) : __ldg(self + e);
+    }
+}
+
 // ---- select_rev / slice_rev over the (outer, D, inner) view of self ---------------------------------------
 // region: start <= d < end and (d - start) % step == 0; src is contiguous [outer, L, inner] with
 // L = ceil((end - start) / step) (select_rev: start = index, end = index + 1, step = 1, L = 1).
@@ -124,6 +171,56 @@ static inline unsigned grid_for(int64_t numel, int threads) {
     if (need > cap) need = cap;
     if (need < 1) need = 1;
     return static_cast<unsigned>(need);
+}
+
+// Merges adjacent dimensions that the source walks contiguously (stride[k] == stride[k + 1] * shape[k + 1], no modulo) and
+// drops extents of 1.  Returns the simplified description (same element order of the output).
+static functs_b200_access_desc merge_dims(const functs_b200_access_desc& in) {
+    functs_b200_access_desc d{};
+    d.src_offset = in.src_offset;
+    int r = 0;
+    for (int k = 0; k < in.rank; ++k) {
+        if (in.out_shape[k] == 1) continue;
+        if (r > 0 && in.src_mod[k] == 0 && d.src_mod[r - 1] == 0 && d.src_stride[r - 1] == in.src_stride[k] * in.out_shape[k]) {
+            d.out_shape[r - 1] *= in.out_shape[k];
+            d.src_stride[r - 1] = in.src_stride[k];
+        } else {
+            d.out_shape[r] = in.out_shape[k];
+            d.src_stride[r] = in.src_stride[k];
+            d.src_mod[r] = in.src_mod[k];
+            ++r;
+        }
+    }
+    d.rank = r;
+    return d;
+}
+
+// If the innermost output dimension reads a contiguous, 16-byte aligned run, re-expresses the gather in 16-byte
+// elements.  Returns the new element size (16) or the old one.
+static int widen_to_16(functs_b200_access_desc& d, int elem_size, const void* src, const void* out) {
+    if (d.rank == 0 || elem_size >= 16) return elem_size;
+    const int v = 16 / elem_size;
+    const int last = d.rank - 1;
+    if (d.src_stride[last] != 1 || d.src_mod[last] != 0 || d.out_shape[last] % v != 0 || d.src_offset % v != 0) return elem_size;
+    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) & 15) != 0) return elem_size;
+    for (int k = 0; k < last; ++k) {
+        if (d.src_stride[k] % v != 0) return elem_size;
+    }
+    d.out_shape[last] /= v;
+    d.src_offset /= v;
+    for (int k = 0; k < last; ++k) d.src_stride[k] /= v;
+    return 16;
+}
+
+static bool fits_32(const functs_b200_access_desc& d, int64_t numel) {
+    if (numel >= (1ll << 31)) return false;
+    int64_t reach = d.src_offset < 0 ? -d.src_offset : d.src_offset;
+    for (int k = 0; k < d.rank; ++k) {
+        const int64_t st = d.src_stride[k] < 0 ? -d.src_stride[k] : d.src_stride[k];
+        if (d.out_shape[k] >= (1ll << 31) || st >= (1ll << 31) || d.src_mod[k] >= (1ll << 31)) return false;
+        reach += st * (d.out_shape[k] - 1);
+    }
+    return reach < (1ll << 31);
 }
 
 template <typename F>
@@ -202,11 +299,40 @@ int functs_b200_access(const void* src, void* out, const functs_b200_access_desc
         numel *= desc->out_shape[k];
     }
     if (numel == 0) return FB_OK;
+    FB_REQUIRE(elem_size == 1 || elem_size == 2 || elem_size == 4 || elem_size == 8, "element size %d is not one of 1, 2, 4, 8",
+               elem_size);
     cudaStream_t st = as_stream(stream);
-    const functs_b200_access_desc d = *desc;
+    functs_b200_access_desc d = merge_dims(*desc);
+    const int width = widen_to_16(d, elem_size, src, out);
+    const int64_t n = numel / (width / elem_size);
+    if (fits_32(d, n)) {
+        AccessDesc32 q{};
+        q.rank = d.rank;
+        q.offset = static_cast<int>(d.src_offset);
+        for (int k = 0; k < d.rank; ++k) {
+            q.shape[k] = static_cast<unsigned>(d.out_shape[k]);
+            q.stride[k] = static_cast<int>(d.src_stride[k]);
+            q.mod[k] = static_cast<unsigned>(d.src_mod[k]);
+        }
+        const unsigned grid = grid_for(n, 256);
+        if (width == 16) {
+            access_kernel32<uint4><<<grid, 256, 0, st>>>(static_cast<const uint4*>(src), static_cast<uint4*>(out), q,
+                                                         static_cast<unsigned>(n));
+        } else {
+            int rc = dispatch_elem(elem_size, [&](auto* tag) {
+                using T = typename std::remove_pointer<decltype(tag)>::type;
+                access_kernel32<T><<<grid, 256, 0, st>>>(static_cast<const T*>(src), static_cast<T*>(out), q, static_cast<unsigned>(n));
+                return FB_OK;
+            });
+            FB_TRY(rc);
+        }
+        count_launch();
+        return check_launch("access_kernel32");
+    }
+    const functs_b200_access_desc d64 = *desc;
     int rc = dispatch_elem(elem_size, [&](auto* tag) {
         using T = typename std::remove_pointer<decltype(tag)>::type;
-        access_kernel<T><<<grid_for(numel, 256), 256, 0, st>>>(static_cast<const T*>(src), static_cast<T*>(out), d, numel);
+        access_kernel<T><<<grid_for(numel, 256), 256, 0, st>>>(static_cast<const T*>(src), static_cast<T*>(out), d64, numel);
         return FB_OK;
     });
     FB_TRY(rc);
@@ -233,6 +359,21 @@ static int assign_region(const void* self, const void* src, void* out, const int
     if (numel == 0) return FB_OK;
     FB_REQUIRE(src != nullptr || L == 0, "%s: null src", what);
     cudaStream_t st = as_stream(stream);
+    // 16-byte elements when the inner run allows it (and everything indexes in 32 bits)
+    if (elem_size == 1 || elem_size == 2 || elem_size == 4 || elem_size == 8) {
+        const int v = 16 / elem_size;
+        const bool aligned = ((reinterpret_cast<uintptr_t>(self) | reinterpret_cast<uintptr_t>(out) |
+                               reinterpret_cast<uintptr_t>(src)) & 15) == 0;
+        if (aligned && inner % v == 0 && numel / v < (1ll << 31) && D < (1ll << 31) && step < (1ll << 31)) {
+            const unsigned n16 = static_cast<unsigned>(numel / v);
+            assign_region_kernel_v16<<<grid_for(n16, 256), 256, 0, st>>>(
+                static_cast<const uint4*>(self), static_cast<const uint4*>(src), static_cast<uint4*>(out), n16,
+                static_cast<unsigned>(D), static_cast<unsigned>(inner / v), static_cast<unsigned>(start),
+                static_cast<unsigned>(end), static_cast<unsigned>(step), static_cast<unsigned>(L));
+            count_launch();
+            return check_launch(what);
+        }
+    }
     int rc = dispatch_elem(elem_size, [&](auto* tag) {
         using T = typename std::remove_pointer<decltype(tag)>::type;
         assign_region_kernel<T><<<grid_for(numel, 256), 256, 0, st>>>(static_cast<const T*>(self), static_cast<const T*>(src),

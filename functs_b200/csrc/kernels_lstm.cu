@@ -19,6 +19,10 @@ int launch_lstm_input_proj_tc(const float* x, const float* w_ih, const float* b_
                               int H, float* pre, void* tc_scratch, int32_t* status, cudaStream_t st);  // kernels_lstm_tc.cu
 int64_t lstm_tc_scratch_bytes(int M, int K, int H);
 bool lstm_tc_supported(int M, int K, int H);
+bool lstm_rtc_supported(int B, int H);
+int64_t lstm_rtc_scratch_bytes(int H);
+int launch_lstm_recurrent_tc(const float* pre, const float* w_hh, int T, int B, int H, float* hs, float* cs, void* h_tiles,
+                             unsigned int* step_counter, int32_t* status, cudaStream_t st);
 
 // ---- fp32 CUDA-core GEMM with bias (check path for launch 1) ------------------------------------------------
 constexpr int kGemmBM = 64, kGemmBN = 64, kGemmBK = 16;
@@ -221,6 +225,9 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
 
 static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
+// what mode 0 means: the combination measured fastest at the configured shape (T = 64, B = 64, H = 512)
+constexpr int kLstmDefaultMode = 3;
+
 }  // namespace fb
 
 namespace fb {
@@ -235,10 +242,12 @@ int64_t functs_b200_lstm_scratch_bytes(int32_t seq_len, int32_t batch, int32_t i
     int64_t total = 256;                                             // step counter
     total += fb::align_up(M * 4 * hidden * 4, 256);                  // pre-activations from the input projection
     total += fb::align_up(fb::lstm_tc_scratch_bytes(static_cast<int>(M), input, hidden), 256);
+    total += fb::align_up(fb::lstm_rtc_scratch_bytes(hidden), 256);  // h tiles of the tensor-core recurrence
     return total;
 }
 
-// mode: 0 = default (tensor-core projection when the shape allows it), 1 = force the fp32 CUDA-core projection
+// mode: 0 = default; 1 = fp32 CUDA cores for both GEMMs; 2 = tensor cores for both (where the shapes allow it);
+//       3 = tensor-core projection + CUDA-core recurrence
 int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
                                   const float* b_hh, int32_t seq_len, int32_t batch, int32_t input, int32_t hidden,
                                   float* hs, float* cs, int32_t* status, void* scratch, void* stream, int32_t mode) {
@@ -254,10 +263,13 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
     unsigned int* counter = reinterpret_cast<unsigned int*>(base);
     float* pre = reinterpret_cast<float*>(base + 256);
     void* tc_scratch = base + 256 + align_up(static_cast<int64_t>(M) * 4 * hidden * 4, 256);
+    void* rtc_scratch = static_cast<unsigned char*>(tc_scratch) + align_up(lstm_tc_scratch_bytes(M, input, hidden), 256);
+    FB_REQUIRE(mode >= 0 && mode <= 3, "lstm_forward: mode %d unknown", mode);
+    if (mode == 0) mode = kLstmDefaultMode;
     FB_TRY(check_cuda(cudaMemsetAsync(counter, 0, 256, st), "memset step counter"));
 
     record_stage_event(0, st);
-    if (mode == 0 && lstm_tc_supported(M, input, hidden)) {
+    if (mode != 1 && lstm_tc_supported(M, input, hidden)) {
         FB_TRY(launch_lstm_input_proj_tc(x, w_ih, b_ih, b_hh, M, input, hidden, pre, tc_scratch, status, st));
     } else {
         dim3 grid(4 * hidden / kGemmBN, (M + kGemmBM - 1) / kGemmBM);
@@ -267,6 +279,11 @@ int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float
     }
 
     record_stage_event(1, st);
+    if (mode == 2 && lstm_rtc_supported(batch, hidden)) {
+        const int rc = launch_lstm_recurrent_tc(pre, w_hh, seq_len, batch, hidden, hs, cs, rtc_scratch, counter, status, st);
+        record_stage_event(2, st);
+        return rc;
+    }
     const int btiles = (batch + kRecB - 1) / kRecB;
     dim3 rgrid(hidden / kRecJ, btiles);
     const int hrow = hidden + 64;

@@ -275,6 +275,321 @@ lstm_tc_gemm_kernel(const unsigned char* __restrict__ a_tiles, const unsigned ch
     }
 }
 
+// ==== the recurrence on the tensor cores =====================================================================
+// Per time step  gates[b, n] = pre[t, b, n] + sum_k h[t-1][b, k] * w_hh[gate(n), k, unit(n)]   (b < 64, n < 4H)
+// as a persistent cooperative kernel.  A CTA owns kRtcUnits = 4 hidden units, i.e. N = 16 gate columns (4 gates x 4
+// units), and ALL batch rows: per step it runs one [128 x 16] += [128 x H] * [H x 16] tcgen05 GEMM (M = 128 is the
+// instruction's tile; rows 64..127 of the A tiles are zero padding that is written once), 3xTF32 like the projection.
+//   B operand   the CTA's slice of w_hh, split into hi / lo TF32 parts and pre-tiled, resident in shared memory for all
+//               steps (H / 32 k-tiles x 4 KB = 64 KB at H = 512);
+//   A operand   h[t-1], hi / lo, pre-tiled: the epilogue of step t-1 (of every CTA) stores its four units of every row
+//               as one 16-byte chunk straight into the tiled global buffer (a [64 x 32] half tile is 8 KB contiguous),
+//               and step t brings it in with bulk copies through a ring of kRtcStages stages (32 KB each);
+//   D           128 lanes x 16 TMEM columns; the epilogue reads rows 0..63 (tcgen05.ld), hands them through shared
+//               memory to 256 threads, one (row, unit) each: add the input projection, gate non-linearities,
+//               c / h update, hs[t] / cs[t] slice assignment, h hi / lo tiles for the next step.
+// Steps are separated by a device-wide arrive / wait counter (the grid is launched cooperatively, one CTA per SM).
+// Every wait is bounded; when one runs out the CTA sets FB_STATUS_WAIT_TIMEOUT, raises its abort flag and every role
+// falls through to the common teardown, where TMEM is released.
+constexpr int kRtcUnits = 4;
+constexpr int kRtcN = 16;
+constexpr int kRtcATile = 128 * kTcBK * 4;        // 16 KB, rows 64..127 stay zero
+constexpr int kRtcAHalf = 64 * kTcBK * 4;         // 8 KB: the rows that exist
+constexpr int kRtcBTile = kRtcN * kTcBK * 4;      // 2 KB
+constexpr int kRtcStageBytes = 2 * kRtcATile;     // A_hi, A_lo
+constexpr int kRtcStages = 4;
+constexpr int kRtcThreads = 320;                  // warp 0: copies, warp 1: MMA, warps 2..9: epilogue
+constexpr int kRtcEpiThreads = 256;
+constexpr int kRtcBatch = 64;
+constexpr int kRtcGateStride = kRtcN + 1;
+constexpr unsigned long long kRtcWaitCycles = 2000000000ull;  // ~1 s: bound of the inter-step wait
+constexpr uint32_t kRtcIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kRtcN >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void rtc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kRtcIdesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_ld_16cols(uint32_t taddr, float* out) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = __uint_as_float(r[i]);
+}
+
+struct RtcShared {
+    uint64_t full[kRtcStages];
+    uint64_t empty[kRtcStages];
+    uint64_t accum;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    float gates[kRtcBatch * kRtcGateStride];
+};
+
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kRtcEpiThreads) : "memory"); }
+
+// grid = H / 4 CTAs (cooperative).  h_tiles: [2 (step parity)][H / 32][hi, lo][8 KB]; pre: [T * B, 4H].
+__global__ void __launch_bounds__(kRtcThreads, 1)
+lstm_recurrent_tc_kernel(const float* __restrict__ pre, const float* __restrict__ w_hh, int T, int H, float* hs, float* cs,
+                         unsigned char* h_tiles, unsigned int* step_counter, int32_t* status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const int KT = H / kTcBK;
+    unsigned char* ring = smem_raw;                                   // kRtcStages x 32 KB
+    unsigned char* btiles = ring + kRtcStages * kRtcStageBytes;       // KT x (hi 2 KB, lo 2 KB)
+    RtcShared& sh = *reinterpret_cast<RtcShared*>(btiles + static_cast<size_t>(KT) * 2 * kRtcBTile);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int j0 = blockIdx.x * kRtcUnits;
+    const unsigned int num_ctas = gridDim.x;
+    constexpr int B = kRtcBatch;
+
+    // ---- set-up: barriers, zero ring (the padding rows must read as zero), resident w_hh slice, TMEM ----
+    if (tid == 0) {
+        for (int s = 0; s < kRtcStages; ++s) {
+            mbar_init(&sh.full[s], 1);
+            mbar_init(&sh.empty[s], 1);
+        }
+        mbar_init(&sh.accum, 1);
+        sh.abort_flag = 0;
+        fence_barrier_init();
+    }
+    for (int i = tid; i < kRtcStages * kRtcStageBytes / 16; i += kRtcThreads) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0, 0, 0, 0);
+    for (int e = tid; e < kRtcN * H; e += kRtcThreads) {
+        // consecutive threads: the 4 units of one (gate, k): a 16-byte read of w_hh
+        const int unit = e & 3, gk = e >> 2;
+        const int k = gk % H, gate = gk / H;
+        const float v = __ldg(w_hh + (static_cast<int64_t>(gate) * H + k) * H + j0 + unit);
+        const float hi = tf32_round(v), lo = tf32_round(__fsub_rn(v, hi));
+        const int n = gate * kRtcUnits + unit;
+        unsigned char* tile = btiles + static_cast<size_t>(k / kTcBK) * 2 * kRtcBTile;
+        const int off = tile_offset(n, k % kTcBK);
+        *reinterpret_cast<float*>(tile + off) = hi;
+        *reinterpret_cast<float*>(tile + kRtcBTile + off) = lo;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(32u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_proxy_async();  // the generic-proxy writes above are read by the tensor core through the async proxy
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+
+    if (warp == 0) {
+        // ---- copies: for every step t >= 1, the KT k-tiles of h[t-1] (hi, lo) ----
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int t = 1; t < T && !sh.abort_flag; ++t) {
+                // every CTA has published h[t-1]
+                const unsigned int target = num_ctas * static_cast<unsigned int>(t);
+                const unsigned long long start = clock64();
+                unsigned int seen;
+                bool ok = true;
+                while (true) {
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(step_counter) : "memory");
+                    if (seen >= target) break;
+                    if (sh.abort_flag || clock64() - start > kRtcWaitCycles) { ok = false; break; }
+                }
+                if (!ok) {
+                    sh.abort_flag = 1;
+                    if (status != nullptr) atomicOr(status, FB_STATUS_WAIT_TIMEOUT);
+                    break;
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");  // the tiles were written by generic stores of other SMs
+                const unsigned char* src = h_tiles + static_cast<size_t>((t - 1) & 1) * KT * 2 * kRtcAHalf;
+                for (int kt = 0; kt < KT; ++kt, ++it) {
+                    const int s = it % kRtcStages;
+                    const uint32_t par = ((it / kRtcStages) & 1) ^ 1;
+                    bool got = false;
+                    for (uint32_t w = 0; w < kTcWaitLimit && !sh.abort_flag; ++w) {
+                        if (mbar_try_wait(&sh.empty[s], par)) { got = true; break; }
+                    }
+                    if (!got) {
+                        sh.abort_flag = 1;
+                        if (status != nullptr) atomicOr(status, FB_STATUS_WAIT_TIMEOUT);
+                        break;
+                    }
+                    unsigned char* dst = ring + s * kRtcStageBytes;
+                    mbar_arrive_expect_tx(&sh.full[s], 2 * kRtcAHalf);
+                    bulk_copy_g2s(dst, src + static_cast<size_t>(kt) * 2 * kRtcAHalf, kRtcAHalf, &sh.full[s]);
+                    bulk_copy_g2s(dst + kRtcATile, src + static_cast<size_t>(kt) * 2 * kRtcAHalf + kRtcAHalf, kRtcAHalf, &sh.full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            constexpr uint32_t lbo = 128u, sbo = 1024u;
+            uint32_t it = 0;
+            for (int t = 1; t < T && !sh.abort_flag; ++t) {
+                uint32_t accumulate = 0;
+                bool failed = false;
+                for (int kt = 0; kt < KT && !failed; ++kt, ++it) {
+                    const int s = it % kRtcStages;
+                    const uint32_t par = (it / kRtcStages) & 1;
+                    bool got = false;
+                    // the first tile of a step only arrives after the inter-step wait: bounded by time, like that wait
+                    const unsigned long long wstart = clock64();
+                    while (!sh.abort_flag) {
+                        if (mbar_try_wait(&sh.full[s], par)) { got = true; break; }
+                        if (clock64() - wstart > 2 * kRtcWaitCycles) break;
+                    }
+                    if (!got) {
+                        sh.abort_flag = 1;
+                        if (status != nullptr) atomicOr(status, FB_STATUS_WAIT_TIMEOUT);
+                        failed = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_hi = smem_u32(ring + s * kRtcStageBytes), a_lo = a_hi + kRtcATile;
+                    const uint32_t b_hi = smem_u32(btiles + static_cast<size_t>(kt) * 2 * kRtcBTile), b_lo = b_hi + kRtcBTile;
+#pragma unroll
+                    for (int kk = 0; kk < kTcBK / 8; ++kk) {
+                        const uint32_t ko = kk * 256;
+                        const uint64_t dah = make_smem_desc(a_hi + ko, lbo, sbo), dal = make_smem_desc(a_lo + ko, lbo, sbo);
+                        const uint64_t dbh = make_smem_desc(b_hi + ko, lbo, sbo), dbl = make_smem_desc(b_lo + ko, lbo, sbo);
+                        rtc_mma(tmem, dal, dbh, accumulate);
+                        accumulate = 1;
+                        rtc_mma(tmem, dah, dbl, 1);
+                        rtc_mma(tmem, dah, dbh, 1);
+                    }
+                    tc_commit(&sh.empty[s]);
+                }
+                if (failed) break;
+                tc_commit(&sh.accum);
+            }
+        }
+    } else {
+        // ---- epilogue: 256 threads, one (row, unit) each ----
+        const int e = tid - 64;
+        const int eb = e >> 2, eu = e & 3;  // row, unit
+        float c_state = 0.0f;
+        float pre_g[4];
+        {
+            const float* prow = pre + static_cast<int64_t>(eb) * (4 * H) + j0 + eu;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) pre_g[g] = __ldg(prow + g * H);
+        }
+        const int kt_mine = j0 / kTcBK;                 // the k-tile this CTA's units belong to
+        const int tile_off = tile_offset(eb, (j0 % kTcBK) + eu);
+        for (int t = 0; t < T; ++t) {
+            float s_g[4] = {0.f, 0.f, 0.f, 0.f};
+            if (t > 0) {
+                bool ok = false;
+                const unsigned long long start = clock64();
+                while (!sh.abort_flag) {
+                    if (mbar_try_wait(&sh.accum, static_cast<uint32_t>((t - 1) & 1))) { ok = true; break; }
+                    if (clock64() - start > 2 * kRtcWaitCycles) break;
+                }
+                if (!ok) {
+                    sh.abort_flag = 1;
+                    if (status != nullptr && lane == 0) atomicOr(status, FB_STATUS_WAIT_TIMEOUT);
+                }
+                // warps 4 and 5 own the TMEM lane quadrants 0 and 1 (rows 0..31, 32..63)
+                if ((warp == 4 || warp == 5) && !sh.abort_flag) {
+                    tc_fence_after();
+                    const int q = warp & 3;
+                    float acc[16];
+                    tc_ld_16cols(tmem + (static_cast<uint32_t>(q * 32) << 16), acc);
+                    float* grow = sh.gates + (q * 32 + lane) * kRtcGateStride;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) grow[i] = acc[i];
+                    tc_fence_before();
+                }
+                epi_barrier();
+                if (sh.abort_flag) break;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) s_g[g] = sh.gates[eb * kRtcGateStride + g * kRtcUnits + eu];
+            }
+            float gate[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) gate[g] = __fadd_rn(pre_g[g], s_g[g]);
+            if (t + 1 < T) {
+                const float* prow = pre + (static_cast<int64_t>(t + 1) * B + eb) * (4 * H) + j0 + eu;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) pre_g[g] = __ldg(prow + g * H);
+            }
+            const float ig = sigmoid_f32(gate[0]);
+            const float fg = sigmoid_f32(gate[1]);
+            const float gg = tanhf(gate[2]);
+            const float og = sigmoid_f32(gate[3]);
+            c_state = __fadd_rn(__fmul_rn(fg, c_state), __fmul_rn(ig, gg));
+            const float hval = __fmul_rn(og, tanhf(c_state));
+            const int64_t o = (static_cast<int64_t>(t) * B + eb) * H + j0 + eu;
+            hs[o] = hval;
+            cs[o] = c_state;
+            if (t + 1 < T) {
+                // h[t] for the next step: hi / lo parts into the pre-tiled buffer of this step's parity
+                const float hi = tf32_round(hval), lo = tf32_round(__fsub_rn(hval, hi));
+                unsigned char* dst = h_tiles + (static_cast<size_t>(t & 1) * KT + kt_mine) * 2 * kRtcAHalf + tile_off;
+                *reinterpret_cast<float*>(dst) = hi;
+                *reinterpret_cast<float*>(dst + kRtcAHalf) = lo;
+                __threadfence();
+                epi_barrier();  // every thread's stores are fenced before the CTA announces the step
+                if (e == 0) atomicAdd(step_counter, 1u);
+            }
+        }
+    }
+    // ---- teardown ----
+    tc_fence_before();
+    __syncthreads();
+    if (sh.abort_flag && threadIdx.x == 0) {
+        const unsigned long long t0 = clock64();
+        while (clock64() - t0 < 400000ull) {
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32u) : "memory");
+    }
+}
+
+bool lstm_rtc_supported(int B, int H) { return B == kRtcBatch && H > 0 && (H % kTcBK) == 0 && (H / kRtcUnits) <= kNumSMs; }
+
+int64_t lstm_rtc_scratch_bytes(int H) { return static_cast<int64_t>(2) * (H / kTcBK) * 2 * kRtcAHalf; }
+
+int launch_lstm_recurrent_tc(const float* pre, const float* w_hh, int T, int B, int H, float* hs, float* cs,
+                             void* h_tiles, unsigned int* step_counter, int32_t* status, cudaStream_t st) {
+    FB_REQUIRE(lstm_rtc_supported(B, H), "lstm tensor-core recurrence: needs batch 64 and hidden a multiple of 32, <= %d",
+               kNumSMs * kRtcUnits);
+    FB_REQUIRE(h_tiles != nullptr && (reinterpret_cast<uintptr_t>(h_tiles) & 255) == 0, "lstm tensor-core recurrence: misaligned scratch");
+    const int KT = H / kTcBK;
+    const size_t smem = static_cast<size_t>(kRtcStages) * kRtcStageBytes + static_cast<size_t>(KT) * 2 * kRtcBTile +
+                        sizeof(RtcShared) + 1024;
+    FB_TRY(check_cuda(cudaFuncSetAttribute(lstm_recurrent_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)),
+                      "lstm_recurrent_tc attr"));
+    int occ = 0, dev = 0, sms = 0;
+    FB_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
+    FB_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "sm count"));
+    FB_TRY(check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, lstm_recurrent_tc_kernel, kRtcThreads, smem), "occupancy"));
+    const int ctas = H / kRtcUnits;
+    if (ctas > occ * sms) {
+        set_error("lstm tensor-core recurrence: %d CTAs cannot be co-resident on %d SMs", ctas, sms);
+        return FB_ERR_UNSUPPORTED;
+    }
+    unsigned char* tiles = static_cast<unsigned char*>(h_tiles);
+    void* args[] = {(void*)&pre, (void*)&w_hh, (void*)&T, (void*)&H, (void*)&hs, (void*)&cs, (void*)&tiles,
+                    (void*)&step_counter, (void*)&status};
+    FB_TRY(check_cuda(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&lstm_recurrent_tc_kernel), dim3(ctas),
+                                                  dim3(kRtcThreads), args, smem, st),
+                      "lstm_recurrent_tc launch"));
+    count_launch();
+    return check_launch("lstm_recurrent_tc_kernel");
+}
+
 bool lstm_tc_supported(int M, int K, int H) {
     return M > 0 && K > 0 && H > 0 && (M % kTcBM) == 0 && (K % kTcBK) == 0 && (H % kTcBN) == 0;
 }

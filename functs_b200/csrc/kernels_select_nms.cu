@@ -579,7 +579,7 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
                      const float* __restrict__ boxes, int64_t num_boxes, int num_classes,
                      const uint64_t* __restrict__ sel_keys, int topk, float* __restrict__ dets,
                      int64_t* __restrict__ labels, int64_t* __restrict__ flat_ids, int64_t* __restrict__ keep,
-                     int32_t* __restrict__ out_counts) {
+                     int32_t* __restrict__ out_counts, int4* __restrict__ records) {
     constexpr size_t kRaw = sizeof(NmsRowsSmem) > sizeof(NmsScanSmem) ? sizeof(NmsRowsSmem) : sizeof(NmsScanSmem);
     __shared__ __align__(16) unsigned char raw[kRaw];
     __shared__ int s_last;
@@ -756,6 +756,13 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
             labels[obase + rank] = static_cast<int64_t>(flat - box * static_cast<uint32_t>(num_classes));
             flat_ids[obase + rank] = static_cast<int64_t>(flat);
             if (keep != nullptr) keep[obase + rank] = c;
+            if (records != nullptr) {  // the 32-byte record of the multi-GPU gather (layout of pack_detections_kernel)
+                records[2 * (obase + rank)] = make_int4(__float_as_int(bx.x), __float_as_int(bx.y), __float_as_int(bx.z),
+                                                        __float_as_int(bx.w));
+                records[2 * (obase + rank) + 1] = make_int4(__float_as_int(key_score(k)),
+                                                            static_cast<int>(flat - box * static_cast<uint32_t>(num_classes)),
+                                                            static_cast<int>(flat), 1);
+            }
         }
     }
     // zero the tail so that the padded outputs are deterministic
@@ -766,6 +773,10 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
         labels[obase + i] = -1;
         flat_ids[obase + i] = -1;
         if (keep != nullptr) keep[obase + i] = -1;
+        if (records != nullptr) {
+            records[2 * (obase + i)] = make_int4(0, 0, 0, 0);
+            records[2 * (obase + i) + 1] = make_int4(0, -1, -1, 0);
+        }
     }
 }
 
@@ -869,7 +880,8 @@ int launch_select_binned(const uint64_t* in_keys, const int32_t* in_counts, int6
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
                        int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
-                       int32_t* status, cudaStream_t st) {
+                       int32_t* status, cudaStream_t st, int32_t* records) {
+    FB_REQUIRE(records == nullptr || (reinterpret_cast<uintptr_t>(records) & 15) == 0, "batched_nms: records must be 16-byte aligned");
     FB_REQUIRE(boxes && sel_keys && sel_counts && dets && labels && flat_ids && out_counts && mask,
                "batched_nms: null pointer");
     FB_REQUIRE(groups > 0 && groups <= 65535 && topk > 0 && topk <= kNmsMaxN && num_classes > 0 && num_boxes > 0,
@@ -903,7 +915,7 @@ int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, c
     dim3 grid(ctas, groups);
     nms_mask_scan_kernel<<<grid, kMaskThreads, 0, st>>>(v.prep, iou_thr, thr_lo, thr_hi, v.mask, v.rowflag, v.ticket, boxes,
                                                         num_boxes, num_classes, sel_keys, topk, dets, labels, flat_ids, keep,
-                                                        out_counts);
+                                                        out_counts, reinterpret_cast<int4*>(records));
     count_launch();
     return check_launch("nms_mask_scan_kernel");
 }
@@ -961,7 +973,7 @@ int functs_b200_batched_nms(const float* boxes, int64_t num_boxes, int32_t num_c
     }
     return fb::launch_batched_nms(boxes, num_boxes, num_classes, sel_keys, sel_counts, groups, topk, iou_thr,
                                   class_offset, dets, labels, flat_ids, keep, out_counts, scratch, 0, status,
-                                  fb::as_stream(stream));
+                                  fb::as_stream(stream), nullptr);
 }
 
 }  // extern "C"

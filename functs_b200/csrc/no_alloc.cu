@@ -21,7 +21,7 @@ namespace fb {
 int launch_batched_nms(const float* boxes, int64_t num_boxes, int num_classes, const uint64_t* sel_keys,
                        const int32_t* sel_counts, int groups, int topk, float iou_thr, int class_offset, float* dets,
                        int64_t* labels, int64_t* flat_ids, int64_t* keep, int32_t* out_counts, void* mask, int prepared,
-                       int32_t* status, cudaStream_t st);
+                       int32_t* status, cudaStream_t st, int32_t* records = nullptr);
 int64_t nms_mask_bytes(int groups);
 
 constexpr int kStaticNmsGroups = 8;

@@ -423,7 +423,7 @@ Operation makeYolo(const Node* node, bool dense) {
         const int64_t ints[] = {B, sizes[0], sizes[1], sizes[2], topk, capacity};
         const double floats[] = {thr, iou};
         void* outs[] = {boxes.data_ptr(), dense ? obj.data_ptr() : nullptr, dense ? cls.data_ptr() : nullptr,
-                        dets.data_ptr(), labels.data_ptr(), ids.data_ptr(), counts.data_ptr()};
+                        dets.data_ptr(), labels.data_ptr(), ids.data_ptr(), counts.data_ptr(), nullptr};
         checkRc(functs_b200_group_launch(gid, in_ptrs, ints, floats, outs, scratch.data_ptr(), status.data_ptr<int>(),
                                          at::cuda::getCurrentCUDAStream().stream()),
                 "yolov3 post-process");

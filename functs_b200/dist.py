@@ -1,8 +1,9 @@
 """Batch sharding across the GPUs of one box and the one exchange step of the path: gathering final detections.
 
 Images (and LSTM sequences) are independent, so a batch is split into contiguous shards, one per rank, with no
-data-path collective; only the fixed-capacity detection records of the last kernel are gathered (NCCL all-gather
-over NVLink on GPUs; the same code runs on gloo/CPU tensors, which is how the host logic is tested).
+data-path collective; only the fixed-capacity detection records of the last kernel are gathered: to one rank
+(gather_records_to) or to all of them (gather_records), NCCL over NVLink on GPUs; the same code runs on gloo / CPU
+tensors, which is how the host logic is tested.
 """
 from typing import List, Tuple
 
@@ -63,6 +64,23 @@ def gather_records(rec: torch.Tensor, group=None, out: torch.Tensor = None) -> t
         dist.all_gather(parts, rec.contiguous(), group=group)
     else:
         dist.all_gather_into_tensor(full, rec.contiguous(), group=group)
+    return full
+
+
+def gather_records_to(rec: torch.Tensor, dst: int = 0, group=None, out: torch.Tensor = None):
+    """Gather of equally sized record shards to ONE rank: -> [world * B, K, 8] on rank `dst`, None on the others.
+    "Only the final detections are gathered": the other ranks just send their 32-byte records (NCCL send / recv pairs
+    over NVLink; the same code runs on gloo / CPU tensors).  `out` is only used on `dst`."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return rec
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    rec = rec.contiguous()
+    if rank != dst:
+        dist.gather(rec, None, dst=dst, group=group)
+        return None
+    full = out if out is not None else torch.empty((world * rec.size(0),) + tuple(rec.shape[1:]), dtype=rec.dtype,
+                                                   device=rec.device)
+    dist.gather(rec, list(full.chunk(world, dim=0)), dst=dst, group=group)
     return full
 
 

@@ -179,13 +179,19 @@ class YoloPostprocessPlan:
         ctr = self.scratch[counts_bytes + hist_bytes: counts_bytes + hist_bytes + self.batch * 16].view(torch.int32)
         return int(ctr.reshape(self.batch, 4)[:, 3].sum())
 
-    def run(self, maps: List[torch.Tensor], score_thr: float = 0.5, iou_thr: float = 0.45) -> None:
+    def run(self, maps: List[torch.Tensor], score_thr: float = 0.5, iou_thr: float = 0.45,
+            records: Optional[torch.Tensor] = None) -> None:
+        """records (optional, int32 [batch, topk, 8]): the NMS kernel also writes the gather records (no pack launch)."""
         s = self.sizes
-        check(lib.functs_b200_yolo_postprocess(maps[0].data_ptr(), maps[1].data_ptr(), maps[2].data_ptr(), self.batch,
-                                               s[0], s[1], s[2], float(score_thr), self.topk, float(iou_thr),
-                                               self.capacity, _ptr(self.boxes), _ptr(self.dets), _ptr(self.labels),
-                                               _ptr(self.flat_ids), _ptr(self.counts), _ptr(self.status),
-                                               _ptr(self.scratch), _stream()), "yolo_postprocess")
+        if records is not None and (records.dtype != torch.int32 or not records.is_contiguous()
+                                    or records.numel() != self.batch * self.topk * 8):
+            raise ValueError("records must be a contiguous int32 [batch, topk, 8] tensor")
+        check(lib.functs_b200_yolo_postprocess_dense(maps[0].data_ptr(), maps[1].data_ptr(), maps[2].data_ptr(), self.batch,
+                                                     s[0], s[1], s[2], float(score_thr), self.topk, float(iou_thr),
+                                                     self.capacity, _ptr(self.boxes), None, None, _ptr(self.dets),
+                                                     _ptr(self.labels), _ptr(self.flat_ids), _ptr(self.counts),
+                                                     _ptr(records), _ptr(self.status), _ptr(self.scratch), _stream()),
+              "yolo_postprocess")
 
 
 # ---- C3 ------------------------------------------------------------------------------------------------------

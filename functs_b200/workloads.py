@@ -131,8 +131,9 @@ class LSTM:
     @staticmethod
     def expected_launches(seq_len: int, batch: int, hidden: int, mode: int = 0) -> int:
         """Kernel launches of one call: operand split + tensor-core projection + recurrence, or (mode 1, or a shape the
-        tensor-core projection does not take) CUDA-core projection + recurrence."""
-        return 3 if (mode == 0 and (seq_len * batch) % 128 == 0 and hidden % 128 == 0) else 2
+        tensor-core projection does not take) CUDA-core projection + recurrence.  The recurrence is one launch in every
+        mode."""
+        return 3 if (mode != 1 and (seq_len * batch) % 128 == 0 and hidden % 128 == 0) else 2
 
     def forward_device(self, x: torch.Tensor, mode: int = 0):
         """x on the device; outputs and scratch are reused across calls; no synchronisation."""

@@ -158,12 +158,14 @@ int functs_b200_yolo_postprocess(const float* map0, const float* map1, const flo
 /* The same with the dense per-box outputs of the decode group kept: obj_out [batch, N] and cls_out [batch, N, 80]
  * (sigmoid of the objectness / class logits), as a program that returns them needs (the slices flat[..., 4] and
  * flat[..., 5:] of yolov3_bbox.py:217-219).  Every score is formed in that case, so the decode launch is the
- * thread-per-box kernel and nothing is pruned; still 3 launches.  NULL for both = functs_b200_yolo_postprocess. */
+ * thread-per-box kernel and nothing is pruned; still 3 launches.  NULL for both = functs_b200_yolo_postprocess.
+ * records (optional, [batch, topk, 8] int32, 16-byte aligned): the NMS kernel also writes every output row as the
+ * 32-byte record of functs_b200_pack_detections, so that a sharded caller can gather right away (no pack launch). */
 int functs_b200_yolo_postprocess_dense(const float* map0, const float* map1, const float* map2, int32_t batch,
                                        int32_t s0, int32_t s1, int32_t s2, float score_thr, int32_t topk,
                                        float iou_thr, int64_t capacity, float* boxes, float* obj_out, float* cls_out,
                                        float* dets, int64_t* labels, int64_t* flat_ids, int32_t* out_counts,
-                                       int32_t* status, void* scratch, void* stream);
+                                       int32_t* records, int32_t* status, void* scratch, void* stream);
 
 /* ---- C3: SSD-style post-process ----------------------------------------------------------- */
 /* Follows functs/benchmark/ai_model/ssd/ssd_bbox.py:121-154 (decode with the strided clamp), :268 (softmax, last
@@ -191,8 +193,11 @@ int64_t functs_b200_lstm_scratch_bytes(int32_t seq_len, int32_t batch, int32_t i
 int functs_b200_lstm_forward(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
                              const float* b_hh, int32_t seq_len, int32_t batch, int32_t input, int32_t hidden,
                              float* hs, float* cs, int32_t* status, void* scratch, void* stream);
-/* Same, with the projection path chosen by the caller: mode 0 = default (tensor cores when the shape allows),
- * mode 1 = fp32 CUDA-core projection (the on-device check of the tensor-core result). */
+/* Same, with the GEMM paths chosen by the caller: mode 0 = default; 1 = fp32 CUDA cores for the input projection and
+ * the recurrence (the on-device check of the tensor-core results); 2 = tcgen05 (3xTF32) for both — the recurrence then
+ * is one persistent kernel whose CTAs keep their slice of w_hh resident in shared memory and exchange h[t] as pre-tiled
+ * TF32 hi / lo operands (needs batch == 64); 3 = tensor-core projection + CUDA-core recurrence.  A shape a tensor-core
+ * path does not take falls back to the CUDA-core form of that GEMM. */
 int functs_b200_lstm_forward_mode(const float* x, const float* w_ih, const float* w_hh, const float* b_ih,
                                   const float* b_hh, int32_t seq_len, int32_t batch, int32_t input, int32_t hidden,
                                   float* hs, float* cs, int32_t* status, void* scratch, void* stream, int32_t mode);

@@ -57,6 +57,9 @@ def _worker(rank, world, port, total, out_dir):
         if total % world == 0:
             full2 = fdist.gather_records(rec)
             ok = ok and torch.equal(full2, full)
+            # gather to one rank: rank 0 gets everything, the others get nothing back
+            full3 = fdist.gather_records_to(rec, 0)
+            ok = ok and ((rank == 0 and torch.equal(full3, full)) or (rank != 0 and full3 is None))
         with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
             f.write("ok" if ok else "mismatch")
     finally:

@@ -250,3 +250,18 @@ def test_pack_detections_matches_host_packing(fb, cuda_device):
     assert torch.equal(got.cpu(), want)
     d2, l2, i2, c2 = fdist.unpack_detections(got.cpu())
     assert torch.equal(d2, dets) and torch.equal(l2, labels) and torch.equal(i2, ids) and torch.equal(c2, counts)
+
+
+def test_postprocess_writes_gather_records(fb, cuda_device):
+    """The one-call post-process can write the 32-byte gather records itself (no pack launch): they must equal what the
+    pack kernel makes of the padded outputs."""
+    from functs_b200 import dist as fdist
+    maps = [m.cuda() for m in W.make_yolo_inputs(3)]
+    plan = fb.ops.YoloPostprocessPlan(3)
+    rec = torch.full((3, 1000, fdist.RECORD_WORDS), 7, dtype=torch.int32, device="cuda")
+    before = fb.launch_count()
+    plan.run(maps, 0.5, 0.45, records=rec)
+    assert fb.launch_count() - before == 3
+    want = fdist.pack_detections(plan.dets, plan.labels, plan.flat_ids, plan.counts)
+    torch.cuda.synchronize()
+    assert torch.equal(rec, want)

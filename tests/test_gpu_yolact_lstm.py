@@ -98,7 +98,7 @@ def lstm_case(fb, seq, batch, hidden, mode):
     """Bar for fp32 values: 1e-5 relative.  h = o * tanh(c) lies in (-1, 1) and passes through zero, so a value is
     measured against max(|want|, 1): 1 is the bound of the gate activations every h and c is formed from.  No absolute
     term.  On top of that the device result is compared with the fp64 evaluation of the same program: the fp32 CUDA-core
-    path (mode 1) must be as close to it as the fp32 CPU oracle itself is (factor 2); the tensor-core path (mode 0)
+    path (mode 1) must be as close to it as the fp32 CPU oracle itself is (factor 2); the tensor-core paths (modes 0, 2, 3)
     splits every fp32 operand into two TF32 numbers, which carry 22 of the 24 mantissa bits, so its products are about
     four times less accurate than fp32 products: factor 10, and always below 1e-5."""
     x, w_ih, w_hh, b_ih, b_hh = W.make_lstm_inputs(seq, batch, hidden)
@@ -130,9 +130,18 @@ def test_lstm_tensor_core_projection_matches_cuda_cores(fb):
     assert err < 1e-5
 
 
-@pytest.mark.parametrize("mode", [1, 0])
+@pytest.mark.parametrize("mode", [1, 0, 2, 3])
 def test_lstm_config_shapes(fb, mode):
     lstm_case(fb, 64, 64, 512, mode)
+
+
+def test_lstm_tensor_core_recurrence_small(fb):
+    """The tcgen05 recurrence (mode 2) on other lengths and on H = 256; a batch other than 64 takes the CUDA-core
+    recurrence under the same mode."""
+    lstm_case(fb, 1, 64, 512, 2)
+    lstm_case(fb, 2, 64, 512, 2)
+    lstm_case(fb, 9, 64, 256, 2)
+    lstm_case(fb, 3, 33, 512, 2)
 
 
 @pytest.mark.parametrize("seq,batch,hidden", [(3, 5, 256), (1, 64, 512), (7, 33, 512), (5, 8, 256)])
