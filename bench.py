@@ -330,10 +330,12 @@ def extra_workloads(torch, fb, W, hbm_peak, peak_kind="measured"):
     return out
 
 
-def bind_to_gpu_numa_node(index: int) -> None:
+def bind_to_gpu_numa_node(index: int):
     """Pins this rank's host threads to the CPU cores next to its GPU (NVML's ideal affinity mask; read-only query), before
     any host buffer is allocated: the pinned input buffers are then first touched, and so placed, on the GPU's own NUMA
-    node, and the host-to-device copies of the ranks do not all cross the same socket link.  Best effort."""
+    node, and the host-to-device copies of the ranks do not all cross the same socket link.  Best effort.  Returns the
+    previous affinity set (restored before the CPU baseline runs, which uses every host core)."""
+    before = os.sched_getaffinity(0)
     try:
         import pynvml
         pynvml.nvmlInit()
@@ -346,6 +348,7 @@ def bind_to_gpu_numa_node(index: int) -> None:
             os.sched_setaffinity(0, cpus & allowed)
     except Exception:
         pass
+    return before
 
 
 def run_ours(args):
@@ -363,7 +366,7 @@ def run_ours(args):
         raise RuntimeError("bench.py needs a CUDA device: functs_b200 has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    bind_to_gpu_numa_node(local)
+    all_cpus = bind_to_gpu_numa_node(local)
     if world > 1:
         # the gather shares the GPU with the next step's kernels: its (few) CTAs must not queue behind theirs
         opts = None
@@ -522,6 +525,7 @@ def run_ours(args):
             with open(traffic_file) as f:
                 line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch_b64")
         if not args.no_extra and world == 1:
+            os.sched_setaffinity(0, all_cpus)   # the CPU baseline may use every host core again
             cpu_rate, cpu_ms, threads = cpu_oracle_rate(BATCH, 5, 1)
             line["cpu_baseline"] = {"value": cpu_rate, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": "the whole batch (64 images) per step x 5 steps, TorchScript CPU oracle", "ms_per_step": cpu_ms}
