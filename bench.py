@@ -10,6 +10,7 @@ detection records with NCCL at the end of every step.  `--impl reference` times 
 TorchScript program the reference's tests use as ground truth) on the host cores instead.
 """
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -36,6 +37,7 @@ def workload_config(world: int) -> dict:
     return {"workload": "YOLOv3-style decode + score>0.5 mask + top-1000 + class-wise NMS 0.45, 3 scales 13/26/52, batch 64 per GPU",
             "batch_per_gpu": BATCH,
             "inputs": "seeded N(0,1) logits, 231.7 MB per step; the GPU arm rotates 3 input sets so that no step finds its logits in the 126 MB L2",
+            "throughput_mode": "GPU arm: two batches in flight on two streams (latency_us is one batch at a time); CPU arm: one call after the other on all host threads",
             "collective": "none" if world == 1 else "gather of the 2 MB detection records of every rank to rank 0 (NCCL), on a second stream while the next step computes"}
 
 
@@ -386,6 +388,12 @@ def run_ours(args):
 
     topk, cap = 1000, NUM_BOXES * 80
     plan = fb.ops.YoloPostprocessPlan(BATCH, SIZES, topk, cap, device=dev)
+    # Throughput mode: two batches in flight on two streams (each with its own outputs and scratch), so that the decode
+    # kernel of one batch (bandwidth-bound, fills the machine) overlaps the top-k / NMS kernels of the other (a few
+    # hundred CTAs of dependent integer work).  Latency (one batch, one stream) is measured and reported separately.
+    in_flight = max(1, min(4, args.in_flight))
+    plans = [plan] + [fb.ops.YoloPostprocessPlan(BATCH, SIZES, topk, cap, device=dev) for _ in range(in_flight - 1)]
+    work_streams = [torch.cuda.Stream(dev) for _ in range(in_flight)]
     rec = torch.empty(BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
     # only rank 0 holds the gathered detections
     rec_all = (torch.empty(world * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
@@ -408,23 +416,27 @@ def run_ours(args):
     import ctypes
     ev_handles = [(ctypes.c_void_p * 4)(*[e.cuda_event for e in row]) for row in ev]
 
-    def step(i, handles=None):
-        if handles is not None:
-            lib.functs_b200_set_stage_events(handles, 4)
-        j = i & 1
-        if world > 1:
-            torch.cuda.current_stream().wait_event(gathered_ev[j])   # the gather that used this record buffer two steps ago is done
-        # memset + decode/mask/compact + binned top-k + NMS: 3 kernels; with N > 1 the NMS kernel also writes the records
-        plan.run(sets[i % n_sets], 0.5, 0.45, records=recs[j] if world > 1 else None)
-        if handles is not None:
-            lib.functs_b200_set_stage_events(None, 0)
-        if world > 1:
-            main = torch.cuda.current_stream()
-            packed_ev[j].record(main)
-            with torch.cuda.stream(comm_stream):
-                comm_stream.wait_event(packed_ev[j])
-                fdist.gather_records_to(recs[j], 0, out=rec_alls[j])
-                gathered_ev[j].record(comm_stream)
+    def step(i, handles=None, pipelined=False):
+        j = i & 1                      # record / gather buffer pair (N > 1)
+        k = i % in_flight              # plan and stream of this batch
+        p = plans[k] if pipelined else plan
+        ctx = torch.cuda.stream(work_streams[k]) if pipelined else contextlib.nullcontext()
+        with ctx:
+            if handles is not None:
+                lib.functs_b200_set_stage_events(handles, 4)
+            cur = torch.cuda.current_stream()
+            if world > 1:
+                cur.wait_event(gathered_ev[j])   # the gather that used this record buffer two steps ago is done
+            # memset + decode/mask/compact + binned top-k + NMS: 3 kernels; with N > 1 the NMS kernel also writes the records
+            p.run(sets[i % n_sets], 0.5, 0.45, records=recs[j] if world > 1 else None)
+            if handles is not None:
+                lib.functs_b200_set_stage_events(None, 0)
+            if world > 1:
+                packed_ev[j].record(cur)
+                with torch.cuda.stream(comm_stream):
+                    comm_stream.wait_event(packed_ev[j])
+                    fdist.gather_records_to(recs[j], 0, out=rec_alls[j])
+                    gathered_ev[j].record(comm_stream)
 
     def barrier():
         if world > 1:
@@ -433,6 +445,8 @@ def run_ours(args):
 
     for i in range(max(args.warmup, 3)):
         step(i)
+    for i in range(max(args.warmup, 3)):
+        step(i, pipelined=True)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -440,20 +454,29 @@ def run_ours(args):
     # The timed unit is a block of exactly `steps` steps between two barriers (device time, CUDA events).  One block of 20
     # steps is under 3 ms of GPU time, so the block is repeated until about a second of device time has been measured;
     # `value` comes from the median block.  The first block also records the per-stage events.
-    def timed_block(with_stage_events: bool):
+    def timed_block(with_stage_events: bool, pipelined: bool):
         t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
-        t_start.record()
+        main = torch.cuda.current_stream()
+        t_start.record(main)
+        if pipelined:
+            for ws in work_streams:
+                ws.wait_event(t_start)
         for i in range(args.steps):
-            step(i, ev_handles[i] if with_stage_events else None)
+            step(i, ev_handles[i] if with_stage_events else None, pipelined)
+        if pipelined:
+            for ws in work_streams:
+                main.wait_stream(ws)
         if world > 1:
-            torch.cuda.current_stream().wait_stream(comm_stream)   # the block ends when the last gather has landed
-        t_end.record()
+            main.wait_stream(comm_stream)   # the block ends when the last gather has landed
+        t_end.record(main)
         barrier()
         return t_start.elapsed_time(t_end)
 
+    # block 0: one batch at a time on one stream, with the per-stage events -> latency and the kernels' own durations
+    seq_ms = timed_block(True, False)
     launches0 = launch_count()
-    block_ms = [timed_block(True)]
+    block_ms = [timed_block(False, in_flight > 1)]
     launches = launch_count() - launches0
     # every rank must run the same number of blocks: rank 0's first block decides
     want = torch.tensor([max(1.0, min(2000.0, 1000.0 / max(block_ms[0], 1e-3)))], dtype=torch.float64, device=dev)
@@ -461,7 +484,7 @@ def run_ours(args):
         dist.broadcast(want, 0)
     repeats = int(want.item())
     for _ in range(repeats - 1):
-        block_ms.append(timed_block(False))
+        block_ms.append(timed_block(False, in_flight > 1))
     total_ms = statistics.median(block_ms)
     fb.ops.raise_on_status(plan.status, "bench")
     decode_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
@@ -492,10 +515,10 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- max over ranks ----
-    stats = torch.tensor([total_ms, e2e_ms, decode_ms, select_ms, nms_ms], dtype=torch.float64, device=dev)
+    stats = torch.tensor([total_ms, e2e_ms, decode_ms, select_ms, nms_ms, seq_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, decode_ms, select_ms, nms_ms = [float(v) for v in stats.tolist()]
+    total_ms, e2e_ms, decode_ms, select_ms, nms_ms, seq_ms = [float(v) for v in stats.tolist()]
 
     if rank == 0:
         ms_per_step = total_ms / args.steps
@@ -508,7 +531,8 @@ def run_ours(args):
             "config": workload_config(world),
             "repeats": repeats, "timed_region_s": sum(block_ms) / 1e3,
             "ms_per_step_spread": {"min": min(block_ms) / args.steps, "median": ms_per_step, "max": max(block_ms) / args.steps},
-            "latency_us": ms_per_step * 1e3, "kernels_per_call": launches / args.steps,
+            "in_flight": in_flight,
+            "latency_us": seq_ms / args.steps * 1e3, "kernels_per_call": launches / args.steps,
             "images_per_s": world * BATCH * 1e3 / ms_per_step,
             "stage_us": {"decode_mask_compact": decode_ms * 1e3, "select_topk": select_ms * 1e3, "nms": nms_ms * 1e3},
             "detections_kept_last_step": kept, "select_fallbacks_last_step": plan.select_fallbacks(),
@@ -594,6 +618,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm-priority", default="high", choices=["high", "normal"],
                     help="stream priority of the multi-GPU gather (N > 1)")
+    ap.add_argument("--in-flight", type=int, default=2, choices=[1, 2, 3, 4],
+                    help="batches in flight in the throughput measurement (2 = two streams, 1 = strictly one after the other)")
     ap.add_argument("--no-extra", action="store_true", help="skip the cpu_baseline leg and the other workloads")
     ap.add_argument("--only", default=None, choices=["yolo", "ssd", "yolact", "lstm", "get_started"],
                     help="run a few calls of one workload and exit (for profiler captures)")
