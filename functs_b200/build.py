@@ -20,6 +20,7 @@ SOURCES = [
     "kernels_lstm.cu",
     "kernels_lstm_tc.cu",
     "no_alloc.cu",
+    "kernels_generic.cu",
 ]
 
 NVCC_FLAGS = [

@@ -8,7 +8,7 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(os.path.dirname(HERE))
 OUT = os.path.join(PKG, "_C" + sysconfig.get_config_var("EXT_SUFFIX"))
-SOURCES = ["immut_ops.cpp", "tensorssa.cpp", "fusion.cpp", "regions.cpp", "shape_infer.cpp", "module.cpp"]
+SOURCES = ["immut_ops.cpp", "tensorssa.cpp", "fusion.cpp", "regions.cpp", "generic_group.cpp", "shape_infer.cpp", "module.cpp"]
 
 
 def stale() -> bool:

@@ -18,7 +18,9 @@
 
 #include <cstdlib>
 #include <fstream>
+#include <atomic>
 #include <functional>
+#include <mutex>
 #include <sstream>
 #include <unordered_map>
 #include <unordered_set>

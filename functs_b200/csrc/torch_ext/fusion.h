@@ -27,6 +27,8 @@ void MatchPrecompiledLoops(const std::shared_ptr<torch::jit::Graph>& graph);
 // loops with carried values, a constant trip count (<= 16) and a small body are unrolled completely
 void UnrollLoopsWithDeps(const std::shared_ptr<torch::jit::Graph>& graph);
 void FuseOps(const std::shared_ptr<torch::jit::Graph>& graph);
+// a map whose body is more than one fusion group -> a chain of maps, one group (or one run of other nodes) each
+void SplitParallelMaps(const std::shared_ptr<torch::jit::Graph>& graph);
 void LowerToParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
 // TensorSSA conversion (+ marker removal) followed by the three passes above and dead-code elimination
 void FaitPipeline(const std::shared_ptr<torch::jit::Graph>& graph);
@@ -65,5 +67,14 @@ torch::jit::Operation createRegionOperation(const torch::jit::Node* node);
 // functor runs that went through the subgraph interpreter instead of a precompiled kernel, in this process
 void countInterpretedRun();
 int64_t InterpretedFunctorRuns();
+// ---- generic group (generic_group.cpp): the subgraph of a functor as ONE launch of the program-interpreting kernel ----
+// inputs: the node's inputs (lists for the parallel arguments of a map); outputs: one IValue per subgraph output (a list
+// of `degree` tensors for a map).  Returns false, with the reason in *why, when the group cannot be expressed as programs.
+bool RunGenericGroup(const std::shared_ptr<torch::jit::Graph>& sub, bool is_map, int64_t degree,
+                     const std::vector<int64_t>& par, const std::vector<c10::IValue>& inputs,
+                     std::vector<c10::IValue>& outputs, std::string* why);
+void countGenericRun();
+int64_t GenericGroupRuns();
+std::string LastGenericRefusal();
 
 }  // namespace functs_b200

@@ -36,8 +36,16 @@ PYBIND11_MODULE(_C, m) {
     m.def("_jit_pass_parallelize_loops", [](std::shared_ptr<Graph> g) { functs_b200::ParallelizeLoops(g); });
     m.def("_jit_pass_fait_fuse_ops", [](std::shared_ptr<Graph> g, py::object /*refined_types*/) { functs_b200::FuseOps(g); },
           py::arg("graph"), py::arg("refined_types") = py::none());
+    // the reference's grouper for graphs that did not go through the ParallelMap pipeline (functs.jit.script(backend="jit"),
+    // functs/csrc/jit/python/init.cpp:40-42 -> FuncTsFuseTensorExprs): here the same entry point groups the fusable ops of a
+    // functionalized graph and lowers the groups to tssa::ParallelFunctor nodes, which run as one launch each
+    m.def("_jit_pass_fuse_tensorexpr", [](std::shared_ptr<Graph> g) {
+        functs_b200::FuseOps(g);
+        functs_b200::LowerToParallelFunctors(g);
+    });
     m.def("_jit_pass_match_precompiled_loops", [](std::shared_ptr<Graph> g) { functs_b200::MatchPrecompiledLoops(g); });
     m.def("_jit_pass_unroll_loops_with_deps", [](std::shared_ptr<Graph> g) { functs_b200::UnrollLoopsWithDeps(g); });
+    m.def("_jit_pass_split_parallel_maps", [](std::shared_ptr<Graph> g) { functs_b200::SplitParallelMaps(g); });
     m.def("_jit_pass_lower_to_parallel_functors", [](std::shared_ptr<Graph> g) { functs_b200::LowerToParallelFunctors(g); });
     m.def("_jit_pass_fait_pipeline",
           [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint) {
@@ -75,6 +83,8 @@ PYBIND11_MODULE(_C, m) {
              std::vector<std::pair<std::string, int64_t>> iroles) { functs_b200::RegisterRegionPattern(name, g, froles, iroles); });
     m.def("_region_pattern_count", []() { return functs_b200::RegionPatternCount(); });
     m.def("_interpreted_functor_runs", []() { return functs_b200::InterpretedFunctorRuns(); });
+    m.def("_generic_group_runs", []() { return functs_b200::GenericGroupRuns(); });
+    m.def("_last_generic_refusal", []() { return functs_b200::LastGenericRefusal(); });
     m.def("_functor_regions", [](std::shared_ptr<Graph> g) {
         // adapter name of every tssa::ParallelFunctor node ("" = interpreted), in graph order
         std::vector<std::string> out;

@@ -244,6 +244,7 @@ std::vector<RegionPattern>& patterns() {
 }
 
 std::atomic<int64_t> g_interpreted_runs{0};
+std::atomic<int64_t> g_generic_runs{0};
 
 // ---- replacement --------------------------------------------------------------------------------------------------
 
@@ -615,6 +616,8 @@ Operation createRegionOperation(const Node* node) {
 
 void countInterpretedRun() { g_interpreted_runs.fetch_add(1, std::memory_order_relaxed); }
 int64_t InterpretedFunctorRuns() { return g_interpreted_runs.load(std::memory_order_relaxed); }
+void countGenericRun() { g_generic_runs.fetch_add(1, std::memory_order_relaxed); }
+int64_t GenericGroupRuns() { return g_generic_runs.load(std::memory_order_relaxed); }
 
 RegionDescription DescribeRegion(const std::shared_ptr<Graph>& graph, const std::vector<int64_t>& fwild,
                                  const std::vector<int64_t>& iwild) {

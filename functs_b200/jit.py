@@ -75,6 +75,16 @@ def functor_regions(g: torch.Graph):
     return list(_C._functor_regions(g))
 
 
+def generic_group_runs() -> int:
+    """How many functor executions of this process ran as one launch of the generic program kernel."""
+    return int(_C._generic_group_runs())
+
+
+def last_generic_refusal() -> str:
+    """Why the most recent group that could not be expressed as a program was refused ("" if none was)."""
+    return str(_C._last_generic_refusal())
+
+
 def interpreted_functor_runs() -> int:
     """How many functor executions of this process went through the subgraph interpreter instead of a precompiled kernel."""
     return int(_C._interpreted_functor_runs())

@@ -249,6 +249,71 @@ int functs_b200_index_rows(const void* self, const int64_t* idx, void* out, int6
 int functs_b200_index_rows_rev(const void* self, const void* src, const int64_t* idx, void* out, int64_t self_rows,
                                int64_t num_idx, int64_t row_elems, int32_t elem_size, int32_t* status, void* stream);
 
+/* ---- generic group: one launch for a fusion group no precompiled kernel covers ------------------------ */
+/* The reference generates one CUDA kernel per fusion group at run time (NVRTC, fait/fuser/graph_builder.cpp:259-712:
+ * every output element is one inlined gather expression; map iterations sit on blockIdx.y,
+ * fait/tensorexpr/functor_parallization.cpp:83-111).  Here the same expression is data: the host flattens the group into
+ * a small postfix program over the output's multi-index, and ONE precompiled kernel evaluates it per element.
+ *   - a LOAD reads input `tensor` at  base + sum_k stride_k * ((mul_k * x[dim_k] + add_k) / div_k)  (dim_k = -1: no x term):
+ *     every Access op (select / slice / squeeze / unsqueeze / permute / expand) on the way to the output has been
+ *     folded into those terms on the host;
+ *   - a COND tests  lo <= v < hi  and  (v - lo) % step == 0  with  v = mul * x[dim] + add  and either falls through or
+ *     jumps to `arg`: the Assign ops (select_rev / slice_rev) and cat / stack become COND ... JUMP ... chains, so only the
+ *     selected operand is evaluated;
+ *   - CONST / UNARY / BINARY work on a small value stack in registers (fp32; comparisons give 1.0 / 0.0).
+ * One program per (map iteration, group output); grid.y walks the programs.  Everything is 32-bit: tensors of 2^31
+ * elements or more are not taken. */
+enum {
+    FB_G_END = 0, FB_G_LOAD = 1, FB_G_CONST = 2, FB_G_COND = 3, FB_G_JUMP = 4,
+    /* unary */ FB_G_EXP = 10, FB_G_SIGMOID = 11, FB_G_TANH = 12, FB_G_RELU = 13, FB_G_NEG = 14, FB_G_CLAMP_MIN = 15,
+    FB_G_CLAMP_MAX = 16, FB_G_ABS = 17, FB_G_SQRT = 18, FB_G_LOG = 19,
+    /* binary */ FB_G_ADD = 30, FB_G_SUB = 31, FB_G_MUL = 32, FB_G_DIV = 33, FB_G_MIN = 34, FB_G_MAX = 35, FB_G_GT = 36,
+    FB_G_GE = 37, FB_G_LT = 38, FB_G_LE = 39, FB_G_EQ = 40, FB_G_NE = 41
+};
+#define FB_G_MAX_INSTR 160
+#define FB_G_MAX_LOADS 24
+#define FB_G_MAX_PREDS 24
+#define FB_G_MAX_TERMS 6
+#define FB_G_MAX_INPUTS 16
+#define FB_G_STACK 12
+typedef struct {
+    uint16_t op;   /* FB_G_* */
+    uint16_t arg;  /* LOAD: load slot; COND: predicate slot (the jump target is in imm_i); JUMP: target */
+    union { float f; int32_t i; } imm; /* CONST / CLAMP_*: the scalar; COND: jump target when the test fails */
+} functs_b200_ginstr;
+typedef struct {
+    int16_t dim;  /* output dimension the coordinate follows, -1 = constant */
+    int16_t div;  /* >= 1 */
+    int32_t mul, add, stride;
+} functs_b200_gterm;
+typedef struct {
+    int32_t tensor;  /* index into in_ptr */
+    int32_t base;
+    int32_t nterms;
+    int32_t dtype;   /* 0 = float32, 1 = uint8 / bool, 2 = int64, 3 = int32 */
+    functs_b200_gterm term[FB_G_MAX_TERMS];
+} functs_b200_gload;
+typedef struct {
+    int32_t dim, mul, add, lo, hi, step;
+} functs_b200_gpred;
+typedef struct {
+    int32_t rank;
+    int32_t shape[8];
+    int32_t numel;
+    int32_t out_dtype;  /* 0 = float32, 1 = bool (uint8) */
+    int32_t ninstr;
+    int32_t reserved[2];  /* keeps sizeof a multiple of 16 */
+    const void* in_ptr[FB_G_MAX_INPUTS];
+    void* out_ptr;
+    functs_b200_ginstr instr[FB_G_MAX_INSTR];
+    functs_b200_gload load[FB_G_MAX_LOADS];
+    functs_b200_gpred pred[FB_G_MAX_PREDS];
+} functs_b200_gprogram;
+/* programs: `count` programs in HOST memory when on_device == 0 (count == 1: passed to the kernel by value) or in DEVICE
+ * memory when on_device != 0; max_numel = the largest numel among them.  One launch. */
+int functs_b200_generic_group_launch(const functs_b200_gprogram* programs, int32_t count, int32_t max_numel,
+                                     int32_t on_device, void* stream);
+
 /* ---- group registry: what the tssa::ParallelFunctor operator binds to ------------------------ */
 /* The reference registers one JIT operator whose Operation runs a compiled group
  * (fait/passes/te_op.cpp:238-249).  Here a group is found by a canonical signature string and launched with

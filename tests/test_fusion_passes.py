@@ -212,3 +212,48 @@ def test_constant_trip_loop_with_carried_tensor_is_unrolled_into_one_group():
     assert "prim::Loop" not in ks
     assert fjit.count_groups(fn.graph) == 1  # all four iterations and the epilogue in one fusion group
     assert torch.equal(fn(x, w), f(x, w))
+
+
+def split_body(feats: List[torch.Tensor]):
+    outs: List[torch.Tensor] = []
+    for i in range(len(feats)):
+        x = feats[i].clone()
+        x[:, 0:2] = torch.sigmoid(x[:, 0:2]) * 2.0   # first group
+        s = x.sum()                                    # a reduction: not fusable, stays between the groups
+        y = x * 3.0 + s                                # second group, reads the per-iteration value s
+        outs.append(torch.tanh(y))
+    return outs
+
+
+def test_map_with_two_groups_is_split():
+    """SplitParallelMaps: the map body [group, sum, group] becomes map{group} -> loop{sum} -> map{group}; the two group maps
+    turn into functors with is_parallel_map = 1, the values between them travel as lists."""
+    feats, _ = make_lists()
+    want = split_body(feats)
+    fn = fjit.build(split_body, (feats,))
+    functors = [n for n in fn.graph.nodes() if n.kind() == "tssa::ParallelFunctor"]
+    assert len(functors) == 2 and all(n.i("is_parallel_map") == 1 for n in functors)
+    ks = kinds(fn.graph, recursive=False)
+    assert ks.count("prim::Loop") == 1 and "tssa::ParallelMap" not in ks
+    loop = [n for n in fn.graph.nodes() if n.kind() == "prim::Loop"][0]
+    assert "aten::sum" in [n.kind() for n in list(loop.blocks())[0].nodes()]
+    got = fn(feats)
+    assert len(got) == len(want)
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, rtol=1e-6, atol=1e-6)
+
+
+def test_fuse_tensorexpr_entry_point_groups_a_functionalized_graph():
+    """_jit_pass_fuse_tensorexpr (the reference binds this name, functs/csrc/jit/python/init.cpp:40-42): groups of a
+    functionalized graph become tssa::ParallelFunctor nodes."""
+    def f(x: torch.Tensor):
+        t = x.clone()
+        t[0] = torch.sigmoid(t[0]) * 2.0
+        return t + 1.0
+    g = torch.jit.script(f).graph.copy()
+    fjit.functionalize_graph(g)
+    _C._jit_pass_fuse_tensorexpr(g)
+    assert "tssa::ParallelFunctor" in kinds(g) and "aten::sigmoid" not in kinds(g, recursive=False)
+    fn = torch._C._create_function_from_graph("f", g)
+    x = torch.randn(4, 5, generator=torch.Generator().manual_seed(1))
+    assert torch.allclose(fn(x), f(x))

@@ -119,6 +119,7 @@ def test_dump_graph_writes_stage_files(J, tmp_path, monkeypatch):
     J.build(W.YolactMasks())
     names = sorted(p.name for p in tmp_path.iterdir())
     assert names == ["after_fuse_ops.rb", "after_match_regions.rb", "after_parallel_functors.rb",
-                     "after_parallelize_loops.rb", "after_tensorssa.rb", "after_unroll_loops.rb"]
+                     "after_parallelize_loops.rb", "after_split_parallel_maps.rb", "after_tensorssa.rb",
+                     "after_unroll_loops.rb"]
     assert "prim::Loop" in (tmp_path / "after_tensorssa.rb").read_text()
     assert "tssa::ParallelFunctor" in (tmp_path / "after_match_regions.rb").read_text()
