@@ -8,6 +8,7 @@
 #include <ATen/ATen.h>
 #include <ATen/InferSize.h>
 #include <ATen/WrapDimUtils.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
@@ -40,6 +41,7 @@ std::vector<int64_t> row_major_strides(at::IntArrayRef shape) {
 }
 
 at::Tensor run_access(const at::Tensor& src_in, Desc& desc) {
+    c10::cuda::CUDAGuard guard(src_in.device());  // launch on the tensor's device, whatever device is current
     at::Tensor src = src_in.contiguous();
     desc.finish();
     at::Tensor out = at::empty(desc.shape, src.options());
@@ -205,6 +207,8 @@ at::Tensor im_repeat(at::Tensor self, at::IntArrayRef reps) {
 }
 
 at::Tensor im_select_rev(at::Tensor self, at::Tensor src, int64_t dim, int64_t index) {
+    c10::cuda::CUDAGuard guard(self.device());
+    TORCH_CHECK(src.device() == self.device(), "select_rev: self and src live on different devices");
     self = self.contiguous();
     dim = at::maybe_wrap_dim(dim, self.dim());
     const int64_t size = self.size(dim);
@@ -222,6 +226,8 @@ at::Tensor im_select_rev(at::Tensor self, at::Tensor src, int64_t dim, int64_t i
 
 at::Tensor im_slice_rev(at::Tensor self, at::Tensor src, int64_t dim, std::optional<c10::SymInt> start,
                      std::optional<c10::SymInt> end, c10::SymInt step_) {
+    c10::cuda::CUDAGuard guard(self.device());
+    TORCH_CHECK(src.device() == self.device(), "slice_rev: self and src live on different devices");
     self = self.contiguous();
     dim = at::maybe_wrap_dim(dim, self.dim());
     const int64_t step = step_.expect_int();
@@ -252,6 +258,7 @@ at::Tensor im_expand_as_rev(at::Tensor self, at::Tensor src, at::Tensor other) {
 }
 
 at::Tensor im_index_tensor(at::Tensor self, c10::List<std::optional<at::Tensor>> indices) {
+    c10::cuda::CUDAGuard guard(self.device());
     TORCH_CHECK(indices.size() >= 1 && indices.get(0).has_value(), "immut::index supports one index tensor on dimension 0");
     for (size_t i = 1; i < indices.size(); ++i) TORCH_CHECK(!indices.get(i).has_value(), "immut::index: only dimension 0");
     at::Tensor idx = indices.get(0)->contiguous();

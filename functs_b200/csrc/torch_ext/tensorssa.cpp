@@ -32,6 +32,8 @@ namespace sym {
 const Symbol update = Symbol::fromQualString("tssa::update");
 const Symbol assign = Symbol::fromQualString("immut::assign");
 const Symbol index = Symbol::fromQualString("immut::index");
+const Symbol select_rev = Symbol::fromQualString("immut::select_rev");
+const Symbol slice_rev = Symbol::fromQualString("immut::slice_rev");
 }  // namespace sym
 
 namespace {
@@ -234,6 +236,12 @@ void RemoveInplace(const std::shared_ptr<Graph>& graph) {
         Node* twin = g->create(pure, n->inputs(), 1);
         twin->insertBefore(n);
         if (twin->maybeSchema() == nullptr) {  // no out-of-place overload with these arguments: leave the op alone
+            twin->destroy();
+            return;
+        }
+        // squeeze_ / unsqueeze_ / transpose_ / t_ ... change the tensor's metadata, not its values: their out-of-place twin
+        // returns a VIEW, and "view, then copy_ back" would be another program.  Such ops stay as they are.
+        if (!twin->schema().returns().empty() && twin->schema().returns()[0].alias_info() != nullptr) {
             twin->destroy();
             return;
         }
@@ -453,7 +461,38 @@ void TensorSSARemoveUpdate(const std::shared_ptr<Graph>& graph) {
         if (n->kind() == sym::update) {
             n->destroy();
         } else if (n->kind() == sym::assign) {
-            n->output()->replaceAllUsesWith(n->input(1));  // assign(self, src) is src
+            // assign(self, src) stands for "self now holds src".  Where the result only feeds the src operand of
+            // select_rev / slice_rev, those ops broadcast and cast src to their destination themselves, so src can take its
+            // place.  Anywhere else (a write to a whole tensor: x.copy_(row), or through a squeeze / permute / view) the
+            // value must have self's shape and dtype: src is used as it is only when both static types are known and
+            // equal, otherwise a cast and an expand_as are inserted (copy_ broadcasts and converts, so must this).
+            Value* self = n->input(0);
+            Value* src = n->input(1);
+            bool only_rev_src = true;
+            for (const Use& u : n->output()->uses()) {
+                const bool rev = u.user->kind() == sym::select_rev || u.user->kind() == sym::slice_rev;
+                only_rev_src = only_rev_src && rev && u.offset == 1;
+            }
+            bool same = only_rev_src;
+            if (!same) {
+                auto ts = self->type()->cast<c10::TensorType>(), td = src->type()->cast<c10::TensorType>();
+                same = ts && td && ts->scalarType() && td->scalarType() && *ts->scalarType() == *td->scalarType() &&
+                       ts->sizes().concrete_sizes() && td->sizes().concrete_sizes() &&
+                       *ts->sizes().concrete_sizes() == *td->sizes().concrete_sizes();
+            }
+            Value* repl = src;
+            if (!same) {
+                Graph* g = n->owningGraph();
+                WithInsertPoint guard(n);
+                Value* f = g->insertConstant(false);
+                Value* none = g->insertConstant(c10::IValue());
+                Node* to = g->insertNode(g->create(aten::to, {src, self, f, f, none}, 1));
+                to->output()->setType(c10::TensorType::get());
+                Node* ex = g->insertNode(g->create(aten::expand_as, {to->output(), self}, 1));
+                ex->output()->setType(self->type());
+                repl = ex->output();
+            }
+            n->output()->replaceAllUsesWith(repl);
             n->destroy();
         }
     });

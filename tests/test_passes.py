@@ -230,3 +230,37 @@ graph(%self : Float(3000, 4, strides=[4, 1], device=cpu),
     want_t = x.clone()
     want_t[:, 0] = s
     assert torch.equal(fn(x, s, 0), want_t)
+
+
+def test_whole_tensor_copy_keeps_shape_and_dtype():
+    """x.copy_(row) broadcasts and converts: after functionalization the value that replaces x must still have x's shape
+    and dtype (a cast and an expand_as are inserted when the static types do not prove that src already has them)."""
+    def bcast(x: torch.Tensor, row: torch.Tensor):
+        x = x.clone()
+        x.copy_(row)
+        return x * 2
+
+    def cast(x: torch.Tensor, i: torch.Tensor):
+        x = x.clone()
+        x.copy_(i)
+        return x + 0.5
+    for fn, args in ((bcast, (torch.rand(3, 4), torch.rand(4))), (cast, (torch.rand(2, 3), torch.arange(6).reshape(2, 3)))):
+        g = torch.jit.script(fn).graph.copy()
+        fjit.functionalize_graph(g)
+        assert "aten::copy_" not in [n.kind() for n in g.nodes()]
+        f = torch._C._create_function_from_graph(fn.__name__, g)
+        got, want = f(*args), fn(*args)
+        assert got.shape == want.shape and got.dtype == want.dtype and torch.equal(got, want)
+
+
+def test_metadata_inplace_ops_are_left_alone():
+    """unsqueeze_ / squeeze_ / t_ change the tensor's shape, not its values: RemoveInplace must not turn them into
+    "view, then copy_ back"."""
+    def f(x: torch.Tensor):
+        y = x.clone()
+        y.unsqueeze_(0)
+        return y + 1
+    g = torch.jit.script(f).graph.copy()
+    _C._jit_pass_remove_inplace(g)
+    kinds = [n.kind() for n in g.nodes()]
+    assert "aten::unsqueeze_" in kinds and "aten::copy_" not in kinds
