@@ -398,13 +398,16 @@ def run_ours(args):
     # only rank 0 holds the gathered detections
     rec_all = (torch.empty(world * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
                if world > 1 and rank == 0 else None)
-    # multi-GPU: the gather of step i runs on a second stream while step i + 1 computes (two record buffers)
+    # multi-GPU: the gather of step i runs on a second stream while the next steps compute; one record buffer more than
+    # there are batches in flight, so that no batch waits for the gather of an earlier one
+    n_rec = 1
     if world > 1:
+        n_rec = max(2, int(args.in_flight) + 1)
         comm_stream = torch.cuda.Stream(dev, priority=-1 if args.comm_priority == "high" else 0)
-        recs = [rec, torch.empty_like(rec)]
-        rec_alls = [rec_all, torch.empty_like(rec_all)] if rank == 0 else [None, None]
-        packed_ev = [torch.cuda.Event(), torch.cuda.Event()]
-        gathered_ev = [torch.cuda.Event(), torch.cuda.Event()]
+        recs = [rec] + [torch.empty_like(rec) for _ in range(n_rec - 1)]
+        rec_alls = ([rec_all] + [torch.empty_like(rec_all) for _ in range(n_rec - 1)]) if rank == 0 else [None] * n_rec
+        packed_ev = [torch.cuda.Event() for _ in range(n_rec)]
+        gathered_ev = [torch.cuda.Event() for _ in range(n_rec)]
         for e in gathered_ev:
             e.record()
     # per-step stage events, recorded inside the one-call entry point through its profiling hook
@@ -417,7 +420,7 @@ def run_ours(args):
     ev_handles = [(ctypes.c_void_p * 4)(*[e.cuda_event for e in row]) for row in ev]
 
     def step(i, handles=None, pipelined=False):
-        j = i & 1                      # record / gather buffer pair (N > 1)
+        j = i % n_rec                  # record / gather buffers (N > 1)
         k = i % in_flight              # plan and stream of this batch
         p = plans[k] if pipelined else plan
         ctx = torch.cuda.stream(work_streams[k]) if pipelined else contextlib.nullcontext()

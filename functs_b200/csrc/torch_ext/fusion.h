@@ -35,6 +35,10 @@ void FaitPipeline(const std::shared_ptr<torch::jit::Graph>& graph);
 // graph inputs take `type_hint` (null entries are skipped); shapes, dtypes and devices are then propagated through the
 // aten:: operators (TorchScript's own propagation) and the immut:: family (shape_infer.cpp)
 void InferShapes(const std::shared_ptr<torch::jit::Graph>& graph, const std::vector<c10::TypePtr>& type_hint);
+// the same, returning the refined list types: (list value, tuple type with one tensor type per element).  A tuple hint for
+// a List[Tensor] graph input describes the list's elements.
+std::vector<std::pair<torch::jit::Value*, c10::TypePtr>> InferShapesRefined(const std::shared_ptr<torch::jit::Graph>& graph,
+                                                                            const std::vector<c10::TypePtr>& type_hint);
 // number of tssa::ParallelFunctor nodes in the graph (all blocks): the unit the launch-count metric counts
 int64_t CountParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
 // the normalisation every graph goes through before regions are matched: TensorSSA conversion, marker removal, CSE,

@@ -51,14 +51,24 @@ PYBIND11_MODULE(_C, m) {
           [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint) {
               // the type hints refine the graph inputs (shapes / dtypes), as the reference's pipeline does first
               for (size_t i = 0; i < type_hint.size() && i < g->inputs().size(); ++i) {
-                  if (type_hint[i]) g->inputs()[i]->setType(type_hint[i]);
+                  // (a tuple hint describes the elements of a list input; the list type itself cannot carry it)
+                  if (type_hint[i] && !(type_hint[i]->cast<c10::TupleType>() && g->inputs()[i]->type()->cast<c10::ListType>()))
+                      g->inputs()[i]->setType(type_hint[i]);
               }
               functs_b200::FaitPipeline(g);
           },
           py::arg("graph"), py::arg("type_hint") = std::vector<c10::TypePtr>());
     m.def("_jit_pass_fait_shape_infer",
-          [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint, py::object /*refined_types*/) {
-              functs_b200::InferShapes(g, type_hint);
+          [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint, py::object refined_types) {
+              // refined_types (a dict, as in the reference's binding): filled with value -> tuple type of every list of
+              // tensors whose elements' types are known; the same pairs are returned keyed by the values' debug names
+              auto pairs = functs_b200::InferShapesRefined(g, type_hint);
+              py::dict by_name;
+              for (auto& kv : pairs) {
+                  by_name[py::str(kv.first->debugName())] = kv.second;
+                  if (!refined_types.is_none()) refined_types[py::cast(kv.first)] = kv.second;
+              }
+              return by_name;
           },
           py::arg("graph"), py::arg("type_hint") = std::vector<c10::TypePtr>(), py::arg("refined_types") = py::none());
     // precompiled regions: pattern programs are registered from Python (functs_b200/patterns.py)

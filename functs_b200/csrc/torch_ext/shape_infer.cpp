@@ -197,6 +197,133 @@ std::optional<Sizes> broadcastSizes(const Sizes& a, const Sizes& b) {
     return out;
 }
 
+// ---- lists of tensors ---------------------------------------------------------------------------------------------------
+// A List[Tensor] type cannot say what its elements look like, so lists are refined on the side: value -> tuple type with
+// one tensor type per element (the reference's `refinedTypes` map, fait/passes/refine_types.h:8, 35-46; graph inputs get
+// theirs from tuple type hints, refine_types.cpp:57-82, 179-195).
+using Refined = std::unordered_map<Value*, c10::TypePtr>;
+
+c10::TupleTypePtr refinedList(const Refined& refined, Value* v) {
+    auto it = refined.find(v);
+    return it == refined.end() ? nullptr : it->second->cast<c10::TupleType>();
+}
+
+// the most specific tensor type every element satisfies: dtype, device and rank if they agree, sizes where all agree
+c10::TypePtr unifyElements(const c10::TupleTypePtr& tup) {
+    c10::TensorTypePtr acc;
+    for (const auto& e : tup->elements()) {
+        auto tt = e->cast<c10::TensorType>();
+        if (!tt) return nullptr;
+        if (!acc) {
+            acc = tt;
+            continue;
+        }
+        if (acc->scalarType() != tt->scalarType() || acc->device() != tt->device() || acc->dim() != tt->dim() || !acc->dim())
+            return c10::TensorType::get();
+        auto a = acc->sizes().concrete_sizes(), b = tt->sizes().concrete_sizes();
+        if (a && b && *a == *b) continue;
+        std::vector<c10::ShapeSymbol> dims;
+        for (size_t k = 0; k < *acc->dim(); ++k) {
+            const auto x = acc->symbolic_sizes().at(k), y = tt->symbolic_sizes().at(k);
+            dims.push_back(x.is_static() && y.is_static() && x.static_size() == y.static_size() ? x : c10::ShapeSymbol::newSymbol());
+        }
+        acc = acc->withSymbolicShapes(c10::SymbolicShape(dims));
+    }
+    return acc;
+}
+
+bool setRefined(Refined& refined, Value* v, c10::TypePtr t) {
+    auto it = refined.find(v);
+    if (it != refined.end() && *it->second == *t) return false;
+    refined[v] = std::move(t);
+    return true;
+}
+
+bool setTensorType(Value* v, const c10::TypePtr& t) {
+    auto tt = t ? t->cast<c10::TensorType>() : nullptr;
+    if (!tt || *v->type() == *tt) return false;
+    auto cur = v->type()->cast<c10::TensorType>();
+    if (cur && cur->sizes().concrete_sizes()) return false;  // already fully known
+    v->setType(tt);
+    return true;
+}
+
+bool refineLists(Block* block, Refined& refined) {
+    static const Symbol kMap = Symbol::fromQualString("tssa::ParallelMap");
+    bool changed = false;
+    for (Node* n : block->nodes()) {
+        if (n->kind() == prim::ListConstruct && n->output()->type()->isSubtypeOf(*c10::ListType::ofTensors())) {
+            std::vector<c10::TypePtr> elems;
+            for (Value* in : n->inputs()) elems.push_back(in->type());
+            changed = setRefined(refined, n->output(), c10::TupleType::create(elems)) || changed;
+        } else if (n->kind() == aten::__getitem__) {
+            if (auto tup = refinedList(refined, n->input(0))) {
+                auto idx = constInt(n->input(1));
+                const int64_t count = static_cast<int64_t>(tup->elements().size());
+                if (idx && *idx >= -count && *idx < count) {
+                    changed = setTensorType(n->output(), tup->elements()[*idx < 0 ? *idx + count : *idx]) || changed;
+                } else {
+                    changed = setTensorType(n->output(), unifyElements(tup)) || changed;  // list[i] with a run-time index
+                }
+            }
+        } else if (n->kind() == kMap) {
+            Block* body = n->blocks()[0];
+            for (size_t k = 1; k < n->inputs().size() && k < body->inputs().size(); ++k) {
+                if (auto tup = refinedList(refined, n->input(k))) changed = setTensorType(body->inputs()[k], unifyElements(tup)) || changed;
+            }
+        } else if ((n->kind() == aten::cat || n->kind() == aten::stack) && n->inputs().size() == 2) {
+            auto tup = refinedList(refined, n->input(0));
+            auto dim = constInt(n->input(1));
+            auto cur = n->output()->type()->cast<c10::TensorType>();
+            if (tup && dim && !tup->elements().empty() && !(cur && cur->sizes().concrete_sizes())) {
+                std::optional<Sizes> out;
+                c10::TensorTypePtr first;
+                bool ok = true;
+                for (const auto& e : tup->elements()) {
+                    auto tt = e->cast<c10::TensorType>();
+                    auto s = tt ? tt->sizes().concrete_sizes() : std::nullopt;
+                    if (!s) {
+                        ok = false;
+                        break;
+                    }
+                    if (!out) {
+                        first = tt;
+                        out = *s;
+                        const int64_t rank = static_cast<int64_t>(s->size()) + (n->kind() == aten::stack ? 1 : 0);
+                        const int64_t d = wrapDim(*dim, rank);
+                        if (d < 0 || d >= rank) {
+                            ok = false;
+                            break;
+                        }
+                        if (n->kind() == aten::stack) out->insert(out->begin() + d, 1);
+                    } else {
+                        const int64_t d = wrapDim(*dim, static_cast<int64_t>(out->size()));
+                        (*out)[d] += n->kind() == aten::stack ? 1 : (*s)[d];
+                    }
+                }
+                if (ok && out && first->scalarType()) {
+                    n->output()->setType(c10::TensorType::createContiguous(*first->scalarType(), first->device().value_or(c10::Device(c10::kCPU)), *out));
+                    changed = true;
+                }
+            }
+        }
+        for (Block* b : n->blocks()) changed = refineLists(b, refined) || changed;
+        // a map's result lists: `degree` elements of the body's result type
+        if (n->kind() == kMap) {
+            auto degree = constInt(n->input(0));
+            Block* body = n->blocks()[0];
+            if (degree && *degree >= 0 && *degree <= 4096) {
+                for (size_t k = 0; k < n->outputs().size() && k < body->outputs().size(); ++k) {
+                    if (!body->outputs()[k]->type()->cast<c10::TensorType>()) continue;
+                    std::vector<c10::TypePtr> elems(static_cast<size_t>(*degree), body->outputs()[k]->type());
+                    changed = setRefined(refined, n->output(k), c10::TupleType::create(elems)) || changed;
+                }
+            }
+        }
+    }
+    return changed;
+}
+
 bool refineBlock(Block* block) {
     bool changed = false;
     for (Node* n : block->nodes()) {
@@ -231,17 +358,42 @@ bool refineBlock(Block* block) {
 
 }  // namespace
 
-void InferShapes(const std::shared_ptr<Graph>& graph, const std::vector<c10::TypePtr>& type_hint) {
+std::vector<std::pair<Value*, c10::TypePtr>> InferShapesRefined(const std::shared_ptr<Graph>& graph,
+                                                                 const std::vector<c10::TypePtr>& type_hint) {
+    Refined refined;
     for (size_t i = 0; i < type_hint.size() && i < graph->inputs().size(); ++i) {
-        if (type_hint[i]) graph->inputs()[i]->setType(type_hint[i]);
+        if (!type_hint[i]) continue;
+        Value* in = graph->inputs()[i];
+        // a tuple hint for a list input describes its elements: kept on the side, the list type itself cannot carry it
+        if (type_hint[i]->cast<c10::TupleType>() && in->type()->cast<c10::ListType>()) refined[in] = type_hint[i];
+        else in->setType(type_hint[i]);
     }
-    // alternate between TorchScript's propagation (aten:: ops) and the immut:: table until nothing changes
+    // alternate between TorchScript's propagation (aten:: ops), the immut:: table and the list refinement until nothing
+    // changes
     for (int round = 0; round < 8; ++round) {
         PropagateInputShapes(graph);     // dtypes, devices, ranks
         std::shared_ptr<Graph> gref = graph;
-        PropagateShapesOnGraph(gref);    // concrete sizes through the aten:: shape functions
-        if (!refineBlock(graph->block())) break;
+        try {
+            PropagateShapesOnGraph(gref);  // concrete sizes through the aten:: shape functions
+        } catch (const c10::Error&) {
+            // TorchScript's symbolic shape analysis gives up on some list-taking operators (cat over a list input): the
+            // tables below and the list refinement still run
+        }
+        // (TorchScript's propagation resets what it does not know, so the list results are re-derived first every round)
+        bool any = false;
+        for (int inner = 0; inner < 8; ++inner) {
+            const bool l = refineLists(graph->block(), refined);
+            const bool t = refineBlock(graph->block());
+            any = any || t;
+            if (!l && !t) break;
+        }
+        if (!any) break;
     }
+    return std::vector<std::pair<Value*, c10::TypePtr>>(refined.begin(), refined.end());
+}
+
+void InferShapes(const std::shared_ptr<Graph>& graph, const std::vector<c10::TypePtr>& type_hint) {
+    InferShapesRefined(graph, type_hint);
 }
 
 }  // namespace functs_b200

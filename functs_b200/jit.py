@@ -45,6 +45,23 @@ def fait_pipeline(g: torch.Graph, type_hint=()) -> None:
     _C._jit_pass_fait_pipeline(g, list(type_hint))
 
 
+def type_hint_of(value):
+    """Type hint of one example input, as the reference's extract_type_hint_from_tensor builds it (functs/jit/_script.py:
+    26-45): dtype + sizes + device for a tensor, a tuple of those for a list / tuple of tensors, None otherwise."""
+    if isinstance(value, torch.Tensor):
+        return torch._C.TensorType.create_from_tensor(value)
+    if isinstance(value, (list, tuple)) and value and all(isinstance(v, torch.Tensor) for v in value):
+        return torch._C.TupleType([torch._C.TensorType.create_from_tensor(v) for v in value])
+    return None
+
+
+def shape_infer(g: torch.Graph, example_inputs=(), has_self: bool = False) -> dict:
+    """Counterpart of the reference's functs.jit.shape_infer (functs/jit/_script.py:48-51): refines the graph's value types
+    from example inputs in place and returns {debug name of a list value: tuple type of its elements}."""
+    hints = ([None] if has_self else []) + [type_hint_of(v) for v in example_inputs]
+    return dict(_C._jit_pass_fait_shape_infer(g, hints))
+
+
 def build(fn, example_inputs=(), add_clone: bool = False):
     """Counterpart of the reference's functs.jit.build(fn, example_inputs) (functs/jit/_build.py): script, optionally
     clone tensor inputs, run the pipeline with the example inputs' types as hints.  Returns the scripted function; its
@@ -59,9 +76,7 @@ def build(fn, example_inputs=(), add_clone: bool = False):
     g = jit_fn.graph
     if add_clone:
         _C._jit_pass_dumb_remove_inter_precedure_mutation(g)
-    hints = []
-    for v in example_inputs:
-        hints.append(torch._C.TensorType.create_from_tensor(v) if isinstance(v, torch.Tensor) else None)
+    hints = [type_hint_of(v) for v in example_inputs]
     if not inspect.isfunction(fn):
         hints = [None] + hints  # self
     from . import patterns

@@ -257,3 +257,30 @@ def test_fuse_tensorexpr_entry_point_groups_a_functionalized_graph():
     fn = torch._C._create_function_from_graph("f", g)
     x = torch.randn(4, 5, generator=torch.Generator().manual_seed(1))
     assert torch.allclose(fn(x), f(x))
+
+
+def test_shape_inference_refines_lists_of_tensors():
+    """Tuple type hints describe the elements of List[Tensor] inputs; list[i] with a constant index, the element
+    parameters of a map and cat / stack over a list take their types from there (the reference's refined list types)."""
+    def heads(feats: List[torch.Tensor]):
+        a = feats[0] * 2.0
+        b = torch.cat(feats, dim=0)
+        return a, b
+    feats, _ = make_lists()
+    g = torch.jit.script(heads).graph.copy()
+    refined = fjit.shape_infer(g, (feats,))
+    assert any(t.kind() == "TupleType" for t in refined.values())
+    by_kind = {n.kind(): n for n in g.nodes()}
+    assert by_kind["aten::__getitem__"].output().type().sizes() == [5, 6]
+    assert by_kind["aten::mul"].output().type().sizes() == [5, 6]
+    assert by_kind["aten::cat"].output().type().sizes() == [5 + 6 + 7, 6]
+    # inside the pipeline: the element parameters of the map over scales get the unified element type (rank and dtype known,
+    # the row count differs per scale)
+    g2 = torch.jit.script(scales_decode).graph.copy()
+    fjit.functionalize_graph(g2)
+    _C._jit_pass_parallelize_loops(g2)
+    fjit.shape_infer(g2, make_lists())
+    m = [n for n in g2.nodes() if n.kind() == "tssa::ParallelMap"][0]
+    params = list(list(m.blocks())[0].inputs())
+    assert params[1].type().dim() == 2 and params[1].type().scalarType() == "Float"
+    assert params[1].type().sizes() is None or params[1].type().sizes()[1] == 6
