@@ -332,6 +332,58 @@ def extra_workloads(torch, fb, W, hbm_peak, peak_kind="measured"):
     return out
 
 
+def simple_ops(torch, fb, hbm_peak, peak_kind):
+    """The two single-group programs the reference times beside its models, three ways on the same device inputs: eager
+    PyTorch (views and in-place writes), the functionalized program node by node (every Access / Assign operator is one of
+    this library's stand-alone kernels), and the whole fusion group as ONE launch of the generic program kernel."""
+    from functs_b200 import jit as J, simpleops
+    out = {}
+    g = torch.Generator().manual_seed(4242)
+    n_sets = 12                                   # 12 x 12.8 MB of images: no call finds its input in the 126 MB L2
+    imgs = [torch.rand(800, 1333, 3, generator=g).cuda() for _ in range(n_sets)]
+    boxes = [torch.randn(3000, 4, generator=g).cuda()]
+    offs = [torch.randn(3000, 4, generator=g).cuda()]
+    cases = {
+        "normalize_800x1333x3": (simpleops.normalize, [(im, 0.45, 4.4) for im in imgs], 2 * 800 * 1333 * 3 * 4),
+        "offset2bbox_3000x4": (simpleops.offset2bbox, [(boxes[0], offs[0])], 3 * 3000 * 4 * 4),
+    }
+    for name, (fn, arg_sets, alg_bytes) in cases.items():
+        want = fn(*arg_sets[0])
+        node_by_node = J.script(fn)
+        fused = J.build(fn, arg_sets[0])
+        it = [0]
+
+        def runner(f):
+            def run():
+                a = arg_sets[it[0] % len(arg_sets)]
+                it[0] += 1
+                return f(*a)
+            return run
+        rec = {}
+        for label, f in (("eager", fn), ("access_assign_kernels", node_by_node), ("one_launch", fused)):
+            it[0] = 0
+            got = f(*arg_sets[0])
+            if not torch.equal(got, want):
+                raise SystemExit(f"bench: {name}/{label} differs from eager by {float((got - want).abs().max())}")
+            r = runner(f)
+            for _ in range(5):
+                r()
+            l0 = fb.launch_count()
+            r()
+            torch.cuda.synchronize()
+            launches = fb.launch_count() - l0
+            rec[label] = {"latency_us": time_events(r, 50, torch) * 1e3, "launches_of_this_library": launches}
+        i0 = J.interpreted_functor_runs()
+        fused(*arg_sets[0])
+        rec["one_launch"]["interpreted_functors"] = J.interpreted_functor_runs() - i0
+        rec["roofline"] = hbm_roofline("generic_group_kernel_param", alg_bytes, rec["one_launch"]["latency_us"] * 1e-3,
+                                       hbm_peak, peak_kind,
+                                       "time of the whole call on the stream (host-side program flattening included when "
+                                       "the device is idle)")
+        out[name] = rec
+    return out
+
+
 def bind_to_gpu_numa_node(index: int):
     """Pins this rank's host threads to the CPU cores next to its GPU (NVML's ideal affinity mask; read-only query), before
     any host buffer is allocated: the pinned input buffers are then first touched, and so placed, on the GPU's own NUMA
@@ -599,7 +651,12 @@ def run_single_workload(args):
         x, w_ih, w_hh, b_ih, b_hh = W.make_lstm_inputs(64, b, 512)
         mod = fb.workloads.LSTM(w_ih, w_hh, b_ih, b_hh, device=dev)
         xd = x.to(dev)
-        fn = lambda: mod.forward_device(xd)
+        fn = lambda: mod.forward_device(xd, args.lstm_mode)
+    elif args.only == "normalize":
+        from functs_b200 import jit as J, simpleops
+        img = torch.rand(800, 1333, 3, device=dev)
+        built = J.build(simpleops.normalize, (img, 0.45, 4.4))
+        fn = lambda: built(img, 0.45, 4.4)
     elif args.only == "get_started":
         a, bb, n = W.make_get_started_inputs()
         fn = lambda: fb.workloads.get_started(a, bb.to(dev), n)
@@ -624,9 +681,11 @@ def main():
     ap.add_argument("--in-flight", type=int, default=3, choices=[1, 2, 3, 4],
                     help="batches in flight in the throughput measurement (one stream each; 1 = strictly one after the other; measured on one B200: 129 / 98 / 92 / 91 us per step for 1 / 2 / 3 / 4)")
     ap.add_argument("--no-extra", action="store_true", help="skip the cpu_baseline leg and the other workloads")
-    ap.add_argument("--only", default=None, choices=["yolo", "ssd", "yolact", "lstm", "get_started"],
+    ap.add_argument("--only", default=None, choices=["yolo", "ssd", "yolact", "lstm", "get_started", "normalize"],
                     help="run a few calls of one workload and exit (for profiler captures)")
     ap.add_argument("--batch", type=int, default=8, help="batch size for --only")
+    ap.add_argument("--lstm-mode", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="--only lstm: 0 library default, 1 CUDA cores, 2 tcgen05 projection and recurrence, 3 tcgen05 projection")
     args = ap.parse_args()
     if args.only is not None:
         run_single_workload(args)

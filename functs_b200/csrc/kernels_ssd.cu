@@ -219,6 +219,7 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
                 // (Measured and dropped: the centre form (hw_a + hw_b) - |cx_a - cx_b| as an add / multiply upper bound of
                 // the overlap.  It is loose when one box contains the other, which priors of one cell do all the time:
                 // the exact test ran so often that the matrix took 24 us per list instead of 15.)
+                // (Also measured and dropped: all votes of a batch first, then the rows with a candidate: 20 us.)
 #pragma unroll
                 for (int u = 0; u < kSsdRowBatch; ++u) {
                     const int i = i0 + u;

@@ -460,6 +460,16 @@ struct Emitter {
             const bool ok = c.add >= lo && c.add < hi && ((c.add - lo) % step) == 0;
             return ok ? -1 : -2;
         }
+        // the coordinate runs over [0, extent) of its output dimension: a test that every value of v = mul * x + add
+        // passes (an assignment to a whole dimension, `t[:] = ...`) or fails costs nothing and, more to the point, does
+        // not duplicate the operand that both of its branches would otherwise carry
+        {
+            const int64_t extent = P.shape[c.dim];
+            const int64_t v0 = c.add, v1 = c.mul * (extent - 1) + c.add;
+            const int64_t vmin = std::min(v0, v1), vmax = std::max(v0, v1);
+            if (vmax < lo || vmin >= hi) return -2;
+            if (vmin >= lo && vmax < hi && (step == 1 || (c.mul % step == 0 && (c.add - lo) % step == 0))) return -1;
+        }
         G_REQUIRE(npreds < FB_G_MAX_PREDS, "too many predicates");
         G_REQUIRE(fits32(c.mul) && fits32(c.add) && fits32(lo) && fits32(hi) && fits32(step), "predicate out of 32-bit range");
         functs_b200_gpred& q = P.pred[npreds];
@@ -496,8 +506,10 @@ struct Emitter {
                 return;
             }
             case Expr::Leaf: {
-                G_REQUIRE(nloads < FB_G_MAX_LOADS, "too many loads");
-                functs_b200_gload& L = P.load[nloads];
+                // described in a scratch slot first: a load equal to an earlier one (the same element of the same tensor,
+                // reached again through another branch or a shared subexpression) reuses that slot
+                functs_b200_gload L;
+                std::memset(&L, 0, sizeof(L));
                 L.tensor = e->tensor;
                 L.dtype = e->dtype;
                 L.nterms = 0;
@@ -522,7 +534,15 @@ struct Emitter {
                 }
                 G_REQUIRE(fits32(base), "offset out of range");
                 L.base = static_cast<int32_t>(base);
-                push(FB_G_LOAD, static_cast<uint16_t>(nloads++));
+                int slot = -1;
+                for (int k = 0; k < nloads && slot < 0; ++k)
+                    if (std::memcmp(&P.load[k], &L, sizeof(L)) == 0) slot = k;
+                if (slot < 0) {
+                    G_REQUIRE(nloads < FB_G_MAX_LOADS, "too many loads");
+                    slot = nloads++;
+                    P.load[slot] = L;
+                }
+                push(FB_G_LOAD, static_cast<uint16_t>(slot));
                 grow(1);
                 return;
             }

@@ -270,7 +270,7 @@ enum {
     /* binary */ FB_G_ADD = 30, FB_G_SUB = 31, FB_G_MUL = 32, FB_G_DIV = 33, FB_G_MIN = 34, FB_G_MAX = 35, FB_G_GT = 36,
     FB_G_GE = 37, FB_G_LT = 38, FB_G_LE = 39, FB_G_EQ = 40, FB_G_NE = 41
 };
-#define FB_G_MAX_INSTR 160
+#define FB_G_MAX_INSTR 256
 #define FB_G_MAX_LOADS 24
 #define FB_G_MAX_PREDS 24
 #define FB_G_MAX_TERMS 6

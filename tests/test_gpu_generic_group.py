@@ -56,7 +56,7 @@ def check(env, fn, args, expect_generic=True):
     n_groups = J.count_groups(built.graph)
     assert n_groups >= 1
     assert all(r == "" for r in J.functor_regions(built.graph)), "these programs match no precompiled region"
-    want = fn(*[[t.clone() for t in a] if isinstance(a, list) else a.clone() for a in args])
+    want = fn(*[[t.clone() for t in a] if isinstance(a, list) else (a.clone() if isinstance(a, torch.Tensor) else a) for a in args])
     built(*args)  # first run builds the executor
     torch.cuda.synchronize()
     l0, g0, i0 = fb.launch_count(), J.generic_group_runs(), J.interpreted_functor_runs()
@@ -130,3 +130,15 @@ def test_split_map_runs_two_launches_plus_the_loop_between(env):
     assert fb.launch_count() - l0 == 2 and J.generic_group_runs() - g0 == 2 and J.interpreted_functor_runs() == i0, J.last_generic_refusal()
     for a, b in zip(got, want):
         assert torch.allclose(a, b, rtol=1e-6, atol=1e-6)
+
+
+def test_reference_simple_programs_are_one_launch_each(env):
+    """The channel-swap normalisation on [800, 1333, 3] and the step-4 box decoding on [3000, 4]: one generic launch each,
+    equal to eager bit for bit."""
+    from functs_b200 import simpleops
+    g = torch.Generator().manual_seed(5)
+    img = torch.rand(800, 1333, 3, generator=g).cuda()
+    assert check(env, simpleops.normalize, (img, 0.45, 4.4)) == (1, 1, 1, 0)
+    boxes = (torch.rand(3000, 4, generator=g) * 100).cuda()
+    offs = torch.randn(3000, 4, generator=g).cuda()
+    assert check(env, simpleops.offset2bbox, (boxes, offs)) == (1, 1, 1, 0)
