@@ -92,34 +92,22 @@ ssd_softmax_decode_kernel(const float* __restrict__ loc, const float* __restrict
 
 // ---- group 2 ------------------------------------------------------------------------------------------------
 constexpr int kSsdNmsThreads = 256;
+constexpr int kSsdNmsMinBlocks = 6;  // CTAs per SM the register allocation aims at (27 KB of shared memory each)
 constexpr int kSsdSelCap = 256;
 constexpr int kSsdWords = kSsdSelCap / 32;
 
-// The class's scores (one contiguous run of the class-major array) are staged in shared memory by one bulk copy and
-// then read twice (histogram pass, collection pass).  A class with more scores than the staging area holds is read
-// from global memory both times.
-struct ClassScores {
-    static constexpr bool kDenseScores = true;
-    const float* s;  // shared or global
-    float thr;
-    bool vec4;       // s is 16-byte aligned
-    __device__ __forceinline__ uint64_t operator()(int i) const {
-        float v = s[i];
-        return (v > thr) ? make_key(v, static_cast<uint32_t>(i)) : 0ull;
-    }
-};
-
-constexpr int kSsdStageMax = 16384;  // scores of one class that the staging area may hold (64 KB)
 constexpr size_t kSsdSelBytes = (sizeof(SelectSmem<kSsdSelCap>) + 127) / 128 * 128;
 constexpr int kSsdRowBatch = 16;  // rows of the suppression matrix one warp tests at a time (4: 419 us, 8: 378, 16: 370)
 
-// dynamic smem: [SelectSmem<256>][staged scores]; after the selection the NMS boxes and the 256 x 8 mask words live in
-// the selection's boundary list and histogram, which are not needed any more
-__global__ void __launch_bounds__(kSsdNmsThreads, 4)
+// dynamic smem: [SelectSmem<256>][kCandCap candidate keys]; after the selection the NMS boxes and the 256 x 8 mask words
+// live in the selection's boundary list and histogram, which are not needed any more.  The class's scores (one contiguous
+// run of the class-major array) are read from global memory once: a sampled score floor, one collection pass, and the
+// exact selection on the few hundred candidates (block_select_topk_sampled).
+__global__ void __launch_bounds__(kSsdNmsThreads, kSsdNmsMinBlocks)
 ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ scores_cm, int num_priors, int num_classes,
                      float score_thr, uint32_t hist_base, int hist_shift, int topk, float iou_thr, float thr_lo,
                      float thr_hi, float* __restrict__ dets, int64_t* __restrict__ prior_ids,
-                     int32_t* __restrict__ out_counts, int stage) {
+                     int32_t* __restrict__ out_counts) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     SelectSmem<kSsdSelCap>& sm = *reinterpret_cast<SelectSmem<kSsdSelCap>*>(smem_raw);
     static_assert(sizeof(NmsBox) * kSsdSelCap <= sizeof(sm.binlist) && sizeof(uint32_t) * kSsdSelCap * kSsdWords <= sizeof(sm.hist),
@@ -131,43 +119,17 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
     float4* sxy = reinterpret_cast<float4*>(sm.binlist);
     float* sarea = reinterpret_cast<float*>(sxy + kSsdSelCap);
     uint32_t* smask = reinterpret_cast<uint32_t*>(sm.hist);
-    float* sscore = reinterpret_cast<float*>(smem_raw + kSsdSelBytes);
+    uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + kSsdSelBytes);
     __shared__ uint32_t keep_words[kSsdWords];
     __shared__ int word_prefix[kSsdWords + 1];
     __shared__ uint32_t or_words[2 * kSsdWords];
-    __shared__ __align__(8) uint64_t bar;
 
     const int cls = blockIdx.x, img = blockIdx.y;
     const int t = threadIdx.x;
     const float* src = scores_cm + (static_cast<int64_t>(img) * num_classes + cls) * num_priors;
-    const float* score_ptr = src;
-    if (stage != 0) {
-        bool staged = false;
-        if (stage == 2) {  // the run starts on a 16-byte boundary and is a multiple of 16 bytes long
-            if (t == 0) {
-                mbar_init(&bar, 1);
-                fence_barrier_init();
-            }
-            __syncthreads();
-            if (t == 0) {
-                mbar_arrive_expect_tx(&bar, static_cast<uint32_t>(num_priors) * 4u);
-                bulk_copy_g2s(sscore, src, static_cast<uint32_t>(num_priors) * 4u, &bar);
-            }
-            staged = mbar_wait_bounded(&bar, 0, 400000u);
-            staged = __syncthreads_and(staged ? 1 : 0) != 0;
-        }
-        if (staged) {
-            score_ptr = sscore;
-        } else if (stage == 1) {
-            for (int i = t; i < num_priors; i += kSsdNmsThreads) sscore[i] = __ldg(src + i);
-            __syncthreads();
-            score_ptr = sscore;
-        }
-        // a copy that did not land in time (never observed): the scores are read from global memory instead; the
-        // landing zone is not used for anything else
-    }
-    ClassScores kf{score_ptr, score_thr, (reinterpret_cast<uintptr_t>(score_ptr) & 15) == 0};
-    const int n = block_select_topk_binned<kSsdNmsThreads, kSsdSelCap, 8>(kf, num_priors, topk, hist_base, hist_shift, sm);
+    const bool vec4 = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+    const int n = block_select_topk_sampled<kSsdNmsThreads, kSsdSelCap>(src, vec4, score_thr, num_priors, topk, hist_base,
+                                                                        hist_shift, sm, cand);
     // (block_select_topk ends with a barrier when n > 1; make the hand-over explicit)
     __syncthreads();
 
@@ -328,11 +290,7 @@ int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_
     FB_REQUIRE(iou_thr > 0.0f && iou_thr < 1.0f, "ssd_class_nms: iou threshold must be in (0, 1)");
     FB_REQUIRE(((reinterpret_cast<uintptr_t>(boxes) | reinterpret_cast<uintptr_t>(scores_cm)) & 15) == 0,
                "ssd_class_nms: boxes and scores must be 16-byte aligned");
-    // stage: 0 = scores read from global memory twice, 1 = staged by plain loads, 2 = staged by one bulk copy
-    const int stage = num_priors > kSsdStageMax ? 0
-                      : ((reinterpret_cast<uintptr_t>(scores_cm) & 15) == 0 && num_priors % 4 == 0) ? 2 : 1;
-    const size_t stage_bytes = stage ? (static_cast<size_t>(num_priors) * 4 + 15) / 16 * 16 : 0;
-    const size_t smem = kSsdSelBytes + stage_bytes;
+    const size_t smem = kSsdSelBytes + sizeof(uint64_t) * kCandCap;
     FB_TRY(check_cuda(cudaFuncSetAttribute(ssd_class_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem)),
                       "ssd_class_nms attr"));
@@ -341,8 +299,7 @@ int functs_b200_ssd_class_nms(const float* boxes, const float* scores_cm, int32_
     const HistParams hp = hist_params_for(score_thr);
     ssd_class_nms_kernel<<<grid, kSsdNmsThreads, smem, as_stream(stream)>>>(boxes, scores_cm, num_priors, num_classes,
                                                                             score_thr, hp.base, hp.shift, topk, iou_thr,
-                                                                            thr_lo, thr_hi, dets, prior_ids, out_counts,
-                                                                            stage);
+                                                                            thr_lo, thr_hi, dets, prior_ids, out_counts);
     count_launch();
     return check_launch("ssd_class_nms_kernel");
 }

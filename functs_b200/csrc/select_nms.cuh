@@ -525,6 +525,168 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
     return result;
 }
 
+// A plain fp32 score array as a key function (key = score above thr, index); kDenseScores lets the binned selection
+// read the array four scores at a time when vec4 says it is 16-byte aligned.
+struct DenseScores {
+    static constexpr bool kDenseScores = true;
+    const float* s;
+    float thr;
+    bool vec4;
+    __device__ __forceinline__ uint64_t operator()(int i) const {
+        const float v = s[i];
+        return (v > thr) ? make_key(v, static_cast<uint32_t>(i)) : 0ull;
+    }
+};
+
+// Keys that already sit in a list (shared memory): the non-dense form of the key functions above.
+struct ListKeys {
+    static constexpr bool kDenseScores = false;
+    const uint64_t* k;
+    __device__ __forceinline__ uint64_t operator()(int i) const { return k[i]; }
+};
+
+constexpr int kCandCap = 1024;  // candidate keys block_select_topk_sampled may collect before it gives up
+
+// The largest digit d with (entries of hist in buckets >= d) >= target, or -1 when the histogram holds fewer.
+// hist is left as it is.  All NT threads must call it.
+template <int NT>
+__device__ int block_hist_rank_bucket(const int* hist, int* red_cnt, int* slot, int target) {
+    static_assert(kHistBins % NT == 0, "the histogram must split evenly over the block");
+    constexpr int per = kHistBins / NT;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int h[per];
+    int s = 0;
+#pragma unroll
+    for (int k = 0; k < per; ++k) {
+        h[k] = hist[tid * per + k];
+        s += h[k];
+    }
+    int incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_down_sync(kFullMask, incl, o);
+        if (lane + o < 32) incl += t;
+    }
+    if (lane == 0) red_cnt[warp] = incl;
+    if (tid == 0) *slot = -1;
+    __syncthreads();
+    int higher = 0;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) higher += (w > warp) ? red_cnt[w] : 0;
+    incl += higher;
+    const int suf = incl - s;
+    if (suf < target && incl >= target) {
+        int cum = suf, d = 0;
+        bool found = false;
+#pragma unroll
+        for (int k = per - 1; k >= 0; --k) {
+            if (!found) {
+                if (cum + h[k] >= target) {
+                    found = true;
+                    d = k;
+                } else {
+                    cum += h[k];
+                }
+            }
+        }
+        *slot = tid * per + d;
+    }
+    __syncthreads();
+    return *slot;
+}
+
+// Same result as block_select_topk_binned for a plain fp32 score array in GLOBAL memory (key = score above thr, index),
+// reading the array once: a spread sample of the scores (one 16-byte chunk per thread) gives a score floor that should
+// leave a few hundred candidates; one pass collects every key at or above the floor into `cand` (kCandCap keys of
+// shared memory, appended with one atomic per warp and round); the exact selection then runs on that list.  The floor
+// is only a guess, the count decides: with fewer than topk candidates (while keys below the floor exist) or more than
+// kCandCap, the two-pass selection over the whole array runs instead, so the result never depends on the sample.
+template <int NT, int SELCAP>
+__device__ int block_select_topk_sampled(const float* __restrict__ s, bool vec4, float thr, int n, int topk,
+                                         uint32_t hist_base, int hist_shift, SelectSmem<SELCAP>& sm, uint64_t* cand) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n4 = vec4 ? (n >> 2) : 0;
+    const float4* s4 = reinterpret_cast<const float4*>(s);
+    uint32_t lo_bits = 0u;  // 0: every score above thr is a candidate
+    if (n > kCandCap && n4 >= NT) {
+        for (int i = tid; i < kHistBins; i += NT) sm.hist[i] = 0;
+        __syncthreads();
+        const float4 q = __ldg(s4 + static_cast<int>((static_cast<int64_t>(tid) * n4) / NT));
+        auto add = [&](float v) {
+            if (v > thr) atomicAdd(&sm.hist[hist_digit(static_cast<uint64_t>(__float_as_uint(v)) << 32, hist_base, hist_shift)], 1);
+        };
+        add(q.x);
+        add(q.y);
+        add(q.z);
+        add(q.w);
+        __syncthreads();
+        // rank in the sample that corresponds to 1.8 * topk in the whole array (the spread of a count of a few dozen
+        // sample hits is about a sixth of it: falling short of topk takes three standard deviations)
+        const int target = static_cast<int>((static_cast<int64_t>(topk) * (4 * NT) * 9) / (static_cast<int64_t>(n) * 5)) + 4;
+        const int d = block_hist_rank_bucket<NT>(sm.hist, sm.red_cnt, &sm.digit, target);
+        if (d > 0) lo_bits = hist_base + (static_cast<uint32_t>(d) << hist_shift);
+    }
+    if (tid == 0) sm.bin_cnt = 0;
+    __syncthreads();
+    // collection: lane-local hit counts, a warp prefix sum, one atomic per warp and round
+    auto append = [&](const uint64_t (&k)[4], int cnt) {
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += t;
+        }
+        const int total = __shfl_sync(kFullMask, incl, 31);
+        if (total != 0) {
+            int base = 0;
+            if (lane == 31) base = atomicAdd(&sm.bin_cnt, total);
+            base = __shfl_sync(kFullMask, base, 31);
+            int pos = base + incl - cnt;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (k[e] != 0ull) {
+                    if (pos < kCandCap) cand[pos] = k[e];
+                    ++pos;
+                }
+            }
+        }
+    };
+    auto key_of = [&](float v, int i) -> uint64_t {
+        return (v > thr && __float_as_uint(v) >= lo_bits) ? make_key(v, static_cast<uint32_t>(i)) : 0ull;
+    };
+    constexpr int UN = 3;
+    for (int c0 = warp * 32 + lane; __any_sync(kFullMask, c0 < n4); c0 += NT * UN) {
+        float4 q[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int c = c0 + u * NT;
+            q[u] = c < n4 ? __ldg(s4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int c = c0 + u * NT;
+            uint64_t k[4];
+            k[0] = key_of(q[u].x, 4 * c);
+            k[1] = key_of(q[u].y, 4 * c + 1);
+            k[2] = key_of(q[u].z, 4 * c + 2);
+            k[3] = key_of(q[u].w, 4 * c + 3);
+            append(k, (k[0] != 0ull) + (k[1] != 0ull) + (k[2] != 0ull) + (k[3] != 0ull));
+        }
+    }
+    for (int i0 = 4 * n4 + warp * 32; i0 < n; i0 += NT) {  // scalar tail (or the whole array when it is not 16-byte aligned)
+        const int i = i0 + lane;
+        uint64_t k[4] = {i < n ? key_of(__ldg(s + i), i) : 0ull, 0ull, 0ull, 0ull};
+        append(k, k[0] != 0ull ? 1 : 0);
+    }
+    __syncthreads();
+    const int c = sm.bin_cnt;
+    __syncthreads();  // (the selections below reset the counter)
+    if (c > kCandCap || (lo_bits != 0u && c < topk)) {
+        return block_select_topk_binned<NT, SELCAP, 8>(DenseScores{s, thr, vec4}, n, topk, hist_base, hist_shift, sm);
+    }
+    return block_select_topk_binned<NT, SELCAP, 2>(ListKeys{cand}, c, topk, hist_base, hist_shift, sm);
+}
+
 // ---- IoU suppression test ------------------------------------------------------------------------
 struct NmsBox {
     float x1, y1, x2, y2, area;
