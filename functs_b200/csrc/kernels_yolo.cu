@@ -788,6 +788,7 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
 
     if (producer) {
         // refill a buffer as soon as all consumer warps have released it
+        int floor_seen = 0;
 #pragma unroll 1
         for (int step = kStStages; step < kStSteps; ++step) {
             const int buf = step % kStStages;
@@ -799,6 +800,15 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             }
             ok = __shfl_sync(kFullMask, ok, 0);
             if (!ok) break;
+            // The image's bucket as other CTAs published it: this warp asks for the word after every refill and hands the
+            // answer of the previous request on to the consumers through shared memory.  The request is in flight while
+            // the warp waits for the next buffer, so nobody ever waits for it.  (The consumer warps used to load the word
+            // themselves, one step ahead: every class step then took at least one L2 round trip, about a microsecond
+            // under load, which was most of the kernel's time.)
+            if (pruning && P.floor != nullptr && lane == 0) {
+                if (floor_seen > *reinterpret_cast<volatile int*>(&sm.prune)) *reinterpret_cast<volatile int*>(&sm.prune) = floor_seen;
+                floor_seen = __ldcg(P.floor + img);
+            }
             // A look at the histogram delays this warp's next refill by several memory round trips, and measured end to
             // end it costs more than it saves; the CTAs of the plain-load levels take the looks instead and every other
             // CTA reads the bucket they publish (P.floor).  Only a pyramid without a plain-load level scans here (first
@@ -821,16 +831,11 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
     const unsigned lt = (1u << lane) - 1u;
     const StEvalArgs ea{P.thr, P.hist_base, P.hist_shift, ghist, gkeys, gcount, P.capacity, P.status};
     int fill = 0, head = 0, tail = 0;  // warp-uniform
-    int published = 0;  // the image's bucket as other CTAs published it: loaded during one step, used at the next
 #pragma unroll 1
     for (int step = 0; step < kStSteps; ++step) {
         const int buf = step % kStStages;
         if (pruning) {
-            int now = *reinterpret_cast<volatile int*>(&sm.prune);  // one broadcast read: the same for all lanes
-            if (P.floor != nullptr) {
-                now = max(now, __shfl_sync(kFullMask, published, 0));
-                if (lane == 0) published = __ldcg(P.floor + img);  // consumed one step later: the latency is hidden
-            }
+            const int now = *reinterpret_cast<volatile int*>(&sm.prune);  // one broadcast read: the same for all lanes
             if (now > prune) {  // raise the cuts of this thread's survivors
                 prune = now;
                 floor_score = __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift));
@@ -860,24 +865,48 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
             float v[kStClasses];
 #pragma unroll
             for (int u = 0; u < kStClasses; ++u) v[u] = sm.ring[buf][u][ls];
-            // once the pruning floor is up most steps have no hit at all in a warp: one vote then skips the packing
-            float vmax = v[0];
+            // All votes of the step first (independent of one another), then one packing round: once the pruning floor is
+            // up a step has a handful of hits per warp or none, and the warp's critical path is what a class step costs.
+            unsigned m[kStClasses];
+            int fresh = 0;
 #pragma unroll
-            for (int u = 1; u < kStClasses; ++u) vmax = fmaxf(vmax, v[u]);
-            if (!__any_sync(kFullMask, vmax > vc)) continue;
+            for (int u = 0; u < kStClasses; ++u) {
+                m[u] = __ballot_sync(kFullMask, v[u] > vc);
+                fresh += __popc(m[u]);
+            }
+            if (fresh == 0) continue;
+            if (tail - head + fresh <= kStQueue) {
+                int off = tail;
+#pragma unroll
+                for (int u = 0; u < kStClasses; ++u) {
+                    if (v[u] > vc) {
+                        YoloHit e;
+                        e.v = v[u];
+                        e.meta = meta0 + static_cast<uint32_t>(u);
+                        ws.queue[(off + __popc(m[u] & lt)) & (kStQueue - 1)] = e;
+                    }
+                    off += __popc(m[u]);
+                }
+                tail = off;
+                __syncwarp();
+                while (tail - head >= 32) {
+                    fill = st_eval_batch(sm.live, &ws, head, 32, ea, prune, fill);
+                    head += 32;
+                }
+                continue;
+            }
+            // more hits than the queue takes at once (no floor yet, or a dense image): kStSub classes at a time
 #pragma unroll
             for (int h = 0; h < kStClasses; h += kStSub) {
 #pragma unroll
                 for (int u = 0; u < kStSub; ++u) {
-                    const bool pred = v[h + u] > vc;
-                    const unsigned m = __ballot_sync(kFullMask, pred);
-                    if (pred) {
+                    if (v[h + u] > vc) {
                         YoloHit e;
                         e.v = v[h + u];
                         e.meta = meta0 + static_cast<uint32_t>(h + u);
-                        ws.queue[(tail + __popc(m & lt)) & (kStQueue - 1)] = e;
+                        ws.queue[(tail + __popc(m[h + u] & lt)) & (kStQueue - 1)] = e;
                     }
-                    tail += __popc(m);
+                    tail += __popc(m[h + u]);
                 }
                 __syncwarp();
                 while (tail - head >= 32) {

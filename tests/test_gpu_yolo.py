@@ -133,6 +133,16 @@ def test_yolo_full_batch_against_oracle(fb, oracle):
     assert batch == 64
 
 
+def test_yolo_fewer_candidates_than_topk_at_config_shapes(fb, oracle):
+    """Logits shifted down: about 650 / 190 candidates per image, fewer than the top-k keeps, so nothing is pruned and the
+    selection takes every candidate (the path the benchmark's inputs never reach at these shapes); with a shift of 1.0
+    (about 2100 candidates) the pruning bucket stays low and almost every candidate is recorded."""
+    for shift in (1.25, 1.5, 1.0):
+        maps = [m - shift for m in W.make_yolo_inputs(3)]
+        exact, batch = check_batch(fb, oracle, maps, (13, 26, 52))
+        print(f"shift {shift}: exact end-to-end images: {exact}/{batch}")
+
+
 def test_yolo_low_threshold_and_small_topk(fb):
     sizes = (13, 26, 52)
     maps = W.make_yolo_inputs(1)
