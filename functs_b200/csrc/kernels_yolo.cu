@@ -334,10 +334,14 @@ struct YoloLiveWarp {
 
 struct YoloLiveSmem {
     int prune;  // latest pruning bucket published for this CTA
+    int done_warps;  // consumer warps that have finished (the scanner warp stops at kLiveThreads / 32)
     YoloLive live[kLiveTile];
     YoloLiveWarp w[kLiveThreads / 32];
     int warp_cnt[kLiveThreads / 32];
 };
+
+// barrier of the kLiveThreads consumer threads of a plain-load CTA (the ninth warp does not take part)
+__device__ __forceinline__ void live_sync() { asm volatile("bar.sync 1, %0;" ::"n"(256) : "memory"); }
 
 __device__ __forceinline__ void live_flush(YoloLiveWarp& ws, int& fill, uint64_t* gkeys, int32_t* gcount, int64_t capacity,
                                            int32_t* status) {
@@ -419,9 +423,9 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
         // a bucket that an earlier CTA derived from the image's histogram stays valid: one load instead of a scan
         int d = 0;
         if (pruning) d = P.floor != nullptr ? __ldcg(P.floor + img) : prune_digit_regs(ghist, P.prune_topk);
-        if (lane == 0) sm.prune = d;
+        if (lane == 0) atomicMax(&sm.prune, d);  // (the scanner warp may have been there already)
     }
-    __syncthreads();
+    live_sync();
     int prune = sm.prune;  // candidates of buckets below this are dropped
     // lowest score of bucket `prune`; 0 while nothing is pruned
     float floor_score = prune > 0 ? __uint_as_float(P.hist_base + (static_cast<uint32_t>(prune) << P.hist_shift)) : 0.0f;
@@ -457,7 +461,7 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
         mine += __popc(bal[q]);
     }
     if (lane == 0) sm.warp_cnt[warp] = mine;
-    __syncthreads();
+    live_sync();
     int wbase = 0, total = 0;
 #pragma unroll
     for (int w = 0; w < kLiveThreads / 32; ++w) {
@@ -477,7 +481,7 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
         }
         wbase += __popc(bal[q]);
     }
-    __syncthreads();
+    live_sync();
 
     // ---- phase 2: thread k walks the class logits of survivor k ----
     YoloLiveWarp& ws = sm.w[warp];
@@ -503,16 +507,7 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
 #pragma unroll 1
         for (int c0 = 0; c0 < kYoloClasses; c0 += kYoloChunk) {
             if (pruning) {
-                // warp 0 takes a fresh look at the histogram twice per pass; every warp picks the result up when it
-                // gets there (a plain shared-memory word: late or early, any published bucket is valid)
-                if (warp == 0 && (c0 == 2 * kYoloChunk || c0 == 5 * kYoloChunk)) {
-                    const int d = prune_digit_regs(ghist, P.prune_topk);
-                    if (lane == 0 && d > sm.prune) {
-                        *reinterpret_cast<volatile int*>(&sm.prune) = d;
-                        if (P.floor != nullptr) atomicMax(P.floor + img, d);
-                    }
-                    __syncwarp();
-                }
+                // the CTA's spare warp looks at the histogram all the time (live_scanner) and leaves the bucket here
                 const int now = *reinterpret_cast<volatile int*>(&sm.prune);
                 if (now > prune) {
                     prune = now;
@@ -556,6 +551,33 @@ __device__ __forceinline__ void yolo_live_level(const YoloParams& P, const int l
     __syncwarp();
     if (tail - head > 0) live_eval_batch(sm, ws, head, tail - head, P, ghist, prune, fill, gkeys, gcount);
     if (fill > 0) live_flush(ws, fill, gkeys, gcount, P.capacity, P.status);
+    __syncwarp();
+    if (lane == 0) atomicAdd(&sm.done_warps, 1);
+}
+
+// The ninth warp of a plain-load CTA (the staged CTAs use theirs as the copy producer): it looks at the image's histogram
+// over and over while the other eight work and publishes every bucket it finds, for its own CTA (shared memory) and for
+// all other CTAs of the image (P.floor).  The earlier the first buckets are out, the less the first wave of CTAs (which
+// starts with nothing to prune by) has to walk and evaluate.  Bounded: it ends when the eight consumer warps are done,
+// and after kLiveScans looks at the latest.
+constexpr int kLiveScans = 256;
+template <int S_T>
+__device__ __forceinline__ void live_scanner(const YoloParams& P, const int lvl, const int local, YoloLiveSmem& sm) {
+    const int S = S_T > 0 ? S_T : P.size[lvl];
+    const int tiles = (3 * S * S + kLiveTile - 1) / kLiveTile;
+    const int img = local / tiles;
+    if (P.hist == nullptr || P.prune_topk <= 0) return;
+    const int32_t* ghist = P.hist + static_cast<int64_t>(img) * kHistBins;
+    const int lane = threadIdx.x & 31;
+    for (int it = 0; it < kLiveScans; ++it) {
+        if (*reinterpret_cast<volatile int*>(&sm.done_warps) >= kLiveThreads / 32) break;
+        const int d = prune_digit_regs(ghist, P.prune_topk);
+        if (lane == 0 && d > *reinterpret_cast<volatile int*>(&sm.prune)) {
+            atomicMax(&sm.prune, d);
+            if (P.floor != nullptr) atomicMax(P.floor + img, d);
+        }
+        __syncwarp();
+    }
 }
 
 // ---- the same with the class planes staged through shared memory by the copy engine -------------------------
@@ -574,7 +596,9 @@ constexpr int kStConsumerWarps = kLiveThreads / 32;
 constexpr int kStThreads = kLiveThreads + 32;  // + the producer warp
 static_assert(kYoloClasses % kStClasses == 0 && kStTile % 4 == 0 && kStTile <= kLiveTile, "staged decode layout");
 
-constexpr int kStKeyStage = 96;  // staged candidate keys per warp (flushed when fewer than 32 slots remain)
+// staged candidate keys per warp, flushed when fewer than 32 slots remain (224 slots, i.e. two flushes instead of five for
+// the CTAs of the first wave, measured: no change)
+constexpr int kStKeyStage = 96;
 
 struct YoloStWarp {
     uint64_t stage[kStKeyStage];
@@ -689,10 +713,7 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
 
     if (t == 0) {
 #pragma unroll
-        for (int b = 0; b < kStStages; ++b) {
-            mbar_init(&sm.full[b], 1);
-            mbar_init(&sm.empty[b], kStConsumerWarps);
-        }
+        for (int b = 0; b < kStStages; ++b) mbar_init(&sm.full[b], 1);  // (the empty barriers: after the first phase)
         fence_barrier_init();
     }
     __syncthreads();
@@ -784,7 +805,16 @@ __device__ __forceinline__ void yolo_staged_level(const YoloParams& P, const int
         }
         wbase += __popc(bal[q]);
     }
+    // Only the warps that hold survivors take part in the ring: the others would do nothing but poll its barriers (and a
+    // polling warp competes with the working ones for issue slots and for the shared-memory pipe), so they leave here.
+    const int nbusy = min(kStConsumerWarps, max(1, (total + 31) >> 5));
+    if (t == 0) {
+#pragma unroll
+        for (int b = 0; b < kStStages; ++b) mbar_init(&sm.empty[b], static_cast<uint32_t>(nbusy));
+        fence_barrier_init();
+    }
     __syncthreads();  // the last CTA-wide barrier: from here on the warps only meet through the ring's mbarriers
+    if (!producer && warp >= nbusy) return;
 
     if (producer) {
         // refill a buffer as soon as all consumer warps have released it
@@ -935,8 +965,14 @@ yolo_decode_staged_kernel(const YoloParams P) {
         if (P.staged[lvl]) {
             yolo_staged_level<0>(P, lvl, local, *reinterpret_cast<YoloStagedSmem*>(st_raw));
         } else {
-            if (threadIdx.x >= kLiveThreads) return;
-            yolo_live_level<0>(P, lvl, local, *reinterpret_cast<YoloLiveSmem*>(st_raw));
+            YoloLiveSmem& sm = *reinterpret_cast<YoloLiveSmem*>(st_raw);
+            if (threadIdx.x == 0) {
+                sm.done_warps = 0;
+                sm.prune = 0;
+            }
+            __syncthreads();
+            if (threadIdx.x >= kLiveThreads) return live_scanner<0>(P, lvl, local, sm);
+            yolo_live_level<0>(P, lvl, local, sm);
         }
     } else if (P.staged[lvl]) {
         YoloStagedSmem& sm = *reinterpret_cast<YoloStagedSmem*>(st_raw);
@@ -944,8 +980,18 @@ yolo_decode_staged_kernel(const YoloParams P) {
         else if (lvl == 1) yolo_staged_level<S1>(P, 1, local, sm);
         else yolo_staged_level<S0>(P, 0, local, sm);
     } else {
-        if (threadIdx.x >= kLiveThreads) return;  // the plain-load form has no producer warp
         YoloLiveSmem& sm = *reinterpret_cast<YoloLiveSmem*>(st_raw);
+        if (threadIdx.x == 0) {
+            sm.done_warps = 0;
+            sm.prune = 0;
+        }
+        __syncthreads();
+        if (threadIdx.x >= kLiveThreads) {  // the plain-load form has no copy producer: its ninth warp watches the histogram
+            if (lvl == 2) live_scanner<S2>(P, 2, local, sm);
+            else if (lvl == 1) live_scanner<S1>(P, 1, local, sm);
+            else live_scanner<S0>(P, 0, local, sm);
+            return;
+        }
         if (lvl == 2) yolo_live_level<S2>(P, 2, local, sm);
         else if (lvl == 1) yolo_live_level<S1>(P, 1, local, sm);
         else yolo_live_level<S0>(P, 0, local, sm);
