@@ -329,6 +329,8 @@ def extra_workloads(torch, fb, W, hbm_peak, peak_kind="measured"):
                                 "note": "algorithmic flops counted once; the 3xTF32 split issues three times as many on "
                                         "the pipe, and the stage time includes the operand split kernel",
                                 "recurrence_tcgen05_tflops": gemm_flop / (modes["tcgen05_3xtf32"]["recurrence_us"] * 1e-6) / 1e12}}
+    del lm, xd
+    out["simple_programs"] = simple_ops(torch, fb, hbm_peak, peak_kind)
     return out
 
 

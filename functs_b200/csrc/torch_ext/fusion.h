@@ -74,9 +74,13 @@ int64_t InterpretedFunctorRuns();
 // ---- generic group (generic_group.cpp): the subgraph of a functor as ONE launch of the program-interpreting kernel ----
 // inputs: the node's inputs (lists for the parallel arguments of a map); outputs: one IValue per subgraph output (a list
 // of `degree` tensors for a map).  Returns false, with the reason in *why, when the group cannot be expressed as programs.
+// plan: per-functor cache of the flattened programs (opaque; created with NewGenericPlan, one per functor node).  A call
+// whose inputs have the shapes, dtypes, devices and scalar values of the previous one only patches the pointers.
+struct GenericPlan;
+std::shared_ptr<GenericPlan> NewGenericPlan();
 bool RunGenericGroup(const std::shared_ptr<torch::jit::Graph>& sub, bool is_map, int64_t degree,
                      const std::vector<int64_t>& par, const std::vector<c10::IValue>& inputs,
-                     std::vector<c10::IValue>& outputs, std::string* why);
+                     std::vector<c10::IValue>& outputs, std::string* why, GenericPlan* plan = nullptr);
 void countGenericRun();
 int64_t GenericGroupRuns();
 std::string LastGenericRefusal();

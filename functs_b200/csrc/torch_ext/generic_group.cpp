@@ -21,6 +21,7 @@
 
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <unordered_map>
 
 #include "../../../include/functs_b200.h"
@@ -96,6 +97,8 @@ struct Val {
 
 struct Builder {
     std::vector<at::Tensor> inputs;  // contiguous device tensors, slot = index
+    std::vector<std::pair<int, int>> sources;  // per slot: (argument of the node, position inside a list argument or -1)
+    int cur_arg = -1, cur_pos = -1;            // where the values fromIValue() is looking at come from
     std::unordered_map<const Value*, Val> env;
 
     ExprP leaf(const at::Tensor& t_in) {
@@ -117,6 +120,7 @@ struct Builder {
         e->dtype = code;
         e->is_bool = code == 1;
         inputs.push_back(t);
+        sources.emplace_back(cur_arg, cur_pos);
         return e;
     }
 
@@ -147,7 +151,11 @@ struct Builder {
             v.il = iv.toIntVector();
         } else if (iv.isTensorList()) {
             v.kind = Val::TensorList;
-            for (const at::Tensor& t : iv.toTensorVector()) v.tl.push_back(leaf(t));
+            int j = 0;
+            for (const at::Tensor& t : iv.toTensorVector()) {
+                cur_pos = j++;
+                v.tl.push_back(leaf(t));
+            }
         } else {
             throw Unsupported("input kind not supported");
         }
@@ -668,17 +676,151 @@ struct Emitter {
 
 }  // namespace
 
+// What a call leaves behind for the next one: the flattened programs and, for every tensor slot of every program, where
+// the tensor came from.  key describes everything the programs depend on (shapes, dtypes, devices, scalar values).
+struct GenericPlan {
+    std::mutex mu;
+    bool valid = false;
+    std::string key;
+    std::vector<functs_b200_gprogram> progs;                  // iterations x outputs (ninstr == 0: an empty output)
+    std::vector<std::vector<std::pair<int, int>>> sources;    // per iteration
+    std::vector<std::vector<int64_t>> out_shape;              // per program
+    int32_t max_numel = 0;
+};
+std::shared_ptr<GenericPlan> NewGenericPlan() { return std::make_shared<GenericPlan>(); }
+
+namespace {
+
+void describe(const c10::IValue& iv, std::string& k) {
+    if (iv.isTensor()) {
+        const at::Tensor& t = iv.toTensor();
+        k += 'T';
+        k += std::to_string(static_cast<int>(t.scalar_type()));
+        k += t.is_cuda() ? 'c' : 'h';
+        k += std::to_string(t.is_cuda() ? t.get_device() : -1);
+        for (int64_t d : t.sizes()) {
+            k += ',';
+            k += std::to_string(d);
+        }
+        k += ';';
+    } else if (iv.isDouble()) {
+        const double d = iv.toDouble();
+        uint64_t bits;
+        std::memcpy(&bits, &d, 8);
+        k += 'D';
+        k += std::to_string(bits);
+        k += ';';
+    } else if (iv.isInt()) {
+        k += 'I';
+        k += std::to_string(iv.toInt());
+        k += ';';
+    } else if (iv.isBool()) {
+        k += iv.toBool() ? "B1;" : "B0;";
+    } else if (iv.isNone()) {
+        k += "N;";
+    } else if (iv.isList()) {
+        k += '[';
+        for (const c10::IValue& e : iv.toListRef()) describe(e, k);
+        k += ']';
+    } else {
+        k += "?;";  // the builder refuses such an input anyway
+    }
+}
+
+at::Tensor sourceTensor(const std::vector<c10::IValue>& inputs, const std::pair<int, int>& src) {
+    const c10::IValue& iv = inputs.at(static_cast<size_t>(src.first));
+    if (src.second < 0) return iv.toTensor();
+    return iv.toListRef().at(static_cast<size_t>(src.second)).toTensor();
+}
+
+// allocates the outputs, points the programs at this call's tensors and launches
+void launchPrograms(std::vector<functs_b200_gprogram> progs, const std::vector<std::vector<std::pair<int, int>>>& sources,
+                    const std::vector<std::vector<int64_t>>& out_shape, int32_t max_numel, size_t n_out, bool is_map,
+                    const std::vector<c10::IValue>& inputs, std::vector<c10::IValue>& outputs) {
+    const size_t iters = progs.size() / n_out;
+    std::vector<std::vector<at::Tensor>> results(n_out);
+    std::vector<at::Tensor> keep_alive;
+    c10::Device device(c10::kCPU);
+    bool have_device = false;
+    for (size_t it = 0; it < iters; ++it) {
+        std::vector<at::Tensor> ins;
+        for (const auto& src : sources[it]) {
+            at::Tensor t = sourceTensor(inputs, src).contiguous();
+            if (!have_device) {
+                device = t.device();
+                have_device = true;
+            }
+            ins.push_back(t);
+            keep_alive.push_back(std::move(t));
+        }
+        for (size_t o = 0; o < n_out; ++o) {
+            functs_b200_gprogram& P = progs[it * n_out + o];
+            at::Tensor out = at::empty(out_shape[it * n_out + o],
+                                       at::TensorOptions().device(device).dtype(P.out_dtype == 1 ? at::kBool : at::kFloat));
+            results[o].push_back(out);
+            if (P.ninstr == 0) continue;
+            P.out_ptr = out.data_ptr();
+            for (size_t k = 0; k < ins.size(); ++k) P.in_ptr[k] = ins[k].data_ptr();
+        }
+    }
+    std::vector<functs_b200_gprogram> live;  // programs of empty outputs are dropped (nothing to compute)
+    for (const auto& P : progs)
+        if (P.ninstr > 0) live.push_back(P);
+    if (!live.empty()) {
+        c10::cuda::CUDAGuard guard(device);
+        void* stream = at::cuda::getCurrentCUDAStream().stream();
+        int rc;
+        if (live.size() == 1) {
+            rc = functs_b200_generic_group_launch(live.data(), 1, max_numel, 0, stream);
+        } else {
+            const int64_t bytes = static_cast<int64_t>(live.size() * sizeof(functs_b200_gprogram));
+            at::Tensor host = at::empty({bytes}, at::TensorOptions().dtype(at::kByte).pinned_memory(true));
+            std::memcpy(host.data_ptr(), live.data(), static_cast<size_t>(bytes));
+            at::Tensor table = host.to(device, /*non_blocking=*/true);  // (the pinned allocator defers the reuse of `host`)
+            rc = functs_b200_generic_group_launch(static_cast<const functs_b200_gprogram*>(table.data_ptr()),
+                                                  static_cast<int32_t>(live.size()), max_numel, 1, stream);
+        }
+        TORCH_CHECK(rc == FB_OK, "functs_b200 generic group: ", functs_b200_last_error());
+    }
+    outputs.clear();
+    for (size_t o = 0; o < n_out; ++o) {
+        if (is_map) outputs.emplace_back(c10::List<at::Tensor>(results[o]));
+        else outputs.emplace_back(results[o][0]);
+    }
+}
+
+}  // namespace
+
 // Runs the subgraph of a functor node as one launch.  stack_inputs: the node's inputs (for a map: lists for the parallel
 // arguments).  Returns false when the group cannot be expressed as programs (nothing has been launched then).
 bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t degree, const std::vector<int64_t>& par,
-                     const std::vector<c10::IValue>& inputs, std::vector<c10::IValue>& outputs, std::string* why) {
+                     const std::vector<c10::IValue>& inputs, std::vector<c10::IValue>& outputs, std::string* why,
+                     GenericPlan* plan) {
+    const size_t n_out = sub->outputs().size();
+    std::string key;
+    if (plan != nullptr) {
+        key.reserve(256);
+        key += std::to_string(degree);
+        key += '|';
+        for (const c10::IValue& iv : inputs) describe(iv, key);
+        std::unique_lock<std::mutex> lock(plan->mu);
+        if (plan->valid && plan->key == key) {
+            // same shapes, dtypes, devices and scalars as the call that built the programs: only the pointers change
+            auto progs = plan->progs;
+            auto sources = plan->sources;
+            auto out_shape = plan->out_shape;
+            const int32_t max_numel = plan->max_numel;
+            lock.unlock();
+            launchPrograms(std::move(progs), sources, out_shape, max_numel, n_out, is_map, inputs, outputs);
+            return true;
+        }
+    }
     try {
-        const size_t n_out = sub->outputs().size();
         const int64_t iters = is_map ? degree : 1;
         G_REQUIRE(iters >= 1 && iters * static_cast<int64_t>(n_out) <= 4096, "too many programs");
         std::vector<functs_b200_gprogram> progs(static_cast<size_t>(iters) * n_out);
-        std::vector<std::vector<at::Tensor>> results(n_out);
-        std::vector<std::vector<at::Tensor>> keep_alive;
+        std::vector<std::vector<std::pair<int, int>>> sources(static_cast<size_t>(iters));
+        std::vector<std::vector<int64_t>> out_shape(progs.size());
         c10::Device device(c10::kCPU);
         bool have_device = false;
         int32_t max_numel = 0;
@@ -697,9 +839,15 @@ bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t deg
                       "subgraph arity does not match the node");
             for (size_t k = 0; k + 1 < sub->inputs().size(); ++k) {
                 c10::IValue iv = inputs[k];
-                if (is_map && k < par.size() && par[k]) iv = iv.toListRef().at(static_cast<size_t>(it));
+                b.cur_arg = static_cast<int>(k);
+                b.cur_pos = -1;
+                if (is_map && k < par.size() && par[k]) {
+                    iv = iv.toListRef().at(static_cast<size_t>(it));
+                    b.cur_pos = static_cast<int>(it);
+                }
                 b.env[sub->inputs()[k + 1]] = b.fromIValue(iv);
             }
+            b.cur_arg = -1;
             for (const Node* n : sub->nodes()) b.node(n);
             for (const at::Tensor& t : b.inputs) {
                 if (!have_device) {
@@ -709,6 +857,7 @@ bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t deg
                 G_REQUIRE(t.device() == device, "tensor inputs on different devices");
             }
             G_REQUIRE(have_device, "a group without tensor inputs");
+            for (const auto& src : b.sources) G_REQUIRE(src.first >= 0, "tensor constant inside the group");
             for (size_t o = 0; o < n_out; ++o) {
                 ExprP e = b.tensorOf(sub->outputs()[o]);
                 G_REQUIRE(e->shape.size() <= 8, "output rank above 8");
@@ -720,14 +869,11 @@ bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t deg
                 for (size_t k = 0; k < e->shape.size(); ++k) P.shape[k] = static_cast<int32_t>(e->shape[k]);
                 P.numel = static_cast<int32_t>(numel);
                 P.out_dtype = e->is_bool ? 1 : 0;
-                at::Tensor out = at::empty(e->shape, at::TensorOptions().device(device).dtype(e->is_bool ? at::kBool : at::kFloat));
-                results[o].push_back(out);
+                out_shape[static_cast<size_t>(it) * n_out + o] = e->shape;
                 if (numel == 0) {
                     P.ninstr = 0;
                     continue;
                 }
-                P.out_ptr = out.data_ptr();
-                for (size_t k = 0; k < b.inputs.size(); ++k) P.in_ptr[k] = b.inputs[k].data_ptr();
                 Emitter em{P};
                 Map id(e->shape.size());
                 for (size_t k = 0; k < id.size(); ++k) {
@@ -738,34 +884,18 @@ bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t deg
                 em.push(FB_G_END);
                 max_numel = std::max(max_numel, P.numel);
             }
-            keep_alive.push_back(std::move(b.inputs));
+            sources[static_cast<size_t>(it)] = b.sources;
         }
-        // programs of empty outputs are dropped (nothing to compute)
-        std::vector<functs_b200_gprogram> live;
-        for (const auto& P : progs)
-            if (P.ninstr > 0) live.push_back(P);
-        if (!live.empty()) {
-            c10::cuda::CUDAGuard guard(device);
-            void* stream = at::cuda::getCurrentCUDAStream().stream();
-            int rc;
-            if (live.size() == 1) {
-                rc = functs_b200_generic_group_launch(live.data(), 1, max_numel, 0, stream);
-            } else {
-                const int64_t bytes = static_cast<int64_t>(live.size() * sizeof(functs_b200_gprogram));
-                at::Tensor host = at::empty({bytes}, at::TensorOptions().dtype(at::kByte).pinned_memory(true));
-                std::memcpy(host.data_ptr(), live.data(), static_cast<size_t>(bytes));
-                at::Tensor table = host.to(device, /*non_blocking=*/true);
-                rc = functs_b200_generic_group_launch(static_cast<const functs_b200_gprogram*>(table.data_ptr()),
-                                                      static_cast<int32_t>(live.size()), max_numel, 1, stream);
-                keep_alive.push_back({host, table});  // (the pinned allocator defers the reuse of `host` until the copy is done)
-            }
-            TORCH_CHECK(rc == FB_OK, "functs_b200 generic group: ", functs_b200_last_error());
+        if (plan != nullptr) {
+            std::lock_guard<std::mutex> lock(plan->mu);
+            plan->key = key;
+            plan->progs = progs;
+            plan->sources = sources;
+            plan->out_shape = out_shape;
+            plan->max_numel = max_numel;
+            plan->valid = true;
         }
-        outputs.clear();
-        for (size_t o = 0; o < n_out; ++o) {
-            if (is_map) outputs.emplace_back(c10::List<at::Tensor>(results[o]));
-            else outputs.emplace_back(results[o][0]);
-        }
+        launchPrograms(std::move(progs), sources, out_shape, max_numel, n_out, is_map, inputs, outputs);
         return true;
     } catch (const Unsupported& u) {
         if (why != nullptr) *why = u.what();
