@@ -37,7 +37,7 @@ def workload_config(world: int) -> dict:
     return {"workload": "YOLOv3-style decode + score>0.5 mask + top-1000 + class-wise NMS 0.45, 3 scales 13/26/52, batch 64 per GPU",
             "batch_per_gpu": BATCH,
             "inputs": "seeded N(0,1) logits, 231.7 MB per step; the GPU arm rotates 3 input sets so that no step finds its logits in the 126 MB L2",
-            "throughput_mode": "GPU arm: up to three batches in flight, one stream each (latency_us is one batch at a time); CPU arm: one call after the other on all host threads",
+            "throughput_mode": "GPU arm: up to three batches in flight, one stream each, a block of steps replayed from a CUDA graph (latency_us is one batch at a time, call by call); CPU arm: one call after the other on all host threads",
             "collective": "none" if world == 1 else "gather of the 2 MB detection records of every rank to rank 0 (NCCL), on a second stream while the next step computes"}
 
 
@@ -455,6 +455,7 @@ def run_ours(args):
     # multi-GPU: the gather of step i runs on a second stream while the next steps compute; one record buffer more than
     # there are batches in flight, so that no batch waits for the gather of an earlier one
     n_rec = 1
+    packed_ev = gathered_ev = cap_packed_ev = cap_gathered_ev = None
     if world > 1:
         n_rec = max(2, int(args.in_flight) + 1)
         comm_stream = torch.cuda.Stream(dev, priority=-1 if args.comm_priority == "high" else 0)
@@ -464,6 +465,8 @@ def run_ours(args):
         gathered_ev = [torch.cuda.Event() for _ in range(n_rec)]
         for e in gathered_ev:
             e.record()
+        cap_packed_ev = [torch.cuda.Event() for _ in range(n_rec)]
+        cap_gathered_ev = [torch.cuda.Event() for _ in range(n_rec)]
     # per-step stage events, recorded inside the one-call entry point through its profiling hook
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     for row in ev:
@@ -473,7 +476,7 @@ def run_ours(args):
     import ctypes
     ev_handles = [(ctypes.c_void_p * 4)(*[e.cuda_event for e in row]) for row in ev]
 
-    def step(i, handles=None, pipelined=False):
+    def step(i, handles=None, pipelined=False, capturing=False):
         j = i % n_rec                  # record / gather buffers (N > 1)
         k = i % in_flight              # plan and stream of this batch
         p = plans[k] if pipelined else plan
@@ -482,18 +485,22 @@ def run_ours(args):
             if handles is not None:
                 lib.functs_b200_set_stage_events(handles, 4)
             cur = torch.cuda.current_stream()
-            if world > 1:
-                cur.wait_event(gathered_ev[j])   # the gather that used this record buffer two steps ago is done
+            # (a capture has events of its own: an event recorded inside a capture cannot be waited for outside it)
+            p_ev, g_ev = (cap_packed_ev, cap_gathered_ev) if capturing else (packed_ev, gathered_ev)
+            if world > 1 and not (capturing and i < n_rec):
+                # the gather that used this record buffer n_rec steps ago is done (inside a capture the first uses have
+                # no earlier gather: a replay starts after the previous one has finished)
+                cur.wait_event(g_ev[j])
             # memset + decode/mask/compact + binned top-k + NMS: 3 kernels; with N > 1 the NMS kernel also writes the records
             p.run(sets[i % n_sets], 0.5, 0.45, records=recs[j] if world > 1 else None)
             if handles is not None:
                 lib.functs_b200_set_stage_events(None, 0)
             if world > 1:
-                packed_ev[j].record(cur)
+                p_ev[j].record(cur)
                 with torch.cuda.stream(comm_stream):
-                    comm_stream.wait_event(packed_ev[j])
+                    comm_stream.wait_event(p_ev[j])
                     fdist.gather_records_to(recs[j], 0, out=rec_alls[j])
-                    gathered_ev[j].record(comm_stream)
+                    g_ev[j].record(comm_stream)
 
     def barrier():
         if world > 1:
@@ -512,21 +519,49 @@ def run_ours(args):
     # The timed unit is a block of exactly `steps` steps between two barriers (device time, CUDA events).  One block of 20
     # steps is under 3 ms of GPU time, so the block is repeated until about a second of device time has been measured;
     # `value` comes from the median block.  The first block also records the per-stage events.
-    def timed_block(with_stage_events: bool, pipelined: bool):
-        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        main = torch.cuda.current_stream()
-        t_start.record(main)
+    def issue_block(main, fork_event, with_stage_events, pipelined, capturing=False):
+        """The `steps` steps of one block, forked from / joined into the stream `main`."""
         if pipelined:
             for ws in work_streams:
-                ws.wait_event(t_start)
+                ws.wait_event(fork_event)
+        if world > 1 and capturing:
+            comm_stream.wait_event(fork_event)
         for i in range(args.steps):
-            step(i, ev_handles[i] if with_stage_events else None, pipelined)
+            step(i, ev_handles[i] if with_stage_events else None, pipelined, capturing)
         if pipelined:
             for ws in work_streams:
                 main.wait_stream(ws)
         if world > 1:
             main.wait_stream(comm_stream)   # the block ends when the last gather has landed
+
+    # Throughput blocks are replayed from a CUDA graph (kernels, memsets, events and the NCCL gather of all `steps` steps,
+    # captured once): issuing a step from Python costs about as much host time as the step takes on the GPU once a
+    # gather call is part of it, and the ranks then run at the speed of rank 0's interpreter.
+    graph, graph_note = None, "off"
+    if in_flight > 1 and not args.no_graph:
+        try:
+            cap_stream = torch.cuda.Stream(dev)
+            g = torch.cuda.CUDAGraph()
+            l_before = launch_count()
+            with torch.cuda.graph(g, stream=cap_stream):
+                fork = torch.cuda.Event()
+                fork.record(cap_stream)
+                issue_block(cap_stream, fork, False, True, capturing=True)
+            graph, graph_note = g, f"one graph per block of {args.steps} steps"
+            graph_launches = launch_count() - l_before
+        except Exception as exc:  # noqa: BLE001 - reported in the JSON line, the block is then issued call by call
+            graph, graph_note = None, f"capture failed: {str(exc).splitlines()[0][:160]}"
+        barrier()
+
+    def timed_block(with_stage_events: bool, pipelined: bool):
+        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        main = torch.cuda.current_stream()
+        t_start.record(main)
+        if pipelined and graph is not None:
+            graph.replay()
+        else:
+            issue_block(main, t_start, with_stage_events, pipelined)
         t_end.record(main)
         barrier()
         return t_start.elapsed_time(t_end)
@@ -535,7 +570,7 @@ def run_ours(args):
     seq_ms = timed_block(True, False)
     launches0 = launch_count()
     block_ms = [timed_block(False, in_flight > 1)]
-    launches = launch_count() - launches0
+    launches = (launch_count() - launches0) if graph is None else graph_launches
     # every rank must run the same number of blocks: rank 0's first block decides
     want = torch.tensor([max(1.0, min(2000.0, 1000.0 / max(block_ms[0], 1e-3)))], dtype=torch.float64, device=dev)
     if world > 1:
@@ -590,6 +625,7 @@ def run_ours(args):
             "repeats": repeats, "timed_region_s": sum(block_ms) / 1e3,
             "ms_per_step_spread": {"min": min(block_ms) / args.steps, "median": ms_per_step, "max": max(block_ms) / args.steps},
             "in_flight": in_flight,
+            "cuda_graph": graph_note,
             "latency_us": seq_ms / args.steps * 1e3, "kernels_per_call": launches / args.steps,
             "images_per_s": world * BATCH * 1e3 / ms_per_step,
             "stage_us": {"decode_mask_compact": decode_ms * 1e3, "select_topk": select_ms * 1e3, "nms": nms_ms * 1e3},
@@ -632,6 +668,14 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+        torch.cuda.synchronize()
+        if graph is not None:
+            # A captured graph that holds NCCL kernels keeps the communicator busy: tearing the process group down with
+            # it alive did not return (the run was killed by its time limit).  Everything is printed and every rank is
+            # past the barrier: leave without the teardown.
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
@@ -683,6 +727,7 @@ def main():
                     help="stream priority of the multi-GPU gather (N > 1)")
     ap.add_argument("--in-flight", type=int, default=3, choices=[1, 2, 3, 4],
                     help="batches in flight in the throughput measurement (one stream each; 1 = strictly one after the other; measured on one B200: 129 / 98 / 92 / 91 us per step for 1 / 2 / 3 / 4)")
+    ap.add_argument("--no-graph", action="store_true", help="issue the throughput blocks call by call instead of replaying a CUDA graph")
     ap.add_argument("--no-extra", action="store_true", help="skip the cpu_baseline leg and the other workloads")
     ap.add_argument("--only", default=None, choices=["yolo", "ssd", "yolact", "lstm", "get_started", "normalize"],
                     help="run a few calls of one workload and exit (for profiler captures)")

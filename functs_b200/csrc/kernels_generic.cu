@@ -7,14 +7,35 @@
 
 namespace fb {
 
-__device__ __forceinline__ float g_load(const functs_b200_gprogram& P, const functs_b200_gload& L, const int* x) {
-    int off = L.base;
+// the element's multi-index stays in registers: every access to it is unrolled over the eight possible dimensions
+struct GIndex {
+    int x[8];
+};
+
+__device__ __forceinline__ int g_dot(const int32_t (&coef)[8], const GIndex& ix, int rank) {
+    int v = 0;
 #pragma unroll
-    for (int k = 0; k < FB_G_MAX_TERMS; ++k) {
-        if (k < L.nterms) {
+    for (int k = 0; k < 8; ++k)
+        if (k < rank) v += coef[k] * ix.x[k];
+    return v;
+}
+
+__device__ __forceinline__ int g_pick(const GIndex& ix, int dim) {
+    int v = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v = (k == dim) ? ix.x[k] : v;
+    return v;
+}
+
+__device__ __forceinline__ float g_load(const functs_b200_gprogram& P, const functs_b200_gload& L, const GIndex& ix) {
+    int off = L.base;
+    if (L.general == 0) {
+        off += g_dot(L.coef, ix, P.rank);
+    } else {  // a coordinate is divided (a read below a strided assignment): term by term
+        for (int k = 0; k < L.nterms; ++k) {
             const functs_b200_gterm t = L.term[k];
             int v = t.add;
-            if (t.dim >= 0) v += t.mul * x[t.dim];
+            if (t.dim >= 0) v += t.mul * g_pick(ix, t.dim);
             if (t.div > 1) v /= t.div;
             off += v * t.stride;
         }
@@ -28,28 +49,50 @@ __device__ __forceinline__ float g_load(const functs_b200_gprogram& P, const fun
     }
 }
 
-__device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const int* x) {
+__device__ __forceinline__ float g_binary(int op, float a, float b) {
+    switch (op) {
+        case FB_G_ADD: return __fadd_rn(a, b);
+        case FB_G_SUB: return __fsub_rn(a, b);
+        case FB_G_MUL: return __fmul_rn(a, b);
+        case FB_G_DIV: return __fdiv_rn(a, b);
+        case FB_G_MIN: return fminf(a, b);
+        case FB_G_MAX: return fmaxf(a, b);
+        case FB_G_GT: return a > b ? 1.0f : 0.0f;
+        case FB_G_GE: return a >= b ? 1.0f : 0.0f;
+        case FB_G_LT: return a < b ? 1.0f : 0.0f;
+        case FB_G_LE: return a <= b ? 1.0f : 0.0f;
+        case FB_G_EQ: return a == b ? 1.0f : 0.0f;
+        case FB_G_NE: return a != b ? 1.0f : 0.0f;
+        default: return a;
+    }
+}
+
+// The value stack: its top lives in a register, the rest in a small local array, so a chain of loads, unary operators and
+// scalar (*_IMM) operators never touches memory.
+__device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const GIndex& ix) {
     float st[FB_G_STACK];
-    int sp = 0;
+    float tos = 0.0f;
+    int sp = 0;  // values on the stack, the one in `tos` included
     int pc = 0;
     for (int guard = 0; guard < 4 * FB_G_MAX_INSTR; ++guard) {
         const functs_b200_ginstr I = P.instr[pc];
         ++pc;
         const int op = I.op;
         if (op == FB_G_END) break;
-        if (op == FB_G_LOAD) {
-            st[sp++] = g_load(P, P.load[I.arg], x);
-        } else if (op == FB_G_CONST) {
-            st[sp++] = I.imm.f;
+        if (op == FB_G_LOAD || op == FB_G_CONST) {
+            const float v = op == FB_G_LOAD ? g_load(P, P.load[I.arg], ix) : I.imm.f;
+            if (sp > 0) st[sp - 1] = tos;
+            tos = v;
+            ++sp;
         } else if (op == FB_G_COND) {
-            const functs_b200_gpred q = P.pred[I.arg];
-            const int v = (q.dim >= 0 ? q.mul * x[q.dim] : 0) + q.add;
+            const functs_b200_gpred& q = P.pred[I.arg];
+            const int v = q.add + g_dot(q.coef, ix, P.rank);
             const bool ok = v >= q.lo && v < q.hi && (q.step <= 1 || ((v - q.lo) % q.step) == 0);
             if (!ok) pc = I.imm.i;
         } else if (op == FB_G_JUMP) {
             pc = I.arg;
         } else if (op < FB_G_ADD) {
-            float a = st[sp - 1];
+            float a = tos;
             switch (op) {
                 case FB_G_EXP: a = expf(a); break;
                 case FB_G_SIGMOID: a = sigmoid_f32(a); break;
@@ -63,45 +106,39 @@ __device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const int
                 case FB_G_LOG: a = logf(a); break;
                 default: break;
             }
-            st[sp - 1] = a;
+            tos = a;
+        } else if (op < FB_G_ADD + FB_G_IMM) {
+            const float b = tos;
+            --sp;
+            tos = g_binary(op, st[sp - 1], b);
+        } else if (op == FB_G_RSUB_IMM) {
+            tos = __fsub_rn(I.imm.f, tos);
+        } else if (op == FB_G_RDIV_IMM) {
+            tos = __fdiv_rn(I.imm.f, tos);
         } else {
-            const float b = st[--sp];
-            float a = st[sp - 1];
-            switch (op) {
-                case FB_G_ADD: a = __fadd_rn(a, b); break;
-                case FB_G_SUB: a = __fsub_rn(a, b); break;
-                case FB_G_MUL: a = __fmul_rn(a, b); break;
-                case FB_G_DIV: a = __fdiv_rn(a, b); break;
-                case FB_G_MIN: a = fminf(a, b); break;
-                case FB_G_MAX: a = fmaxf(a, b); break;
-                case FB_G_GT: a = a > b ? 1.0f : 0.0f; break;
-                case FB_G_GE: a = a >= b ? 1.0f : 0.0f; break;
-                case FB_G_LT: a = a < b ? 1.0f : 0.0f; break;
-                case FB_G_LE: a = a <= b ? 1.0f : 0.0f; break;
-                case FB_G_EQ: a = a == b ? 1.0f : 0.0f; break;
-                case FB_G_NE: a = a != b ? 1.0f : 0.0f; break;
-                default: break;
-            }
-            st[sp - 1] = a;
+            tos = g_binary(op - FB_G_IMM, tos, I.imm.f);
         }
     }
-    return sp > 0 ? st[sp - 1] : 0.0f;
+    return tos;
 }
 
 __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
     const int stride = gridDim.x * blockDim.x;
     for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < P.numel; e += stride) {
-        int x[8];
-        int rem = e;
+        GIndex ix;
+        uint32_t rem = static_cast<uint32_t>(e);
 #pragma unroll
         for (int k = 7; k >= 0; --k) {
-            x[k] = 0;
-            if (k < P.rank) {
-                x[k] = rem % P.shape[k];
-                rem /= P.shape[k];
+            ix.x[k] = 0;
+            if (k < P.rank && P.shape[k] > 1) {
+                // multiply-shift division by the extent (magic and shift come from the host)
+                const uint32_t hi = __umulhi(P.div_magic[k], rem);
+                const uint32_t q = (((rem - hi) >> 1) + hi) >> P.div_shift[k];
+                ix.x[k] = static_cast<int>(rem - q * static_cast<uint32_t>(P.shape[k]));
+                rem = q;
             }
         }
-        const float v = g_eval(P, x);
+        const float v = g_eval(P, ix);
         if (P.out_dtype == 0) static_cast<float*>(P.out_ptr)[e] = v;
         else static_cast<uint8_t*>(P.out_ptr)[e] = v != 0.0f ? 1 : 0;
     }
@@ -130,24 +167,56 @@ static int validate_program(const functs_b200_gprogram& P) {
         n *= P.shape[k];
     }
     FB_REQUIRE(n == P.numel, "generic group: numel does not match the shape");
-    // static stack-depth and slot check, so that the kernel needs no run-time checks
+    for (int k = 0; k < P.rank; ++k) FB_REQUIRE(P.shape[k] == 1 || P.div_shift[k] < 32, "generic group: bad divisor shift");
+    // static slot and stack-depth check, so that the kernel needs no run-time checks: jumps go forward, so one pass
+    // over the program carries the depth along (depth_at[pc] = depth on arrival through a jump, -1 = none yet)
     FB_REQUIRE(P.instr[P.ninstr - 1].op == FB_G_END, "generic group: the program must end with END");
+    int depth_at[FB_G_MAX_INSTR + 1];
+    for (int pc = 0; pc <= FB_G_MAX_INSTR; ++pc) depth_at[pc] = -1;
+    int depth = 0;
+    bool reachable = true;
     for (int pc = 0; pc < P.ninstr; ++pc) {
+        if (depth_at[pc] >= 0) {
+            FB_REQUIRE(!reachable || depth == depth_at[pc], "generic group: the branches of a COND leave different stack depths");
+            depth = depth_at[pc];
+            reachable = true;
+        }
+        FB_REQUIRE(reachable, "generic group: unreachable instruction");
         const functs_b200_ginstr& I = P.instr[pc];
-        if (I.op == FB_G_LOAD) {
-            FB_REQUIRE(I.arg < FB_G_MAX_LOADS, "generic group: load slot out of range");
-            const functs_b200_gload& L = P.load[I.arg];
-            FB_REQUIRE(L.tensor >= 0 && L.tensor < FB_G_MAX_INPUTS && P.in_ptr[L.tensor] != nullptr && L.nterms >= 0 &&
-                           L.nterms <= FB_G_MAX_TERMS && L.dtype >= 0 && L.dtype <= 3,
-                       "generic group: bad load");
-            for (int k = 0; k < L.nterms; ++k)
-                FB_REQUIRE(L.term[k].dim >= -1 && L.term[k].dim < P.rank && L.term[k].div >= 1, "generic group: bad load term");
-        } else if (I.op == FB_G_COND) {
-            FB_REQUIRE(I.arg < FB_G_MAX_PREDS && I.imm.i > pc && I.imm.i < P.ninstr && P.pred[I.arg].dim >= -1 &&
-                           P.pred[I.arg].dim < P.rank,
-                       "generic group: bad COND");
-        } else if (I.op == FB_G_JUMP) {
+        const int op = I.op;
+        if (op == FB_G_END) {
+            FB_REQUIRE(depth == 1, "generic group: the program must leave exactly one value");
+            reachable = false;
+        } else if (op == FB_G_LOAD || op == FB_G_CONST) {
+            if (op == FB_G_LOAD) {
+                FB_REQUIRE(I.arg < FB_G_MAX_LOADS, "generic group: load slot out of range");
+                const functs_b200_gload& L = P.load[I.arg];
+                FB_REQUIRE(L.tensor >= 0 && L.tensor < FB_G_MAX_INPUTS && P.in_ptr[L.tensor] != nullptr && L.nterms >= 0 &&
+                               L.nterms <= FB_G_MAX_TERMS && L.dtype >= 0 && L.dtype <= 3,
+                           "generic group: bad load");
+                for (int k = 0; k < L.nterms; ++k)
+                    FB_REQUIRE(L.term[k].dim >= -1 && L.term[k].dim < P.rank && L.term[k].div >= 1, "generic group: bad load term");
+            }
+            ++depth;
+            FB_REQUIRE(depth <= FB_G_STACK, "generic group: value stack too deep");
+        } else if (op == FB_G_COND) {
+            FB_REQUIRE(I.arg < FB_G_MAX_PREDS && I.imm.i > pc && I.imm.i < P.ninstr, "generic group: bad COND");
+            FB_REQUIRE(depth_at[I.imm.i] < 0 || depth_at[I.imm.i] == depth, "generic group: inconsistent stack depth at a jump target");
+            depth_at[I.imm.i] = depth;
+        } else if (op == FB_G_JUMP) {
             FB_REQUIRE(I.arg > pc && I.arg < P.ninstr, "generic group: jumps go forward");
+            FB_REQUIRE(depth_at[I.arg] < 0 || depth_at[I.arg] == depth, "generic group: inconsistent stack depth at a jump target");
+            depth_at[I.arg] = depth;
+            reachable = false;
+        } else if (op >= FB_G_EXP && op <= FB_G_LOG) {
+            FB_REQUIRE(depth >= 1, "generic group: unary operator on an empty stack");
+        } else if (op >= FB_G_ADD && op <= FB_G_NE) {
+            FB_REQUIRE(depth >= 2, "generic group: binary operator needs two values");
+            --depth;
+        } else if ((op >= FB_G_ADD + FB_G_IMM && op <= FB_G_NE + FB_G_IMM) || op == FB_G_RSUB_IMM || op == FB_G_RDIV_IMM) {
+            FB_REQUIRE(depth >= 1, "generic group: scalar operator on an empty stack");
+        } else {
+            FB_REQUIRE(false, "generic group: unknown instruction %d", op);
         }
     }
     return FB_OK;

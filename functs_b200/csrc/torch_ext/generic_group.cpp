@@ -426,6 +426,28 @@ struct Builder {
 };
 
 // ---- program emission -------------------------------------------------------------------------------------------------
+// d >= 2 as a multiply-shift divisor for 32-bit dividends: q = mulhi(magic, n); (((n - q) >> 1) + q) >> shift == n / d
+// (the round-up variant of division by an invariant integer; exact for every n < 2^32).  d = 1 is not used by the kernel.
+void divisorOf(uint32_t d, uint32_t& magic, uint32_t& shift) {
+    magic = 0;
+    shift = 0;
+    if (d < 2) return;
+    uint32_t log2d = 31;
+    while (((d >> log2d) & 1u) == 0u) --log2d;
+    if ((d & (d - 1)) == 0) {  // a power of two: magic 0 turns the expression into n >> log2d
+        shift = log2d - 1;
+        return;
+    }
+    const uint64_t two = 1ull << (32 + log2d);
+    uint64_t m = two / d;
+    const uint64_t rem = two - m * d;
+    m += m;
+    const uint64_t twice = rem + rem;
+    if (twice >= d) m += 1;
+    magic = static_cast<uint32_t>(m + 1);
+    shift = log2d;
+}
+
 struct Emitter {
     functs_b200_gprogram& P;
     int nloads = 0, npreds = 0;
@@ -481,8 +503,8 @@ struct Emitter {
         G_REQUIRE(npreds < FB_G_MAX_PREDS, "too many predicates");
         G_REQUIRE(fits32(c.mul) && fits32(c.add) && fits32(lo) && fits32(hi) && fits32(step), "predicate out of 32-bit range");
         functs_b200_gpred& q = P.pred[npreds];
-        q.dim = c.dim;
-        q.mul = static_cast<int32_t>(c.mul);
+        std::memset(&q, 0, sizeof(q));
+        q.coef[c.dim] = static_cast<int32_t>(c.mul);
         q.add = static_cast<int32_t>(c.add);
         q.lo = static_cast<int32_t>(lo);
         q.hi = static_cast<int32_t>(hi);
@@ -542,6 +564,25 @@ struct Emitter {
                 }
                 G_REQUIRE(fits32(base), "offset out of range");
                 L.base = static_cast<int32_t>(base);
+                L.general = 0;
+                for (int k = 0; k < L.nterms; ++k) L.general |= L.term[k].div > 1 ? 1 : 0;
+                if (L.general == 0) {
+                    // base + sum_k coef[k] * x[k]: constant parts of the terms go into the base
+                    int64_t b2 = base, coef[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    for (int k = 0; k < L.nterms; ++k) {
+                        const functs_b200_gterm& t = L.term[k];
+                        b2 += static_cast<int64_t>(t.add) * t.stride;
+                        if (t.dim >= 0) coef[t.dim] += static_cast<int64_t>(t.mul) * t.stride;
+                    }
+                    G_REQUIRE(fits32(b2), "offset out of range");
+                    L.base = static_cast<int32_t>(b2);
+                    for (int k = 0; k < 8; ++k) {
+                        G_REQUIRE(fits32(coef[k]), "index coefficient out of range");
+                        L.coef[k] = static_cast<int32_t>(coef[k]);
+                    }
+                    L.nterms = 0;
+                    std::memset(L.term, 0, sizeof(L.term));
+                }
                 int slot = -1;
                 for (int k = 0; k < nloads && slot < 0; ++k)
                     if (std::memcmp(&P.load[k], &L, sizeof(L)) == 0) slot = k;
@@ -561,6 +602,35 @@ struct Emitter {
                 return;
             }
             case Expr::Binary: {
+                const bool c0 = e->in[0]->kind == Expr::Const, c1 = e->in[1]->kind == Expr::Const;
+                if (c0 != c1) {
+                    // a scalar operand travels inside the instruction: no push, no pop
+                    const ExprP& t = e->in[c0 ? 1 : 0];
+                    const float imm = static_cast<float>(e->in[c0 ? 0 : 1]->f);
+                    int op = e->op;
+                    if (c0) {  // scalar on the left: commute, or mirror the comparison, or use the reversed forms
+                        switch (e->op) {
+                            case FB_G_SUB: op = FB_G_RSUB_IMM - FB_G_IMM; break;
+                            case FB_G_DIV: op = FB_G_RDIV_IMM - FB_G_IMM; break;
+                            case FB_G_GT: op = FB_G_LT; break;
+                            case FB_G_GE: op = FB_G_LE; break;
+                            case FB_G_LT: op = FB_G_GT; break;
+                            case FB_G_LE: op = FB_G_GE; break;
+                            default: break;  // add, mul, min, max, eq, ne commute
+                        }
+                    }
+                    // (the operand has the result's shape or broadcasts into it: same rule as below)
+                    Map ma(t->shape.size());
+                    const size_t lead = e->shape.size() - t->shape.size();
+                    for (size_t q = 0; q < t->shape.size(); ++q) {
+                        if (t->shape[q] == 1 && e->shape[q + lead] != 1) ma[q] = Coord{};
+                        else ma[q] = m[q + lead];
+                    }
+                    emit(t, ma);
+                    const int k = push(static_cast<uint16_t>(op + FB_G_IMM));
+                    P.instr[k].imm.f = imm;
+                    return;
+                }
                 for (int side = 0; side < 2; ++side) {
                     const ExprP& a = e->in[side];
                     if (a->kind == Expr::Const) {
@@ -869,6 +939,7 @@ bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t deg
                 for (size_t k = 0; k < e->shape.size(); ++k) P.shape[k] = static_cast<int32_t>(e->shape[k]);
                 P.numel = static_cast<int32_t>(numel);
                 P.out_dtype = e->is_bool ? 1 : 0;
+                for (size_t k = 0; k < e->shape.size(); ++k) divisorOf(static_cast<uint32_t>(e->shape[k]), P.div_magic[k], P.div_shift[k]);
                 out_shape[static_cast<size_t>(it) * n_out + o] = e->shape;
                 if (numel == 0) {
                     P.ninstr = 0;

@@ -254,21 +254,27 @@ int functs_b200_index_rows_rev(const void* self, const void* src, const int64_t*
  * every output element is one inlined gather expression; map iterations sit on blockIdx.y,
  * fait/tensorexpr/functor_parallization.cpp:83-111).  Here the same expression is data: the host flattens the group into
  * a small postfix program over the output's multi-index, and ONE precompiled kernel evaluates it per element.
- *   - a LOAD reads input `tensor` at  base + sum_k stride_k * ((mul_k * x[dim_k] + add_k) / div_k)  (dim_k = -1: no x term):
- *     every Access op (select / slice / squeeze / unsqueeze / permute / expand) on the way to the output has been
- *     folded into those terms on the host;
- *   - a COND tests  lo <= v < hi  and  (v - lo) % step == 0  with  v = mul * x[dim] + add  and either falls through or
- *     jumps to `arg`: the Assign ops (select_rev / slice_rev) and cat / stack become COND ... JUMP ... chains, so only the
- *     selected operand is evaluated;
- *   - CONST / UNARY / BINARY work on a small value stack in registers (fp32; comparisons give 1.0 / 0.0).
+ *   - a LOAD reads input `tensor` at  base + sum_k coef[k] * x[k]  (x = the output element's multi-index): every Access
+ *     op (select / slice / squeeze / unsqueeze / permute / expand) on the way to the output has been folded into those
+ *     coefficients on the host.  Only a read below a strided assignment needs a division of a coordinate; such a load
+ *     has general != 0 and is described by terms: base + sum_k stride_k * ((mul_k * x[dim_k] + add_k) / div_k);
+ *   - a COND tests  lo <= v < hi  and  (v - lo) % step == 0  with  v = add + sum_k coef[k] * x[k]  (one non-zero
+ *     coefficient) and either falls through or jumps: the Assign ops (select_rev / slice_rev) and cat / stack become
+ *     COND ... JUMP ... chains, so only the selected operand is evaluated;
+ *   - CONST / UNARY / BINARY work on a small value stack (fp32; comparisons give 1.0 / 0.0); a binary operator with a
+ *     scalar operand is one *_IMM instruction (RSUB / RDIV: the scalar is the left operand).
  * One program per (map iteration, group output); grid.y walks the programs.  Everything is 32-bit: tensors of 2^31
- * elements or more are not taken. */
+ * elements or more are not taken.  div_magic / div_shift: the output shape's dimensions as multiply-shift divisors
+ * (q = mulhi(magic, n); ((n - q) >> 1) + q >> shift; unused for extent 1), filled in by the host. */
 enum {
     FB_G_END = 0, FB_G_LOAD = 1, FB_G_CONST = 2, FB_G_COND = 3, FB_G_JUMP = 4,
     /* unary */ FB_G_EXP = 10, FB_G_SIGMOID = 11, FB_G_TANH = 12, FB_G_RELU = 13, FB_G_NEG = 14, FB_G_CLAMP_MIN = 15,
     FB_G_CLAMP_MAX = 16, FB_G_ABS = 17, FB_G_SQRT = 18, FB_G_LOG = 19,
     /* binary */ FB_G_ADD = 30, FB_G_SUB = 31, FB_G_MUL = 32, FB_G_DIV = 33, FB_G_MIN = 34, FB_G_MAX = 35, FB_G_GT = 36,
-    FB_G_GE = 37, FB_G_LT = 38, FB_G_LE = 39, FB_G_EQ = 40, FB_G_NE = 41
+    FB_G_GE = 37, FB_G_LT = 38, FB_G_LE = 39, FB_G_EQ = 40, FB_G_NE = 41,
+    /* binary with the scalar imm as right operand: FB_G_IMM + the binary code; the two with it as left operand */
+    FB_G_IMM = 30, /* FB_G_ADD + FB_G_IMM = 60 ... FB_G_NE + FB_G_IMM = 71 */
+    FB_G_RSUB_IMM = 80, FB_G_RDIV_IMM = 81
 };
 #define FB_G_MAX_INSTR 256
 #define FB_G_MAX_LOADS 24
@@ -279,7 +285,7 @@ enum {
 typedef struct {
     uint16_t op;   /* FB_G_* */
     uint16_t arg;  /* LOAD: load slot; COND: predicate slot (the jump target is in imm_i); JUMP: target */
-    union { float f; int32_t i; } imm; /* CONST / CLAMP_*: the scalar; COND: jump target when the test fails */
+    union { float f; int32_t i; } imm; /* CONST / CLAMP_* / *_IMM: the scalar; COND: jump target when the test fails */
 } functs_b200_ginstr;
 typedef struct {
     int16_t dim;  /* output dimension the coordinate follows, -1 = constant */
@@ -289,12 +295,16 @@ typedef struct {
 typedef struct {
     int32_t tensor;  /* index into in_ptr */
     int32_t base;
-    int32_t nterms;
     int32_t dtype;   /* 0 = float32, 1 = uint8 / bool, 2 = int64, 3 = int32 */
+    int32_t general; /* 0: coef[]; else: nterms terms */
+    int32_t coef[8];
+    int32_t nterms;
+    int32_t reserved;
     functs_b200_gterm term[FB_G_MAX_TERMS];
 } functs_b200_gload;
 typedef struct {
-    int32_t dim, mul, add, lo, hi, step;
+    int32_t coef[8];
+    int32_t add, lo, hi, step;
 } functs_b200_gpred;
 typedef struct {
     int32_t rank;
@@ -302,9 +312,11 @@ typedef struct {
     int32_t numel;
     int32_t out_dtype;  /* 0 = float32, 1 = bool (uint8) */
     int32_t ninstr;
-    int32_t reserved[2];  /* keeps sizeof a multiple of 16 */
+    uint32_t div_magic[8];
+    uint32_t div_shift[8];
     const void* in_ptr[FB_G_MAX_INPUTS];
     void* out_ptr;
+    int32_t reserved[2];  /* keeps sizeof a multiple of 16 */
     functs_b200_ginstr instr[FB_G_MAX_INSTR];
     functs_b200_gload load[FB_G_MAX_LOADS];
     functs_b200_gpred pred[FB_G_MAX_PREDS];
