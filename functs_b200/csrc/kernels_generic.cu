@@ -139,8 +139,9 @@ __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
             }
         }
         const float v = g_eval(P, ix);
-        if (P.out_dtype == 0) static_cast<float*>(P.out_ptr)[e] = v;
-        else static_cast<uint8_t*>(P.out_ptr)[e] = v != 0.0f ? 1 : 0;
+        const int o = g_dot(P.out_coef, ix, P.rank);
+        if (P.out_dtype == 0) static_cast<float*>(P.out_ptr)[o] = v;
+        else static_cast<uint8_t*>(P.out_ptr)[o] = v != 0.0f ? 1 : 0;
     }
 }
 
@@ -167,6 +168,26 @@ static int validate_program(const functs_b200_gprogram& P) {
         n *= P.shape[k];
     }
     FB_REQUIRE(n == P.numel, "generic group: numel does not match the shape");
+    {
+        // out_coef must place the elements one to one into [0, numel): the largest offset is numel - 1 and the
+        // coefficients, sorted, are the running products of the extents (a permutation of contiguous strides)
+        int64_t top = 0;
+        for (int k = 0; k < P.rank; ++k) {
+            FB_REQUIRE(P.out_coef[k] >= 0, "generic group: negative output coefficient");
+            top += static_cast<int64_t>(P.out_coef[k]) * (P.shape[k] - 1);
+        }
+        FB_REQUIRE(top == static_cast<int64_t>(P.numel) - 1, "generic group: the output coefficients do not cover the output");
+        bool used[8] = {false, false, false, false, false, false, false, false};
+        int64_t run = 1;
+        for (int step = 0; step < P.rank; ++step) {
+            int pick = -1;
+            for (int k = 0; k < P.rank && pick < 0; ++k)
+                if (!used[k] && (P.shape[k] == 1 || P.out_coef[k] == run)) pick = k;
+            FB_REQUIRE(pick >= 0, "generic group: the output coefficients are not a permutation of contiguous strides");
+            used[pick] = true;
+            run *= P.shape[pick];
+        }
+    }
     for (int k = 0; k < P.rank; ++k) FB_REQUIRE(P.shape[k] == 1 || P.div_shift[k] < 32, "generic group: bad divisor shift");
     // static slot and stack-depth check, so that the kernel needs no run-time checks: jumps go forward, so one pass
     // over the program carries the depth along (depth_at[pc] = depth on arrival through a jump, -1 = none yet)

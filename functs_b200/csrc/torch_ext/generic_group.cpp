@@ -448,6 +448,75 @@ void divisorOf(uint32_t d, uint32_t& magic, uint32_t& shift) {
     shift = log2d;
 }
 
+// Orders the dimensions the kernel decomposes the element number over: the lanes of a warp (fastest dimension) run
+// along a dimension that no COND tests, so that a warp takes one path through the program instead of one per lane; the
+// tested dimensions come next (their values still change close together in time, which keeps the rows they select from
+// in cache), the others last.  Without a COND the output's own order stays.  Everything that names a dimension (loads,
+// predicates, extents, divisors) is renumbered; out_coef keeps the element's place in the contiguous output.
+void orderDimensionsForLanes(functs_b200_gprogram& P) {
+    const int rank = P.rank;
+    int64_t stride[8];
+    {
+        int64_t run = 1;
+        for (int k = rank - 1; k >= 0; --k) {
+            stride[k] = run;
+            run *= P.shape[k];
+        }
+    }
+    bool tested[8] = {false, false, false, false, false, false, false, false};
+    bool any = false;
+    for (int pc = 0; pc < P.ninstr; ++pc) {
+        if (P.instr[pc].op != FB_G_COND) continue;
+        const functs_b200_gpred& q = P.pred[P.instr[pc].arg];
+        for (int k = 0; k < rank; ++k)
+            if (q.coef[k] != 0 && P.shape[k] > 1) tested[k] = any = true;
+    }
+    int order[8];  // order[p] = the output dimension at position p (position rank - 1 is the fastest)
+    for (int k = 0; k < rank; ++k) order[k] = k;
+    if (any) {
+        // lane dimension: the innermost untested one with at least a warp's worth of extent, else the largest untested
+        int lane_dim = -1;
+        for (int k = rank - 1; k >= 0 && lane_dim < 0; --k)
+            if (!tested[k] && P.shape[k] >= 32) lane_dim = k;
+        if (lane_dim < 0) {
+            for (int k = 0; k < rank; ++k)
+                if (!tested[k] && P.shape[k] > 1 && (lane_dim < 0 || P.shape[k] > P.shape[lane_dim])) lane_dim = k;
+        }
+        if (lane_dim >= 0) {
+            int p = rank - 1;
+            order[p--] = lane_dim;
+            for (int k = rank - 1; k >= 0; --k)
+                if (tested[k]) order[p--] = k;
+            for (int k = rank - 1; k >= 0; --k)
+                if (!tested[k] && k != lane_dim) order[p--] = k;
+        }
+    }
+    int where[8];  // position of every output dimension
+    for (int p = 0; p < rank; ++p) where[order[p]] = p;
+    int32_t shape[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int p = 0; p < rank; ++p) {
+        shape[p] = P.shape[order[p]];
+        P.out_coef[p] = static_cast<int32_t>(stride[order[p]]);
+    }
+    for (int p = 0; p < 8; ++p) {
+        P.shape[p] = shape[p];
+        P.div_magic[p] = P.div_shift[p] = 0;
+        if (p < rank) divisorOf(static_cast<uint32_t>(shape[p]), P.div_magic[p], P.div_shift[p]);
+        else P.out_coef[p] = 0;
+    }
+    auto renumber = [&](int32_t (&coef)[8]) {
+        int32_t c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int p = 0; p < rank; ++p) c[p] = coef[order[p]];
+        for (int p = 0; p < 8; ++p) coef[p] = c[p];
+    };
+    for (int k = 0; k < FB_G_MAX_LOADS; ++k) {
+        renumber(P.load[k].coef);
+        for (int t = 0; t < P.load[k].nterms; ++t)
+            if (P.load[k].term[t].dim >= 0) P.load[k].term[t].dim = static_cast<int16_t>(where[P.load[k].term[t].dim]);
+    }
+    for (int k = 0; k < FB_G_MAX_PREDS; ++k) renumber(P.pred[k].coef);
+}
+
 struct Emitter {
     functs_b200_gprogram& P;
     int nloads = 0, npreds = 0;
@@ -953,6 +1022,7 @@ bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t deg
                 }
                 em.emit(e, id);
                 em.push(FB_G_END);
+                orderDimensionsForLanes(P);
                 max_numel = std::max(max_numel, P.numel);
             }
             sources[static_cast<size_t>(it)] = b.sources;

@@ -265,7 +265,10 @@ int functs_b200_index_rows_rev(const void* self, const void* src, const int64_t*
  *     scalar operand is one *_IMM instruction (RSUB / RDIV: the scalar is the left operand).
  * One program per (map iteration, group output); grid.y walks the programs.  Everything is 32-bit: tensors of 2^31
  * elements or more are not taken.  div_magic / div_shift: the output shape's dimensions as multiply-shift divisors
- * (q = mulhi(magic, n); ((n - q) >> 1) + q >> shift; unused for extent 1), filled in by the host. */
+ * (q = mulhi(magic, n); ((n - q) >> 1) + q >> shift; unused for extent 1), filled in by the host.
+ * The dimensions need not be in the output's own order: thread e works on the element whose multi-index is the
+ * decomposition of e over `shape` (last dimension fastest) and stores it at sum_k out_coef[k] * x[k].  The host orders
+ * them so that the lanes of a warp run along a dimension no COND tests (one path per warp instead of one per lane). */
 enum {
     FB_G_END = 0, FB_G_LOAD = 1, FB_G_CONST = 2, FB_G_COND = 3, FB_G_JUMP = 4,
     /* unary */ FB_G_EXP = 10, FB_G_SIGMOID = 11, FB_G_TANH = 12, FB_G_RELU = 13, FB_G_NEG = 14, FB_G_CLAMP_MIN = 15,
@@ -314,6 +317,7 @@ typedef struct {
     int32_t ninstr;
     uint32_t div_magic[8];
     uint32_t div_shift[8];
+    int32_t out_coef[8];  /* the element's place in the output: sum_k out_coef[k] * x[k] */
     const void* in_ptr[FB_G_MAX_INPUTS];
     void* out_ptr;
     int32_t reserved[2];  /* keeps sizeof a multiple of 16 */
