@@ -68,7 +68,7 @@ SIGNATURES = {
     "functs_b200_slice_rev": (c_int32, [P, P, P, POINTER(c_int64), c_int32, c_int32, c_int64, c_int64, c_int64, c_int32, P]),
     "functs_b200_index_rows": (c_int32, [P, P, P, c_int64, c_int64, c_int64, c_int32, P, P]),
     "functs_b200_index_rows_rev": (c_int32, [P, P, P, P, c_int64, c_int64, c_int64, c_int32, P, P]),
-    "functs_b200_generic_group_launch": (c_int32, [P, c_int32, c_int32, c_int32, P]),
+    "functs_b200_generic_group_launch": (c_int32, [P, c_int32, c_int32, c_int32, c_int32, P]),
     "functs_b200_group_lookup": (c_int32, [c_char_p]),
     "functs_b200_group_count": (c_int32, []),
     "functs_b200_group_signature": (c_char_p, [c_int32]),

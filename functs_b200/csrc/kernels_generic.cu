@@ -12,30 +12,33 @@ struct GIndex {
     int x[8];
 };
 
-__device__ __forceinline__ int g_dot(const int32_t (&coef)[8], const GIndex& ix, int rank) {
+// R: the largest rank the instantiation serves (coefficients and indices beyond the program's rank are zero)
+template <int R>
+__device__ __forceinline__ int g_dot(const int32_t (&coef)[8], const GIndex& ix) {
     int v = 0;
 #pragma unroll
-    for (int k = 0; k < 8; ++k)
-        if (k < rank) v += coef[k] * ix.x[k];
+    for (int k = 0; k < R; ++k) v += coef[k] * ix.x[k];
     return v;
 }
 
+template <int R>
 __device__ __forceinline__ int g_pick(const GIndex& ix, int dim) {
     int v = 0;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) v = (k == dim) ? ix.x[k] : v;
+    for (int k = 0; k < R; ++k) v = (k == dim) ? ix.x[k] : v;
     return v;
 }
 
+template <int R>
 __device__ __forceinline__ float g_load(const functs_b200_gprogram& P, const functs_b200_gload& L, const GIndex& ix) {
     int off = L.base;
     if (L.general == 0) {
-        off += g_dot(L.coef, ix, P.rank);
+        off += g_dot<R>(L.coef, ix);
     } else {  // a coordinate is divided (a read below a strided assignment): term by term
         for (int k = 0; k < L.nterms; ++k) {
             const functs_b200_gterm t = L.term[k];
             int v = t.add;
-            if (t.dim >= 0) v += t.mul * g_pick(ix, t.dim);
+            if (t.dim >= 0) v += t.mul * g_pick<R>(ix, t.dim);
             if (t.div > 1) v /= t.div;
             off += v * t.stride;
         }
@@ -69,6 +72,7 @@ __device__ __forceinline__ float g_binary(int op, float a, float b) {
 
 // The value stack: its top lives in a register, the rest in a small local array, so a chain of loads, unary operators and
 // scalar (*_IMM) operators never touches memory.
+template <int R>
 __device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const GIndex& ix) {
     float st[FB_G_STACK];
     float tos = 0.0f;
@@ -80,13 +84,13 @@ __device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const GIn
         const int op = I.op;
         if (op == FB_G_END) break;
         if (op == FB_G_LOAD || op == FB_G_CONST) {
-            const float v = op == FB_G_LOAD ? g_load(P, P.load[I.arg], ix) : I.imm.f;
+            const float v = op == FB_G_LOAD ? g_load<R>(P, P.load[I.arg], ix) : I.imm.f;
             if (sp > 0) st[sp - 1] = tos;
             tos = v;
             ++sp;
         } else if (op == FB_G_COND) {
             const functs_b200_gpred& q = P.pred[I.arg];
-            const int v = q.add + g_dot(q.coef, ix, P.rank);
+            const int v = q.add + g_dot<R>(q.coef, ix);
             const bool ok = v >= q.lo && v < q.hi && (q.step <= 1 || ((v - q.lo) % q.step) == 0);
             if (!ok) pc = I.imm.i;
         } else if (op == FB_G_JUMP) {
@@ -122,6 +126,7 @@ __device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const GIn
     return tos;
 }
 
+template <int R>
 __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
     const int stride = gridDim.x * blockDim.x;
     for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < P.numel; e += stride) {
@@ -130,7 +135,7 @@ __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
 #pragma unroll
         for (int k = 7; k >= 0; --k) {
             ix.x[k] = 0;
-            if (k < P.rank && P.shape[k] > 1) {
+            if (k < R && P.shape[k] > 1) {  // (extents beyond the program's rank are zero)
                 // multiply-shift division by the extent (magic and shift come from the host)
                 const uint32_t hi = __umulhi(P.div_magic[k], rem);
                 const uint32_t q = (((rem - hi) >> 1) + hi) >> P.div_shift[k];
@@ -138,17 +143,20 @@ __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
                 rem = q;
             }
         }
-        const float v = g_eval(P, ix);
-        const int o = g_dot(P.out_coef, ix, P.rank);
+        const float v = g_eval<R>(P, ix);
+        const int o = g_dot<R>(P.out_coef, ix);
         if (P.out_dtype == 0) static_cast<float*>(P.out_ptr)[o] = v;
         else static_cast<uint8_t*>(P.out_ptr)[o] = v != 0.0f ? 1 : 0;
     }
 }
 
-// the program travels as a kernel parameter (constant bank): no device memory, no copy
-__global__ void __launch_bounds__(256) generic_group_kernel_param(const __grid_constant__ functs_b200_gprogram P) { g_run(P); }
+// the program travels as a kernel parameter (constant bank): no device memory, no copy.  R = 2, 4, 8: the instantiation
+// for programs of rank <= R (index arithmetic is unrolled over R dimensions)
+template <int R>
+__global__ void __launch_bounds__(256) generic_group_kernel_param(const __grid_constant__ functs_b200_gprogram P) { g_run<R>(P); }
 
 // several programs (map iterations x outputs) in device memory; the CTA stages its own in shared memory
+template <int R>
 __global__ void __launch_bounds__(256) generic_group_kernel_table(const functs_b200_gprogram* __restrict__ progs) {
     __shared__ functs_b200_gprogram P;
     const int4* src = reinterpret_cast<const int4*>(progs + blockIdx.y);
@@ -156,7 +164,7 @@ __global__ void __launch_bounds__(256) generic_group_kernel_table(const functs_b
     static_assert(sizeof(functs_b200_gprogram) % 16 == 0, "the program is copied in 16-byte pieces");
     for (int i = threadIdx.x; i < static_cast<int>(sizeof(functs_b200_gprogram) / 16); i += blockDim.x) dst[i] = __ldg(src + i);
     __syncthreads();
-    g_run(P);
+    if (P.rank <= R) g_run<R>(P);  // (the launcher passes the largest rank of the table; a wrong value computes nothing)
 }
 
 static int validate_program(const functs_b200_gprogram& P) {
@@ -246,7 +254,7 @@ static int validate_program(const functs_b200_gprogram& P) {
 }  // namespace fb
 
 extern "C" int functs_b200_generic_group_launch(const functs_b200_gprogram* programs, int32_t count, int32_t max_numel,
-                                                int32_t on_device, void* stream) {
+                                                int32_t max_rank, int32_t on_device, void* stream) {
     using namespace fb;
     FB_REQUIRE(programs != nullptr && count > 0 && count <= 65535 && max_numel >= 0, "generic group: bad arguments");
     if (max_numel == 0) return FB_OK;
@@ -257,11 +265,17 @@ extern "C" int functs_b200_generic_group_launch(const functs_b200_gprogram* prog
     if (!on_device) {
         FB_REQUIRE(count == 1, "generic group: %d programs in host memory (only one can travel as a kernel parameter)", count);
         FB_TRY(validate_program(programs[0]));
-        generic_group_kernel_param<<<static_cast<unsigned>(need), 256, 0, st>>>(programs[0]);
+        const int rank = programs[0].rank;
+        if (rank <= 2) generic_group_kernel_param<2><<<static_cast<unsigned>(need), 256, 0, st>>>(programs[0]);
+        else if (rank <= 4) generic_group_kernel_param<4><<<static_cast<unsigned>(need), 256, 0, st>>>(programs[0]);
+        else generic_group_kernel_param<8><<<static_cast<unsigned>(need), 256, 0, st>>>(programs[0]);
     } else {
         FB_REQUIRE((reinterpret_cast<uintptr_t>(programs) & 15) == 0, "generic group: the program table must be 16-byte aligned");
+        FB_REQUIRE(max_rank >= 0 && max_rank <= 8, "generic group: bad maximum rank");
         dim3 grid(static_cast<unsigned>(need), static_cast<unsigned>(count));
-        generic_group_kernel_table<<<grid, 256, 0, st>>>(programs);
+        if (max_rank <= 2) generic_group_kernel_table<2><<<grid, 256, 0, st>>>(programs);
+        else if (max_rank <= 4) generic_group_kernel_table<4><<<grid, 256, 0, st>>>(programs);
+        else generic_group_kernel_table<8><<<grid, 256, 0, st>>>(programs);
     }
     count_launch();
     return check_launch("generic_group_kernel");

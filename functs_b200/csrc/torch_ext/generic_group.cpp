@@ -903,21 +903,26 @@ void launchPrograms(std::vector<functs_b200_gprogram> progs, const std::vector<s
         }
     }
     std::vector<functs_b200_gprogram> live;  // programs of empty outputs are dropped (nothing to compute)
-    for (const auto& P : progs)
-        if (P.ninstr > 0) live.push_back(P);
+    int32_t max_rank = 0;
+    for (const auto& P : progs) {
+        if (P.ninstr > 0) {
+            live.push_back(P);
+            max_rank = std::max(max_rank, P.rank);
+        }
+    }
     if (!live.empty()) {
         c10::cuda::CUDAGuard guard(device);
         void* stream = at::cuda::getCurrentCUDAStream().stream();
         int rc;
         if (live.size() == 1) {
-            rc = functs_b200_generic_group_launch(live.data(), 1, max_numel, 0, stream);
+            rc = functs_b200_generic_group_launch(live.data(), 1, max_numel, max_rank, 0, stream);
         } else {
             const int64_t bytes = static_cast<int64_t>(live.size() * sizeof(functs_b200_gprogram));
             at::Tensor host = at::empty({bytes}, at::TensorOptions().dtype(at::kByte).pinned_memory(true));
             std::memcpy(host.data_ptr(), live.data(), static_cast<size_t>(bytes));
             at::Tensor table = host.to(device, /*non_blocking=*/true);  // (the pinned allocator defers the reuse of `host`)
             rc = functs_b200_generic_group_launch(static_cast<const functs_b200_gprogram*>(table.data_ptr()),
-                                                  static_cast<int32_t>(live.size()), max_numel, 1, stream);
+                                                  static_cast<int32_t>(live.size()), max_numel, max_rank, 1, stream);
         }
         TORCH_CHECK(rc == FB_OK, "functs_b200 generic group: ", functs_b200_last_error());
     }

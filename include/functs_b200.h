@@ -326,9 +326,10 @@ typedef struct {
     functs_b200_gpred pred[FB_G_MAX_PREDS];
 } functs_b200_gprogram;
 /* programs: `count` programs in HOST memory when on_device == 0 (count == 1: passed to the kernel by value) or in DEVICE
- * memory when on_device != 0; max_numel = the largest numel among them.  One launch. */
+ * memory when on_device != 0; max_numel / max_rank = the largest numel / rank among them (a program of a higher rank
+ * than max_rank is not run).  One launch. */
 int functs_b200_generic_group_launch(const functs_b200_gprogram* programs, int32_t count, int32_t max_numel,
-                                     int32_t on_device, void* stream);
+                                     int32_t max_rank, int32_t on_device, void* stream);
 
 /* ---- group registry: what the tssa::ParallelFunctor operator binds to ------------------------ */
 /* The reference registers one JIT operator whose Operation runs a compiled group
