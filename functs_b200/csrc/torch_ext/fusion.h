@@ -29,6 +29,8 @@ void UnrollLoopsWithDeps(const std::shared_ptr<torch::jit::Graph>& graph);
 void FuseOps(const std::shared_ptr<torch::jit::Graph>& graph);
 // a map whose body is more than one fusion group -> a chain of maps, one group (or one run of other nodes) each
 void SplitParallelMaps(const std::shared_ptr<torch::jit::Graph>& graph);
+// maps with a constant trip count and a self-contained body, written out iteration by iteration (not in the default pipeline)
+void UnrollSimpleMaps(const std::shared_ptr<torch::jit::Graph>& graph);
 void LowerToParallelFunctors(const std::shared_ptr<torch::jit::Graph>& graph);
 // TensorSSA conversion (+ marker removal) followed by the three passes above and dead-code elimination
 void FaitPipeline(const std::shared_ptr<torch::jit::Graph>& graph);

@@ -46,6 +46,7 @@ PYBIND11_MODULE(_C, m) {
     m.def("_jit_pass_match_precompiled_loops", [](std::shared_ptr<Graph> g) { functs_b200::MatchPrecompiledLoops(g); });
     m.def("_jit_pass_unroll_loops_with_deps", [](std::shared_ptr<Graph> g) { functs_b200::UnrollLoopsWithDeps(g); });
     m.def("_jit_pass_split_parallel_maps", [](std::shared_ptr<Graph> g) { functs_b200::SplitParallelMaps(g); });
+    m.def("_jit_pass_unroll_simple_maps", [](std::shared_ptr<Graph> g) { functs_b200::UnrollSimpleMaps(g); });
     m.def("_jit_pass_lower_to_parallel_functors", [](std::shared_ptr<Graph> g) { functs_b200::LowerToParallelFunctors(g); });
     m.def("_jit_pass_fait_pipeline",
           [](std::shared_ptr<Graph> g, std::vector<c10::TypePtr> type_hint) {

@@ -284,3 +284,39 @@ def test_shape_inference_refines_lists_of_tensors():
     params = list(list(m.blocks())[0].inputs())
     assert params[1].type().dim() == 2 and params[1].type().scalarType() == "Float"
     assert params[1].type().sizes() is None or params[1].type().sizes()[1] == 6
+
+
+def captures_outer(feats: List[torch.Tensor], w: torch.Tensor):
+    outs: List[torch.Tensor] = []
+    for i in range(3):
+        outs.append(feats[i] * w)
+    return outs
+
+
+def test_unroll_simple_maps():
+    """A map with a constant trip count and a self-contained body is written out per index (list[i] reads, one
+    ListConstruct); a map that captures an outer tensor is not simple and stays (fait/passes/parallelize_loops.cpp:372-392)."""
+    g = torch.jit.script(scales_decode).graph.copy()
+    torch._C._jit_pass_inline(g)
+    _C._jit_pass_convert_to_tensorssa(g)
+    _C._jit_pass_tensorssa_remove_update(g)
+    _C._jit_pass_parallelize_loops(g)
+    assert "tssa::ParallelMap" in kinds(g, recursive=False)
+    _C._jit_pass_unroll_simple_maps(g)
+    ks = kinds(g)
+    assert "tssa::ParallelMap" not in ks and "prim::Loop" not in ks
+    assert ks.count("aten::__getitem__") == 6 and ks.count("aten::sigmoid") == 3 and ks.count("prim::ListConstruct") >= 1
+    torch._C._jit_pass_lint(g)
+    feats, offs = make_lists()
+    want = scales_decode(feats, offs)
+    got = _C._create_function_from_graph("unrolled", g)(feats, offs)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+    g2 = torch.jit.script(captures_outer).graph.copy()
+    torch._C._jit_pass_inline(g2)
+    _C._jit_pass_convert_to_tensorssa(g2)
+    _C._jit_pass_parallelize_loops(g2)
+    assert "tssa::ParallelMap" in kinds(g2, recursive=False)
+    _C._jit_pass_unroll_simple_maps(g2)
+    assert "tssa::ParallelMap" in kinds(g2, recursive=False)
