@@ -84,10 +84,8 @@ lstm_input_proj_simt_kernel(const float* __restrict__ x, const float* __restrict
 // ---- persistent recurrent kernel ----------------------------------------------------------------------------
 constexpr int kRecThreads = 256;
 constexpr int kRecB = 32;      // batch rows per tile
-constexpr int kRecJ = 8;       // hidden units per CTA
-constexpr int kRecCols = 32;   // 4 gates x 8 units
+constexpr int kRecJ = 8;       // hidden units per CTA (4 gates x 8 units = 32 columns, in 16 groups of 2)
 constexpr int kRecKS = 16;     // k-slices (threads along K)
-constexpr int kRecCG = 16;     // column groups of 2 columns
 constexpr int kPartStride = 40;
 constexpr unsigned long long kWaitCycles = 2000000000ull;  // ~1 s: bound of the inter-step wait
 
