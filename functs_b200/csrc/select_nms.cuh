@@ -321,6 +321,13 @@ __device__ int block_select_topk(KeyFn key, int n, int topk, SelectSmem<SELCAP>&
     return result;
 }
 
+// The exact generic selection as an out-of-line call: it is the rare way out of the binned selections below, and its
+// code (three passes, two sorts) should not sit in the middle of their instruction stream.
+template <int NT, int SELCAP, int UNROLL, class KeyFn>
+__device__ __noinline__ int block_select_topk_outlined(KeyFn key, int n, int topk, SelectSmem<SELCAP>* sm) {
+    return block_select_topk<NT, SELCAP, UNROLL>(key, n, topk, *sm);
+}
+
 // Same result as block_select_topk, but in two passes for keys whose scores lie above a known threshold: one pass
 // fills the coarse score histogram (hist_digit), the second collects the keys above / inside the boundary bucket,
 // and only the boundary bucket is sorted.  Falls back to block_select_topk when that bucket exceeds kBinListCap.
@@ -439,7 +446,7 @@ __device__ int block_select_topk_binned(KeyFn key, int n, int topk, uint32_t his
     const int dstar = sm.digit;  // -1: everything is selected
     if (sm.inbin > kBinListCap) {
         __syncthreads();
-        return block_select_topk<NT, SELCAP, UNROLL>(key, n, topk, sm);
+        return block_select_topk_outlined<NT, SELCAP, UNROLL>(key, n, topk, &sm);
     }
     auto place = [&](uint64_t k) {
         const int d = hist_digit(k, hist_base, hist_shift);
@@ -595,6 +602,13 @@ __device__ int block_hist_rank_bucket(const int* hist, int* red_cnt, int* slot, 
     return *slot;
 }
 
+// the two-pass selection over a whole score array, out of line (the sampled selection's rare way out)
+template <int NT, int SELCAP>
+__device__ __noinline__ int block_select_dense_outlined(const float* s, bool vec4, float thr, int n, int topk, uint32_t hist_base,
+                                                        int hist_shift, SelectSmem<SELCAP>* sm) {
+    return block_select_topk_binned<NT, SELCAP, 8>(DenseScores{s, thr, vec4}, n, topk, hist_base, hist_shift, *sm);
+}
+
 // Same result as block_select_topk_binned for a plain fp32 score array in GLOBAL memory (key = score above thr, index),
 // reading the array once: a spread sample of the scores (one 16-byte chunk per thread) gives a score floor that should
 // leave a few hundred candidates; one pass collects every key at or above the floor into `cand` (kCandCap keys of
@@ -682,7 +696,7 @@ __device__ int block_select_topk_sampled(const float* __restrict__ s, bool vec4,
     const int c = sm.bin_cnt;
     __syncthreads();  // (the selections below reset the counter)
     if (c > kCandCap || (lo_bits != 0u && c < topk)) {
-        return block_select_topk_binned<NT, SELCAP, 8>(DenseScores{s, thr, vec4}, n, topk, hist_base, hist_shift, sm);
+        return block_select_dense_outlined<NT, SELCAP>(s, vec4, thr, n, topk, hist_base, hist_shift, &sm);
     }
     return block_select_topk_binned<NT, SELCAP, 2>(ListKeys{cand}, c, topk, hist_base, hist_shift, sm);
 }
