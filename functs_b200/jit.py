@@ -55,6 +55,44 @@ def type_hint_of(value):
     return None
 
 
+_JSON_DTYPES = {"Float": torch.float32, "Double": torch.float64, "Half": torch.float16, "BFloat16": torch.bfloat16,
+                "Long": torch.int64, "Int": torch.int32, "Short": torch.int16, "Char": torch.int8, "Byte": torch.uint8,
+                "Bool": torch.bool}
+
+
+def parse_input_types(spec, device="cuda") -> list:
+    """Type hints from the reference's JSON input-type specs (fait/models/*.json, read there by parseInputTypes,
+    fait/passes/refine_types.cpp:131-177): a list of {"kind": "TensorType", "shape": [...], "dtype": "Float"} /
+    {"kind": "TupleType", "elements": [...]} / {"kind": "ListType", "element": {...}} / BoolType / IntType / FloatType
+    records, one per graph input.  `spec` is the JSON text, a path to such a file, or the parsed list.  Tensors are
+    contiguous and live on `device`, as in the reference."""
+    import json
+    import os
+    if isinstance(spec, (str, bytes, os.PathLike)):
+        text = spec
+        if not str(spec).lstrip().startswith("["):
+            with open(spec) as f:
+                text = f.read()
+        spec = json.loads(text)
+
+    def one(rec):
+        kind = rec["kind"]
+        if kind == "TensorType":
+            if rec["dtype"] not in _JSON_DTYPES:
+                raise ValueError(f"unknown dtype {rec['dtype']!r} in a TensorType record")
+            return (torch._C.TensorType.get().with_dtype(_JSON_DTYPES[rec["dtype"]])
+                    .with_sizes([int(v) for v in rec["shape"]]).with_device(torch.device(device)))
+        if kind == "TupleType":
+            return torch._C.TupleType([one(e) for e in rec["elements"]])
+        if kind == "ListType":
+            return torch._C.ListType(one(rec["element"]))
+        if kind in ("BoolType", "IntType", "FloatType"):
+            return getattr(torch._C, kind).get()
+        raise ValueError(f"cannot parse type record of kind {kind!r}")
+
+    return [one(rec) for rec in spec]
+
+
 def shape_infer(g: torch.Graph, example_inputs=(), has_self: bool = False) -> dict:
     """Counterpart of the reference's functs.jit.shape_infer (functs/jit/_script.py:48-51): refines the graph's value types
     from example inputs in place and returns {debug name of a list value: tuple type of its elements}."""

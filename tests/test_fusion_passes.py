@@ -320,3 +320,36 @@ def test_unroll_simple_maps():
     assert "tssa::ParallelMap" in kinds(g2, recursive=False)
     _C._jit_pass_unroll_simple_maps(g2)
     assert "tssa::ParallelMap" in kinds(g2, recursive=False)
+
+
+def test_json_input_type_specs():
+    """The reference's JSON type specs (fait/models/*.json format) become the type hints the pipeline takes."""
+    from functs_b200 import jit as J
+    spec = """[
+      {"kind": "TupleType", "elements": [
+        {"kind": "TensorType", "shape": [5, 6], "dtype": "Float"},
+        {"kind": "TensorType", "shape": [6, 6], "dtype": "Float"},
+        {"kind": "TensorType", "shape": [7, 6], "dtype": "Float"}]},
+      {"kind": "ListType", "element": {"kind": "TensorType", "shape": [5, 2], "dtype": "Float"}},
+      {"kind": "IntType"}, {"kind": "BoolType"}, {"kind": "FloatType"},
+      {"kind": "TensorType", "shape": [3, 4], "dtype": "Long"}
+    ]"""
+    hints = J.parse_input_types(spec, device="cpu")
+    assert len(hints) == 6
+    assert isinstance(hints[0], torch._C.TupleType) and [e.sizes() for e in hints[0].elements()] == [[5, 6], [6, 6], [7, 6]]
+    assert hints[0].elements()[0].dtype() == torch.float32
+    assert isinstance(hints[1], torch._C.ListType) and hints[1].getElementType().sizes() == [5, 2]
+    assert str(hints[2]) == "int" and str(hints[3]) == "bool" and str(hints[4]) == "float"
+    assert hints[5].dtype() == torch.int64 and hints[5].sizes() == [3, 4]
+    # the tuple hint refines a list input: shapes flow into the map's element parameters
+    g = torch.jit.script(scales_decode).graph.copy()
+    torch._C._jit_pass_inline(g)
+    _C._jit_pass_convert_to_tensorssa(g)
+    _C._jit_pass_tensorssa_remove_update(g)
+    offs = J.parse_input_types('[{"kind": "TupleType", "elements": [{"kind": "TensorType", "shape": [5, 2], "dtype": "Float"},'
+                               '{"kind": "TensorType", "shape": [6, 2], "dtype": "Float"},'
+                               '{"kind": "TensorType", "shape": [7, 2], "dtype": "Float"}]}]', device="cpu")
+    refined = _C._jit_pass_fait_shape_infer(g, [hints[0], offs[0]])
+    assert any(isinstance(t, torch._C.TupleType) for t in refined.values())
+    with pytest.raises(ValueError):
+        J.parse_input_types('[{"kind": "DictType"}]')
