@@ -589,7 +589,8 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
     const int lane = t & 31, warp = t >> 5;
     const unsigned char* prep = prep_g + static_cast<int64_t>(g) * kPrepBytes;
     const NmsPrepHeader h = *reinterpret_cast<const NmsPrepHeader*>(prep);
-    const int n = h.n, nb = h.nb, reach = h.reach;
+    // the record comes from memory: whatever it holds, nothing below indexes beyond the shared arrays
+    const int n = min(max(h.n, 0), kNmsMaxN), nb = min(max(h.nb, 1), kMaskMaxBuckets), reach = max(h.reach, 0);
     const int rt = gridDim.x;
     uint32_t* gmask = mask_g + static_cast<int64_t>(g) * kNmsMaxN * kNmsWords;
     uint8_t* gflag = rowflag_g + static_cast<int64_t>(g) * kNmsMaxN;
@@ -615,15 +616,15 @@ nms_mask_scan_kernel(const unsigned char* __restrict__ prep_g, float thr, float 
         uint32_t* myrow = rs.rowbuf[warp];
         for (int i = warp * rt + static_cast<int>(blockIdx.x); i < n; i += (kMaskThreads / 32) * rt) {
             const NmsBox bi = rs.sb[i];
-            const int li = rs.slabel[i];
-            const int p0 = rs.bstart[max(li - reach, 0)], p1 = rs.bstart[min(li + reach + 1, nb)];
+            const int li = min(static_cast<int>(rs.slabel[i]), nb - 1);
+            const int p0 = max(rs.bstart[max(li - reach, 0)], 0), p1 = min(rs.bstart[min(li + reach + 1, nb)], n);
             myrow[lane] = 0u;
             __syncwarp();
             for (int base = p0; base < p1; base += 32) {
                 const int p = base + lane;
                 if (p < p1) {
                     const int j = rs.order[p];
-                    if (j > i && iou_exceeds(bi, rs.sb[j], thr, thr_lo, thr_hi)) atomicOr(&myrow[j >> 5], 1u << (j & 31));
+                    if (j > i && j < n && iou_exceeds(bi, rs.sb[j], thr, thr_lo, thr_hi)) atomicOr(&myrow[j >> 5], 1u << (j & 31));
                 }
             }
             __syncwarp();
