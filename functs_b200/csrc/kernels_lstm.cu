@@ -81,6 +81,26 @@ lstm_input_proj_simt_kernel(const float* __restrict__ x, const float* __restrict
     }
 }
 
+// asynchronous 16-byte copy global (L2) -> shared memory, in commit groups
+__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most `pending` of this thread's commit groups are still in flight (pending is a compile-time value
+// wherever this is called: the switch folds away)
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+    switch (pending) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+        case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
+}
+
 // ---- persistent recurrent kernel ----------------------------------------------------------------------------
 constexpr int kRecThreads = 256;
 constexpr int kRecB = 32;      // batch rows per tile
@@ -152,37 +172,60 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
             __syncthreads();
             if (s_abort) return;
         }
-        // ---- stage h[t-1] rows b0..b0+31 ----
-        {
-            const float4* src = reinterpret_cast<const float4*>(hs + (static_cast<int64_t>(t > 0 ? t - 1 : 0) * B) * H);
-            for (int e = tid; e < kRecB * (H / 4); e += kRecThreads) {
-                const int r = e / (H / 4), q = e - r * (H / 4);
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (t > 0 && b0 + r < B) v = __ldcg(src + static_cast<int64_t>(b0 + r) * (H / 4) + q);
-                const int k = q * 4;
-                *reinterpret_cast<float4*>(h_s + r * HROW + k + (k / KSL) * 4) = v;
+        // ---- stage h[t-1] and accumulate, four rows at a time ----
+        // A warp holds two k-slices (lanes 0-15: slice 2w, lanes 16-31: slice 2w + 1) and needs, of h[t-1], only their
+        // 2 x KSL columns of the CTA's 32 rows: it fetches them itself with asynchronous copies (L2 -> shared memory, one
+        // commit group per block of four rows; 16 consecutive lanes write one row's 16 chunks, so the copies do not
+        // collide on banks) and starts multiplying as soon as the first block has landed, while the others are still on
+        // their way.  No block barrier between staging and arithmetic.  The order of the additions inside every dot
+        // product is the slice's k order, as before.
+        constexpr int kRowsPerGroup = 4, kGroups = kRecB / kRowsPerGroup;
+        static_assert(KSL / 4 * 2 == 16 || KSL / 4 * 2 == 8, "a row's chunks of both slices: 16 (H = 512) or 8 (H = 256)");
+        constexpr int kChunks = KSL / 4 * 2;  // 16-byte chunks per row and warp
+        if (t > 0) {
+            const int warp = tid >> 5, lane = tid & 31;
+            const float* hsrc = hs + (static_cast<int64_t>(t - 1) * B) * H;
+#pragma unroll
+            for (int g = 0; g < kGroups; ++g) {
+#pragma unroll
+                for (int e = lane; e < kRowsPerGroup * kChunks; e += 32) {
+                    const int r = g * kRowsPerGroup + e / kChunks, c = e % kChunks;
+                    const int kcol = (2 * warp + c / (KSL / 4)) * KSL + 4 * (c % (KSL / 4));
+                    float* dst = h_s + r * HROW + kcol + (kcol / KSL) * 4;
+                    if (b0 + r < B) cp_async_16(dst, hsrc + static_cast<int64_t>(b0 + r) * H + kcol);
+                    else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                cp_async_commit();
             }
         }
-        __syncthreads();
-        // ---- partial dot products over this thread's k-slice ----
         {
             const float* hrow = h_s + ks * KSL + ks * 4;
-#pragma unroll 4
-            for (int b = 0; b < kRecB; ++b) {
-                float a0 = 0.0f, a1 = 0.0f;
 #pragma unroll
-                for (int q = 0; q < KSL / 4; ++q) {
-                    const float4 hv = *reinterpret_cast<const float4*>(hrow + b * HROW + q * 4);
-                    a0 = fmaf(hv.x, w[4 * q + 0][0], a0);
-                    a1 = fmaf(hv.x, w[4 * q + 0][1], a1);
-                    a0 = fmaf(hv.y, w[4 * q + 1][0], a0);
-                    a1 = fmaf(hv.y, w[4 * q + 1][1], a1);
-                    a0 = fmaf(hv.z, w[4 * q + 2][0], a0);
-                    a1 = fmaf(hv.z, w[4 * q + 2][1], a1);
-                    a0 = fmaf(hv.w, w[4 * q + 3][0], a0);
-                    a1 = fmaf(hv.w, w[4 * q + 3][1], a1);
+            for (int g = 0; g < kGroups; ++g) {
+                if (t > 0) {
+                    cp_async_wait_pending(kGroups - 1 - g);  // row blocks 0 .. g have landed
+                    __syncwarp();
                 }
-                *reinterpret_cast<float2*>(part + (ks * kRecB + b) * kPartStride + cg * 2) = make_float2(a0, a1);
+#pragma unroll
+                for (int bb = 0; bb < kRowsPerGroup; ++bb) {
+                    const int b = g * kRowsPerGroup + bb;
+                    float a0 = 0.0f, a1 = 0.0f;
+                    if (t > 0) {
+#pragma unroll
+                        for (int q = 0; q < KSL / 4; ++q) {
+                            const float4 hv = *reinterpret_cast<const float4*>(hrow + b * HROW + q * 4);
+                            a0 = fmaf(hv.x, w[4 * q + 0][0], a0);
+                            a1 = fmaf(hv.x, w[4 * q + 0][1], a1);
+                            a0 = fmaf(hv.y, w[4 * q + 1][0], a0);
+                            a1 = fmaf(hv.y, w[4 * q + 1][1], a1);
+                            a0 = fmaf(hv.z, w[4 * q + 2][0], a0);
+                            a1 = fmaf(hv.z, w[4 * q + 2][1], a1);
+                            a0 = fmaf(hv.w, w[4 * q + 3][0], a0);
+                            a1 = fmaf(hv.w, w[4 * q + 3][1], a1);
+                        }
+                    }
+                    *reinterpret_cast<float2*>(part + (ks * kRecB + b) * kPartStride + cg * 2) = make_float2(a0, a1);
+                }
             }
         }
         __syncthreads();
@@ -215,9 +258,13 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
             }
         }
         // ---- publish ----
-        __threadfence();
+        // the block barrier orders every thread's stores before thread 0's fence, and that fence (cumulative, device
+        // scope) orders them before the counter update: one fence per CTA instead of one per thread
         __syncthreads();
-        if (tid == 0 && t + 1 < T) atomicAdd(step_counter, 1u);
+        if (tid == 0 && t + 1 < T) {
+            __threadfence();
+            atomicAdd(step_counter, 1u);
+        }
     }
 }
 
