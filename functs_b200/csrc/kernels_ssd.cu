@@ -182,6 +182,9 @@ ssd_class_nms_kernel(const float* __restrict__ boxes, const float* __restrict__ 
                 // the overlap.  It is loose when one box contains the other, which priors of one cell do all the time:
                 // the exact test ran so often that the matrix took 24 us per list instead of 15.)
                 // (Also measured and dropped: all votes of a batch first, then the rows with a candidate: 20 us.)
+                // (And: the union test as a sum of per-box terms, inter >= c * a_i + c * a_j with c = thr / (1 + thr), plus a
+                // row mask on the vote instead of the per-lane i < j test: two instructions fewer per pair on paper, 299 us
+                // against 292 for the kernel.)
 #pragma unroll
                 for (int u = 0; u < kSsdRowBatch; ++u) {
                     const int i = i0 + u;
