@@ -102,7 +102,7 @@ __device__ __forceinline__ void cp_async_wait_pending(int pending) {
 }
 
 // ---- persistent recurrent kernel ----------------------------------------------------------------------------
-constexpr int kRecThreads = 256;
+constexpr int kRecThreads = 512;  // two halves of 256: each takes 16 of the CTA's 32 rows in the multiply phase
 constexpr int kRecB = 32;      // batch rows per tile
 constexpr int kRecJ = 8;       // hidden units per CTA (4 gates x 8 units = 32 columns, in 16 groups of 2)
 constexpr int kRecKS = 16;     // k-slices (threads along K)
@@ -121,8 +121,9 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
     __shared__ int s_abort;
 
     const int tid = threadIdx.x;
-    const int ks = tid >> 4;  // 0..15
-    const int cg = tid & 15;  // 0..15 -> columns 2cg, 2cg+1
+    const int half = tid >> 8;        // which 16 rows this thread multiplies
+    const int ks = (tid & 255) >> 4;  // 0..15
+    const int cg = tid & 15;          // 0..15 -> columns 2cg, 2cg+1
     const int j0 = blockIdx.x * kRecJ;
     const int b0 = blockIdx.y * kRecB;
     const unsigned int num_ctas = gridDim.x * gridDim.y;
@@ -140,13 +141,14 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
         }
     }
     // epilogue ownership: thread -> (row eb, unit ej); its cell state lives in a register across steps
-    const int eb = tid >> 3, ej = tid & 7;
+    const bool epi = tid < kRecB * kRecJ;  // one epilogue thread per (row, unit)
+    const int eb = (tid >> 3) & (kRecB - 1), ej = tid & 7;
     float c_state = 0.0f;
     if (tid == 0) s_abort = 0;
     __syncthreads();
     // the input projection of step t does not depend on h: it is fetched one step ahead, before the inter-step wait
     float pre_g[4] = {0.f, 0.f, 0.f, 0.f};
-    if (b0 + eb < B) {
+    if (epi && b0 + eb < B) {
         const float* prow = pre + (static_cast<int64_t>(0) * B + b0 + eb) * (4 * H) + j0 + ej;
 #pragma unroll
         for (int g = 0; g < 4; ++g) pre_g[g] = __ldg(prow + g * H);
@@ -179,17 +181,17 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
         // collide on banks) and starts multiplying as soon as the first block has landed, while the others are still on
         // their way.  No block barrier between staging and arithmetic.  The order of the additions inside every dot
         // product is the slice's k order, as before.
-        constexpr int kRowsPerGroup = 4, kGroups = kRecB / kRowsPerGroup;
+        constexpr int kRowsPerGroup = 4, kGroups = kRecB / 2 / kRowsPerGroup;  // per half
         static_assert(KSL / 4 * 2 == 16 || KSL / 4 * 2 == 8, "a row's chunks of both slices: 16 (H = 512) or 8 (H = 256)");
         constexpr int kChunks = KSL / 4 * 2;  // 16-byte chunks per row and warp
         if (t > 0) {
-            const int warp = tid >> 5, lane = tid & 31;
+            const int warp = (tid & 255) >> 5, lane = tid & 31;  // (the k-slices of this warp: 2 * warp, 2 * warp + 1)
             const float* hsrc = hs + (static_cast<int64_t>(t - 1) * B) * H;
 #pragma unroll
             for (int g = 0; g < kGroups; ++g) {
 #pragma unroll
                 for (int e = lane; e < kRowsPerGroup * kChunks; e += 32) {
-                    const int r = g * kRowsPerGroup + e / kChunks, c = e % kChunks;
+                    const int r = half * (kRecB / 2) + g * kRowsPerGroup + e / kChunks, c = e % kChunks;
                     const int kcol = (2 * warp + c / (KSL / 4)) * KSL + 4 * (c % (KSL / 4));
                     float* dst = h_s + r * HROW + kcol + (kcol / KSL) * 4;
                     if (b0 + r < B) cp_async_16(dst, hsrc + static_cast<int64_t>(b0 + r) * H + kcol);
@@ -208,7 +210,7 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
                 }
 #pragma unroll
                 for (int bb = 0; bb < kRowsPerGroup; ++bb) {
-                    const int b = g * kRowsPerGroup + bb;
+                    const int b = half * (kRecB / 2) + g * kRowsPerGroup + bb;
                     float a0 = 0.0f, a1 = 0.0f;
                     if (t > 0) {
 #pragma unroll
@@ -232,7 +234,7 @@ lstm_recurrent_kernel(const float* __restrict__ pre, const float* __restrict__ w
         // ---- reduce the 16 slices, add the input projection, gates, slice-assign into hs[t], cs[t] ----
         {
             const int gb = b0 + eb;
-            if (gb < B) {
+            if (epi && gb < B) {
                 float gate[4];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
