@@ -215,3 +215,28 @@ def test_yolo_topk_pruning_does_not_change_results(fb):
     for a, b in zip(results[1], results[0]):
         assert torch.equal(a, b)
     assert cand[1] < cand[0]
+
+
+def test_one_call_postprocess_replays_from_a_cuda_graph(fb):
+    """The one-call post-process allocates nothing and never synchronises: captured once, a replay on new logits in the
+    same buffers gives what a direct call gives."""
+    maps_a = [m.cuda() for m in W.make_yolo_inputs(4)]
+    maps_b = [m.cuda() for m in W.make_yolo_inputs(4, first=4)]
+    plan = fb.ops.YoloPostprocessPlan(4)
+    ref = fb.ops.YoloPostprocessPlan(4)
+    static_in = [m.clone() for m in maps_a]
+    plan.run(static_in, 0.5, 0.45)  # first call outside the capture (kernel attributes, lazy module loading)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=stream):
+        plan.run(static_in, 0.5, 0.45)
+    for maps in (maps_b, maps_a):
+        for dst, src in zip(static_in, maps):
+            dst.copy_(src)
+        g.replay()
+        ref.run(maps, 0.5, 0.45)
+        torch.cuda.synchronize()
+        assert int(plan.status.item()) == 0 and int(ref.status.item()) == 0
+        assert torch.equal(plan.counts, ref.counts)
+        assert torch.equal(plan.dets, ref.dets) and torch.equal(plan.labels, ref.labels) and torch.equal(plan.flat_ids, ref.flat_ids)
