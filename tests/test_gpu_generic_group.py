@@ -142,3 +142,39 @@ def test_reference_simple_programs_are_one_launch_each(env):
     boxes = (torch.rand(3000, 4, generator=g) * 100).cuda()
     offs = torch.randn(3000, 4, generator=g).cuda()
     assert check(env, simpleops.offset2bbox, (boxes, offs)) == (1, 1, 1, 0)
+
+
+def rank5(x: torch.Tensor, y: torch.Tensor):
+    t = x.clone()
+    t[:, :, 1, :, 0:3] = torch.relu(t[:, :, 1, :, 0:3]) - y
+    u = t.permute(0, 2, 1, 3, 4) * 0.5
+    return u, t[:, 0, :, 1:3, :] > 0.25
+
+
+def test_rank_five_program_and_bool_output(env):
+    """Index arithmetic over five dimensions (the rank-8 instantiation), a permuted output and a bool output."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(3, 4, 5, 6, 7, generator=g).cuda()
+    y = torch.randn(6, 3, generator=g).cuda()
+    check(env, rank5, (x, y))
+
+
+def scaled(x: torch.Tensor, s: float):
+    t = x.clone()
+    t[1:, :] = t[1:, :] * s
+    return t + 1.0
+
+
+def test_cached_programs_follow_shapes_and_scalars(env):
+    """The flattened program of a functor is kept between calls: another shape or another scalar value rebuilds it, the
+    same ones only re-point it; the results are those of the eager program every time."""
+    fb, J = env
+    g = torch.Generator().manual_seed(12)
+    a = torch.randn(9, 17, generator=g).cuda()
+    b = torch.randn(33, 5, generator=g).cuda()
+    built = J.build(scaled, (a, 2.0))
+    for x, s in ((a, 2.0), (a, 2.0), (a, -0.75), (b, -0.75), (a, 2.0), (b.t().contiguous().t(), 3.5)):
+        i0 = J.interpreted_functor_runs()
+        got = built(x, s)
+        assert J.interpreted_functor_runs() == i0, J.last_generic_refusal()
+        assert torch.equal(got, scaled(x, s))
