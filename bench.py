@@ -38,7 +38,7 @@ def workload_config(world: int) -> dict:
             "batch_per_gpu": BATCH,
             "inputs": "seeded N(0,1) logits, 231.7 MB per step; the GPU arm rotates 3 input sets so that no step finds its logits in the 126 MB L2",
             "throughput_mode": "GPU arm: up to three batches in flight, one stream each, a block of steps replayed from a CUDA graph (latency_us is one batch at a time, call by call); CPU arm: one call after the other on all host threads",
-            "collective": "none" if world == 1 else "gather of the 2 MB detection records of every rank to rank 0 (NCCL), on a second stream while the next step computes"}
+            "collective": "none" if world == 1 else "gather of the 2 MB detection records of every rank to rank 0 over NVLink, on a second stream while the next steps compute (how: the line's gather key)"}
 
 
 def measured_peaks():
@@ -452,12 +452,13 @@ def run_ours(args):
     # only rank 0 holds the gathered detections
     rec_all = (torch.empty(world * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
                if world > 1 and rank == 0 else None)
-    # multi-GPU: the gather of step i runs on a second stream while the next steps compute; one record buffer more than
-    # there are batches in flight, so that no batch waits for the gather of an earlier one
+    # multi-GPU: the gather of step i runs on a second stream while the next steps compute; ten record buffers in rotation,
+    # so that no batch waits for the gather of an earlier one
     n_rec = 1
     packed_ev = gathered_ev = cap_packed_ev = cap_gathered_ev = None
+    pusher, gather_note = None, "NCCL gather (dist.gather) per step"
     if world > 1:
-        n_rec = max(2, int(args.in_flight) + 1)
+        n_rec = max(2, int(args.in_flight) + 1, int(args.rec_buffers) if args.rec_buffers > 0 else 10)
         comm_stream = torch.cuda.Stream(dev, priority=-1 if args.comm_priority == "high" else 0)
         recs = [rec] + [torch.empty_like(rec) for _ in range(n_rec - 1)]
         rec_alls = ([rec_all] + [torch.empty_like(rec_all) for _ in range(n_rec - 1)]) if rank == 0 else [None] * n_rec
@@ -467,6 +468,15 @@ def run_ours(args):
             e.record()
         cap_packed_ev = [torch.cuda.Event() for _ in range(n_rec)]
         cap_gathered_ev = [torch.cuda.Event() for _ in range(n_rec)]
+        # The gather itself: NCCL send / receive pairs (dist.gather), or --gather one-sided: every rank pushes its records
+        # into its slot of rank 0's buffers with an asynchronous copy (CUDA IPC mapping, copy engine over NVLink, no
+        # kernel on either side).  Measured at N = 2: 98 us per step one-sided against 88 with NCCL, hence the default.
+        if args.gather == "one-sided":
+            try:
+                pusher = fdist.OneSidedGather((BATCH, topk, fdist.RECORD_WORDS), n_rec, dev, dst=0)
+                gather_note = "one-sided: asynchronous peer copies into rank 0's buffers (CUDA IPC), one small all-reduce per block"
+            except RuntimeError as exc:
+                pusher, gather_note = None, f"NCCL gather (one-sided set-up failed: {str(exc)[:120]})"
     # per-step stage events, recorded inside the one-call entry point through its profiling hook
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     for row in ev:
@@ -499,7 +509,12 @@ def run_ours(args):
                 p_ev[j].record(cur)
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(p_ev[j])
-                    fdist.gather_records_to(recs[j], 0, out=rec_alls[j])
+                    if args.no_gather:
+                        pass
+                    elif pusher is not None:
+                        pusher.push(recs[j], j)          # copy engine over NVLink into rank 0's buffer: no kernel
+                    else:
+                        fdist.gather_records_to(recs[j], 0, out=rec_alls[j])
                     g_ev[j].record(comm_stream)
 
     def barrier():
@@ -532,6 +547,9 @@ def run_ours(args):
             for ws in work_streams:
                 main.wait_stream(ws)
         if world > 1:
+            if pusher is not None and not args.no_gather:
+                with torch.cuda.stream(comm_stream):
+                    pusher.landed()         # one small all-reduce: every rank's pushes of this block have arrived
             main.wait_stream(comm_stream)   # the block ends when the last gather has landed
 
     # Throughput blocks are replayed from a CUDA graph (kernels, memsets, events and the NCCL gather of all `steps` steps,
@@ -626,6 +644,8 @@ def run_ours(args):
             "ms_per_step_spread": {"min": min(block_ms) / args.steps, "median": ms_per_step, "max": max(block_ms) / args.steps},
             "in_flight": in_flight,
             "cuda_graph": graph_note,
+            **({"gather": gather_note} if world > 1 else {}),
+            **({"diagnostic": "gather skipped (--no-gather): not a result"} if args.no_gather else {}),
             "latency_us": seq_ms / args.steps * 1e3, "kernels_per_call": launches / args.steps,
             "images_per_s": world * BATCH * 1e3 / ms_per_step,
             "stage_us": {"decode_mask_compact": decode_ms * 1e3, "select_topk": select_ms * 1e3, "nms": nms_ms * 1e3},
@@ -727,6 +747,11 @@ def main():
                     help="stream priority of the multi-GPU gather (N > 1)")
     ap.add_argument("--in-flight", type=int, default=3, choices=[1, 2, 3, 4],
                     help="batches in flight in the throughput measurement (one stream each; 1 = strictly one after the other; measured on one B200: 129 / 98 / 92 / 91 us per step for 1 / 2 / 3 / 4)")
+    ap.add_argument("--rec-buffers", type=int, default=0, help="N > 1: record buffers in rotation (default 10: with four, a step now and then waited for the gather of the fourth step before it)")
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "one-sided"],
+                    help="N > 1: NCCL send / receive pairs, or asynchronous peer copies into rank 0's buffers")
+    ap.add_argument("--no-gather", action="store_true",
+                    help="diagnostic (N > 1): write the detection records but skip the gather (the number is then not a result)")
     ap.add_argument("--no-graph", action="store_true", help="issue the throughput blocks call by call instead of replaying a CUDA graph")
     ap.add_argument("--no-extra", action="store_true", help="skip the cpu_baseline leg and the other workloads")
     ap.add_argument("--only", default=None, choices=["yolo", "ssd", "yolact", "lstm", "get_started", "normalize"],

@@ -48,6 +48,7 @@ SIGNATURES = {
     "functs_b200_nms_scratch_bytes": (c_int64, [c_int32, c_int32]),
     "functs_b200_batched_nms": (c_int32, [P, c_int64, c_int32, P, P, c_int32, c_int32, c_float, c_int32, P, P, P, P, P, P, P, P]),
     "functs_b200_pack_detections": (c_int32, [P, P, P, P, c_int32, c_int32, P, P]),
+    "functs_b200_push_records": (c_int32, [P, P, c_int64, P]),
     "functs_b200_batched_nms_static_max_groups": (c_int32, []),
     "functs_b200_batched_nms_static": (c_int32, [P, c_int64, c_int32, P, P, c_int32, c_int32, c_float, c_int32, P, P, P, P, P, P, P]),
     "functs_b200_yolo_decode": (c_int32, [P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, P, P, P, P, P, c_int64, P, P, P]),

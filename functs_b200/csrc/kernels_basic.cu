@@ -461,4 +461,13 @@ int functs_b200_pack_detections(const float* dets, const int64_t* labels, const 
     return check_launch("pack_detections_kernel");
 }
 
+int functs_b200_push_records(void* dst, const int32_t* records, int64_t bytes, void* stream) {
+    using namespace fb;
+    FB_REQUIRE(dst != nullptr && records != nullptr && bytes > 0, "push_records: null pointer or empty copy");
+    FB_REQUIRE(((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(records) | static_cast<uintptr_t>(bytes)) & 15) == 0,
+               "push_records: pointers and size must be multiples of 16 bytes");
+    return check_cuda(cudaMemcpyAsync(dst, records, static_cast<size_t>(bytes), cudaMemcpyDefault, as_stream(stream)),
+                      "push_records copy");
+}
+
 }  // extern "C"

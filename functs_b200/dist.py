@@ -97,3 +97,72 @@ def gather_ragged(rec: torch.Tensor, total: int, group=None) -> torch.Tensor:
     parts: List[torch.Tensor] = [full[r * cap:r * cap + (e - s)] for r, (s, e) in enumerate(sizes)]
     return torch.cat(parts, dim=0)
 
+
+
+class OneSidedGather:
+    """Gather of equally sized record shards to ONE rank without a kernel on either side: the destination rank owns
+    `n_buffers` buffers [world * B, K, 8], the other ranks of the box open them through CUDA IPC handles and push their shard
+    into their slot with an asynchronous copy (copy engine over NVLink, functs_b200_push_records).  NCCL's send / receive
+    kernels need streaming multiprocessors that a bandwidth-bound kernel in flight has filled; a copy engine does not.
+    `landed()` is one small all-reduce: when it has completed on a rank, every push that any rank issued before its own
+    call (on the same stream) has arrived.  CUDA tensors on the GPUs of one box only; on gloo / CPU tensors (the host-side
+    tests) the pushes are plain gathers.
+
+    Setting it up is collective (every rank of the group must construct it with the same arguments)."""
+
+    def __init__(self, shard_shape, n_buffers: int, device, dst: int = 0, group=None):
+        self.group, self.dst = group, dst
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.shard_shape = tuple(shard_shape)
+        self.device = torch.device(device)
+        self.on_gpu = self.device.type == "cuda"
+        full_shape = (self.world * self.shard_shape[0],) + self.shard_shape[1:]
+        self.shard_bytes = 4
+        for d in self.shard_shape:
+            self.shard_bytes *= int(d)
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.buffers = None   # on dst: the owned buffers; elsewhere: the same memory, opened through IPC
+        if self.rank == dst:
+            self.buffers = [torch.empty(full_shape, dtype=torch.int32, device=self.device) for _ in range(n_buffers)]
+        if not self.on_gpu:
+            return
+        if self.shard_bytes % 16 != 0:
+            raise ValueError("OneSidedGather: a shard must be a multiple of 16 bytes")
+        from torch.multiprocessing.reductions import reduce_tensor
+        payload = [[reduce_tensor(b) for b in self.buffers] if self.rank == dst else None]
+        dist.broadcast_object_list(payload, src=dst, group=group)
+        problem = ""
+        if self.rank != dst:
+            try:
+                self.buffers = [fn(*args) for fn, args in payload[0]]
+                for b in self.buffers:
+                    if tuple(b.shape) != full_shape or b.dtype != torch.int32 or not b.is_contiguous():
+                        problem = "the opened buffer does not look like the destination's"
+            except Exception as exc:  # noqa: BLE001 - every rank must learn of it, or the others would wait for ever
+                problem = f"{type(exc).__name__}: {exc}"
+        # every rank has opened the handles (or none goes on): the failure of one is the failure of all
+        ok = torch.tensor([0 if problem else 1], dtype=torch.int32, device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            raise RuntimeError("OneSidedGather: a rank could not open the destination's buffers" + (f" ({problem})" if problem else ""))
+
+    def push(self, rec: torch.Tensor, buffer: int) -> None:
+        """Enqueues, on the current stream, the copy of this rank's shard into its slot of buffer `buffer` on the destination."""
+        if tuple(rec.shape) != self.shard_shape or rec.dtype != torch.int32 or not rec.is_contiguous():
+            raise ValueError("OneSidedGather.push: a contiguous int32 tensor of the shard shape is expected")
+        if not self.on_gpu:
+            parts = list(self.buffers[buffer].chunk(self.world, dim=0)) if self.rank == self.dst else None
+            dist.gather(rec, parts, dst=self.dst, group=self.group)
+            return
+        from ._lib import check, lib
+        target = self.buffers[buffer].data_ptr() + self.rank * self.shard_bytes
+        check(lib.functs_b200_push_records(target, rec.data_ptr(), self.shard_bytes,
+                                           torch.cuda.current_stream(rec.device).cuda_stream), "push_records")
+
+    def landed(self) -> None:
+        """One small collective on the current stream: behind it, every push issued before it by any rank has arrived."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def gathered(self, buffer: int):
+        """The destination's buffer (None on the other ranks)."""
+        return self.buffers[buffer] if self.rank == self.dst else None

@@ -130,6 +130,13 @@ int functs_b200_batched_nms_static(const float* boxes, int64_t num_boxes, int32_
 int functs_b200_pack_detections(const float* dets, const int64_t* labels, const int64_t* flat_ids, const int32_t* counts,
                                 int32_t groups, int32_t topk, int32_t* records, void* stream);
 
+/* Pushes `bytes` of packed records from this GPU into a buffer that may live on another GPU of the box (a pointer this
+ * process got by opening the owner's CUDA IPC handle): one asynchronous copy on `stream`, carried out by a copy engine
+ * over NVLink, no kernel on either GPU.  The one-sided form of "only the final detections are gathered": every rank
+ * pushes its shard into its slot of the destination rank's buffer; the caller confirms arrival with one small
+ * collective per block of steps.  Both pointers 16-byte aligned, bytes a multiple of 16. */
+int functs_b200_push_records(void* dst, const int32_t* records, int64_t bytes, void* stream);
+
 /* ---- C2: YOLOv3-style decode + score mask + top-k + class-wise NMS ----------------------- */
 /* Follows functs/benchmark/ai_model/yolov3/yolov3_bbox.py:195-243 at the configured shapes:
  * three NCHW logit maps [batch, 255, S, S]; box order is level, y, x, anchor. */

@@ -72,3 +72,41 @@ def test_gather_two_ranks_gloo(tmp_path):
         mp.spawn(_worker, args=(2, port, total, str(tmp_path)), nprocs=2, join=True)
         for r in range(2):
             assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
+
+
+def _one_sided_worker(rank, world, port, q):
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        g = fdist.OneSidedGather((3, 5, fdist.RECORD_WORDS), 2, "cpu", dst=0)
+        out = []
+        for step in range(4):
+            rec = torch.full((3, 5, fdist.RECORD_WORDS), 100 * step + rank, dtype=torch.int32)
+            g.push(rec, step % 2)
+            g.landed()
+            if rank == 0:
+                out.append(g.gathered(step % 2).clone())
+            else:
+                assert g.gathered(step % 2) is None
+        q.put((rank, out))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_one_sided_gather_host_logic():
+    """On gloo / CPU tensors the pushes are plain gathers: every rank's shard ends up in its slot of the destination's
+    buffer, buffer after buffer."""
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_one_sided_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=180) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for step, full in enumerate(res[0]):
+        assert full.shape == (6, 5, 8)
+        assert int(full[:3].min()) == int(full[:3].max()) == 100 * step
+        assert int(full[3:].min()) == int(full[3:].max()) == 100 * step + 1
+    assert res[1] == []
