@@ -455,28 +455,33 @@ def run_ours(args):
     # multi-GPU: the gather of step i runs on a second stream while the next steps compute; ten record buffers in rotation,
     # so that no batch waits for the gather of an earlier one
     n_rec = 1
+    group = 1                      # steps whose records travel in one gather (N > 1)
     packed_ev = gathered_ev = cap_packed_ev = cap_gathered_ev = None
-    pusher, gather_note = None, "NCCL gather (dist.gather) per step"
+    pusher, gather_note = None, "NCCL gather (dist.gather)"
     if world > 1:
-        n_rec = max(2, int(args.in_flight) + 1, int(args.rec_buffers) if args.rec_buffers > 0 else 10)
+        group = max(1, int(args.gather_every))
+        n_rec = max(2, -(-(int(args.rec_buffers) if args.rec_buffers > 0 else 10) // group), -(-(in_flight + group) // group))
         comm_stream = torch.cuda.Stream(dev, priority=-1 if args.comm_priority == "high" else 0)
-        recs = [rec] + [torch.empty_like(rec) for _ in range(n_rec - 1)]
-        rec_alls = ([rec_all] + [torch.empty_like(rec_all) for _ in range(n_rec - 1)]) if rank == 0 else [None] * n_rec
-        packed_ev = [torch.cuda.Event() for _ in range(n_rec)]
+        # record buffers: n_rec groups of `group` steps each; a group is gathered in one go when its last step is done
+        recs = [torch.empty(group, BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev) for _ in range(n_rec)]
+        rec_alls = ([torch.empty(world * group * BATCH, topk, fdist.RECORD_WORDS, dtype=torch.int32, device=dev)
+                     for _ in range(n_rec)] if rank == 0 else [None] * n_rec)
+        packed_ev = [[torch.cuda.Event() for _ in range(group)] for _ in range(n_rec)]
         gathered_ev = [torch.cuda.Event() for _ in range(n_rec)]
         for e in gathered_ev:
             e.record()
-        cap_packed_ev = [torch.cuda.Event() for _ in range(n_rec)]
+        cap_packed_ev = [[torch.cuda.Event() for _ in range(group)] for _ in range(n_rec)]
         cap_gathered_ev = [torch.cuda.Event() for _ in range(n_rec)]
         # The gather itself: NCCL send / receive pairs (dist.gather), or --gather one-sided: every rank pushes its records
         # into its slot of rank 0's buffers with an asynchronous copy (CUDA IPC mapping, copy engine over NVLink, no
         # kernel on either side).  Measured at N = 2: 98 us per step one-sided against 88 with NCCL, hence the default.
         if args.gather == "one-sided":
             try:
-                pusher = fdist.OneSidedGather((BATCH, topk, fdist.RECORD_WORDS), n_rec, dev, dst=0)
+                pusher = fdist.OneSidedGather((group * BATCH, topk, fdist.RECORD_WORDS), n_rec, dev, dst=0)
                 gather_note = "one-sided: asynchronous peer copies into rank 0's buffers (CUDA IPC), one small all-reduce per block"
             except RuntimeError as exc:
                 pusher, gather_note = None, f"NCCL gather (one-sided set-up failed: {str(exc)[:120]})"
+        gather_note += f"; the records of {group} consecutive steps per transfer" if group > 1 else "; one transfer per step"
     # per-step stage events, recorded inside the one-call entry point through its profiling hook
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     for row in ev:
@@ -486,9 +491,9 @@ def run_ours(args):
     import ctypes
     ev_handles = [(ctypes.c_void_p * 4)(*[e.cuda_event for e in row]) for row in ev]
 
-    def step(i, handles=None, pipelined=False, capturing=False):
-        j = i % n_rec                  # record / gather buffers (N > 1)
-        k = i % in_flight              # plan and stream of this batch
+    def step(i, handles=None, pipelined=False, capturing=False, last=False):
+        j, slot = (i // group) % n_rec, i % group   # record buffer group and place inside it (N > 1)
+        k = i % in_flight                            # plan and stream of this batch
         p = plans[k] if pipelined else plan
         ctx = torch.cuda.stream(work_streams[k]) if pipelined else contextlib.nullcontext()
         with ctx:
@@ -497,36 +502,40 @@ def run_ours(args):
             cur = torch.cuda.current_stream()
             # (a capture has events of its own: an event recorded inside a capture cannot be waited for outside it)
             p_ev, g_ev = (cap_packed_ev, cap_gathered_ev) if capturing else (packed_ev, gathered_ev)
-            if world > 1 and not (capturing and i < n_rec):
-                # the gather that used this record buffer n_rec steps ago is done (inside a capture the first uses have
-                # no earlier gather: a replay starts after the previous one has finished)
+            if world > 1 and not (capturing and i < n_rec * group):
+                # the gather that used this group of record buffers n_rec groups ago is done (inside a capture the first
+                # uses have no earlier gather: a replay starts after the previous one has finished)
                 cur.wait_event(g_ev[j])
             # memset + decode/mask/compact + binned top-k + NMS: 3 kernels; with N > 1 the NMS kernel also writes the records
-            p.run(sets[i % n_sets], 0.5, 0.45, records=recs[j] if world > 1 else None)
+            p.run(sets[i % n_sets], 0.5, 0.45, records=recs[j][slot] if world > 1 else None)
             if handles is not None:
                 lib.functs_b200_set_stage_events(None, 0)
             if world > 1:
-                p_ev[j].record(cur)
-                with torch.cuda.stream(comm_stream):
-                    comm_stream.wait_event(p_ev[j])
-                    if args.no_gather:
-                        pass
-                    elif pusher is not None:
-                        pusher.push(recs[j], j)          # copy engine over NVLink into rank 0's buffer: no kernel
-                    else:
-                        fdist.gather_records_to(recs[j], 0, out=rec_alls[j])
-                    g_ev[j].record(comm_stream)
+                p_ev[j][slot].record(cur)
+                if slot == group - 1 or last:   # the group is complete (or the block ends): its records travel now
+                    with torch.cuda.stream(comm_stream):
+                        for q in range(slot + 1):
+                            comm_stream.wait_event(p_ev[j][q])
+                        whole = recs[j].view(group * BATCH, topk, fdist.RECORD_WORDS)
+                        if args.no_gather:
+                            pass
+                        elif pusher is not None:
+                            pusher.push(whole, j)        # copy engine over NVLink into rank 0's buffer: no kernel
+                        else:
+                            fdist.gather_records_to(whole, 0, out=rec_alls[j])
+                        g_ev[j].record(comm_stream)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
+    n_warm = max(args.warmup, 3)
+    for i in range(n_warm):
+        step(i, last=i == n_warm - 1)
     barrier()  # the pipelined steps run on other streams and reuse the first plan's outputs and scratch
-    for i in range(max(args.warmup, 3)):
-        step(i, pipelined=True)
+    for i in range(n_warm):
+        step(i, pipelined=True, last=i == n_warm - 1)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -542,7 +551,7 @@ def run_ours(args):
         if world > 1 and capturing:
             comm_stream.wait_event(fork_event)
         for i in range(args.steps):
-            step(i, ev_handles[i] if with_stage_events else None, pipelined, capturing)
+            step(i, ev_handles[i] if with_stage_events else None, pipelined, capturing, last=i == args.steps - 1)
         if pipelined:
             for ws in work_streams:
                 main.wait_stream(ws)
@@ -748,6 +757,8 @@ def main():
     ap.add_argument("--in-flight", type=int, default=3, choices=[1, 2, 3, 4],
                     help="batches in flight in the throughput measurement (one stream each; 1 = strictly one after the other; measured on one B200: 129 / 98 / 92 / 91 us per step for 1 / 2 / 3 / 4)")
     ap.add_argument("--rec-buffers", type=int, default=0, help="N > 1: record buffers in rotation (default 10: with four, a step now and then waited for the gather of the fourth step before it)")
+    ap.add_argument("--gather-every", type=int, default=4,
+                    help="N > 1: the records of this many consecutive steps travel in one gather")
     ap.add_argument("--gather", default="nccl", choices=["nccl", "one-sided"],
                     help="N > 1: NCCL send / receive pairs, or asynchronous peer copies into rank 0's buffers")
     ap.add_argument("--no-gather", action="store_true",
