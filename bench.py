@@ -512,7 +512,14 @@ def run_ours(args):
                 lib.functs_b200_set_stage_events(None, 0)
             if world > 1:
                 p_ev[j][slot].record(cur)
-                if slot == group - 1 or last:   # the group is complete (or the block ends): its records travel now
+                if not pipelined:
+                    # one batch at a time (the latency block): this step's records travel on their own, right away
+                    with torch.cuda.stream(comm_stream):
+                        comm_stream.wait_event(p_ev[j][slot])
+                        if not args.no_gather:
+                            fdist.gather_records_to(recs[j][slot], 0, out=rec_all)
+                        g_ev[j].record(comm_stream)
+                elif slot == group - 1 or last:   # the group is complete (or the block ends): its records travel now
                     with torch.cuda.stream(comm_stream):
                         for q in range(slot + 1):
                             comm_stream.wait_event(p_ev[j][q])
