@@ -29,26 +29,61 @@ __device__ __forceinline__ int g_pick(const GIndex& ix, int dim) {
     return v;
 }
 
-template <int R>
-__device__ __forceinline__ float g_load(const functs_b200_gprogram& P, const functs_b200_gload& L, const GIndex& ix) {
-    int off = L.base;
-    if (L.general == 0) {
-        off += g_dot<R>(L.coef, ix);
-    } else {  // a coordinate is divided (a read below a strided assignment): term by term
-        for (int k = 0; k < L.nterms; ++k) {
-            const functs_b200_gterm t = L.term[k];
-            int v = t.add;
-            if (t.dim >= 0) v += t.mul * g_pick<R>(ix, t.dim);
-            if (t.div > 1) v /= t.div;
-            off += v * t.stride;
-        }
-    }
-    const void* p = P.in_ptr[L.tensor];
-    switch (L.dtype) {
+__device__ __forceinline__ float g_fetch(const void* p, int dtype, int off) {
+    switch (dtype) {
         case 0: return __ldg(static_cast<const float*>(p) + off);
         case 1: return static_cast<float>(__ldg(static_cast<const uint8_t*>(p) + off));
         case 2: return static_cast<float>(__ldg(static_cast<const long long*>(p) + off));
         default: return static_cast<float>(__ldg(static_cast<const int*>(p) + off));
+    }
+}
+
+// V values of one load: the V elements a thread works on are neighbours along the fastest dimension (position
+// rank - 1), which no predicate tests, so their offsets differ by that dimension's coefficient only.  `last` is the
+// number of valid elements minus one (an element beyond the extent re-reads the last valid one; it is never stored).
+template <int R, int V>
+__device__ __forceinline__ void g_load(const functs_b200_gprogram& P, const functs_b200_gload& L, const GIndex& ix, int last,
+                                       float (&out)[V]) {
+    const void* p = P.in_ptr[L.tensor];
+    if (L.general == 0) {
+        const int off = L.base + g_dot<R>(L.coef, ix);
+        int step = 0;
+#pragma unroll
+        for (int k = 0; k < R; ++k) step = (k == P.rank - 1) ? L.coef[k] : step;
+#pragma unroll
+        for (int v = 0; v < V; ++v) out[v] = g_fetch(p, L.dtype, off + min(v, last) * step);
+    } else {  // a coordinate is divided (a read below a strided assignment): term by term, element by element
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            GIndex iv = ix;
+#pragma unroll
+            for (int k = 0; k < R; ++k) iv.x[k] += (k == P.rank - 1) ? min(v, last) : 0;
+            int off = L.base;
+            for (int k = 0; k < L.nterms; ++k) {
+                const functs_b200_gterm t = L.term[k];
+                int c = t.add;
+                if (t.dim >= 0) c += t.mul * g_pick<R>(iv, t.dim);
+                if (t.div > 1) c /= t.div;
+                off += c * t.stride;
+            }
+            out[v] = g_fetch(p, L.dtype, off);
+        }
+    }
+}
+
+__device__ __forceinline__ float g_unary(int op, float a, float imm) {
+    switch (op) {
+        case FB_G_EXP: return expf(a);
+        case FB_G_SIGMOID: return sigmoid_f32(a);
+        case FB_G_TANH: return tanhf(a);
+        case FB_G_RELU: return fmaxf(a, 0.0f);
+        case FB_G_NEG: return -a;
+        case FB_G_CLAMP_MIN: return fmaxf(a, imm);
+        case FB_G_CLAMP_MAX: return fminf(a, imm);
+        case FB_G_ABS: return fabsf(a);
+        case FB_G_SQRT: return sqrtf(a);
+        case FB_G_LOG: return logf(a);
+        default: return a;
     }
 }
 
@@ -70,12 +105,14 @@ __device__ __forceinline__ float g_binary(int op, float a, float b) {
     }
 }
 
-// The value stack: its top lives in a register, the rest in a small local array, so a chain of loads, unary operators and
-// scalar (*_IMM) operators never touches memory.
-template <int R>
-__device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const GIndex& ix) {
-    float st[FB_G_STACK];
-    float tos = 0.0f;
+// The value stack, V values wide: its top lives in registers, the rest in a small local array, so a chain of loads, unary
+// operators and scalar (*_IMM) operators never touches memory.  One pass through the program serves the thread's V
+// elements: decoding an instruction and testing a predicate cost the same for one element as for four.
+template <int R, int V>
+__device__ __forceinline__ void g_eval(const functs_b200_gprogram& P, const GIndex& ix, int last, float (&tos)[V]) {
+    float st[FB_G_STACK][V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) tos[v] = 0.0f;
     int sp = 0;  // values on the stack, the one in `tos` included
     int pc = 0;
     for (int guard = 0; guard < 4 * FB_G_MAX_INSTR; ++guard) {
@@ -84,52 +121,50 @@ __device__ __forceinline__ float g_eval(const functs_b200_gprogram& P, const GIn
         const int op = I.op;
         if (op == FB_G_END) break;
         if (op == FB_G_LOAD || op == FB_G_CONST) {
-            const float v = op == FB_G_LOAD ? g_load<R>(P, P.load[I.arg], ix) : I.imm.f;
-            if (sp > 0) st[sp - 1] = tos;
-            tos = v;
+            if (sp > 0) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) st[sp - 1][v] = tos[v];
+            }
+            if (op == FB_G_LOAD) {
+                g_load<R, V>(P, P.load[I.arg], ix, last, tos);
+            } else {
+#pragma unroll
+                for (int v = 0; v < V; ++v) tos[v] = I.imm.f;
+            }
             ++sp;
         } else if (op == FB_G_COND) {
             const functs_b200_gpred& q = P.pred[I.arg];
-            const int v = q.add + g_dot<R>(q.coef, ix);
-            const bool ok = v >= q.lo && v < q.hi && (q.step <= 1 || ((v - q.lo) % q.step) == 0);
+            const int c = q.add + g_dot<R>(q.coef, ix);
+            const bool ok = c >= q.lo && c < q.hi && (q.step <= 1 || ((c - q.lo) % q.step) == 0);
             if (!ok) pc = I.imm.i;
         } else if (op == FB_G_JUMP) {
             pc = I.arg;
         } else if (op < FB_G_ADD) {
-            float a = tos;
-            switch (op) {
-                case FB_G_EXP: a = expf(a); break;
-                case FB_G_SIGMOID: a = sigmoid_f32(a); break;
-                case FB_G_TANH: a = tanhf(a); break;
-                case FB_G_RELU: a = fmaxf(a, 0.0f); break;
-                case FB_G_NEG: a = -a; break;
-                case FB_G_CLAMP_MIN: a = fmaxf(a, I.imm.f); break;
-                case FB_G_CLAMP_MAX: a = fminf(a, I.imm.f); break;
-                case FB_G_ABS: a = fabsf(a); break;
-                case FB_G_SQRT: a = sqrtf(a); break;
-                case FB_G_LOG: a = logf(a); break;
-                default: break;
-            }
-            tos = a;
+#pragma unroll
+            for (int v = 0; v < V; ++v) tos[v] = g_unary(op, tos[v], I.imm.f);
         } else if (op < FB_G_ADD + FB_G_IMM) {
-            const float b = tos;
             --sp;
-            tos = g_binary(op, st[sp - 1], b);
+#pragma unroll
+            for (int v = 0; v < V; ++v) tos[v] = g_binary(op, st[sp - 1][v], tos[v]);
         } else if (op == FB_G_RSUB_IMM) {
-            tos = __fsub_rn(I.imm.f, tos);
+#pragma unroll
+            for (int v = 0; v < V; ++v) tos[v] = __fsub_rn(I.imm.f, tos[v]);
         } else if (op == FB_G_RDIV_IMM) {
-            tos = __fdiv_rn(I.imm.f, tos);
+#pragma unroll
+            for (int v = 0; v < V; ++v) tos[v] = __fdiv_rn(I.imm.f, tos[v]);
         } else {
-            tos = g_binary(op - FB_G_IMM, tos, I.imm.f);
+#pragma unroll
+            for (int v = 0; v < V; ++v) tos[v] = g_binary(op - FB_G_IMM, tos[v], I.imm.f);
         }
     }
-    return tos;
 }
 
-template <int R>
+// One work item = V neighbouring elements along the fastest dimension (V = P.vec; the extent of that dimension in
+// `shape` is then the number of V-blocks, lane_extent the number of elements).
+template <int R, int V>
 __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
     const int stride = gridDim.x * blockDim.x;
-    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < P.numel; e += stride) {
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < P.work; e += stride) {
         GIndex ix;
         uint32_t rem = static_cast<uint32_t>(e);
 #pragma unroll
@@ -143,17 +178,37 @@ __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
                 rem = q;
             }
         }
-        const float v = g_eval<R>(P, ix);
+        int last = 0, ostep = 0;
+        if (V > 1) {
+            int first = 0;
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                if (k == P.rank - 1) {
+                    ix.x[k] *= V;
+                    first = ix.x[k];
+                    ostep = P.out_coef[k];
+                }
+            }
+            last = min(V, P.lane_extent - first) - 1;
+        }
+        float val[V];
+        g_eval<R, V>(P, ix, last, val);
         const int o = g_dot<R>(P.out_coef, ix);
-        if (P.out_dtype == 0) static_cast<float*>(P.out_ptr)[o] = v;
-        else static_cast<uint8_t*>(P.out_ptr)[o] = v != 0.0f ? 1 : 0;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            if (v <= last) {
+                if (P.out_dtype == 0) static_cast<float*>(P.out_ptr)[o + v * ostep] = val[v];
+                else static_cast<uint8_t*>(P.out_ptr)[o + v * ostep] = val[v] != 0.0f ? 1 : 0;
+            }
+        }
     }
 }
 
 // the program travels as a kernel parameter (constant bank): no device memory, no copy.  R = 2, 4, 8: the instantiation
-// for programs of rank <= R (index arithmetic is unrolled over R dimensions)
-template <int R>
-__global__ void __launch_bounds__(256) generic_group_kernel_param(const __grid_constant__ functs_b200_gprogram P) { g_run<R>(P); }
+// for programs of rank <= R (index arithmetic is unrolled over R dimensions); V = elements per thread
+constexpr int kGenericVec = 4;
+template <int R, int V>
+__global__ void __launch_bounds__(256) generic_group_kernel_param(const __grid_constant__ functs_b200_gprogram P) { g_run<R, V>(P); }
 
 // several programs (map iterations x outputs) in device memory; the CTA stages its own in shared memory
 template <int R>
@@ -164,25 +219,38 @@ __global__ void __launch_bounds__(256) generic_group_kernel_table(const functs_b
     static_assert(sizeof(functs_b200_gprogram) % 16 == 0, "the program is copied in 16-byte pieces");
     for (int i = threadIdx.x; i < static_cast<int>(sizeof(functs_b200_gprogram) / 16); i += blockDim.x) dst[i] = __ldg(src + i);
     __syncthreads();
-    if (P.rank <= R) g_run<R>(P);  // (the launcher passes the largest rank of the table; a wrong value computes nothing)
+    if (P.rank > R) return;  // (the launcher passes the largest rank of the table; a wrong value computes nothing)
+    if (P.vec == kGenericVec) g_run<R, kGenericVec>(P);
+    else g_run<R, 1>(P);
 }
 
 static int validate_program(const functs_b200_gprogram& P) {
     FB_REQUIRE(P.rank >= 0 && P.rank <= 8 && P.numel >= 0 && P.ninstr > 0 && P.ninstr <= FB_G_MAX_INSTR && P.out_ptr != nullptr,
                "generic group: bad program header");
-    int64_t n = 1;
+    // `shape` is what the element number is decomposed over; with vec > 1 its last extent counts blocks of vec elements
+    // and lane_extent is the true extent of that dimension
+    FB_REQUIRE(P.vec == 1 || (P.vec == kGenericVec && P.rank >= 1), "generic group: bad elements-per-thread value");
+    int64_t n = 1, w = 1;
+    int extent[8] = {1, 1, 1, 1, 1, 1, 1, 1};
     for (int k = 0; k < P.rank; ++k) {
         FB_REQUIRE(P.shape[k] > 0, "generic group: empty or negative extent");
-        n *= P.shape[k];
+        extent[k] = P.shape[k];
+        if (P.vec > 1 && k == P.rank - 1) {
+            FB_REQUIRE(P.lane_extent > 0 && P.shape[k] == (P.lane_extent + P.vec - 1) / P.vec,
+                       "generic group: the block count of the fastest dimension does not match its extent");
+            extent[k] = P.lane_extent;
+        }
+        n *= extent[k];
+        w *= P.shape[k];
     }
-    FB_REQUIRE(n == P.numel, "generic group: numel does not match the shape");
+    FB_REQUIRE(n == P.numel && w == P.work, "generic group: numel / work do not match the shape");
     {
         // out_coef must place the elements one to one into [0, numel): the largest offset is numel - 1 and the
         // coefficients, sorted, are the running products of the extents (a permutation of contiguous strides)
         int64_t top = 0;
         for (int k = 0; k < P.rank; ++k) {
             FB_REQUIRE(P.out_coef[k] >= 0, "generic group: negative output coefficient");
-            top += static_cast<int64_t>(P.out_coef[k]) * (P.shape[k] - 1);
+            top += static_cast<int64_t>(P.out_coef[k]) * (extent[k] - 1);
         }
         FB_REQUIRE(top == static_cast<int64_t>(P.numel) - 1, "generic group: the output coefficients do not cover the output");
         bool used[8] = {false, false, false, false, false, false, false, false};
@@ -190,11 +258,16 @@ static int validate_program(const functs_b200_gprogram& P) {
         for (int step = 0; step < P.rank; ++step) {
             int pick = -1;
             for (int k = 0; k < P.rank && pick < 0; ++k)
-                if (!used[k] && (P.shape[k] == 1 || P.out_coef[k] == run)) pick = k;
+                if (!used[k] && (extent[k] == 1 || P.out_coef[k] == run)) pick = k;
             FB_REQUIRE(pick >= 0, "generic group: the output coefficients are not a permutation of contiguous strides");
             used[pick] = true;
-            run *= P.shape[pick];
+            run *= extent[pick];
         }
+    }
+    if (P.vec > 1) {  // no predicate may depend on the dimension whose neighbours share one pass through the program
+        for (int pc = 0; pc < P.ninstr; ++pc)
+            if (P.instr[pc].op == FB_G_COND && P.instr[pc].arg < FB_G_MAX_PREDS)
+                FB_REQUIRE(P.pred[P.instr[pc].arg].coef[P.rank - 1] == 0, "generic group: a predicate tests the vectorised dimension");
     }
     for (int k = 0; k < P.rank; ++k) FB_REQUIRE(P.shape[k] == 1 || P.div_shift[k] < 32, "generic group: bad divisor shift");
     // static slot and stack-depth check, so that the kernel needs no run-time checks: jumps go forward, so one pass
@@ -253,12 +326,12 @@ static int validate_program(const functs_b200_gprogram& P) {
 
 }  // namespace fb
 
-extern "C" int functs_b200_generic_group_launch(const functs_b200_gprogram* programs, int32_t count, int32_t max_numel,
+extern "C" int functs_b200_generic_group_launch(const functs_b200_gprogram* programs, int32_t count, int32_t max_work,
                                                 int32_t max_rank, int32_t on_device, void* stream) {
     using namespace fb;
-    FB_REQUIRE(programs != nullptr && count > 0 && count <= 65535 && max_numel >= 0, "generic group: bad arguments");
-    if (max_numel == 0) return FB_OK;
-    int64_t need = (static_cast<int64_t>(max_numel) + 255) / 256;
+    FB_REQUIRE(programs != nullptr && count > 0 && count <= 65535 && max_work >= 0, "generic group: bad arguments");
+    if (max_work == 0) return FB_OK;
+    int64_t need = (static_cast<int64_t>(max_work) + 255) / 256;
     const int64_t cap = static_cast<int64_t>(kNumSMs) * 8;
     if (need > cap) need = cap;
     cudaStream_t st = as_stream(stream);
@@ -266,9 +339,16 @@ extern "C" int functs_b200_generic_group_launch(const functs_b200_gprogram* prog
         FB_REQUIRE(count == 1, "generic group: %d programs in host memory (only one can travel as a kernel parameter)", count);
         FB_TRY(validate_program(programs[0]));
         const int rank = programs[0].rank;
-        if (rank <= 2) generic_group_kernel_param<2><<<static_cast<unsigned>(need), 256, 0, st>>>(programs[0]);
-        else if (rank <= 4) generic_group_kernel_param<4><<<static_cast<unsigned>(need), 256, 0, st>>>(programs[0]);
-        else generic_group_kernel_param<8><<<static_cast<unsigned>(need), 256, 0, st>>>(programs[0]);
+        const unsigned g = static_cast<unsigned>(need);
+        if (programs[0].vec == kGenericVec) {
+            if (rank <= 2) generic_group_kernel_param<2, kGenericVec><<<g, 256, 0, st>>>(programs[0]);
+            else if (rank <= 4) generic_group_kernel_param<4, kGenericVec><<<g, 256, 0, st>>>(programs[0]);
+            else generic_group_kernel_param<8, kGenericVec><<<g, 256, 0, st>>>(programs[0]);
+        } else {
+            if (rank <= 2) generic_group_kernel_param<2, 1><<<g, 256, 0, st>>>(programs[0]);
+            else if (rank <= 4) generic_group_kernel_param<4, 1><<<g, 256, 0, st>>>(programs[0]);
+            else generic_group_kernel_param<8, 1><<<g, 256, 0, st>>>(programs[0]);
+        }
     } else {
         FB_REQUIRE((reinterpret_cast<uintptr_t>(programs) & 15) == 0, "generic group: the program table must be 16-byte aligned");
         FB_REQUIRE(max_rank >= 0 && max_rank <= 8, "generic group: bad maximum rank");

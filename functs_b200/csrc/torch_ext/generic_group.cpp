@@ -498,12 +498,28 @@ void orderDimensionsForLanes(functs_b200_gprogram& P) {
         shape[p] = P.shape[order[p]];
         P.out_coef[p] = static_cast<int32_t>(stride[order[p]]);
     }
+    // A thread takes four neighbouring elements of the fastest dimension through the program in one pass when no COND
+    // tests that dimension (decoding and predicates are then paid once for the four), the dimension is long enough to
+    // matter, and a quarter of the threads still fills the GPU (a small output wants more threads, not longer ones:
+    // the step-4 box decoding on [3000, 4] took 21 us with four elements per thread against 12.5 with one).
+    P.vec = 1;
+    P.lane_extent = rank > 0 ? shape[rank - 1] : 1;
+    if (rank > 0 && !tested[order[rank - 1]] && shape[rank - 1] >= 8 && P.numel >= 4 * 148 * 256 * 2) {
+        P.vec = 4;
+        shape[rank - 1] = (shape[rank - 1] + 3) / 4;
+    }
+    int64_t work = 1;
     for (int p = 0; p < 8; ++p) {
         P.shape[p] = shape[p];
         P.div_magic[p] = P.div_shift[p] = 0;
-        if (p < rank) divisorOf(static_cast<uint32_t>(shape[p]), P.div_magic[p], P.div_shift[p]);
-        else P.out_coef[p] = 0;
+        if (p < rank) {
+            divisorOf(static_cast<uint32_t>(shape[p]), P.div_magic[p], P.div_shift[p]);
+            work *= shape[p];
+        } else {
+            P.out_coef[p] = 0;
+        }
     }
+    P.work = static_cast<int32_t>(work);
     auto renumber = [&](int32_t (&coef)[8]) {
         int32_t c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int p = 0; p < rank; ++p) c[p] = coef[order[p]];
@@ -1028,7 +1044,7 @@ bool RunGenericGroup(const std::shared_ptr<Graph>& sub, bool is_map, int64_t deg
                 em.emit(e, id);
                 em.push(FB_G_END);
                 orderDimensionsForLanes(P);
-                max_numel = std::max(max_numel, P.numel);
+                max_numel = std::max(max_numel, P.work);
             }
             sources[static_cast<size_t>(it)] = b.sources;
         }

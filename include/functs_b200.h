@@ -275,7 +275,8 @@ int functs_b200_index_rows_rev(const void* self, const void* src, const int64_t*
  * (q = mulhi(magic, n); ((n - q) >> 1) + q >> shift; unused for extent 1), filled in by the host.
  * The dimensions need not be in the output's own order: thread e works on the element whose multi-index is the
  * decomposition of e over `shape` (last dimension fastest) and stores it at sum_k out_coef[k] * x[k].  The host orders
- * them so that the lanes of a warp run along a dimension no COND tests (one path per warp instead of one per lane). */
+ * them so that the lanes of a warp run along a dimension no COND tests (one path per warp instead of one per lane), and
+ * lets a thread take vec neighbouring elements of that dimension through the program in one pass. */
 enum {
     FB_G_END = 0, FB_G_LOAD = 1, FB_G_CONST = 2, FB_G_COND = 3, FB_G_JUMP = 4,
     /* unary */ FB_G_EXP = 10, FB_G_SIGMOID = 11, FB_G_TANH = 12, FB_G_RELU = 13, FB_G_NEG = 14, FB_G_CLAMP_MIN = 15,
@@ -325,6 +326,10 @@ typedef struct {
     uint32_t div_magic[8];
     uint32_t div_shift[8];
     int32_t out_coef[8];  /* the element's place in the output: sum_k out_coef[k] * x[k] */
+    int32_t vec;          /* elements per thread: 1, or 4 neighbours along the fastest dimension (which no COND may test) */
+    int32_t lane_extent;  /* vec > 1: elements along the fastest dimension (shape holds the number of blocks of vec) */
+    int32_t work;         /* product of shape: thread work items */
+    int32_t pad0;
     const void* in_ptr[FB_G_MAX_INPUTS];
     void* out_ptr;
     int32_t reserved[2];  /* keeps sizeof a multiple of 16 */
@@ -333,9 +338,9 @@ typedef struct {
     functs_b200_gpred pred[FB_G_MAX_PREDS];
 } functs_b200_gprogram;
 /* programs: `count` programs in HOST memory when on_device == 0 (count == 1: passed to the kernel by value) or in DEVICE
- * memory when on_device != 0; max_numel / max_rank = the largest numel / rank among them (a program of a higher rank
+ * memory when on_device != 0; max_work / max_rank = the largest work / rank among them (a program of a higher rank
  * than max_rank is not run).  One launch. */
-int functs_b200_generic_group_launch(const functs_b200_gprogram* programs, int32_t count, int32_t max_numel,
+int functs_b200_generic_group_launch(const functs_b200_gprogram* programs, int32_t count, int32_t max_work,
                                      int32_t max_rank, int32_t on_device, void* stream);
 
 /* ---- group registry: what the tssa::ParallelFunctor operator binds to ------------------------ */

@@ -178,3 +178,18 @@ def test_cached_programs_follow_shapes_and_scalars(env):
         got = built(x, s)
         assert J.interpreted_functor_runs() == i0, J.last_generic_refusal()
         assert torch.equal(got, scaled(x, s))
+
+
+def strided_big(x: torch.Tensor, y: torch.Tensor):
+    t = x.clone()
+    t[:, 1::2] = torch.clamp(t[:, 1::2] * 2.0, min=-0.5, max=0.5)
+    return torch.tanh(t) + y, t[:, 3:50] > 0.0
+
+
+def test_four_elements_per_thread_with_divided_coordinates(env):
+    """Large enough for four elements per thread along the untested dimension (4099 rows: a ragged last block), with a read
+    below a strided assignment (a divided coordinate in the load) and a broadcast operand."""
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(4099, 96, generator=g).cuda()
+    y = torch.randn(96, generator=g).cuda()
+    check(env, strided_big, (x, y))
