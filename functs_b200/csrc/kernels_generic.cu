@@ -38,9 +38,11 @@ __device__ __forceinline__ float g_fetch(const void* p, int dtype, int off) {
     }
 }
 
-// V values of one load: the V elements a thread works on are neighbours along the fastest dimension (position
-// rank - 1), which no predicate tests, so their offsets differ by that dimension's coefficient only.  `last` is the
-// number of valid elements minus one (an element beyond the extent re-reads the last valid one; it is never stored).
+// V values of one load: the V elements a thread works on lie kLaneStep apart along the fastest dimension (position
+// rank - 1; the lanes of a warp take neighbouring elements, so a warp's load covers one contiguous run), which no
+// predicate tests, so their offsets differ by multiples of that dimension's coefficient only.  `last` is the number of
+// valid elements minus one (an element beyond the extent re-reads the last valid one; it is never stored).
+constexpr int kLaneStep = 32;
 template <int R, int V>
 __device__ __forceinline__ void g_load(const functs_b200_gprogram& P, const functs_b200_gload& L, const GIndex& ix, int last,
                                        float (&out)[V]) {
@@ -51,13 +53,13 @@ __device__ __forceinline__ void g_load(const functs_b200_gprogram& P, const func
 #pragma unroll
         for (int k = 0; k < R; ++k) step = (k == P.rank - 1) ? L.coef[k] : step;
 #pragma unroll
-        for (int v = 0; v < V; ++v) out[v] = g_fetch(p, L.dtype, off + min(v, last) * step);
+        for (int v = 0; v < V; ++v) out[v] = g_fetch(p, L.dtype, off + min(v, last) * (kLaneStep * step));
     } else {  // a coordinate is divided (a read below a strided assignment): term by term, element by element
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             GIndex iv = ix;
 #pragma unroll
-            for (int k = 0; k < R; ++k) iv.x[k] += (k == P.rank - 1) ? min(v, last) : 0;
+            for (int k = 0; k < R; ++k) iv.x[k] += (k == P.rank - 1) ? kLaneStep * min(v, last) : 0;
             int off = L.base;
             for (int k = 0; k < L.nterms; ++k) {
                 const functs_b200_gterm t = L.term[k];
@@ -159,8 +161,9 @@ __device__ __forceinline__ void g_eval(const functs_b200_gprogram& P, const GInd
     }
 }
 
-// One work item = V neighbouring elements along the fastest dimension (V = P.vec; the extent of that dimension in
-// `shape` is then the number of V-blocks, lane_extent the number of elements).
+// One work item = V elements of the fastest dimension, kLaneStep apart (V = P.vec): work item q of a row takes elements
+// (q / 32) * 32 * V + q % 32 + 32 * v, so the 32 lanes of a warp read and write contiguous runs.  The extent of that
+// dimension in `shape` is then the number of work items per row (a multiple of 32), lane_extent the number of elements.
 template <int R, int V>
 __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
     const int stride = gridDim.x * blockDim.x;
@@ -184,12 +187,13 @@ __device__ __forceinline__ void g_run(const functs_b200_gprogram& P) {
 #pragma unroll
             for (int k = 0; k < R; ++k) {
                 if (k == P.rank - 1) {
-                    ix.x[k] *= V;
+                    ix.x[k] = (ix.x[k] >> 5) * (kLaneStep * V) + (ix.x[k] & 31);
                     first = ix.x[k];
-                    ostep = P.out_coef[k];
+                    ostep = kLaneStep * P.out_coef[k];
                 }
             }
-            last = min(V, P.lane_extent - first) - 1;
+            if (first >= P.lane_extent) continue;  // the row's last block of work items is only partly used
+            last = min(V - 1, (P.lane_extent - 1 - first) / kLaneStep);
         }
         float val[V];
         g_eval<R, V>(P, ix, last, val);
@@ -236,8 +240,8 @@ static int validate_program(const functs_b200_gprogram& P) {
         FB_REQUIRE(P.shape[k] > 0, "generic group: empty or negative extent");
         extent[k] = P.shape[k];
         if (P.vec > 1 && k == P.rank - 1) {
-            FB_REQUIRE(P.lane_extent > 0 && P.shape[k] == (P.lane_extent + P.vec - 1) / P.vec,
-                       "generic group: the block count of the fastest dimension does not match its extent");
+            FB_REQUIRE(P.lane_extent > 0 && P.shape[k] == (P.lane_extent + kLaneStep * P.vec - 1) / (kLaneStep * P.vec) * kLaneStep,
+                       "generic group: the work items of the fastest dimension do not match its extent");
             extent[k] = P.lane_extent;
         }
         n *= extent[k];

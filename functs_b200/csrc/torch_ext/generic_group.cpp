@@ -506,7 +506,7 @@ void orderDimensionsForLanes(functs_b200_gprogram& P) {
     P.lane_extent = rank > 0 ? shape[rank - 1] : 1;
     if (rank > 0 && !tested[order[rank - 1]] && shape[rank - 1] >= 8 && P.numel >= 4 * 148 * 256 * 2) {
         P.vec = 4;
-        shape[rank - 1] = (shape[rank - 1] + 3) / 4;
+        shape[rank - 1] = (shape[rank - 1] + 127) / 128 * 32;  // work items per row: blocks of 32 lanes x 4 elements
     }
     int64_t work = 1;
     for (int p = 0; p < 8; ++p) {

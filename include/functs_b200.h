@@ -326,8 +326,9 @@ typedef struct {
     uint32_t div_magic[8];
     uint32_t div_shift[8];
     int32_t out_coef[8];  /* the element's place in the output: sum_k out_coef[k] * x[k] */
-    int32_t vec;          /* elements per thread: 1, or 4 neighbours along the fastest dimension (which no COND may test) */
-    int32_t lane_extent;  /* vec > 1: elements along the fastest dimension (shape holds the number of blocks of vec) */
+    int32_t vec;          /* elements per thread: 1, or 4 along the fastest dimension (which no COND may test), 32 apart */
+    int32_t lane_extent;  /* vec > 1: elements along the fastest dimension (shape holds the work items per row:
+                             32 for every started block of 32 * vec elements) */
     int32_t work;         /* product of shape: thread work items */
     int32_t pad0;
     const void* in_ptr[FB_G_MAX_INPUTS];
